@@ -1,0 +1,153 @@
+/* symmetrix_b200 -- C ABI of the B200-native MACE energy+force evaluator.
+ *
+ * This is the drop-in boundary for the evaluation path of wcwitt/symmetrix: every entry
+ * point below replaces one piece of the reference's `class MACE` (CPU) /
+ * `class MACEKokkos<Precision>` (device) interface, which is what the reference's pybind11
+ * module and its LAMMPS pair style bind. Plain pointers and sizes only; no C++ or torch
+ * types cross this boundary. All functions return 0 on success and a non-zero status
+ * otherwise; the message is then available from smx_last_error(). Nothing throws.
+ *
+ * Conventions shared by all calls
+ *  - `mem_space` says where the caller's arrays live: SMX_HOST or SMX_DEVICE (pointers valid
+ *    on the evaluator's device). Host arrays are copied in/out by the library.
+ *  - Edges are grouped by receiver node (CSR): node i owns `num_neigh[i]` consecutive edges.
+ *    `neigh_indices[e]` is the row of the sender's features, `xyz[3e..3e+2] = x_j - x_i`,
+ *    `r[e] = |xyz_e|`. This is exactly the argument list of the reference
+ *    (libsymmetrix/source/mace.hpp:28-36).
+ *  - Work is issued on the evaluator's own CUDA stream; calls return after the stream has
+ *    been synchronised when any output goes to host memory.
+ *  - One evaluator per GPU and per host thread; an evaluator is not thread-safe (neither is
+ *    the reference: all scratch is per-object state, mace.hpp:40-164).
+ */
+#ifndef SYMMETRIX_B200_H
+#define SYMMETRIX_B200_H
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct smx_evaluator* smx_handle;
+
+enum { SMX_HOST = 0, SMX_DEVICE = 1 };
+enum { SMX_FP32 = 32, SMX_FP64 = 64 };
+
+enum {
+    SMX_OK = 0,
+    SMX_ERR_INVALID_ARGUMENT = 1, /* bad size, unknown name, null pointer                     */
+    SMX_ERR_MODEL = 2,            /* model file missing, not JSON, or outside the supported set */
+    SMX_ERR_CUDA = 3,             /* a CUDA runtime call or kernel launch failed               */
+    SMX_ERR_UNSUPPORTED = 4,      /* feature of the reference that this build does not cover   */
+    SMX_ERR_NO_DEVICE = 5         /* no usable CUDA device: there is no CPU fallback           */
+};
+
+typedef struct smx_model_info {
+    int num_elements;   /* MACE::num_elements  (mace.hpp:19) */
+    int num_channels;   /* MACE::num_channels  (mace.hpp:20) */
+    double r_cut;       /* MACE::r_cut         (mace.hpp:21) */
+    int l_max, num_lm;  /* MACE::l_max, num_lm (mace.hpp:22) */
+    int L_max, num_LM;  /* MACE::L_max, num_LM (mace.hpp:23) */
+    int num_paths;      /* number of tensor-product paths, Phi1_l.size() (mace.hpp:115)      */
+    int num_lelm1lm2;   /* MACE::num_lelm1lm2  (mace.hpp:112) */
+    int num_lme;        /* MACE::num_lme       (mace.hpp:112) */
+    int has_zbl;        /* MACE::has_zbl       (mace.hpp:39)  */
+    int precision;      /* SMX_FP32 or SMX_FP64: arithmetic type of features and weights     */
+    int device;         /* CUDA device ordinal the evaluator lives on                        */
+} smx_model_info;
+
+/* Replaces the constructor MACE::MACE(std::string filename) -> load_from_json
+ * (libsymmetrix/source/mace.cpp:12-15,905-1030; device twin mace_kokkos.cpp:1544-1887).
+ * `precision` selects what MACEKokkos<float> / MACEKokkos<double> select in the reference
+ * (symmetrix/source/symmetrix/symmetrix_calc.py:49). Fails with SMX_ERR_NO_DEVICE when no GPU
+ * is present. */
+int smx_create(const char* json_path, int precision, int device, smx_handle* out);
+
+/* Replaces the destructor of MACE / MACEKokkos. */
+void smx_destroy(smx_handle h);
+
+/* Message of the last failing call on `h` (or of the last failing smx_create when h is NULL).
+ * Stands in for the C++ exceptions the reference reports errors with
+ * (e.g. cubic_spline.cpp:19-20; nlohmann parse_error surfacing in symmetrix_calc.py:54-68). */
+const char* smx_last_error(smx_handle h);
+
+/* Replaces reads of the public data members num_elements, num_channels, r_cut, l_max, num_lm,
+ * L_max, num_LM, has_zbl (mace.hpp:18-39). */
+int smx_info(smx_handle h, smx_model_info* info);
+
+/* Replaces reads of MACE::atomic_numbers / MACE::atomic_energies (mace.hpp:24-25), which the
+ * pair style and the ASE calculator use to map species to model types
+ * (pair_symmetrix/pair_symmetrix_mace.cpp:122-138; symmetrix_calc.py:75-81). `cap` is the
+ * capacity of `out`; the return value is the number of elements of the model. */
+int smx_atomic_numbers(smx_handle h, int* out, int cap);
+int smx_atomic_energies(smx_handle h, double* out, int cap);
+
+/* Replaces MACE::compute_node_energies_forces (libsymmetrix/source/mace.cpp:17-64; device twin
+ * mace_kokkos.cpp:49-98): zero the outputs, run all forward stages, the readouts and all reverse
+ * stages. Results stay on the device and are read with smx_get_array("node_energies" /
+ * "node_forces") or reduced with smx_reduce_forces. */
+int smx_compute(smx_handle h, int num_nodes, const int* node_types, const int* num_neigh,
+                const int* neigh_indices, const int* neigh_types, const double* xyz,
+                const double* r, long num_edges, int mem_space);
+
+/* Replaces the individual stage methods of MACE that the message-passing pair-style mode calls
+ * one by one (mace.hpp:40-164; call sequence pair_symmetrix/pair_symmetrix_mace.cpp:444-495):
+ * name is one of compute_Y, compute_R0, compute_A0, compute_M0, compute_H1, compute_R1,
+ * compute_Phi1, compute_A1, compute_M1, compute_H2, compute_readouts, reverse_H2, reverse_M1,
+ * reverse_A1, reverse_Phi1, reverse_H1, reverse_M0, reverse_A0 (the *_scaled stages are accepted
+ * and do nothing, as in the reference when the model has no density normalisation).
+ * `zero_dxyz` / `zero_H1_adj` carry the flags of reverse_Phi1 / reverse_H2 (mace.hpp:118,159).
+ * Radial functions and harmonics are recomputed inside the edge kernels, so compute_Y /
+ * compute_R0 / compute_R1 only record the edge arrays they are given. A sequence of stage calls
+ * must start with smx_begin, which replaces the zero-fill of node_energies / node_forces that
+ * callers do by hand (pair_symmetrix_mace.cpp:437-440). */
+int smx_begin(smx_handle h, int num_nodes, const int* node_types, const int* num_neigh,
+              const int* neigh_indices, const int* neigh_types, const double* xyz,
+              const double* r, long num_edges, int mem_space);
+int smx_stage(smx_handle h, const char* name, int zero_dxyz, int zero_H1_adj);
+
+/* Replaces reads of the public result / intermediate vectors of MACE (node_energies,
+ * node_forces, A0, A0_adj, M0, M0_adj, H1, H1_adj, Phi1, Phi1_adj, A1, A1_adj, M1, M1_adj, H2,
+ * H2_adj: symmetrix/source/cpp/mace.cpp:14-33) -- copies `name` to `dst` as doubles.
+ * `*n` receives the number of elements; at most `cap` are written. */
+int smx_get_array(smx_handle h, const char* name, double* dst, long cap, long* n, int mem_space);
+
+/* Replaces writes to those members; the message-passing mode swaps H1 / H1_adj in and out with
+ * rows for ghost atoms appended (pair_symmetrix_mace.cpp:463-471,488-490). `n` may exceed the
+ * current length (the array grows, as std::vector assignment does). */
+int smx_set_array(smx_handle h, const char* name, const double* src, long n, int mem_space);
+
+/* Replaces the force / energy / virial reduction every caller performs on the per-edge partial
+ * forces: f[i] -= nf_ij, f[j] += nf_ij, virial += sym(xyz_ij (x) nf_ij), energy = sum of node
+ * energies (pair_symmetrix/pair_symmetrix_mace.cpp:324-368; symmetrix_calc.py:85-102).
+ * `atom_forces` has 3*num_rows doubles with num_rows >= 1 + max(neigh_indices); `virial` has 6
+ * (xx, yy, zz, xy, xz, yz). Any output pointer may be NULL. Deterministic (no atomics). */
+int smx_reduce_forces(smx_handle h, int num_rows, double* atom_forces, double* virial,
+                      double* energy, int mem_space);
+
+/* Milliseconds spent on the device by the last smx_compute (CUDA events on the evaluator's
+ * stream). The reference has no counterpart; the Kokkos build relies on external tools. */
+int smx_last_device_ms(smx_handle h, double* ms);
+
+/* Number of kernels the evaluator launched since creation (for benchmark bookkeeping). */
+long smx_launch_count(smx_handle h);
+
+/* Neighbour list on the device -- replaces, for callers without their own, the external
+ * builders the reference's callers rely on: ase/matscipy `neighbor_list('ijdD', atoms, r_cut)`
+ * (symmetrix_calc.py:12-16,77) and the LAMMPS full list filtered by r^2 < r_cut^2
+ * (pair_symmetrix_mace.cpp:249-315). Edge rule, float64 arithmetic and ordering are stated in
+ * symmetrix_b200/structures.py::neighbor_list, which is the host statement of the same rule.
+ * Builds the CSR arrays of the evaluator for `num_atoms` atoms in a periodic cell (row vectors
+ * `cell[9]`, `pbc[3]`), keeps them on the device as the current edge set (as smx_begin does)
+ * and returns the edge count. `types[i]` is the model type of atom i. */
+int smx_build_neighbors(smx_handle h, int num_atoms, const double* positions, const int* types,
+                        const double* cell, const int* pbc, double r_cut, long* num_edges,
+                        int mem_space);
+/* Copies out the edge arrays of the current edge set (any pointer may be NULL). */
+int smx_get_edges(smx_handle h, int* num_neigh, int* neigh_indices, int* neigh_types,
+                  int* shifts, double* xyz, double* r, int mem_space);
+/* smx_compute on the current edge set (after smx_build_neighbors). */
+int smx_compute_current(smx_handle h);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SYMMETRIX_B200_H */

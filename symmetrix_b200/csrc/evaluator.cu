@@ -1,0 +1,874 @@
+// Host side of the evaluator and the extern "C" entry points declared in include/symmetrix_b200.h.
+// Mirrors the stage structure of the reference's `class MACE` (libsymmetrix/source/mace.hpp:12-169):
+// one method per compute_*/reverse_* stage, run in the order of MACE::compute_node_energies_forces
+// (mace.cpp:17-64). There is no CPU path: creation fails when no CUDA device is usable.
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstring>
+#include <memory>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include <cub/cub.cuh>
+
+#include "../../include/symmetrix_b200.h"
+#include "common.cuh"
+#include "kernels.cuh"
+#include "model.hpp"
+#include "neighbors.cuh"
+
+namespace smx {
+
+template <typename T>
+static std::vector<T> cast_vec(const std::vector<double>& v) {
+    std::vector<T> o(v.size());
+    for (size_t i = 0; i < v.size(); ++i) o[i] = static_cast<T>(v[i]);
+    return o;
+}
+
+struct CastToLL {
+    __host__ __device__ long long operator()(const int& v) const { return static_cast<long long>(v); }
+};
+
+class EvaluatorBase {
+public:
+    virtual ~EvaluatorBase() = default;
+    HostModel model;
+    int precision = 64, device = 0;
+    std::string last_error;
+    long launches = 0;
+    double last_ms = 0.0;
+
+    virtual void begin(int N, const int* node_types, const int* num_neigh, const int* neigh_indices,
+                       const int* neigh_types, const double* xyz, const double* r, long E, int mem_space) = 0;
+    virtual void stage(const std::string& name, bool zero_dxyz, bool zero_H1_adj) = 0;
+    virtual void compute_all() = 0;
+    virtual long get_array(const std::string& name, double* dst, long cap, int mem_space) = 0;
+    virtual void set_array(const std::string& name, const double* src, long n, int mem_space) = 0;
+    virtual void reduce_forces(int rows, double* f, double* virial, double* energy, int mem_space) = 0;
+    virtual long build_neighbors(int natoms, const double* pos, const int* types, const double* cell, const int* pbc,
+                                 double r_cut, int mem_space) = 0;
+    virtual void get_edges(int* num_neigh, int* neigh_indices, int* neigh_types, int* shifts, double* xyz, double* r, int mem_space) = 0;
+};
+
+template <typename T>
+class Evaluator final : public EvaluatorBase {
+public:
+    cudaStream_t stream = nullptr;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    int num_sms = 148;
+
+    // model tables on the device
+    DevBuf<T> coef0, coef1, H0_w, A0_w, H1_w, A1_w, H2_w_H1, H2_w_M1, ro1, ro2_w1, ro2_w2, z_c, coefM0, coefM1;
+    DevBuf<double> E0;
+    DevBuf<int> z_ptr, z_lm1, prog0, prog0_off, mono0_off, prog1, prog1_off, mono1_off;
+    SplineMeta sm{};
+
+    // current edge set
+    int N = 0;
+    long E = 0;
+    int h1_rows = 0;
+    bool have_edges = false;
+    DevBuf<int> in_node_types, in_num_neigh, in_neigh_indices, in_neigh_types, in_shifts;
+    DevBuf<double> in_xyz, in_r;
+    const int *node_types = nullptr, *num_neigh = nullptr, *neigh_indices = nullptr, *neigh_types = nullptr;
+    const double *xyz = nullptr, *r = nullptr;
+    DevBuf<long long> first_neigh, in_ptr;
+    DevBuf<int> perm, sorted_types, type_seg, iota, in_edge, sorted_senders;
+    DevBuf<unsigned char> cub_tmp;
+    int sender_rows = -1;
+
+    // per-call arrays
+    DevBuf<T> Phi0, A0, A0_adj, Phi0_adj, M0, M0_adj, H1, H1_adj, Phi1, dPhi1, A1, A1_adj, M1, M1_adj, H2, H2_adj, Hmsg;
+    DevBuf<double> node_energies, node_forces, scratch_d, partials, out7, atom_f;
+    DevBuf<GemmProblem<T>> problems;
+    std::vector<GemmProblem<T>> host_problems;
+    NeighborBuilder nb;
+
+    explicit Evaluator(HostModel&& m, int dev) {
+        model = std::move(m);
+        device = dev;
+        precision = sizeof(T) == 4 ? 32 : 64;
+        SMX_CUDA(cudaSetDevice(dev));
+        SMX_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
+        SMX_CUDA(cudaEventCreate(&ev0));
+        SMX_CUDA(cudaEventCreate(&ev1));
+        cudaDeviceProp prop{};
+        SMX_CUDA(cudaGetDeviceProperties(&prop, dev));
+        num_sms = prop.multiProcessorCount;
+        upload_model();
+    }
+    ~Evaluator() override {
+        cudaSetDevice(device);
+        if (stream) cudaStreamSynchronize(stream);
+        if (ev0) cudaEventDestroy(ev0);
+        if (ev1) cudaEventDestroy(ev1);
+        if (stream) cudaStreamDestroy(stream);
+    }
+
+    void upload_model() {
+        const HostModel& m = model;
+        coef0.upload(cast_vec<T>(m.coef0), stream);
+        coef1.upload(cast_vec<T>(m.coef1), stream);
+        H0_w.upload(cast_vec<T>(m.H0_w), stream);
+        A0_w.upload(cast_vec<T>(m.A0_w), stream);
+        H1_w.upload(cast_vec<T>(m.H1_w), stream);
+        A1_w.upload(cast_vec<T>(m.A1_w), stream);
+        H2_w_H1.upload(cast_vec<T>(m.H2_w_H1), stream);
+        H2_w_M1.upload(cast_vec<T>(m.H2_w_M1), stream);
+        ro1.upload(cast_vec<T>(m.ro1), stream);
+        ro2_w1.upload(cast_vec<T>(m.ro2_w1), stream);
+        ro2_w2.upload(cast_vec<T>(m.ro2_w2), stream);
+        z_c.upload(cast_vec<T>(m.z_c), stream);
+        coefM0.upload(cast_vec<T>(m.coef_M0), stream);
+        coefM1.upload(cast_vec<T>(m.coef_M1), stream);
+        E0.upload(m.atomic_energies, stream);
+        z_ptr.upload(m.z_ptr, stream);
+        z_lm1.upload(m.z_lm1, stream);
+        {
+            std::vector<int> words, offs;
+            for (const auto& p : m.prog0) { offs.push_back(static_cast<int>(words.size())); words.insert(words.end(), p.words.begin(), p.words.end()); }
+            prog0.upload(words, stream);
+            prog0_off.upload(offs, stream);
+            mono0_off.upload(std::vector<int>(m.mono_off0.begin(), m.mono_off0.end() - 1), stream);
+            prog1.upload(m.prog1.words, stream);
+            prog1_off.upload(std::vector<int>{0}, stream);
+            mono1_off.upload(std::vector<int>{0}, stream);
+        }
+        sm.h = m.spline_h;
+        sm.num_bins = m.num_bins;
+        sm.num_elements = m.num_elements;
+        SMX_CUDA(cudaStreamSynchronize(stream));
+        // the host copies of the big tables are no longer needed
+        model.coef0.clear(); model.coef0.shrink_to_fit();
+        model.coef1.clear(); model.coef1.shrink_to_fit();
+        model.coef_M0.clear(); model.coef_M0.shrink_to_fit();
+    }
+
+    // ------------------------------------------------------------------ launch helpers
+    template <typename Kern>
+    int persistent_grid(Kern kern, int block, size_t smem, long long work_items) {
+        int per_sm = 1;
+        SMX_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, block, smem));
+        if (per_sm < 1) per_sm = 1;
+        long long g = static_cast<long long>(num_sms) * per_sm;
+        if (g > work_items) g = work_items;
+        return g < 1 ? 1 : static_cast<int>(g);
+    }
+    void check_launch(const char* what) {
+        cudaError_t err = cudaGetLastError();
+        if (err != cudaSuccess) throw CudaError(std::string(what) + ": " + cudaGetErrorString(err));
+        launches += 1;
+    }
+    int channel_block() const { return std::min(kChannelBlock, ((model.K + 31) / 32) * 32); }
+
+    // ------------------------------------------------------------------ edge set
+    template <typename U>
+    const U* stage_input(const U* src, size_t count, DevBuf<U>& buf, int mem_space) {
+        if (mem_space == SMX_DEVICE) return src;
+        buf.resize(count, stream);
+        if (count) SMX_CUDA(cudaMemcpyAsync(buf.p, src, count * sizeof(U), cudaMemcpyHostToDevice, stream));
+        return buf.p;
+    }
+
+    void begin(int n_nodes, const int* nt, const int* nn, const int* ni, const int* et, const double* x, const double* rr,
+               long n_edges, int mem_space) override {
+        if (n_nodes < 0 || n_edges < 0) throw ArgError("negative size");
+        if (n_nodes > 0 && (!nt || !nn)) throw ArgError("null node array");
+        if (n_edges > 0 && (!ni || !et || !x || !rr)) throw ArgError("null edge array");
+        if (mem_space != SMX_HOST && mem_space != SMX_DEVICE) throw ArgError("mem_space must be SMX_HOST or SMX_DEVICE");
+        SMX_CUDA(cudaSetDevice(device));
+        node_types = stage_input(nt, n_nodes, in_node_types, mem_space);
+        num_neigh = stage_input(nn, n_nodes, in_num_neigh, mem_space);
+        neigh_indices = stage_input(ni, n_edges, in_neigh_indices, mem_space);
+        neigh_types = stage_input(et, n_edges, in_neigh_types, mem_space);
+        xyz = stage_input(x, 3 * static_cast<size_t>(n_edges), in_xyz, mem_space);
+        r = stage_input(rr, n_edges, in_r, mem_space);
+        adopt_edges(n_nodes, n_edges);
+    }
+
+    // Derived index arrays of the current edge set: CSR offsets and nodes sorted by element type.
+    void adopt_edges(int n_nodes, long n_edges) {
+        N = n_nodes;
+        E = n_edges;
+        h1_rows = N;
+        sender_rows = -1;
+        have_edges = true;
+        first_neigh.resize(static_cast<size_t>(N) + 1, stream);
+        if (N > 0) {
+            cub::TransformInputIterator<long long, CastToLL, const int*> it(num_neigh, CastToLL());
+            size_t bytes = 0;
+            SMX_CUDA(cub::DeviceScan::ExclusiveSum(nullptr, bytes, it, first_neigh.p, N, stream));
+            cub_tmp.resize(bytes, stream);
+            SMX_CUDA(cub::DeviceScan::ExclusiveSum(cub_tmp.p, bytes, it, first_neigh.p, N, stream));
+            launches += 1;
+        }
+        const long long total = E;
+        SMX_CUDA(cudaMemcpyAsync(first_neigh.p + N, &total, sizeof(long long), cudaMemcpyHostToDevice, stream));
+        // nodes sorted by element type (stable), and the segment of each type
+        perm.resize(N, stream);
+        sorted_types.resize(N, stream);
+        type_seg.resize(model.num_elements + 1, stream);
+        if (N > 0) {
+            iota.resize(N, stream);
+            iota_kernel<<<std::min(1024, (N + 255) / 256), 256, 0, stream>>>(N, iota.p);
+            check_launch("iota");
+            int bits = 1;
+            while ((1 << bits) < model.num_elements) ++bits;
+            size_t bytes = 0;
+            SMX_CUDA(cub::DeviceRadixSort::SortPairs(nullptr, bytes, node_types, sorted_types.p, iota.p, perm.p, N, 0, bits, stream));
+            cub_tmp.resize(bytes, stream);
+            SMX_CUDA(cub::DeviceRadixSort::SortPairs(cub_tmp.p, bytes, node_types, sorted_types.p, iota.p, perm.p, N, 0, bits, stream));
+            launches += 1;
+        }
+        segment_offsets_int_kernel<<<1, 128, 0, stream>>>(N, sorted_types.p, model.num_elements, type_seg.p);
+        check_launch("type segments");
+        // outputs the caller zero-fills in the reference (mace.cpp:27-30)
+        node_energies.resize(N, stream);
+        node_energies.zero(stream);
+        node_forces.resize(3 * static_cast<size_t>(E), stream);
+        node_forces.zero(stream);
+    }
+
+    // Edges grouped by sender row (stable in edge order), for the atomic-free scatters.
+    void ensure_sender_lists(int rows) {
+        if (sender_rows == rows) return;
+        in_ptr.resize(static_cast<size_t>(rows) + 1, stream);
+        in_edge.resize(E, stream);
+        sorted_senders.resize(E, stream);
+        if (E > 0) {
+            if (E > 0x7fffffffL) throw UnsupportedError("more than 2^31 edges in one call");
+            iota.resize(E, stream);
+            iota_kernel<<<std::min<long>(4096, (E + 255) / 256), 256, 0, stream>>>(static_cast<int>(E), iota.p);
+            check_launch("iota");
+            int bits = 1;
+            while ((1LL << bits) < rows) ++bits;
+            size_t bytes = 0;
+            SMX_CUDA(cub::DeviceRadixSort::SortPairs(nullptr, bytes, neigh_indices, sorted_senders.p, iota.p, in_edge.p,
+                                                     static_cast<int>(E), 0, bits, stream));
+            cub_tmp.resize(bytes, stream);
+            SMX_CUDA(cub::DeviceRadixSort::SortPairs(cub_tmp.p, bytes, neigh_indices, sorted_senders.p, iota.p, in_edge.p,
+                                                     static_cast<int>(E), 0, bits, stream));
+            launches += 1;
+        }
+        segment_offsets_kernel<<<std::min(1024, (rows + 256) / 256), 256, 0, stream>>>(E, sorted_senders.p, rows, in_ptr.p);
+        check_launch("sender segments");
+        sender_rows = rows;
+    }
+
+    void require_edges() const {
+        if (!have_edges) throw ArgError("no edge set: call smx_begin / smx_compute / smx_build_neighbors first");
+    }
+
+    // ------------------------------------------------------------------ GEMM plumbing
+    void run_gemms(const std::vector<GemmProblem<T>>& list, long long max_rows, int max_cols) {
+        if (list.empty() || max_rows <= 0) return;
+        problems.resize(list.size(), stream);
+        SMX_CUDA(cudaMemcpyAsync(problems.p, list.data(), list.size() * sizeof(GemmProblem<T>), cudaMemcpyHostToDevice, stream));
+        SMX_CUDA(cudaStreamSynchronize(stream));  // `list` is a temporary of the caller
+        dim3 grid(static_cast<unsigned>((max_rows + kGemmBM - 1) / kGemmBM), (max_cols + kGemmBN - 1) / kGemmBN,
+                  static_cast<unsigned>(list.size()));
+        gemm_rows_kernel<T><<<grid, 256, 0, stream>>>(problems.p);
+        check_launch("gemm_rows_kernel");
+    }
+    GemmProblem<T> problem(const T* A, T* C, const T* B, bool by_type, int type, int sub_count, long long a_ns, long long a_off,
+                           long long a_ss, long long c_ns, long long c_off, long long c_ss, int Kd, int Nc, int ldb, bool transB,
+                           bool acc) {
+        GemmProblem<T> p{};
+        p.A = A; p.C = C; p.B = B;
+        p.perm = by_type ? perm.p : nullptr;
+        p.seg = by_type ? type_seg.p : nullptr;
+        p.seg_index = type;
+        p.num_nodes = N;
+        p.sub_count = sub_count;
+        p.a_node_stride = a_ns; p.a_off = a_off; p.a_sub_stride = a_ss;
+        p.c_node_stride = c_ns; p.c_off = c_off; p.c_sub_stride = c_ss;
+        p.Kd = Kd; p.Nc = Nc; p.ldb = ldb; p.transB = transB ? 1 : 0; p.accumulate = acc ? 1 : 0;
+        return p;
+    }
+
+    // ------------------------------------------------------------------ stages
+    Layer0Args<T> layer0_args() {
+        Layer0Args<T> a{};
+        a.N = N; a.K = model.K;
+        a.node_types = node_types; a.first_neigh = first_neigh.p; a.neigh_indices = neigh_indices; a.neigh_types = neigh_types;
+        a.xyz = xyz; a.r = r; a.coef0 = coef0.p; a.sm = sm; a.H0_w = H0_w.p;
+        a.Phi0 = Phi0.p; a.Phi0_adj = Phi0_adj.p; a.node_forces = node_forces.p;
+        return a;
+    }
+
+    void compute_A0() {   // MACE::compute_A0, mace.cpp:150-201
+        const int K = model.K;
+        Phi0.resize(static_cast<size_t>(N) * kNumLm * K, stream);
+        A0.resize(static_cast<size_t>(N) * kNumLm * K, stream);
+        if (N == 0) return;
+        const int block = channel_block();
+        const int grid = persistent_grid(layer0_forward_kernel<T>, block, 0, N);
+        layer0_forward_kernel<T><<<grid, block, 0, stream>>>(layer0_args());
+        check_launch("layer0_forward_kernel");
+        std::vector<GemmProblem<T>> list;
+        for (int a = 0; a < model.num_elements; ++a)
+            for (int l = 0; l <= kLmaxSH; ++l)
+                list.push_back(problem(Phi0.p, A0.p, A0_w.p + (static_cast<size_t>(a) * (kLmaxSH + 1) + l) * K * K, true, a, 2 * l + 1,
+                                       16LL * K, 1LL * l * l * K, K, 16LL * K, 1LL * l * l * K, K, K, K, K, false, false));
+        run_gemms(list, 7LL * N, K);
+    }
+
+    void reverse_A0() {   // MACE::reverse_A0, mace.cpp:203-271
+        const int K = model.K;
+        if (A0_adj.n != static_cast<size_t>(N) * kNumLm * K) throw ArgError("reverse_A0: A0_adj has not been computed");
+        Phi0_adj.resize(static_cast<size_t>(N) * kNumLm * K, stream);
+        if (N == 0) return;
+        std::vector<GemmProblem<T>> list;
+        for (int a = 0; a < model.num_elements; ++a)
+            for (int l = 0; l <= kLmaxSH; ++l)
+                list.push_back(problem(A0_adj.p, Phi0_adj.p, A0_w.p + (static_cast<size_t>(a) * (kLmaxSH + 1) + l) * K * K, true, a,
+                                       2 * l + 1, 16LL * K, 1LL * l * l * K, K, 16LL * K, 1LL * l * l * K, K, K, K, K, true, false));
+        run_gemms(list, 7LL * N, K);
+        const int block = channel_block();
+        const int grid = persistent_grid(layer0_reverse_kernel<T>, block, 0, N);
+        layer0_reverse_kernel<T><<<grid, block, 0, stream>>>(layer0_args());
+        check_launch("layer0_reverse_kernel");
+    }
+
+    PolyArgs<T> poly_args(bool first) {
+        PolyArgs<T> a{};
+        a.N = N; a.K = model.K; a.node_types = node_types;
+        if (first) {
+            a.num_out = model.num_LM; a.num_mono = model.num_mono0;
+            a.prog = prog0.p; a.prog_off = prog0_off.p; a.mono_off = mono0_off.p; a.coef = coefM0.p;
+            a.A = A0.p; a.M = M0.p; a.M_adj = M0_adj.p; a.A_adj = A0_adj.p;
+        } else {
+            a.num_out = 1; a.num_mono = model.num_mono1;
+            a.prog = prog1.p; a.prog_off = prog1_off.p; a.mono_off = mono1_off.p; a.coef = coefM1.p;
+            a.A = A1.p; a.M = M1.p; a.M_adj = M1_adj.p; a.A_adj = A1_adj.p;
+        }
+        return a;
+    }
+    void run_poly(bool first, bool reverse) {
+        if (N == 0) return;
+        const int block = 128;
+        const long long total = static_cast<long long>(N) * model.K;
+        const size_t smem = (reverse ? 2 : 1) * kNumLm * block * sizeof(T);
+        if (reverse) {
+            const int grid = static_cast<int>(std::min<long long>((total + block - 1) / block, 65535LL * 16));
+            poly_reverse_kernel<T><<<grid, block, smem, stream>>>(poly_args(first));
+            check_launch("poly_reverse_kernel");
+        } else {
+            const int grid = static_cast<int>(std::min<long long>((total + block - 1) / block, 65535LL * 16));
+            poly_forward_kernel<T><<<grid, block, smem, stream>>>(poly_args(first));
+            check_launch("poly_forward_kernel");
+        }
+    }
+
+    void compute_M0() {   // MACE::compute_M0, mace.cpp:348-370
+        if (A0.n != static_cast<size_t>(N) * kNumLm * model.K) throw ArgError("compute_M0: A0 has not been computed");
+        M0.resize(static_cast<size_t>(N) * model.num_LM * model.K, stream);
+        run_poly(true, false);
+    }
+    void reverse_M0() {   // MACE::reverse_M0, mace.cpp:372-395
+        if (M0_adj.n != static_cast<size_t>(N) * model.num_LM * model.K) throw ArgError("reverse_M0: M0_adj has not been computed");
+        A0_adj.resize(static_cast<size_t>(N) * kNumLm * model.K, stream);
+        run_poly(true, true);
+    }
+    void compute_M1() {   // MACE::compute_M1, mace.cpp:759-777
+        if (A1.n != static_cast<size_t>(N) * kNumLm * model.K) throw ArgError("compute_M1: A1 has not been computed");
+        M1.resize(static_cast<size_t>(N) * model.K, stream);
+        run_poly(false, false);
+    }
+    void reverse_M1() {   // MACE::reverse_M1, mace.cpp:779-794
+        if (M1_adj.n != static_cast<size_t>(N) * model.K) throw ArgError("reverse_M1: M1_adj has not been computed");
+        A1_adj.resize(static_cast<size_t>(N) * kNumLm * model.K, stream);
+        run_poly(false, true);
+    }
+
+    void compute_H1() {   // MACE::compute_H1, mace.cpp:397-423
+        const int K = model.K, nLM = model.num_LM;
+        if (M0.n != static_cast<size_t>(N) * nLM * K) throw ArgError("compute_H1: M0 has not been computed");
+        H1.resize(static_cast<size_t>(N) * nLM * K, stream);
+        h1_rows = N;
+        std::vector<GemmProblem<T>> list;
+        for (int l = 0; l <= model.L_max; ++l)
+            list.push_back(problem(M0.p, H1.p, H1_w.p + static_cast<size_t>(l) * K * K, false, 0, 2 * l + 1, 1LL * nLM * K,
+                                   1LL * l * l * K, K, 1LL * nLM * K, 1LL * l * l * K, K, K, K, K, false, false));
+        run_gemms(list, static_cast<long long>(2 * model.L_max + 1) * N, K);
+    }
+    void reverse_H1() {   // MACE::reverse_H1, mace.cpp:425-451
+        const int K = model.K, nLM = model.num_LM;
+        if (H1_adj.n < static_cast<size_t>(N) * nLM * K) throw ArgError("reverse_H1: H1_adj has not been computed");
+        M0_adj.resize(static_cast<size_t>(N) * nLM * K, stream);
+        std::vector<GemmProblem<T>> list;
+        for (int l = 0; l <= model.L_max; ++l)
+            list.push_back(problem(H1_adj.p, M0_adj.p, H1_w.p + static_cast<size_t>(l) * K * K, false, 0, 2 * l + 1, 1LL * nLM * K,
+                                   1LL * l * l * K, K, 1LL * nLM * K, 1LL * l * l * K, K, K, K, K, true, false));
+        run_gemms(list, static_cast<long long>(2 * model.L_max + 1) * N, K);
+    }
+
+    TPArgs<T> tp_args() {
+        TPArgs<T> a{};
+        a.N = N; a.K = model.K;
+        a.node_types = node_types; a.first_neigh = first_neigh.p; a.neigh_indices = neigh_indices; a.neigh_types = neigh_types;
+        a.xyz = xyz; a.r = r; a.coef1 = coef1.p; a.sm = sm;
+        a.z_ptr = z_ptr.p; a.z_lm1 = z_lm1.p; a.z_c = z_c.p;
+        a.H = H1.p; a.Phi1 = Phi1.p; a.dPhi1 = dPhi1.p; a.Hmsg = Hmsg.p; a.node_forces = node_forces.p;
+        return a;
+    }
+    template <int LF>
+    void launch_tp(bool reverse) {
+        const int block = channel_block();
+        if (reverse) {
+            const int grid = persistent_grid(tp_reverse_kernel<T, LF>, block, 0, N);
+            tp_reverse_kernel<T, LF><<<grid, block, 0, stream>>>(tp_args());
+            check_launch("tp_reverse_kernel");
+        } else {
+            const int grid = persistent_grid(tp_forward_kernel<T, LF>, block, 0, N);
+            tp_forward_kernel<T, LF><<<grid, block, 0, stream>>>(tp_args());
+            check_launch("tp_forward_kernel");
+        }
+    }
+    void dispatch_tp(bool reverse) {
+        switch (model.L_max) {
+            case 0: launch_tp<0>(reverse); break;
+            case 1: launch_tp<1>(reverse); break;
+            case 2: launch_tp<2>(reverse); break;
+            default: throw UnsupportedError("L_max > 2");
+        }
+    }
+
+    void compute_Phi1() {   // MACE::compute_Phi1, mace.cpp:453-502
+        const int K = model.K;
+        if (H1.n < static_cast<size_t>(N) * model.num_LM * K) throw ArgError("compute_Phi1: H1 has not been computed");
+        Phi1.resize(static_cast<size_t>(N) * model.tp.Q * K, stream);
+        if (N == 0) return;
+        dispatch_tp(false);
+    }
+    void reverse_Phi1(bool zero_dxyz, bool zero_H1_adj) {   // MACE::reverse_Phi1, mace.cpp:504-605
+        const int K = model.K, nLM = model.num_LM;
+        if (dPhi1.n != static_cast<size_t>(N) * model.tp.Q * K) throw ArgError("reverse_Phi1: Phi1_adj has not been computed");
+        const size_t hsize = static_cast<size_t>(h1_rows) * nLM * K;
+        if (H1_adj.n != hsize) { H1_adj.resize(hsize, stream, true); }
+        if (zero_dxyz) node_forces.zero(stream);
+        if (zero_H1_adj) H1_adj.zero(stream);
+        if (N == 0) return;
+        Hmsg.resize(static_cast<size_t>(E) * nLM * K, stream);
+        dispatch_tp(true);
+        ensure_sender_lists(std::max(h1_rows, N));
+        if (E > 0) {
+            const int width = nLM * K;
+            const int block = std::min(256, ((width + 31) / 32) * 32);
+            const int grid = std::min(h1_rows, num_sms * 16);
+            sender_gather_kernel<T><<<grid, block, 0, stream>>>(h1_rows, width, in_ptr.p, in_edge.p, Hmsg.p, H1_adj.p);
+            check_launch("sender_gather_kernel");
+        }
+    }
+
+    void compute_A1() {   // MACE::compute_A1, mace.cpp:607-642
+        const int K = model.K;
+        const TPTable& tp = model.tp;
+        if (Phi1.n != static_cast<size_t>(N) * tp.Q * K) throw ArgError("compute_A1: Phi1 has not been computed");
+        A1.resize(static_cast<size_t>(N) * kNumLm * K, stream);
+        std::vector<GemmProblem<T>> list;
+        for (int l = 0; l <= kLmaxSH; ++l)
+            list.push_back(problem(Phi1.p, A1.p, A1_w.p + model.A1_w_off[l], false, 0, 2 * l + 1, 1LL * tp.Q * K, 1LL * tp.lme_off[l] * K,
+                                   1LL * tp.n_e[l] * K, 16LL * K, 1LL * l * l * K, K, tp.n_e[l] * K, K, K, false, false));
+        run_gemms(list, 7LL * N, K);
+    }
+    void reverse_A1() {   // MACE::reverse_A1, mace.cpp:644-679
+        const int K = model.K;
+        const TPTable& tp = model.tp;
+        if (A1_adj.n != static_cast<size_t>(N) * kNumLm * K) throw ArgError("reverse_A1: A1_adj has not been computed");
+        dPhi1.resize(static_cast<size_t>(N) * tp.Q * K, stream);
+        std::vector<GemmProblem<T>> list;
+        int max_cols = K;
+        for (int l = 0; l <= kLmaxSH; ++l) {
+            list.push_back(problem(A1_adj.p, dPhi1.p, A1_w.p + model.A1_w_off[l], false, 0, 2 * l + 1, 16LL * K, 1LL * l * l * K, K,
+                                   1LL * tp.Q * K, 1LL * tp.lme_off[l] * K, 1LL * tp.n_e[l] * K, K, tp.n_e[l] * K, K, true, false));
+            max_cols = std::max(max_cols, tp.n_e[l] * K);
+        }
+        run_gemms(list, 7LL * N, max_cols);
+    }
+
+    void compute_H2() {   // MACE::compute_H2, mace.cpp:796-832
+        const int K = model.K, nLM = model.num_LM;
+        if (M1.n != static_cast<size_t>(N) * K) throw ArgError("compute_H2: M1 has not been computed");
+        H2.resize(static_cast<size_t>(N) * K, stream);
+        std::vector<GemmProblem<T>> list;
+        for (int a = 0; a < model.num_elements; ++a)
+            list.push_back(problem(H1.p, H2.p, H2_w_H1.p + static_cast<size_t>(a) * K * K, true, a, 1, 1LL * nLM * K, 0, 0, K, 0, 0, K, K, K,
+                                   false, false));
+        run_gemms(list, N, K);
+        list.clear();
+        list.push_back(problem(M1.p, H2.p, H2_w_M1.p, false, 0, 1, K, 0, 0, K, 0, 0, K, K, K, false, true));
+        run_gemms(list, N, K);
+    }
+    void reverse_H2(bool zero_H1_adj) {   // MACE::reverse_H2, mace.cpp:834-874
+        const int K = model.K, nLM = model.num_LM;
+        if (H2_adj.n != static_cast<size_t>(N) * K) throw ArgError("reverse_H2: H2_adj has not been computed");
+        const size_t hsize = static_cast<size_t>(h1_rows) * nLM * K;
+        if (H1_adj.n != hsize) H1_adj.resize(hsize, stream, true);
+        M1_adj.resize(static_cast<size_t>(N) * K, stream);
+        if (zero_H1_adj) H1_adj.zero(stream);
+        std::vector<GemmProblem<T>> list;
+        for (int a = 0; a < model.num_elements; ++a)
+            list.push_back(problem(H2_adj.p, H1_adj.p, H2_w_H1.p + static_cast<size_t>(a) * K * K, true, a, 1, K, 0, 0, 1LL * nLM * K, 0, 0, K, K,
+                                   K, true, true));
+        list.push_back(problem(H2_adj.p, M1_adj.p, H2_w_M1.p, false, 0, 1, K, 0, 0, K, 0, 0, K, K, K, true, false));
+        run_gemms(list, N, K);
+    }
+
+    void compute_readouts() {   // MACE::compute_readouts, mace.cpp:876-903
+        const int K = model.K, nLM = model.num_LM;
+        if (H2.n != static_cast<size_t>(N) * K) throw ArgError("compute_readouts: H2 has not been computed");
+        H1_adj.resize(static_cast<size_t>(h1_rows) * nLM * K, stream);
+        H1_adj.zero(stream);
+        H2_adj.resize(static_cast<size_t>(N) * K, stream);
+        if (N == 0) return;
+        ReadoutArgs<T> a{};
+        a.N = N; a.K = K; a.nLM = nLM; a.node_types = node_types; a.E0 = E0.p;
+        a.ro1 = ro1.p; a.W1 = ro2_w1.p; a.w2 = ro2_w2.p; a.scale = static_cast<T>(model.ro2_scale);
+        a.H1 = H1.p; a.H2 = H2.p; a.node_energies = node_energies.p; a.H1_adj = H1_adj.p; a.H2_adj = H2_adj.p;
+        const int block = 128;
+        const int grid = std::min((N + 3) / 4, num_sms * 16);
+        readout_kernel<T><<<grid, block, 0, stream>>>(a);
+        check_launch("readout_kernel");
+    }
+
+    void stage(const std::string& s, bool zero_dxyz, bool zero_H1_adj) override {
+        require_edges();
+        SMX_CUDA(cudaSetDevice(device));
+        if (s == "compute_Y" || s == "compute_R0" || s == "compute_R1") return;  // fused into the edge kernels
+        if (s == "compute_A0_scaled" || s == "compute_A1_scaled" || s == "reverse_A0_scaled" || s == "reverse_A1_scaled") return;
+        if (s == "compute_A0") compute_A0();
+        else if (s == "compute_M0") compute_M0();
+        else if (s == "compute_H1") compute_H1();
+        else if (s == "compute_Phi1") compute_Phi1();
+        else if (s == "compute_A1") compute_A1();
+        else if (s == "compute_M1") compute_M1();
+        else if (s == "compute_H2") compute_H2();
+        else if (s == "compute_readouts") compute_readouts();
+        else if (s == "reverse_H2") reverse_H2(zero_H1_adj);
+        else if (s == "reverse_M1") reverse_M1();
+        else if (s == "reverse_A1") reverse_A1();
+        else if (s == "reverse_Phi1") reverse_Phi1(zero_dxyz, zero_H1_adj);
+        else if (s == "reverse_H1") reverse_H1();
+        else if (s == "reverse_M0") reverse_M0();
+        else if (s == "reverse_A0") reverse_A0();
+        else throw ArgError("unknown stage '" + s + "'");
+    }
+
+    void compute_all() override {   // order of MACE::compute_node_energies_forces, mace.cpp:17-64
+        require_edges();
+        SMX_CUDA(cudaSetDevice(device));
+        SMX_CUDA(cudaEventRecord(ev0, stream));
+        compute_A0(); compute_M0(); compute_H1();
+        compute_Phi1(); compute_A1(); compute_M1(); compute_H2();
+        compute_readouts();
+        reverse_H2(false); reverse_M1(); reverse_A1(); reverse_Phi1(false, false);
+        reverse_H1(); reverse_M0(); reverse_A0();
+        SMX_CUDA(cudaEventRecord(ev1, stream));
+        SMX_CUDA(cudaStreamSynchronize(stream));
+        float ms = 0.f;
+        SMX_CUDA(cudaEventElapsedTime(&ms, ev0, ev1));
+        last_ms = ms;
+    }
+
+    // ------------------------------------------------------------------ array access
+    struct Field { DevBuf<T>* t = nullptr; DevBuf<double>* d = nullptr; };
+    Field field(const std::string& s) {
+        Field f;
+        if (s == "node_energies") f.d = &node_energies;
+        else if (s == "node_forces") f.d = &node_forces;
+        else if (s == "A0") f.t = &A0;
+        else if (s == "A0_adj") f.t = &A0_adj;
+        else if (s == "M0") f.t = &M0;
+        else if (s == "M0_adj") f.t = &M0_adj;
+        else if (s == "H1") f.t = &H1;
+        else if (s == "H1_adj") f.t = &H1_adj;
+        else if (s == "Phi1") f.t = &Phi1;
+        else if (s == "Phi1_adj") f.t = &dPhi1;
+        else if (s == "A1") f.t = &A1;
+        else if (s == "A1_adj") f.t = &A1_adj;
+        else if (s == "M1") f.t = &M1;
+        else if (s == "M1_adj") f.t = &M1_adj;
+        else if (s == "H2") f.t = &H2;
+        else if (s == "H2_adj") f.t = &H2_adj;
+        else throw ArgError("unknown array '" + s + "'");
+        return f;
+    }
+
+    long get_array(const std::string& name, double* dst, long cap, int mem_space) override {
+        SMX_CUDA(cudaSetDevice(device));
+        Field f = field(name);
+        const size_t n = f.t ? f.t->n : f.d->n;
+        const size_t ncopy = std::min<size_t>(n, cap < 0 ? 0 : static_cast<size_t>(cap));
+        if (ncopy == 0 || !dst) return static_cast<long>(n);
+        const double* src = nullptr;
+        if (f.t) {
+            scratch_d.resize(ncopy, stream);
+            convert_kernel<T, double><<<static_cast<int>(std::min<size_t>((ncopy + 255) / 256, 4096)), 256, 0, stream>>>(
+                static_cast<long long>(ncopy), f.t->p, scratch_d.p);
+            check_launch("convert_kernel");
+            src = scratch_d.p;
+        } else {
+            src = f.d->p;
+        }
+        SMX_CUDA(cudaMemcpyAsync(dst, src, ncopy * sizeof(double),
+                                 mem_space == SMX_DEVICE ? cudaMemcpyDeviceToDevice : cudaMemcpyDeviceToHost, stream));
+        SMX_CUDA(cudaStreamSynchronize(stream));
+        return static_cast<long>(n);
+    }
+
+    void set_array(const std::string& name, const double* src, long n, int mem_space) override {
+        SMX_CUDA(cudaSetDevice(device));
+        if (n < 0 || (n > 0 && !src)) throw ArgError("set_array: bad source");
+        Field f = field(name);
+        if (f.d) {
+            f.d->resize(n, stream);
+            if (n) SMX_CUDA(cudaMemcpyAsync(f.d->p, src, n * sizeof(double),
+                                           mem_space == SMX_DEVICE ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, stream));
+        } else {
+            f.t->resize(n, stream);
+            const double* dsrc = src;
+            if (mem_space != SMX_DEVICE) {
+                scratch_d.resize(n, stream);
+                if (n) SMX_CUDA(cudaMemcpyAsync(scratch_d.p, src, n * sizeof(double), cudaMemcpyHostToDevice, stream));
+                dsrc = scratch_d.p;
+            }
+            if (n) {
+                convert_kernel<double, T><<<static_cast<int>(std::min<size_t>((n + 255) / 256, 4096)), 256, 0, stream>>>(n, dsrc, f.t->p);
+                check_launch("convert_kernel");
+            }
+        }
+        if (name == "H1" || name == "H1_adj") {
+            const size_t row = static_cast<size_t>(model.num_LM) * model.K;
+            if (static_cast<size_t>(n) % row != 0) throw ArgError("set_array: H1 length is not a multiple of num_LM * num_channels");
+            const int rows = static_cast<int>(static_cast<size_t>(n) / row);
+            if (name == "H1") h1_rows = rows;
+        }
+        SMX_CUDA(cudaStreamSynchronize(stream));
+    }
+
+    void reduce_forces(int rows, double* f, double* virial, double* energy, int mem_space) override {
+        require_edges();
+        SMX_CUDA(cudaSetDevice(device));
+        if (rows < N) throw ArgError("reduce_forces: num_rows must be at least num_nodes");
+        const cudaMemcpyKind kind = mem_space == SMX_DEVICE ? cudaMemcpyDeviceToDevice : cudaMemcpyDeviceToHost;
+        if (f) {
+            ensure_sender_lists(std::max(rows, std::max(h1_rows, N)));
+            const int srows = sender_rows;
+            atom_f.resize(3 * static_cast<size_t>(srows), stream);
+            if (srows > 0) {
+                atom_forces_kernel<<<std::min((srows + 127) / 128, num_sms * 16), 128, 0, stream>>>(srows, N, first_neigh.p, in_ptr.p, in_edge.p,
+                                                                                                  node_forces.p, atom_f.p);
+                check_launch("atom_forces_kernel");
+                SMX_CUDA(cudaMemcpyAsync(f, atom_f.p, 3 * static_cast<size_t>(rows) * sizeof(double), kind, stream));
+            }
+        }
+        if (virial || energy) {
+            const int blocks = std::max(1, std::min(num_sms * 4, static_cast<int>((std::max<long>(E, N) + 255) / 256)));
+            partials.resize(static_cast<size_t>(blocks) * 7, stream);
+            out7.resize(7, stream);
+            energy_virial_partial_kernel<<<blocks, 256, 0, stream>>>(N, E, node_energies.p, xyz, node_forces.p, partials.p);
+            check_launch("energy_virial_partial_kernel");
+            energy_virial_final_kernel<<<1, 32, 0, stream>>>(blocks, partials.p, out7.p);
+            check_launch("energy_virial_final_kernel");
+            if (energy) SMX_CUDA(cudaMemcpyAsync(energy, out7.p, sizeof(double), kind, stream));
+            if (virial) SMX_CUDA(cudaMemcpyAsync(virial, out7.p + 1, 6 * sizeof(double), kind, stream));
+        }
+        SMX_CUDA(cudaStreamSynchronize(stream));
+    }
+
+    // ------------------------------------------------------------------ neighbour list
+    long build_neighbors(int natoms, const double* pos, const int* types, const double* cell, const int* pbc, double r_cut,
+                         int mem_space) override {
+        SMX_CUDA(cudaSetDevice(device));
+        if (natoms < 0 || (natoms > 0 && (!pos || !types)) || !cell || !pbc) throw ArgError("build_neighbors: bad arguments");
+        const int* d_types = stage_input(types, natoms, in_node_types, mem_space);
+        long n_edges = 0;
+        nb.build(natoms, pos, d_types, cell, pbc, r_cut, mem_space == SMX_DEVICE, stream, launches, in_num_neigh, in_neigh_indices,
+                 in_neigh_types, in_shifts, in_xyz, in_r, n_edges);
+        node_types = d_types;
+        num_neigh = in_num_neigh.p; neigh_indices = in_neigh_indices.p; neigh_types = in_neigh_types.p;
+        xyz = in_xyz.p; r = in_r.p;
+        adopt_edges(natoms, n_edges);
+        SMX_CUDA(cudaStreamSynchronize(stream));
+        return n_edges;
+    }
+
+    void get_edges(int* o_nn, int* o_ni, int* o_et, int* o_sh, double* o_xyz, double* o_r, int mem_space) override {
+        require_edges();
+        SMX_CUDA(cudaSetDevice(device));
+        const cudaMemcpyKind kind = mem_space == SMX_DEVICE ? cudaMemcpyDeviceToDevice : cudaMemcpyDeviceToHost;
+        if (o_nn && N) SMX_CUDA(cudaMemcpyAsync(o_nn, num_neigh, N * sizeof(int), kind, stream));
+        if (o_ni && E) SMX_CUDA(cudaMemcpyAsync(o_ni, neigh_indices, E * sizeof(int), kind, stream));
+        if (o_et && E) SMX_CUDA(cudaMemcpyAsync(o_et, neigh_types, E * sizeof(int), kind, stream));
+        if (o_sh && E) {
+            if (in_shifts.n != 3 * static_cast<size_t>(E)) throw ArgError("get_edges: shifts exist only for edge sets built by smx_build_neighbors");
+            SMX_CUDA(cudaMemcpyAsync(o_sh, in_shifts.p, 3 * E * sizeof(int), kind, stream));
+        }
+        if (o_xyz && E) SMX_CUDA(cudaMemcpyAsync(o_xyz, xyz, 3 * E * sizeof(double), kind, stream));
+        if (o_r && E) SMX_CUDA(cudaMemcpyAsync(o_r, r, E * sizeof(double), kind, stream));
+        SMX_CUDA(cudaStreamSynchronize(stream));
+    }
+};
+
+}  // namespace smx
+
+// =================================================================================================
+// extern "C" entry points
+// =================================================================================================
+struct smx_evaluator {
+    std::unique_ptr<smx::EvaluatorBase> impl;
+};
+
+namespace {
+thread_local std::string g_create_error;
+
+template <typename Fn>
+int guarded(smx_handle h, Fn&& fn) {
+    if (!h || !h->impl) return SMX_ERR_INVALID_ARGUMENT;
+    try {
+        fn(*h->impl);
+        return SMX_OK;
+    } catch (const smx::ArgError& e) {
+        h->impl->last_error = e.what();
+        return SMX_ERR_INVALID_ARGUMENT;
+    } catch (const smx::UnsupportedError& e) {
+        h->impl->last_error = e.what();
+        return SMX_ERR_UNSUPPORTED;
+    } catch (const smx::CudaError& e) {
+        h->impl->last_error = e.what();
+        return SMX_ERR_CUDA;
+    } catch (const std::exception& e) {
+        h->impl->last_error = e.what();
+        return SMX_ERR_INVALID_ARGUMENT;
+    }
+}
+}  // namespace
+
+extern "C" {
+
+int smx_create(const char* json_path, int precision, int device, smx_handle* out) {
+    if (!out) return SMX_ERR_INVALID_ARGUMENT;
+    *out = nullptr;
+    try {
+        if (!json_path) throw smx::ArgError("smx_create: null path");
+        if (precision != SMX_FP32 && precision != SMX_FP64) throw smx::ArgError("smx_create: precision must be 32 or 64");
+        // the model is read and validated first, so a bad file is reported as such on any machine
+        smx::HostModel m = smx::load_model_file(json_path);
+        int count = 0;
+        if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0) {
+            cudaGetLastError();
+            g_create_error = "no CUDA device available: this library has no CPU path";
+            return SMX_ERR_NO_DEVICE;
+        }
+        if (device < 0 || device >= count) throw smx::ArgError("smx_create: device ordinal out of range");
+        auto h = std::make_unique<smx_evaluator>();
+        if (precision == SMX_FP32) h->impl = std::make_unique<smx::Evaluator<float>>(std::move(m), device);
+        else h->impl = std::make_unique<smx::Evaluator<double>>(std::move(m), device);
+        *out = h.release();
+        return SMX_OK;
+    } catch (const smx::ArgError& e) { g_create_error = e.what(); return SMX_ERR_INVALID_ARGUMENT;
+    } catch (const smx::UnsupportedError& e) { g_create_error = e.what(); return SMX_ERR_UNSUPPORTED;
+    } catch (const smx::CudaError& e) { g_create_error = e.what(); return SMX_ERR_CUDA;
+    } catch (const std::exception& e) { g_create_error = e.what(); return SMX_ERR_MODEL; }  // JsonError, ModelError, I/O
+}
+
+void smx_destroy(smx_handle h) { delete h; }
+
+const char* smx_last_error(smx_handle h) {
+    if (!h || !h->impl) return g_create_error.c_str();
+    return h->impl->last_error.c_str();
+}
+
+int smx_info(smx_handle h, smx_model_info* info) {
+    if (!info) return SMX_ERR_INVALID_ARGUMENT;
+    return guarded(h, [&](smx::EvaluatorBase& e) {
+        const smx::HostModel& m = e.model;
+        info->num_elements = m.num_elements; info->num_channels = m.K; info->r_cut = m.r_cut;
+        info->l_max = m.l_max; info->num_lm = m.num_lm; info->L_max = m.L_max; info->num_LM = m.num_LM;
+        info->num_paths = m.tp.P; info->num_lelm1lm2 = m.tp.T; info->num_lme = m.tp.Q;
+        info->has_zbl = m.has_zbl ? 1 : 0; info->precision = e.precision; info->device = e.device;
+    });
+}
+
+int smx_atomic_numbers(smx_handle h, int* out, int cap) {
+    if (!h || !h->impl) return -1;
+    const auto& v = h->impl->model.atomic_numbers;
+    for (int i = 0; i < static_cast<int>(v.size()) && i < cap && out; ++i) out[i] = v[i];
+    return static_cast<int>(v.size());
+}
+int smx_atomic_energies(smx_handle h, double* out, int cap) {
+    if (!h || !h->impl) return -1;
+    const auto& v = h->impl->model.atomic_energies;
+    for (int i = 0; i < static_cast<int>(v.size()) && i < cap && out; ++i) out[i] = v[i];
+    return static_cast<int>(v.size());
+}
+
+int smx_begin(smx_handle h, int num_nodes, const int* node_types, const int* num_neigh, const int* neigh_indices,
+              const int* neigh_types, const double* xyz, const double* r, long num_edges, int mem_space) {
+    return guarded(h, [&](smx::EvaluatorBase& e) {
+        e.begin(num_nodes, node_types, num_neigh, neigh_indices, neigh_types, xyz, r, num_edges, mem_space);
+    });
+}
+
+int smx_compute(smx_handle h, int num_nodes, const int* node_types, const int* num_neigh, const int* neigh_indices,
+                const int* neigh_types, const double* xyz, const double* r, long num_edges, int mem_space) {
+    return guarded(h, [&](smx::EvaluatorBase& e) {
+        e.begin(num_nodes, node_types, num_neigh, neigh_indices, neigh_types, xyz, r, num_edges, mem_space);
+        e.compute_all();
+    });
+}
+
+int smx_compute_current(smx_handle h) {
+    return guarded(h, [&](smx::EvaluatorBase& e) { e.compute_all(); });
+}
+
+int smx_stage(smx_handle h, const char* name, int zero_dxyz, int zero_H1_adj) {
+    return guarded(h, [&](smx::EvaluatorBase& e) {
+        if (!name) throw smx::ArgError("smx_stage: null name");
+        e.stage(name, zero_dxyz != 0, zero_H1_adj != 0);
+    });
+}
+
+int smx_get_array(smx_handle h, const char* name, double* dst, long cap, long* n, int mem_space) {
+    return guarded(h, [&](smx::EvaluatorBase& e) {
+        if (!name) throw smx::ArgError("smx_get_array: null name");
+        const long count = e.get_array(name, dst, cap, mem_space);
+        if (n) *n = count;
+    });
+}
+
+int smx_set_array(smx_handle h, const char* name, const double* src, long n, int mem_space) {
+    return guarded(h, [&](smx::EvaluatorBase& e) {
+        if (!name) throw smx::ArgError("smx_set_array: null name");
+        e.set_array(name, src, n, mem_space);
+    });
+}
+
+int smx_reduce_forces(smx_handle h, int num_rows, double* atom_forces, double* virial, double* energy, int mem_space) {
+    return guarded(h, [&](smx::EvaluatorBase& e) { e.reduce_forces(num_rows, atom_forces, virial, energy, mem_space); });
+}
+
+int smx_last_device_ms(smx_handle h, double* ms) {
+    return guarded(h, [&](smx::EvaluatorBase& e) { if (ms) *ms = e.last_ms; });
+}
+
+long smx_launch_count(smx_handle h) { return (h && h->impl) ? h->impl->launches : -1; }
+
+int smx_build_neighbors(smx_handle h, int num_atoms, const double* positions, const int* types, const double* cell,
+                        const int* pbc, double r_cut, long* num_edges, int mem_space) {
+    return guarded(h, [&](smx::EvaluatorBase& e) {
+        const long n = e.build_neighbors(num_atoms, positions, types, cell, pbc, r_cut, mem_space);
+        if (num_edges) *num_edges = n;
+    });
+}
+
+int smx_get_edges(smx_handle h, int* num_neigh, int* neigh_indices, int* neigh_types, int* shifts, double* xyz, double* r,
+                  int mem_space) {
+    return guarded(h, [&](smx::EvaluatorBase& e) { e.get_edges(num_neigh, neigh_indices, neigh_types, shifts, xyz, r, mem_space); });
+}
+
+}  // extern "C"

@@ -1,0 +1,869 @@
+// CUDA kernels of the MACE energy+force path for sm_100a.
+//
+// Data layout in HBM (all row-major, channel index fastest, one arithmetic type T per evaluator):
+//   node features  A0/A1 [N][16][K], M0/H1 [rows][nLM][K], Phi1 [N][Q][K], M1/H2 [N][K]
+//   spline tables  [pair][bin][function][4]  (one 16/32-byte vector load per function and edge)
+//   contraction    coefficients [element][monomial][K]
+// One thread owns one channel k of one receiver node, so every global access is a contiguous
+// run of K values across the CTA. Per-edge quantities that do not depend on the channel
+// (harmonics, their gradients, coupling blocks, spline bin) are computed once per edge into
+// shared memory and broadcast. No per-edge channel array (R0, R1, Y, Phi1r of the reference,
+// libsymmetrix/source/mace.hpp:44-113) is ever written to HBM.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <utility>
+
+#include "tp_tables.hpp"
+
+namespace smx {
+
+constexpr int kEdgeBatch = 8;       // edges staged in shared memory per pass
+constexpr int kChannelBlock = 128;  // threads per CTA of the edge kernels; more channels are done in chunks
+constexpr int kMaxWarps = kChannelBlock / 32;
+// the coupling blocks of the L_max = 2 tensor product are three times larger: stage fewer edges
+constexpr int tp_edge_batch(int LF) { return LF >= 2 ? 4 : kEdgeBatch; }
+
+// Compile-time loop: f(std::integral_constant<int, 0>{}), ..., f(std::integral_constant<int, N-1>{}).
+// The tensor-product kernels index their register accumulators with path-dependent offsets, which
+// must be constants for the accumulators to stay in registers.
+template <typename F, int... I>
+__device__ __forceinline__ void static_for_impl(F&& f, std::integer_sequence<int, I...>) {
+    (f(std::integral_constant<int, I>{}), ...);
+}
+template <int N, typename F>
+__device__ __forceinline__ void static_for(F&& f) {
+    static_for_impl(f, std::make_integer_sequence<int, N>{});
+}
+template <int LF>
+struct TPConst {
+    static constexpr TPTable t = make_tp_table(LF);
+};
+
+template <typename T> struct Vec4;
+template <> struct alignas(16) Vec4<float> { float x, y, z, w; };
+template <> struct alignas(32) Vec4<double> { double x, y, z, w; };
+
+template <typename T>
+__device__ __forceinline__ Vec4<T> load4(const T* p);
+template <>
+__device__ __forceinline__ Vec4<float> load4<float>(const float* p) {
+    const float4 v = __ldg(reinterpret_cast<const float4*>(p));
+    return {v.x, v.y, v.z, v.w};
+}
+template <>
+__device__ __forceinline__ Vec4<double> load4<double>(const double* p) {
+    const double2 a = __ldg(reinterpret_cast<const double2*>(p));
+    const double2 b = __ldg(reinterpret_cast<const double2*>(p) + 1);
+    return {a.x, a.y, b.x, b.y};
+}
+
+template <typename T>
+__device__ __forceinline__ T warp_sum(T v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Real spherical harmonics up to l = 3 of the direction (a, b, c) = xyz / r, in the convention the
+// reference feeds its tensor products with (mace.cpp:118-148: orthonormal real harmonics of the
+// axis-shuffled vector (z, x, y), times 2 sqrt(pi), lm = l*l + l + m), written as polynomials in
+// the un-shuffled components. g[c][lm] receives the Cartesian gradient d Y_lm / d xyz_c.
+// ---------------------------------------------------------------------------------------------
+template <typename T, bool GRAD>
+__host__ __device__ inline void real_sh3(T a, T b, T c, T inv_r, T* __restrict__ Y, T (*__restrict__ g)[kNumLm]) {
+    const T s3 = T(1.7320508075688772935), s15 = T(3.8729833462074168852), s5h = T(1.1180339887498948482);
+    const T s105 = T(10.246950765959598383), s7h = T(1.3228756555322952953);
+    const T k9 = T(2.0916500663351888699);   // sqrt(35/8)
+    const T k11 = T(1.6201851746019651311);  // sqrt(21/8)
+    const T aa = a * a, bb = b * b, cc = c * c;
+    Y[0] = T(1);
+    Y[1] = s3 * a; Y[2] = s3 * b; Y[3] = s3 * c;
+    Y[4] = s15 * c * a;
+    Y[5] = s15 * a * b;
+    Y[6] = s5h * (T(3) * bb - T(1));
+    Y[7] = s15 * c * b;
+    Y[8] = T(0.5) * s15 * (cc - aa);
+    Y[9] = k9 * a * (T(3) * cc - aa);
+    Y[10] = s105 * a * b * c;
+    Y[11] = k11 * a * (T(5) * bb - T(1));
+    Y[12] = s7h * b * (T(5) * bb - T(3));
+    Y[13] = k11 * c * (T(5) * bb - T(1));
+    Y[14] = T(0.5) * s105 * b * (cc - aa);
+    Y[15] = k9 * c * (cc - T(3) * aa);
+    if constexpr (GRAD) {
+        T d[3][kNumLm];
+        d[0][0] = 0; d[1][0] = 0; d[2][0] = 0;
+        d[0][1] = s3; d[1][1] = 0; d[2][1] = 0;
+        d[0][2] = 0; d[1][2] = s3; d[2][2] = 0;
+        d[0][3] = 0; d[1][3] = 0; d[2][3] = s3;
+        d[0][4] = s15 * c; d[1][4] = 0; d[2][4] = s15 * a;
+        d[0][5] = s15 * b; d[1][5] = s15 * a; d[2][5] = 0;
+        d[0][6] = 0; d[1][6] = T(6) * s5h * b; d[2][6] = 0;
+        d[0][7] = 0; d[1][7] = s15 * c; d[2][7] = s15 * b;
+        d[0][8] = -s15 * a; d[1][8] = 0; d[2][8] = s15 * c;
+        d[0][9] = k9 * T(3) * (cc - aa); d[1][9] = 0; d[2][9] = k9 * T(6) * a * c;
+        d[0][10] = s105 * b * c; d[1][10] = s105 * a * c; d[2][10] = s105 * a * b;
+        d[0][11] = k11 * (T(5) * bb - T(1)); d[1][11] = k11 * T(10) * a * b; d[2][11] = 0;
+        d[0][12] = 0; d[1][12] = s7h * (T(15) * bb - T(3)); d[2][12] = 0;
+        d[0][13] = 0; d[1][13] = k11 * T(10) * b * c; d[2][13] = k11 * (T(5) * bb - T(1));
+        d[0][14] = -s105 * a * b; d[1][14] = T(0.5) * s105 * (cc - aa); d[2][14] = s105 * b * c;
+        d[0][15] = -k9 * T(6) * a * c; d[1][15] = 0; d[2][15] = k9 * T(3) * (cc - aa);
+        // chain rule through u = xyz / r: grad = (d - u (u . d)) / r
+#pragma unroll
+        for (int lm = 0; lm < kNumLm; ++lm) {
+            const T rad = d[0][lm] * a + d[1][lm] * b + d[2][lm] * c;
+            g[0][lm] = (d[0][lm] - rad * a) * inv_r;
+            g[1][lm] = (d[1][lm] - rad * b) * inv_r;
+            g[2][lm] = (d[2][lm] - rad * c) * inv_r;
+        }
+    }
+}
+
+// Per-edge, channel-independent quantities staged in shared memory.
+template <typename T>
+struct EdgeStage {
+    T Y[kNumLm];              // harmonics
+    T dY[3][kNumLm];          // gradients (reverse kernels only)
+    T x;                      // r - h * bin
+    T ux, uy, uz;             // unit vector
+    long long coef_base;      // (pair * num_bins + bin) * F * 4
+    int j;                    // sender row
+    int tj;                   // sender type
+};
+
+struct SplineMeta {
+    double h;
+    int num_bins;
+    int num_elements;
+};
+
+// Fill stage[e] for the edges [e0, e0 + nb) of node i; executed by threads 0..nb-1.
+template <typename T, bool GRAD>
+__device__ __forceinline__ void stage_edge(EdgeStage<T>& s, long long edge, int type_i, const int* __restrict__ neigh_indices,
+                                           const int* __restrict__ neigh_types, const double* __restrict__ xyz,
+                                           const double* __restrict__ r, const SplineMeta sm, int F) {
+    const double rr = r[edge];
+    const double inv = 1.0 / rr;
+    const double ax = xyz[3 * edge] * inv, ay = xyz[3 * edge + 1] * inv, az = xyz[3 * edge + 2] * inv;
+    s.ux = T(ax); s.uy = T(ay); s.uz = T(az);
+    real_sh3<T, GRAD>(T(ax), T(ay), T(az), T(inv), s.Y, s.dY);
+    // bin and offset exactly as CubicSplineSet::evaluate_derivs (cubic_spline_set.cpp:55-56),
+    // clamped to the last interval so that r within rounding of r_cut stays inside the table
+    int bin = static_cast<int>(rr / sm.h);
+    bin = bin < 0 ? 0 : (bin > sm.num_bins - 1 ? sm.num_bins - 1 : bin);
+    s.x = T(rr - sm.h * bin);
+    const int tj = neigh_types[edge];
+    s.tj = tj;
+    s.j = neigh_indices[edge];
+    const int lo = type_i <= tj ? type_i : tj, hi = type_i <= tj ? tj : type_i;
+    const int pair = lo * (2 * sm.num_elements - lo - 1) / 2 + hi;   // mace.cpp:81-83
+    s.coef_base = (static_cast<long long>(pair) * sm.num_bins + bin) * F * 4;
+}
+
+// =============================================================================================
+// Layer 0, forward: Phi0[i, lm, k] = sum_j R0_ab(r_ij)[l, k] * Y_ij[lm] * H0[b, k]
+// (first half of MACE::compute_A0, mace.cpp:159-178, with compute_Y / compute_R0 fused in).
+// =============================================================================================
+template <typename T>
+struct Layer0Args {
+    int N, K;
+    const int* node_types; const long long* first_neigh; const int* neigh_indices; const int* neigh_types;
+    const double* xyz; const double* r;
+    const T* coef0; SplineMeta sm;
+    const T* H0_w;          // [E][K]
+    T* Phi0;                // [N][16][K]          (forward output)
+    const T* Phi0_adj;      // [N][16][K]          (reverse input)
+    double* node_forces;    // [3 * num_edges]     (reverse: accumulated into)
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kChannelBlock) layer0_forward_kernel(const Layer0Args<T> a) {
+    __shared__ EdgeStage<T> st[kEdgeBatch];
+    const int F = (kLmaxSH + 1) * a.K;
+    for (int i = blockIdx.x; i < a.N; i += gridDim.x)
+    for (int kc = 0; kc < a.K; kc += blockDim.x) {
+        const int k = kc + threadIdx.x;
+        const bool active = k < a.K;
+        const long long e_begin = a.first_neigh[i], e_end = a.first_neigh[i + 1];
+        const int type_i = a.node_types[i];
+        T acc[kNumLm];
+#pragma unroll
+        for (int lm = 0; lm < kNumLm; ++lm) acc[lm] = T(0);
+        for (long long e0 = e_begin; e0 < e_end; e0 += kEdgeBatch) {
+            const int nb = static_cast<int>(e_end - e0 < kEdgeBatch ? e_end - e0 : kEdgeBatch);
+            __syncthreads();
+            if (threadIdx.x < nb)
+                stage_edge<T, false>(st[threadIdx.x], e0 + threadIdx.x, type_i, a.neigh_indices, a.neigh_types, a.xyz, a.r, a.sm, F);
+            __syncthreads();
+            if (active) {
+                for (int e = 0; e < nb; ++e) {
+                    const EdgeStage<T>& s = st[e];
+                    const T h0 = a.H0_w[s.tj * a.K + k];
+                    const T x = s.x;
+                    const T* cb = a.coef0 + s.coef_base + 4 * k;
+#pragma unroll
+                    for (int l = 0; l <= kLmaxSH; ++l) {
+                        const Vec4<T> c = load4<T>(cb + 4 * l * a.K);
+                        const T R = (c.x + x * (c.y + x * (c.z + x * c.w))) * h0;
+#pragma unroll
+                        for (int lm = l * l; lm < (l + 1) * (l + 1); ++lm) acc[lm] += R * s.Y[lm];
+                    }
+                }
+            }
+        }
+        if (active) {
+            T* out = a.Phi0 + (static_cast<size_t>(i) * kNumLm) * a.K + k;
+#pragma unroll
+            for (int lm = 0; lm < kNumLm; ++lm) out[static_cast<size_t>(lm) * a.K] = acc[lm];
+        }
+    }
+}
+
+// =============================================================================================
+// Layer 0, reverse: per-edge partial forces
+//   nf[ij] -= sum_{lm,k} Phi0_adj[i,lm,k] H0[b,k] (xhat R0'[l,k] Y[lm] + R0[l,k] grad Y[lm])
+// (second half of MACE::reverse_A0, mace.cpp:238-269).
+// =============================================================================================
+template <typename T>
+__global__ void __launch_bounds__(kChannelBlock) layer0_reverse_kernel(const Layer0Args<T> a) {
+    __shared__ EdgeStage<T> st[kEdgeBatch];
+    __shared__ T red[kMaxWarps][kEdgeBatch][4];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    const int F = (kLmaxSH + 1) * a.K;
+    for (int i = blockIdx.x; i < a.N; i += gridDim.x)
+    for (int kc = 0; kc < a.K; kc += blockDim.x) {
+        const int k = kc + threadIdx.x;
+        const bool active = k < a.K;
+        const long long e_begin = a.first_neigh[i], e_end = a.first_neigh[i + 1];
+        const int type_i = a.node_types[i];
+        T d[kNumLm];
+#pragma unroll
+        for (int lm = 0; lm < kNumLm; ++lm)
+            d[lm] = active ? a.Phi0_adj[(static_cast<size_t>(i) * kNumLm + lm) * a.K + k] : T(0);
+        for (long long e0 = e_begin; e0 < e_end; e0 += kEdgeBatch) {
+            const int nb = static_cast<int>(e_end - e0 < kEdgeBatch ? e_end - e0 : kEdgeBatch);
+            __syncthreads();
+            if (threadIdx.x < nb)
+                stage_edge<T, true>(st[threadIdx.x], e0 + threadIdx.x, type_i, a.neigh_indices, a.neigh_types, a.xyz, a.r, a.sm, F);
+            __syncthreads();
+            for (int e = 0; e < nb; ++e) {
+                const EdgeStage<T>& s = st[e];
+                T fr = 0, fx = 0, fy = 0, fz = 0;
+                if (active) {
+                    const T h0 = a.H0_w[s.tj * a.K + k];
+                    const T x = s.x;
+                    const T* cb = a.coef0 + s.coef_base + 4 * k;
+#pragma unroll
+                    for (int l = 0; l <= kLmaxSH; ++l) {
+                        const Vec4<T> c = load4<T>(cb + 4 * l * a.K);
+                        const T R = (c.x + x * (c.y + x * (c.z + x * c.w))) * h0;
+                        const T Rd = (c.y + x * (T(2) * c.z + T(3) * x * c.w)) * h0;
+                        T sv = 0, gx = 0, gy = 0, gz = 0;
+#pragma unroll
+                        for (int lm = l * l; lm < (l + 1) * (l + 1); ++lm) {
+                            sv += d[lm] * s.Y[lm];
+                            gx += d[lm] * s.dY[0][lm];
+                            gy += d[lm] * s.dY[1][lm];
+                            gz += d[lm] * s.dY[2][lm];
+                        }
+                        fr += Rd * sv; fx += R * gx; fy += R * gy; fz += R * gz;
+                    }
+                }
+                fr = warp_sum(fr); fx = warp_sum(fx); fy = warp_sum(fy); fz = warp_sum(fz);
+                if (lane == 0) { red[warp][e][0] = fr; red[warp][e][1] = fx; red[warp][e][2] = fy; red[warp][e][3] = fz; }
+            }
+            __syncthreads();
+            if (threadIdx.x < nb) {
+                const int e = threadIdx.x;
+                double tr = 0, tx = 0, ty = 0, tz = 0;
+                for (int w = 0; w < nwarps; ++w) { tr += red[w][e][0]; tx += red[w][e][1]; ty += red[w][e][2]; tz += red[w][e][3]; }
+                double* nf = a.node_forces + 3 * (e0 + e);
+                nf[0] -= double(st[e].ux) * tr + tx;
+                nf[1] -= double(st[e].uy) * tr + ty;
+                nf[2] -= double(st[e].uz) * tr + tz;
+            }
+        }
+    }
+}
+
+// =============================================================================================
+// Layer 1 tensor product.
+// Per edge the CTA first builds, for every path p, the coupling block
+//     Z_p[m, m2] = sum_{m1} C^{l m}_{l1 m1, l2 m2} Y_ij[l1 m1]         (channel-independent)
+// and then every channel does
+//     Phi1[i, (l m e_p), k] += R1_p(r_ij)[k] * sum_{m2} Z_p[m, m2] H1[j, (l2 m2), k].
+// This equals the reference's two-step form (Phi1r, then the Clebsch-Gordan COO contraction,
+// mace.cpp:453-502) with the sums reordered; Phi1r is never formed.
+// =============================================================================================
+template <typename T>
+struct TPArgs {
+    int N, K;
+    const int* node_types; const long long* first_neigh; const int* neigh_indices; const int* neigh_types;
+    const double* xyz; const double* r;
+    const T* coef1; SplineMeta sm;
+    const int* z_ptr; const int* z_lm1; const T* z_c;   // coupling entries per block entry
+    const T* H;             // sender features [rows][nLM][K]
+    T* Phi1;                // forward output [N][Q][K]
+    const T* dPhi1;         // reverse input  [N][Q][K]
+    T* Hmsg;                // reverse output [num_edges][nLM][K]: adjoint message of each edge to its sender
+    double* node_forces;    // reverse: accumulated into
+};
+
+template <typename T, int LF>
+__global__ void __launch_bounds__(kChannelBlock) tp_forward_kernel(const TPArgs<T> a) {
+    constexpr TPTable tp = make_tp_table(LF);
+    constexpr int kEdgeBatch = tp_edge_batch(LF);
+    __shared__ EdgeStage<T> st[kEdgeBatch];
+    __shared__ T Z[kEdgeBatch][tp.NZ];
+    const int F = tp.P * a.K;
+    for (int i = blockIdx.x; i < a.N; i += gridDim.x)
+    for (int kc = 0; kc < a.K; kc += blockDim.x) {
+        const int k = kc + threadIdx.x;
+        const bool active = k < a.K;
+        const long long e_begin = a.first_neigh[i], e_end = a.first_neigh[i + 1];
+        const int type_i = a.node_types[i];
+        T acc[tp.Q];
+#pragma unroll
+        for (int q = 0; q < tp.Q; ++q) acc[q] = T(0);
+        for (long long e0 = e_begin; e0 < e_end; e0 += kEdgeBatch) {
+            const int nb = static_cast<int>(e_end - e0 < kEdgeBatch ? e_end - e0 : kEdgeBatch);
+            __syncthreads();
+            if (threadIdx.x < nb)
+                stage_edge<T, false>(st[threadIdx.x], e0 + threadIdx.x, type_i, a.neigh_indices, a.neigh_types, a.xyz, a.r, a.sm, F);
+            __syncthreads();
+            for (int w = threadIdx.x; w < nb * tp.NZ; w += blockDim.x) {
+                const int e = w / tp.NZ, z = w - e * tp.NZ;
+                T v = 0;
+                for (int n = a.z_ptr[z]; n < a.z_ptr[z + 1]; ++n) v += a.z_c[n] * st[e].Y[a.z_lm1[n]];
+                Z[e][z] = v;
+            }
+            __syncthreads();
+            if (active) {
+                for (int e = 0; e < nb; ++e) {
+                    const EdgeStage<T>& s = st[e];
+                    const T x = s.x;
+                    const T* cb = a.coef1 + s.coef_base + 4 * k;
+                    const T* hrow = a.H + static_cast<size_t>(s.j) * tp.nLM * a.K + k;
+                    T h[tp.nLM];
+#pragma unroll
+                    for (int lm2 = 0; lm2 < tp.nLM; ++lm2) h[lm2] = __ldg(hrow + static_cast<size_t>(lm2) * a.K);
+                    const T* zrow = Z[e];
+                    static_for<tp.P>([&](auto pc) {
+                        constexpr int p = decltype(pc)::value;
+                        constexpr int l = TPConst<LF>::t.l[p], l2 = TPConst<LF>::t.l2[p], n2 = 2 * l2 + 1, zo = TPConst<LF>::t.zoff[p];
+                        const Vec4<T> c = load4<T>(cb + 4 * p * a.K);
+                        const T R = c.x + x * (c.y + x * (c.z + x * c.w));
+                        static_for<2 * l + 1>([&](auto mc) {
+                            constexpr int m = decltype(mc)::value;
+                            T tmp = 0;
+                            static_for<n2>([&](auto m2c) {
+                                constexpr int m2 = decltype(m2c)::value;
+                                tmp += zrow[zo + m * n2 + m2] * h[l2 * l2 + m2];
+                            });
+                            acc[TPConst<LF>::t.lme(p, m)] += R * tmp;
+                        });
+                    });
+                }
+            }
+        }
+        if (active) {
+            T* out = a.Phi1 + static_cast<size_t>(i) * tp.Q * a.K + k;
+#pragma unroll
+            for (int q = 0; q < tp.Q; ++q) out[static_cast<size_t>(q) * a.K] = acc[q];
+        }
+    }
+}
+
+// Reverse of the tensor product (MACE::reverse_Phi1, mace.cpp:504-605) for one receiver per CTA:
+//   message to the sender   Hmsg[ij, (l2 m2), k] = sum_p R1_p[k] sum_m Z_p[m, m2] dPhi1[i, (l m e_p), k]
+//   partial force           nf[ij] -= xhat * sum_{p,k} R1_p'[k] q_p[k] + sum_{p,k} R1_p[k] q^c_p[k]
+// with q_p = sum_{m,m2} Z_p[m,m2] dPhi1 H1_j and q^c_p the same with Z built from d Y / d xyz_c.
+template <typename T, int LF>
+__global__ void __launch_bounds__(kChannelBlock) tp_reverse_kernel(const TPArgs<T> a) {
+    constexpr TPTable tp = make_tp_table(LF);
+    constexpr int kEdgeBatch = tp_edge_batch(LF);
+    __shared__ EdgeStage<T> st[kEdgeBatch];
+    __shared__ Vec4<T> Z4[kEdgeBatch][tp.NZ];     // {Z, Zx, Zy, Zz}
+    __shared__ T red[kMaxWarps][kEdgeBatch][4];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    const int F = tp.P * a.K;
+    for (int i = blockIdx.x; i < a.N; i += gridDim.x)
+    for (int kc = 0; kc < a.K; kc += blockDim.x) {
+        const int k = kc + threadIdx.x;
+        const bool active = k < a.K;
+        const long long e_begin = a.first_neigh[i], e_end = a.first_neigh[i + 1];
+        const int type_i = a.node_types[i];
+        T d[tp.Q];
+#pragma unroll
+        for (int q = 0; q < tp.Q; ++q)
+            d[q] = active ? a.dPhi1[(static_cast<size_t>(i) * tp.Q + q) * a.K + k] : T(0);
+        for (long long e0 = e_begin; e0 < e_end; e0 += kEdgeBatch) {
+            const int nb = static_cast<int>(e_end - e0 < kEdgeBatch ? e_end - e0 : kEdgeBatch);
+            __syncthreads();
+            if (threadIdx.x < nb)
+                stage_edge<T, true>(st[threadIdx.x], e0 + threadIdx.x, type_i, a.neigh_indices, a.neigh_types, a.xyz, a.r, a.sm, F);
+            __syncthreads();
+            for (int w = threadIdx.x; w < nb * tp.NZ; w += blockDim.x) {
+                const int e = w / tp.NZ, z = w - e * tp.NZ;
+                T v = 0, vx = 0, vy = 0, vz = 0;
+                for (int n = a.z_ptr[z]; n < a.z_ptr[z + 1]; ++n) {
+                    const T c = a.z_c[n];
+                    const int lm1 = a.z_lm1[n];
+                    v += c * st[e].Y[lm1]; vx += c * st[e].dY[0][lm1]; vy += c * st[e].dY[1][lm1]; vz += c * st[e].dY[2][lm1];
+                }
+                Z4[e][z] = {v, vx, vy, vz};
+            }
+            __syncthreads();
+            for (int e = 0; e < nb; ++e) {
+                const EdgeStage<T>& s = st[e];
+                T fr = 0, fx = 0, fy = 0, fz = 0;
+                if (active) {
+                    const T x = s.x;
+                    const T* cb = a.coef1 + s.coef_base + 4 * k;
+                    const T* hrow = a.H + static_cast<size_t>(s.j) * tp.nLM * a.K + k;
+                    T h[tp.nLM], msg[tp.nLM];
+#pragma unroll
+                    for (int lm2 = 0; lm2 < tp.nLM; ++lm2) { h[lm2] = __ldg(hrow + static_cast<size_t>(lm2) * a.K); msg[lm2] = T(0); }
+                    const Vec4<T>* zrow = Z4[e];
+                    static_for<tp.P>([&](auto pc) {
+                        constexpr int p = decltype(pc)::value;
+                        constexpr int l = TPConst<LF>::t.l[p], l2 = TPConst<LF>::t.l2[p], n2 = 2 * l2 + 1, zo = TPConst<LF>::t.zoff[p];
+                        const Vec4<T> c = load4<T>(cb + 4 * p * a.K);
+                        const T R = c.x + x * (c.y + x * (c.z + x * c.w));
+                        const T Rd = c.y + x * (T(2) * c.z + T(3) * x * c.w);
+                        T q = 0, qx = 0, qy = 0, qz = 0;
+                        static_for<n2>([&](auto m2c) {
+                            constexpr int m2 = decltype(m2c)::value;
+                            T u = 0, ux = 0, uy = 0, uz = 0;
+                            static_for<2 * l + 1>([&](auto mc) {
+                                constexpr int m = decltype(mc)::value;
+                                const Vec4<T> zz = zrow[zo + m * n2 + m2];
+                                const T dv = d[TPConst<LF>::t.lme(p, m)];
+                                u += zz.x * dv; ux += zz.y * dv; uy += zz.z * dv; uz += zz.w * dv;
+                            });
+                            const T hv = h[l2 * l2 + m2];
+                            msg[l2 * l2 + m2] += R * u;
+                            q += hv * u; qx += hv * ux; qy += hv * uy; qz += hv * uz;
+                        });
+                        fr += Rd * q; fx += R * qx; fy += R * qy; fz += R * qz;
+                    });
+                    T* mrow = a.Hmsg + static_cast<size_t>(e0 + e) * tp.nLM * a.K + k;
+#pragma unroll
+                    for (int lm2 = 0; lm2 < tp.nLM; ++lm2) mrow[static_cast<size_t>(lm2) * a.K] = msg[lm2];
+                }
+                fr = warp_sum(fr); fx = warp_sum(fx); fy = warp_sum(fy); fz = warp_sum(fz);
+                if (lane == 0) { red[warp][e][0] = fr; red[warp][e][1] = fx; red[warp][e][2] = fy; red[warp][e][3] = fz; }
+            }
+            __syncthreads();
+            if (threadIdx.x < nb) {
+                const int e = threadIdx.x;
+                double tr = 0, tx = 0, ty = 0, tz = 0;
+                for (int w = 0; w < nwarps; ++w) { tr += red[w][e][0]; tx += red[w][e][1]; ty += red[w][e][2]; tz += red[w][e][3]; }
+                double* nf = a.node_forces + 3 * (e0 + e);
+                nf[0] -= double(st[e].ux) * tr + tx;
+                nf[1] -= double(st[e].uy) * tr + ty;
+                nf[2] -= double(st[e].uz) * tr + tz;
+            }
+        }
+    }
+}
+
+// Sum of the adjoint messages of all edges that have row j as their sender, in the fixed order
+// of the sender-sorted edge list (deterministic; takes the place of the atomic scatter the
+// reference's device code uses, mace_kokkos.cpp:1008-1010):
+//   H_adj[j, :, :] += sum_{e in in_edges(j)} Hmsg[e, :, :]
+template <typename T>
+__global__ void sender_gather_kernel(int rows, int width, const long long* __restrict__ in_ptr,
+                                     const int* __restrict__ in_edge, const T* __restrict__ Hmsg, T* __restrict__ H_adj) {
+    for (int j = blockIdx.x; j < rows; j += gridDim.x) {
+        const long long b = in_ptr[j], e = in_ptr[j + 1];
+        for (int c = threadIdx.x; c < width; c += blockDim.x) {
+            T acc = 0;
+            for (long long n = b; n < e; ++n) acc += Hmsg[static_cast<size_t>(in_edge[n]) * width + c];
+            H_adj[static_cast<size_t>(j) * width + c] += acc;
+        }
+    }
+}
+
+// =============================================================================================
+// Symmetric contraction (MACE::compute_M0 / compute_M1, mace.cpp:348-370,759-777, and their
+// reverses :372-395,779-794). One thread per (node, channel) walks the nested Horner program of
+// each output component; the 16 inputs of the thread live in shared memory, [variable][thread].
+// =============================================================================================
+template <typename T>
+struct PolyArgs {
+    int N, K;
+    int num_out;                 // output components (nLM for M0, 1 for M1)
+    int num_mono;                // monomial rows per element in `coef`
+    const int* node_types;
+    const int* prog;             // concatenated programs
+    const int* prog_off;         // [num_out] start of each program
+    const int* mono_off;         // [num_out] first coefficient row of each program
+    const T* coef;               // [E][num_mono][K]
+    const T* A;                  // [N][16][K]
+    T* M;                        // forward output [N][num_out][K]
+    const T* M_adj;              // reverse input  [N][num_out][K]
+    T* A_adj;                    // reverse output [N][16][K] (overwritten)
+};
+
+template <typename T>
+__global__ void poly_forward_kernel(const PolyArgs<T> a) {
+    extern __shared__ unsigned char smem_raw[];
+    T* As = reinterpret_cast<T*>(smem_raw);           // [16][blockDim.x]
+    const int nt = blockDim.x;
+    const long long total = static_cast<long long>(a.N) * a.K;
+    for (long long base = static_cast<long long>(blockIdx.x) * nt; base < total; base += static_cast<long long>(gridDim.x) * nt) {
+        const long long idx = base + threadIdx.x;
+        const bool active = idx < total;
+        const int i = active ? static_cast<int>(idx / a.K) : 0;
+        const int k = active ? static_cast<int>(idx - static_cast<long long>(i) * a.K) : 0;
+        if (active) {
+#pragma unroll
+            for (int q = 0; q < kNumLm; ++q) As[q * nt + threadIdx.x] = a.A[(static_cast<size_t>(i) * kNumLm + q) * a.K + k];
+        }
+        if (active) {
+            const T* cf = a.coef + static_cast<size_t>(a.node_types[i]) * a.num_mono * a.K + k;
+            for (int o = 0; o < a.num_out; ++o) {
+                const int* w = a.prog + a.prog_off[o];
+                const T* c = cf + static_cast<size_t>(a.mono_off[o]) * a.K;
+                int pc = 0;
+                const int n1 = w[pc++];
+                T total_v = 0;
+                for (int g1 = 0; g1 < n1; ++g1) {
+                    const int q1 = w[pc], mu1 = w[pc + 1], n2 = w[pc + 2];
+                    pc += 3;
+                    T s1 = mu1 >= 0 ? c[static_cast<size_t>(mu1) * a.K] : T(0);
+                    for (int g2 = 0; g2 < n2; ++g2) {
+                        const int q2 = w[pc], mu2 = w[pc + 1], n3 = w[pc + 2];
+                        pc += 3;
+                        T s2 = mu2 >= 0 ? c[static_cast<size_t>(mu2) * a.K] : T(0);
+                        for (int g3 = 0; g3 < n3; ++g3) {
+                            s2 += c[static_cast<size_t>(w[pc + 1]) * a.K] * As[w[pc] * nt + threadIdx.x];
+                            pc += 2;
+                        }
+                        s1 += s2 * As[q2 * nt + threadIdx.x];
+                    }
+                    total_v += s1 * As[q1 * nt + threadIdx.x];
+                }
+                a.M[(static_cast<size_t>(i) * a.num_out + o) * a.K + k] = total_v;
+            }
+        }
+    }
+}
+
+template <typename T>
+__global__ void poly_reverse_kernel(const PolyArgs<T> a) {
+    extern __shared__ unsigned char smem_raw[];
+    const int nt = blockDim.x;
+    T* As = reinterpret_cast<T*>(smem_raw);           // [16][nt]
+    T* Gs = As + kNumLm * nt;                         // [16][nt] gradient accumulators
+    const long long total = static_cast<long long>(a.N) * a.K;
+    for (long long base = static_cast<long long>(blockIdx.x) * nt; base < total; base += static_cast<long long>(gridDim.x) * nt) {
+        const long long idx = base + threadIdx.x;
+        if (idx >= total) continue;
+        const int i = static_cast<int>(idx / a.K);
+        const int k = static_cast<int>(idx - static_cast<long long>(i) * a.K);
+        const int t = threadIdx.x;
+#pragma unroll
+        for (int q = 0; q < kNumLm; ++q) {
+            As[q * nt + t] = a.A[(static_cast<size_t>(i) * kNumLm + q) * a.K + k];
+            Gs[q * nt + t] = T(0);
+        }
+        const T* cf = a.coef + static_cast<size_t>(a.node_types[i]) * a.num_mono * a.K + k;
+        for (int o = 0; o < a.num_out; ++o) {
+            const T seed = a.M_adj[(static_cast<size_t>(i) * a.num_out + o) * a.K + k];
+            const int* w = a.prog + a.prog_off[o];
+            const T* c = cf + static_cast<size_t>(a.mono_off[o]) * a.K;
+            int pc = 0;
+            const int n1 = w[pc++];
+            for (int g1 = 0; g1 < n1; ++g1) {
+                const int q1 = w[pc], mu1 = w[pc + 1], n2 = w[pc + 2];
+                pc += 3;
+                const T a1 = As[q1 * nt + t];
+                T s1 = mu1 >= 0 ? c[static_cast<size_t>(mu1) * a.K] : T(0);
+                const T adj1 = seed * a1;                       // adjoint of the q1 bracket
+                for (int g2 = 0; g2 < n2; ++g2) {
+                    const int q2 = w[pc], mu2 = w[pc + 1], n3 = w[pc + 2];
+                    pc += 3;
+                    const T a2 = As[q2 * nt + t];
+                    T s2 = mu2 >= 0 ? c[static_cast<size_t>(mu2) * a.K] : T(0);
+                    const T adj2 = adj1 * a2;                   // adjoint of the (q1, q2) bracket
+                    for (int g3 = 0; g3 < n3; ++g3) {
+                        const T c3 = c[static_cast<size_t>(w[pc + 1]) * a.K];
+                        const int q3 = w[pc];
+                        s2 += c3 * As[q3 * nt + t];
+                        Gs[q3 * nt + t] += adj2 * c3;
+                        pc += 2;
+                    }
+                    Gs[q2 * nt + t] += adj1 * s2;
+                    s1 += s2 * a2;
+                }
+                Gs[q1 * nt + t] += seed * s1;
+            }
+        }
+#pragma unroll
+        for (int q = 0; q < kNumLm; ++q) a.A_adj[(static_cast<size_t>(i) * kNumLm + q) * a.K + k] = Gs[q * nt + t];
+    }
+}
+
+// =============================================================================================
+// Channel-mixing linears as row-gathered GEMMs: C[row, :] (+)= A[row, :] . B  (or . B^T).
+// A row of a problem is addressed as (node, sub): node = perm ? perm[seg_begin + r / sub_count]
+// : r / sub_count, sub = r % sub_count, at A + node*a_node_stride + a_off + sub*a_sub_stride.
+// One problem list entry per (element type, degree l) block; blockIdx.z selects the problem.
+// Covers the dgemm/dgemv calls of compute_A0/H1/A1/H2 and their reverses (mace.cpp:184-198,
+// 406-420, 623-637, 804-830 and :215-229, 434-448, 659-674, 846-872).
+// =============================================================================================
+template <typename T>
+struct GemmProblem {
+    const T* A; T* C; const T* B;
+    const int* perm;         // optional node permutation (nodes sorted by element type)
+    const int* seg;          // optional device array of segment offsets into perm
+    int seg_index;           // this problem covers perm[seg[seg_index] .. seg[seg_index + 1])
+    int num_nodes;           // used when seg == nullptr
+    int sub_count;           // rows per node
+    long long a_node_stride, a_off, a_sub_stride;
+    long long c_node_stride, c_off, c_sub_stride;
+    int Kd, Nc;              // inner dimension, output columns
+    int ldb;                 // leading dimension of B
+    int transB;              // 0: B is [Kd][Nc]; 1: B is [Nc][Kd] and used transposed
+    int accumulate;          // 0: C = A.B ; 1: C += A.B
+};
+
+constexpr int kGemmBM = 64, kGemmBN = 64, kGemmBK = 16;
+
+template <typename T>
+__global__ void __launch_bounds__(256) gemm_rows_kernel(const GemmProblem<T>* __restrict__ problems) {
+    const GemmProblem<T> pb = problems[blockIdx.z];
+    int node_begin = 0, node_count = pb.num_nodes;
+    if (pb.seg) { node_begin = pb.seg[pb.seg_index]; node_count = pb.seg[pb.seg_index + 1] - node_begin; }
+    const long long M = static_cast<long long>(node_count) * pb.sub_count;
+    const long long row0 = static_cast<long long>(blockIdx.x) * kGemmBM;
+    const int col0 = blockIdx.y * kGemmBN;
+    if (row0 >= M || col0 >= pb.Nc) return;
+
+    __shared__ T As[kGemmBK][kGemmBM + 1];
+    __shared__ T Bs[kGemmBK][kGemmBN + 1];
+    __shared__ long long a_base[kGemmBM];
+    __shared__ long long c_base[kGemmBM];
+    const int tid = threadIdx.x;
+    if (tid < kGemmBM) {
+        const long long r = row0 + tid;
+        if (r < M) {
+            const long long n = r / pb.sub_count;
+            const int sub = static_cast<int>(r - n * pb.sub_count);
+            const long long node = pb.perm ? pb.perm[node_begin + n] : (node_begin + n);
+            a_base[tid] = node * pb.a_node_stride + pb.a_off + sub * pb.a_sub_stride;
+            c_base[tid] = node * pb.c_node_stride + pb.c_off + sub * pb.c_sub_stride;
+        } else {
+            a_base[tid] = -1;
+            c_base[tid] = -1;
+        }
+    }
+    __syncthreads();
+    const int tx = tid & 15, ty = tid >> 4;     // 16 x 16 threads, 4 x 4 outputs each
+    T acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = T(0);
+
+    for (int k0 = 0; k0 < pb.Kd; k0 += kGemmBK) {
+        // A tile: 64 rows x 16 k; thread loads 4 elements (coalesced along k within a row)
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+            const int lin = tid + it * 256;
+            const int rr = lin >> 4, kk = lin & 15;
+            T v = T(0);
+            if (a_base[rr] >= 0 && k0 + kk < pb.Kd) v = pb.A[a_base[rr] + k0 + kk];
+            As[kk][rr] = v;
+        }
+        // B tile: 16 k x 64 cols
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+            const int lin = tid + it * 256;
+            T v = T(0);
+            if (!pb.transB) {
+                const int kk = lin >> 6, cc = lin & 63;
+                if (k0 + kk < pb.Kd && col0 + cc < pb.Nc) v = pb.B[static_cast<size_t>(k0 + kk) * pb.ldb + col0 + cc];
+                Bs[kk][cc] = v;
+            } else {
+                const int cc = lin >> 4, kk = lin & 15;
+                if (k0 + kk < pb.Kd && col0 + cc < pb.Nc) v = pb.B[static_cast<size_t>(col0 + cc) * pb.ldb + k0 + kk];
+                Bs[kk][cc] = v;
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < kGemmBK; ++kk) {
+            T av[4], bv[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) av[i] = As[kk][ty * 4 + i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) bv[j] = Bs[kk][tx + 16 * j];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] += av[i] * bv[j];
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const long long cb = c_base[ty * 4 + i];
+        if (cb < 0) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int col = col0 + tx + 16 * j;
+            if (col < pb.Nc) {
+                T* dst = pb.C + cb + col;
+                *dst = pb.accumulate ? (*dst + acc[i][j]) : acc[i][j];
+            }
+        }
+    }
+}
+
+// =============================================================================================
+// Readouts (MACE::compute_readouts, mace.cpp:876-903 with MultilayerPerceptron::evaluate_gradient,
+// multilayer_perceptron.cpp:76-150, hidden width 16): one warp per node.
+//   E_i += E0[a] + w1 . H1[i,0,:] + w2 . (s * silu(W1 H2[i]))
+//   H1_adj[i,0,:] = w1 ;  H2_adj[i,:] = W1^T (w2 * s * silu'(W1 H2[i]))
+// H1_adj must have been zero-filled by the caller (the reference zero-fills it here).
+// =============================================================================================
+template <typename T>
+struct ReadoutArgs {
+    int N, K, nLM;
+    const int* node_types;
+    const double* E0;
+    const T* ro1; const T* W1; const T* w2; T scale;
+    const T* H1; const T* H2;
+    double* node_energies;
+    T* H1_adj; T* H2_adj;
+};
+
+template <typename T>
+__global__ void readout_kernel(const ReadoutArgs<T> a) {
+    const int lane = threadIdx.x & 31;
+    const int warp_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int warps_total = (gridDim.x * blockDim.x) >> 5;
+    for (int i = warp_global; i < a.N; i += warps_total) {
+        const T* h1 = a.H1 + static_cast<size_t>(i) * a.nLM * a.K;
+        const T* h2 = a.H2 + static_cast<size_t>(i) * a.K;
+        T lin = 0;
+        T z[16];
+#pragma unroll
+        for (int h = 0; h < 16; ++h) z[h] = 0;
+        for (int k = lane; k < a.K; k += 32) {
+            lin += a.ro1[k] * h1[k];
+            a.H1_adj[static_cast<size_t>(i) * a.nLM * a.K + k] = a.ro1[k];
+            const T v = h2[k];
+#pragma unroll
+            for (int h = 0; h < 16; ++h) z[h] += a.W1[h * a.K + k] * v;
+        }
+        lin = warp_sum(lin);
+        T e2 = 0;
+        T g[16];
+#pragma unroll
+        for (int h = 0; h < 16; ++h) {
+            const T zz = warp_sum(z[h]);
+            const T sig = T(1) / (T(1) + exp(-zz));
+            e2 += a.w2[h] * (a.scale * zz * sig);
+            g[h] = a.w2[h] * (a.scale * sig + a.scale * zz * sig * (T(1) - sig));
+        }
+        if (lane == 0) a.node_energies[i] += a.E0[a.node_types[i]] + double(lin) + double(e2);
+        for (int k = lane; k < a.K; k += 32) {
+            T s = 0;
+#pragma unroll
+            for (int h = 0; h < 16; ++h) s += g[h] * a.W1[h * a.K + k];
+            a.H2_adj[static_cast<size_t>(i) * a.K + k] = s;
+        }
+    }
+}
+
+// =============================================================================================
+// Small helpers
+// =============================================================================================
+__global__ void iota_kernel(int n, int* out) {
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) out[i] = i;
+}
+
+// offsets[v] = first position in the sorted key array with key >= v, for v = 0..num_values
+__global__ void segment_offsets_kernel(long long n, const int* __restrict__ sorted_keys, int num_values, long long* __restrict__ offsets) {
+    for (int v = blockIdx.x * blockDim.x + threadIdx.x; v <= num_values; v += gridDim.x * blockDim.x) {
+        long long lo = 0, hi = n;
+        while (lo < hi) {
+            const long long mid = (lo + hi) >> 1;
+            if (sorted_keys[mid] < v) lo = mid + 1; else hi = mid;
+        }
+        offsets[v] = lo;
+    }
+}
+__global__ void segment_offsets_int_kernel(int n, const int* __restrict__ sorted_keys, int num_values, int* __restrict__ offsets) {
+    for (int v = blockIdx.x * blockDim.x + threadIdx.x; v <= num_values; v += gridDim.x * blockDim.x) {
+        int lo = 0, hi = n;
+        while (lo < hi) {
+            const int mid = (lo + hi) >> 1;
+            if (sorted_keys[mid] < v) lo = mid + 1; else hi = mid;
+        }
+        offsets[v] = lo;
+    }
+}
+
+template <typename S, typename D>
+__global__ void convert_kernel(long long n, const S* __restrict__ src, D* __restrict__ dst) {
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n; i += static_cast<long long>(gridDim.x) * blockDim.x)
+        dst[i] = static_cast<D>(src[i]);
+}
+
+// Per-atom forces from per-edge partial forces, without atomics:
+//   f[i] = - sum_{e in row i} nf[e] + sum_{e in in_edges(i)} nf[e]
+// (pair_symmetrix/pair_symmetrix_mace.cpp:334-347; symmetrix_calc.py:93-97)
+__global__ void atom_forces_kernel(int rows, int N, const long long* __restrict__ first_neigh, const long long* __restrict__ in_ptr,
+                                   const int* __restrict__ in_edge, const double* __restrict__ nf, double* __restrict__ f) {
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < rows; i += gridDim.x * blockDim.x) {
+        double fx = 0, fy = 0, fz = 0;
+        if (i < N)
+            for (long long e = first_neigh[i]; e < first_neigh[i + 1]; ++e) { fx -= nf[3 * e]; fy -= nf[3 * e + 1]; fz -= nf[3 * e + 2]; }
+        for (long long n = in_ptr[i]; n < in_ptr[i + 1]; ++n) {
+            const long long e = in_edge[n];
+            fx += nf[3 * e]; fy += nf[3 * e + 1]; fz += nf[3 * e + 2];
+        }
+        f[3 * i] = fx; f[3 * i + 1] = fy; f[3 * i + 2] = fz;
+    }
+}
+
+// Block-wise partial sums of {energy, virial xx yy zz xy xz yz}; partials[block][7].
+// Virial convention of pair_symmetrix_mace.cpp:349-368.
+__global__ void energy_virial_partial_kernel(int N, long long E, const double* __restrict__ node_energies, const double* __restrict__ xyz,
+                                             const double* __restrict__ nf, double* __restrict__ partials) {
+    __shared__ double sh[7][256];
+    double v[7] = {0, 0, 0, 0, 0, 0, 0};
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < N; i += stride) v[0] += node_energies[i];
+    for (long long e = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; e < E; e += stride) {
+        const double x = xyz[3 * e], y = xyz[3 * e + 1], z = xyz[3 * e + 2];
+        const double fx = nf[3 * e], fy = nf[3 * e + 1], fz = nf[3 * e + 2];
+        v[1] += x * fx; v[2] += y * fy; v[3] += z * fz;
+        v[4] += 0.5 * (x * fy + y * fx); v[5] += 0.5 * (x * fz + z * fx); v[6] += 0.5 * (y * fz + z * fy);
+    }
+    for (int c = 0; c < 7; ++c) sh[c][threadIdx.x] = v[c];
+    __syncthreads();
+    for (int s = blockDim.x >> 1; s > 0; s >>= 1) {
+        if (threadIdx.x < s)
+            for (int c = 0; c < 7; ++c) sh[c][threadIdx.x] += sh[c][threadIdx.x + s];
+        __syncthreads();
+    }
+    if (threadIdx.x < 7) partials[blockIdx.x * 7 + threadIdx.x] = sh[threadIdx.x][0];
+}
+__global__ void energy_virial_final_kernel(int num_blocks, const double* __restrict__ partials, double* __restrict__ out7) {
+    if (threadIdx.x < 7) {
+        double s = 0;
+        for (int b = 0; b < num_blocks; ++b) s += partials[b * 7 + threadIdx.x];
+        out7[threadIdx.x] = s;
+    }
+}
+
+}  // namespace smx

@@ -1,0 +1,362 @@
+// Host-side model: reads a symmetrix JSON model file and prepares the tables the kernels use.
+// Replaces MACE::load_from_json (libsymmetrix/source/mace.cpp:905-1030; device twin
+// mace_kokkos.cpp:1544-1887). Everything is kept in double here; the evaluator casts to its
+// arithmetic type when uploading.
+#pragma once
+
+#include <algorithm>
+#include <array>
+#include <cmath>
+#include <fstream>
+#include <limits>
+#include <map>
+#include <sstream>
+#include <string>
+#include <vector>
+
+#include "json_min.hpp"
+#include "tp_tables.hpp"
+
+namespace smx {
+
+struct ModelError : std::runtime_error {
+    using std::runtime_error::runtime_error;
+};
+struct UnsupportedError : std::runtime_error {
+    using std::runtime_error::runtime_error;
+};
+
+// A sparse polynomial of degree <= 3 in the 16 variables A[i, :, k], shared by all channels and
+// element types (which only change the coefficients), compiled to a nested Horner program:
+//   P = sum_q1 A[q1] (c1 + sum_{q2} A[q2] (c2 + sum_{q3} c3 A[q3]))
+// Word stream: [n1] then per q1 group [q1, mu1, n2], per q2 group [q2, mu2, n3], per leaf [q3, mu3];
+// mu is the row of the coefficient in the model's monomial order (-1: no such monomial).
+// Takes the place of the product DAG the reference builds per (element, LM, channel)
+// (libsymmetrix/source/multivariate_polynomial.cpp:10-101).
+struct PolyProgram {
+    std::vector<int> words;
+    int num_monomials = 0;
+    int num_leaves = 0, num_pairs = 0;
+};
+
+inline PolyProgram compile_polynomial(const std::vector<std::vector<int>>& monomials, int num_vars) {
+    struct Pair { int mu = -1; std::vector<std::pair<int, int>> leaves; };
+    struct Head { int mu = -1; std::map<int, Pair> pairs; };
+    std::map<int, Head> heads;
+    for (size_t mu = 0; mu < monomials.size(); ++mu) {
+        std::vector<int> m = monomials[mu];
+        std::sort(m.begin(), m.end());
+        if (m.empty() || m.size() > 3) throw UnsupportedError("symmetric contraction: monomial degree must be 1..3");
+        for (int q : m)
+            if (q < 0 || q >= num_vars) throw ModelError("symmetric contraction: variable index out of range");
+        Head& h = heads[m[0]];
+        if (m.size() == 1) { if (h.mu < 0) h.mu = static_cast<int>(mu); continue; }
+        Pair& p = h.pairs[m[1]];
+        if (m.size() == 2) { if (p.mu < 0) p.mu = static_cast<int>(mu); continue; }
+        bool dup = false;
+        for (auto& lf : p.leaves) dup = dup || (lf.first == m[2]);
+        if (!dup) p.leaves.emplace_back(m[2], static_cast<int>(mu));
+    }
+    PolyProgram prog;
+    prog.num_monomials = static_cast<int>(monomials.size());
+    prog.words.push_back(static_cast<int>(heads.size()));
+    for (auto& [q1, h] : heads) {
+        prog.words.push_back(q1);
+        prog.words.push_back(h.mu);
+        prog.words.push_back(static_cast<int>(h.pairs.size()));
+        for (auto& [q2, p] : h.pairs) {
+            prog.words.push_back(q2);
+            prog.words.push_back(p.mu);
+            prog.words.push_back(static_cast<int>(p.leaves.size()));
+            prog.num_pairs += 1;
+            for (auto& lf : p.leaves) {
+                prog.words.push_back(lf.first);
+                prog.words.push_back(lf.second);
+                prog.num_leaves += 1;
+            }
+        }
+    }
+    return prog;
+}
+
+struct HostModel {
+    // basic information (mace.hpp:18-25)
+    int num_elements = 0, K = 0, l_max = 0, L_max = 0, num_lm = 0, num_LM = 0;
+    double r_cut = 0.0;
+    std::vector<int> atomic_numbers;
+    std::vector<double> atomic_energies;
+    bool has_zbl = false;
+
+    // radial splines: coefficient tables [pair][bin][function][4] (cubic_spline_set.cpp:5-25)
+    double spline_h = 0.0;
+    int num_bins = 0;                // G - 1
+    int num_pairs = 0;               // E (E + 1) / 2 unordered pairs
+    int F0 = 0, F1 = 0;              // functions per pair: (l_max+1) K and P K
+    std::vector<double> coef0, coef1;
+
+    std::vector<double> H0_w;        // [E][K]
+    std::vector<double> A0_w;        // [E][l_max+1][K][K]
+    std::vector<double> H1_w;        // [L_max+1][K][K]
+    std::vector<double> A1_w;        // concatenated per l: [n_e(l) K][K], path blocks in canonical order
+    std::array<long, kLmaxSH + 2> A1_w_off{};
+    std::vector<double> H2_w_H1;     // [E][K][K]
+    std::vector<double> H2_w_M1;     // [K][K]
+    std::vector<double> ro1;         // [K]
+    std::vector<double> ro2_w1;      // [16][K]
+    std::vector<double> ro2_w2;      // [16]
+    double ro2_scale = 1.0;
+
+    // tensor product: canonical table + coupling entries per (path block entry z): Z[z] = sum C * Y[lm1]
+    TPTable tp{};
+    std::vector<int> path_file_to_canon;   // index by the file's path number
+    std::vector<int> lme_file_to_canon;    // output slot permutation (identity for canonical files)
+    std::vector<int> z_ptr, z_lm1;
+    std::vector<double> z_c;
+
+    // symmetric contractions: programs per LM (M0) and one for M1; coefficients [element][monomial][K]
+    std::vector<PolyProgram> prog0;
+    std::vector<int> mono_off0;            // first monomial row of each LM in coef_M0
+    int num_mono0 = 0;
+    std::vector<double> coef_M0;
+    PolyProgram prog1;
+    int num_mono1 = 0;
+    std::vector<double> coef_M1;
+};
+
+namespace detail {
+
+inline std::vector<std::vector<int>> int_lists(const JsonValue& v) {
+    std::vector<std::vector<int>> out;
+    if (v.type == JsonValue::NumArray && v.nums.empty()) return out;
+    if (v.type != JsonValue::Array) throw ModelError("model file: expected a list of index lists");
+    for (const auto& row : v.arr) out.push_back(row.flat_int());
+    return out;
+}
+
+// Spline coefficients of one pair table: values/derivs [F][G] -> c[bin][F][4], formulas of
+// CubicSplineSet::CubicSplineSet (cubic_spline_set.cpp:13-24).
+inline void spline_coefficients(const JsonValue& values, const JsonValue& derivs, double h, int F, int G,
+                                const std::vector<int>& fn_map, double* c) {
+    if (static_cast<int>(values.size()) != F || static_cast<int>(derivs.size()) != F)
+        throw ModelError("model file: radial spline table has the wrong number of functions");
+    for (int f = 0; f < F; ++f) {
+        const auto& v = values.arr.empty() ? values : values.arr[f];
+        const auto& d = derivs.arr.empty() ? derivs : derivs.arr[f];
+        if (v.type != JsonValue::NumArray || d.type != JsonValue::NumArray ||
+            static_cast<int>(v.nums.size()) != G || static_cast<int>(d.nums.size()) != G)
+            throw ModelError("model file: radial spline table has ragged rows");
+        const int fo = fn_map.empty() ? f : fn_map[f];
+        for (int i = 0; i < G - 1; ++i) {
+            double* o = c + (static_cast<size_t>(i) * F + fo) * 4;
+            const double v0 = v.nums[i], v1 = v.nums[i + 1], d0 = d.nums[i], d1 = d.nums[i + 1];
+            o[0] = v0;
+            o[1] = d0;
+            o[2] = (-3 * v0 - 2 * h * d0 + 3 * v1 - h * d1) / (h * h);
+            o[3] = (2 * v0 + h * d0 - 2 * v1 + h * d1) / (h * h * h);
+        }
+    }
+}
+
+}  // namespace detail
+
+inline HostModel load_model_file(const std::string& filename) {
+    std::ifstream f(filename, std::ios::binary);
+    if (!f) throw ModelError("cannot open model file '" + filename + "'");
+    std::string text((std::istreambuf_iterator<char>(f)), std::istreambuf_iterator<char>());
+    JsonValue file = JsonParser(text.data(), text.data() + text.size()).parse();
+    text.clear();
+    text.shrink_to_fit();
+    if (file.type != JsonValue::Object) throw JsonError("[json] model file is not a JSON object");
+
+    HostModel m;
+    m.num_elements = file.at("num_elements").as_int();
+    m.K = file.at("num_channels").as_int();
+    m.r_cut = file.at("r_cut").as_double();
+    m.l_max = file.at("l_max").as_int();
+    m.L_max = file.at("L_max").as_int();
+    m.num_lm = (m.l_max + 1) * (m.l_max + 1);
+    m.num_LM = (m.L_max + 1) * (m.L_max + 1);
+    m.atomic_numbers = file.at("atomic_numbers").flat_int();
+    m.atomic_energies = file.at("atomic_energies").flat();
+    m.has_zbl = file.at("has_zbl").as_bool();
+    const int E = m.num_elements, K = m.K;
+    if (static_cast<int>(m.atomic_numbers.size()) != E || static_cast<int>(m.atomic_energies.size()) != E)
+        throw ModelError("model file: atomic_numbers / atomic_energies do not match num_elements");
+    if (m.l_max != kLmaxSH) throw UnsupportedError("only l_max == 3 is supported (as in the reference exporter)");
+    if (m.L_max < 0 || m.L_max > 2) throw UnsupportedError("hidden features up to L_max == 2 are supported");
+    if (K < 1 || K > 1024) throw UnsupportedError("num_channels must be in 1..1024");
+    if (m.has_zbl) throw UnsupportedError("ZBL pair repulsion is not covered by this build");
+    if (file.at("A0_scaled").as_bool() || file.at("A1_scaled").as_bool())
+        throw UnsupportedError("density-normalised interactions (A0_scaled / A1_scaled) are not covered by this build");
+
+    // ---- tensor-product paths: map the file's order onto the canonical table
+    m.tp = make_tp_table(m.L_max);
+    const std::vector<int> pl = file.at("Phi1_l").flat_int(), pl1 = file.at("Phi1_l1").flat_int(),
+                           pl2 = file.at("Phi1_l2").flat_int();
+    const int P = static_cast<int>(pl.size());
+    if (P != m.tp.P || pl1.size() != pl.size() || pl2.size() != pl.size())
+        throw UnsupportedError("tensor-product path list differs from the standard l_max=3 enumeration");
+    m.path_file_to_canon.assign(P, -1);
+    std::vector<int> file_e(P, 0), file_ne(kLmaxSH + 1, 0);
+    for (int p = 0; p < P; ++p) {
+        if (p > 0 && pl[p] < pl[p - 1]) throw ModelError("Phi1_l must be sorted by non-decreasing l");
+        if (pl[p] < 0 || pl[p] > kLmaxSH) throw ModelError("Phi1_l out of range");
+        file_e[p] = file_ne[pl[p]]++;
+        for (int c = 0; c < m.tp.P; ++c)
+            if (m.tp.l[c] == pl[p] && m.tp.l1[c] == pl1[p] && m.tp.l2[c] == pl2[p]) m.path_file_to_canon[p] = c;
+        if (m.path_file_to_canon[p] < 0) throw UnsupportedError("tensor-product path not in the standard enumeration");
+    }
+    {
+        std::vector<int> seen(P, 0);
+        for (int c : m.path_file_to_canon) seen[c] += 1;
+        for (int s : seen) if (s != 1) throw UnsupportedError("duplicate tensor-product path");
+    }
+    // file lme / t decoders
+    std::vector<int> file_lme_off(kLmaxSH + 2, 0), file_toff(P + 1, 0);
+    for (int l = 0; l <= kLmaxSH; ++l) file_lme_off[l + 1] = file_lme_off[l] + (2 * l + 1) * file_ne[l];
+    for (int p = 0; p < P; ++p) file_toff[p + 1] = file_toff[p] + (2 * pl1[p] + 1) * (2 * pl2[p] + 1);
+    m.lme_file_to_canon.assign(m.tp.Q, -1);
+    for (int p = 0; p < P; ++p) {
+        const int l = pl[p], c = m.path_file_to_canon[p];
+        for (int mm = 0; mm < 2 * l + 1; ++mm)
+            m.lme_file_to_canon[file_lme_off[l] + mm * file_ne[l] + file_e[p]] = m.tp.lme(c, mm);
+    }
+    {   // coupling entries grouped by block entry z
+        const std::vector<int> cg_lme = file.at("Phi1_lme").flat_int(), cg_t = file.at("Phi1_lelm1lm2").flat_int();
+        const std::vector<double> cg_c = file.at("Phi1_clebsch_gordan").flat();
+        if (cg_lme.size() != cg_c.size() || cg_t.size() != cg_c.size())
+            throw ModelError("model file: Clebsch-Gordan COO arrays differ in length");
+        std::vector<std::vector<std::pair<int, double>>> per_z(m.tp.NZ);
+        for (size_t n = 0; n < cg_c.size(); ++n) {
+            const int t = cg_t[n], lme = cg_lme[n];
+            if (t < 0 || t >= file_toff[P] || lme < 0 || lme >= m.tp.Q) throw ModelError("Clebsch-Gordan index out of range");
+            int p = 0;
+            while (t >= file_toff[p + 1]) ++p;
+            const int l = pl[p], l1 = pl1[p], l2 = pl2[p];
+            const int rem = t - file_toff[p];
+            const int i1 = rem / (2 * l2 + 1), i2 = rem % (2 * l2 + 1);
+            // the output slot must belong to the same path
+            const int rel = lme - file_lme_off[l];
+            if (rel < 0 || rel >= (2 * l + 1) * file_ne[l] || rel % file_ne[l] != file_e[p])
+                throw ModelError("Clebsch-Gordan entry couples a path to another path's output slot");
+            const int mm = rel / file_ne[l];
+            const int c = m.path_file_to_canon[p];
+            const int z = m.tp.zoff[c] + mm * (2 * l2 + 1) + i2;
+            per_z[z].emplace_back(l1 * l1 + i1, cg_c[n]);
+        }
+        m.z_ptr.push_back(0);
+        for (auto& lst : per_z) {
+            for (auto& en : lst) { m.z_lm1.push_back(en.first); m.z_c.push_back(en.second); }
+            m.z_ptr.push_back(static_cast<int>(m.z_lm1.size()));
+        }
+    }
+
+    // ---- radial splines
+    m.spline_h = file.at("radial_spline_h").as_double();
+    m.num_pairs = E * (E + 1) / 2;
+    m.F0 = (m.l_max + 1) * K;
+    m.F1 = P * K;
+    auto load_splines = [&](const char* vkey, const char* dkey, int F, const std::vector<int>& fn_map,
+                            std::vector<double>& out) {
+        const JsonValue& vals = file.at(vkey);
+        const JsonValue& ders = file.at(dkey);
+        if (static_cast<int>(vals.size()) != m.num_pairs || static_cast<int>(ders.size()) != m.num_pairs || vals.type != JsonValue::Array)
+            throw ModelError(std::string("model file: ") + vkey + " must have one table per unordered element pair");
+        const JsonValue& first = vals.arr[0];
+        if (first.type != JsonValue::Array || first.arr.empty()) throw ModelError("model file: empty radial spline table");
+        const int G = static_cast<int>(first.arr[0].size());
+        if (G < 2) throw ModelError("model file: radial splines need at least two nodes");
+        if (m.num_bins == 0) m.num_bins = G - 1;
+        if (m.num_bins != G - 1) throw ModelError("model file: radial spline tables differ in length");
+        out.assign(static_cast<size_t>(m.num_pairs) * (G - 1) * F * 4, 0.0);
+        for (int pr = 0; pr < m.num_pairs; ++pr)
+            detail::spline_coefficients(vals.arr[pr], ders.arr[pr], m.spline_h, F, G, fn_map,
+                                        out.data() + static_cast<size_t>(pr) * (G - 1) * F * 4);
+    };
+    load_splines("radial_spline_values_0", "radial_spline_derivs_0", m.F0, {}, m.coef0);
+    std::vector<int> fn_map(m.F1);
+    for (int p = 0; p < P; ++p)
+        for (int k = 0; k < K; ++k) fn_map[p * K + k] = m.path_file_to_canon[p] * K + k;
+    load_splines("radial_spline_values_1", "radial_spline_derivs_1", m.F1, fn_map, m.coef1);
+
+    // ---- dense weights
+    auto expect = [&](const std::vector<double>& v, size_t n, const char* key) {
+        if (v.size() != n) throw ModelError(std::string("model file: ") + key + " has the wrong size");
+    };
+    m.H0_w = file.at("H0_weights").flat();  expect(m.H0_w, size_t(E) * K, "H0_weights");
+    m.A0_w = file.at("A0_weights").flat();  expect(m.A0_w, size_t(E) * (m.l_max + 1) * K * K, "A0_weights");
+    m.H1_w = file.at("H1_weights").flat();  expect(m.H1_w, size_t(m.L_max + 1) * K * K, "H1_weights");
+    {
+        const JsonValue& a1 = file.at("A1_weights");
+        if (static_cast<int>(a1.size()) != m.l_max + 1) throw ModelError("model file: A1_weights needs one matrix per l");
+        long off = 0;
+        for (int l = 0; l <= m.l_max; ++l) {
+            std::vector<double> w = a1.arr.empty() ? std::vector<double>() : a1.arr[l].flat();
+            const int ne = m.tp.n_e[l];
+            expect(w, size_t(ne) * K * K, "A1_weights[l]");
+            m.A1_w_off[l] = off;
+            m.A1_w.resize(off + long(ne) * K * K);
+            // permute the e-blocks of rows from file order to canonical order
+            for (int p = 0; p < P; ++p) {
+                if (pl[p] != l) continue;
+                const int ec = m.tp.e[m.path_file_to_canon[p]];
+                std::copy(w.begin() + long(file_e[p]) * K * K, w.begin() + long(file_e[p] + 1) * K * K,
+                          m.A1_w.begin() + off + long(ec) * K * K);
+            }
+            off += long(ne) * K * K;
+        }
+        m.A1_w_off[m.l_max + 1] = off;
+    }
+    m.H2_w_H1 = file.at("H2_weights_for_H1").flat();  expect(m.H2_w_H1, size_t(E) * K * K, "H2_weights_for_H1");
+    m.H2_w_M1 = file.at("H2_weights_for_M1").flat();  expect(m.H2_w_M1, size_t(K) * K, "H2_weights_for_M1");
+    m.ro1 = file.at("readout_1_weights").flat();      expect(m.ro1, K, "readout_1_weights");
+    m.ro2_w1 = file.at("readout_2_weights_1").flat(); expect(m.ro2_w1, size_t(16) * K, "readout_2_weights_1");
+    m.ro2_w2 = file.at("readout_2_weights_2").flat(); expect(m.ro2_w2, 16, "readout_2_weights_2");
+    m.ro2_scale = file.at("readout_2_scale_factor").as_double();
+
+    // ---- symmetric contractions
+    {
+        const JsonValue& monos = file.at("M0_monomials");
+        const JsonValue& weights = file.at("M0_weights");
+        m.mono_off0.assign(m.num_LM + 1, 0);
+        for (int lm = 0; lm < m.num_LM; ++lm) {
+            auto lists = detail::int_lists(monos.at(std::to_string(lm)));
+            m.prog0.push_back(compile_polynomial(lists, m.num_lm));
+            m.mono_off0[lm + 1] = m.mono_off0[lm] + static_cast<int>(lists.size());
+        }
+        m.num_mono0 = m.mono_off0[m.num_LM];
+        m.coef_M0.assign(size_t(E) * m.num_mono0 * K, 0.0);
+        for (int a = 0; a < E; ++a) {
+            const JsonValue& wa = weights.at(std::to_string(a));
+            for (int lm = 0; lm < m.num_LM; ++lm) {
+                const JsonValue& wl = wa.at(std::to_string(lm));
+                const int nm = m.mono_off0[lm + 1] - m.mono_off0[lm];
+                for (int k = 0; k < K; ++k) {
+                    const JsonValue& wk = wl.at(std::to_string(k));
+                    if (static_cast<int>(wk.size()) != nm) throw ModelError("M0_weights row length differs from M0_monomials");
+                    for (int mu = 0; mu < nm; ++mu)
+                        m.coef_M0[(size_t(a) * m.num_mono0 + m.mono_off0[lm] + mu) * K + k] = wk.nums[mu];
+                }
+            }
+        }
+    }
+    {
+        auto lists = detail::int_lists(file.at("M1_monomials"));
+        m.prog1 = compile_polynomial(lists, m.num_lm);
+        m.num_mono1 = static_cast<int>(lists.size());
+        const JsonValue& weights = file.at("M1_weights");
+        m.coef_M1.assign(size_t(E) * m.num_mono1 * K, 0.0);
+        for (int a = 0; a < E; ++a) {
+            const JsonValue& wa = weights.at(std::to_string(a));
+            for (int k = 0; k < K; ++k) {
+                const JsonValue& wk = wa.at(std::to_string(k));
+                if (static_cast<int>(wk.size()) != m.num_mono1) throw ModelError("M1_weights row length differs from M1_monomials");
+                for (int mu = 0; mu < m.num_mono1; ++mu)
+                    m.coef_M1[(size_t(a) * m.num_mono1 + mu) * K + k] = wk.nums[mu];
+            }
+        }
+    }
+    return m;
+}
+
+}  // namespace smx

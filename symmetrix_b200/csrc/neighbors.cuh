@@ -1,0 +1,255 @@
+// Full periodic neighbour list on the device, written directly in the evaluator's CSR form.
+//
+// Edge rule (identical, operation for operation, to symmetrix_b200/structures.py::neighbor_list,
+// which restates what the reference's callers do, pair_symmetrix/pair_symmetrix_mace.cpp:249-315):
+//   p = x_j + ((n0*a0 + n1*a1) + n2*a2)        image position, float64, no fused multiply-add
+//   d = p - x_i
+//   keep iff (d0*d0 + d1*d1) + d2*d2 < r_cut*r_cut, excluding i == j with a zero shift
+// Rows are ordered by (sender index, shift code), so the list is a pure function of its inputs.
+// Candidates come from a uniform grid over fractional coordinates whose cells are at least
+// r_cut(1+1e-9) thick; positions are expected inside the cell (wrap them first).
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cmath>
+
+#include <cub/cub.cuh>
+
+#include "common.cuh"
+
+namespace smx {
+
+struct NeighGrid {
+    double cell[9];      // rows are lattice vectors
+    double inv[9];       // inverse of the cell matrix: frac = pos . inv
+    int nb[3];           // bins per axis
+    int reach[3];        // bins to search on each side
+    int pbc[3];
+    double rc2;
+};
+
+__device__ __forceinline__ int neigh_bin(const NeighGrid& g, const double* x, int* b3) {
+    int id = 0;
+#pragma unroll
+    for (int a = 0; a < 3; ++a) {
+        const double s = x[0] * g.inv[0 * 3 + a] + x[1] * g.inv[1 * 3 + a] + x[2] * g.inv[2 * 3 + a];
+        int b = static_cast<int>(floor(s * g.nb[a]));
+        b = b < 0 ? 0 : (b >= g.nb[a] ? g.nb[a] - 1 : b);
+        b3[a] = b;
+        id = id * g.nb[a] + b;
+    }
+    return id;
+}
+
+__global__ void neigh_bin_kernel(int n, const double* __restrict__ pos, NeighGrid g, int* __restrict__ bin_of) {
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        int b3[3];
+        bin_of[i] = neigh_bin(g, pos + 3 * i, b3);
+    }
+}
+
+// Exact edge test; returns true and fills d/r2 when image (j, n) of atom j is a neighbour of i.
+__device__ __forceinline__ bool neigh_test(const NeighGrid& g, const double* xi, const double* xj, int n0, int n1, int n2,
+                                           double* d, double* r2) {
+#pragma unroll
+    for (int c = 0; c < 3; ++c) {
+        const double sv = __dadd_rn(__dadd_rn(__dmul_rn(double(n0), g.cell[0 + c]), __dmul_rn(double(n1), g.cell[3 + c])),
+                                    __dmul_rn(double(n2), g.cell[6 + c]));
+        const double p = __dadd_rn(xj[c], sv);
+        d[c] = __dsub_rn(p, xi[c]);
+    }
+    *r2 = __dadd_rn(__dadd_rn(__dmul_rn(d[0], d[0]), __dmul_rn(d[1], d[1])), __dmul_rn(d[2], d[2]));
+    return *r2 < g.rc2;
+}
+
+__device__ __forceinline__ unsigned long long neigh_key(int j, int n0, int n1, int n2) {
+    const unsigned long long code = (static_cast<unsigned long long>(n0 + 64) * 128 + (n1 + 64)) * 128 + (n2 + 64);
+    return (static_cast<unsigned long long>(j) << 32) | code;
+}
+
+// One thread per receiver atom. COUNT: number of edges of the row. Otherwise: write the keys of
+// the row, sort them (rows are short), then expand each key into the edge arrays.
+template <bool COUNT>
+__global__ void neigh_rows_kernel(int n, const double* __restrict__ pos, const int* __restrict__ types, NeighGrid g,
+                                  const int* __restrict__ bin_start, const int* __restrict__ sorted_atoms,
+                                  int* __restrict__ num_neigh, const long long* __restrict__ first_neigh,
+                                  unsigned long long* __restrict__ keys, int* __restrict__ neigh_indices,
+                                  int* __restrict__ neigh_types, int* __restrict__ shifts, double* __restrict__ xyz,
+                                  double* __restrict__ r) {
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        const double xi[3] = {pos[3 * i], pos[3 * i + 1], pos[3 * i + 2]};
+        int b3[3];
+        neigh_bin(g, xi, b3);
+        long long out = COUNT ? 0 : first_neigh[i];
+        const long long row_begin = out;
+        int count = 0;
+        for (int o0 = -g.reach[0]; o0 <= g.reach[0]; ++o0) {
+            const int v0 = b3[0] + o0;
+            const int n0 = static_cast<int>(floor(double(v0) / g.nb[0]));
+            if (n0 != 0 && !g.pbc[0]) continue;
+            const int c0 = v0 - n0 * g.nb[0];
+            for (int o1 = -g.reach[1]; o1 <= g.reach[1]; ++o1) {
+                const int v1 = b3[1] + o1;
+                const int n1 = static_cast<int>(floor(double(v1) / g.nb[1]));
+                if (n1 != 0 && !g.pbc[1]) continue;
+                const int c1 = v1 - n1 * g.nb[1];
+                for (int o2 = -g.reach[2]; o2 <= g.reach[2]; ++o2) {
+                    const int v2 = b3[2] + o2;
+                    const int n2 = static_cast<int>(floor(double(v2) / g.nb[2]));
+                    if (n2 != 0 && !g.pbc[2]) continue;
+                    const int c2 = v2 - n2 * g.nb[2];
+                    const int bin = (c0 * g.nb[1] + c1) * g.nb[2] + c2;
+                    for (int s = bin_start[bin]; s < bin_start[bin + 1]; ++s) {
+                        const int j = sorted_atoms[s];
+                        if (j == i && n0 == 0 && n1 == 0 && n2 == 0) continue;
+                        double d[3], r2;
+                        if (neigh_test(g, xi, pos + 3 * j, n0, n1, n2, d, &r2)) {
+                            if (!COUNT) keys[out++] = neigh_key(j, n0, n1, n2);
+                            ++count;
+                        }
+                    }
+                }
+            }
+        }
+        if (COUNT) {
+            num_neigh[i] = count;
+        } else {
+            // insertion sort of the row's keys
+            for (long long a = row_begin + 1; a < out; ++a) {
+                const unsigned long long key = keys[a];
+                long long b = a - 1;
+                while (b >= row_begin && keys[b] > key) { keys[b + 1] = keys[b]; --b; }
+                keys[b + 1] = key;
+            }
+            for (long long e = row_begin; e < out; ++e) {
+                const unsigned long long key = keys[e];
+                const int j = static_cast<int>(key >> 32);
+                const unsigned int code = static_cast<unsigned int>(key & 0xffffffffu);
+                const int n2 = static_cast<int>(code % 128) - 64, n1 = static_cast<int>((code / 128) % 128) - 64,
+                          n0 = static_cast<int>(code / (128 * 128)) - 64;
+                double d[3], r2;
+                neigh_test(g, xi, pos + 3 * j, n0, n1, n2, d, &r2);
+                neigh_indices[e] = j;
+                neigh_types[e] = types[j];
+                shifts[3 * e] = n0; shifts[3 * e + 1] = n1; shifts[3 * e + 2] = n2;
+                xyz[3 * e] = d[0]; xyz[3 * e + 1] = d[1]; xyz[3 * e + 2] = d[2];
+                r[e] = __dsqrt_rn(r2);
+            }
+        }
+    }
+}
+
+__global__ void neigh_iota_kernel(int n, int* out) {
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) out[i] = i;
+}
+__global__ void neigh_offsets_kernel(int n, const int* __restrict__ sorted_keys, int num_values, int* __restrict__ offsets) {
+    for (int v = blockIdx.x * blockDim.x + threadIdx.x; v <= num_values; v += gridDim.x * blockDim.x) {
+        int lo = 0, hi = n;
+        while (lo < hi) {
+            const int mid = (lo + hi) >> 1;
+            if (sorted_keys[mid] < v) lo = mid + 1; else hi = mid;
+        }
+        offsets[v] = lo;
+    }
+}
+
+struct NeighCast {
+    __host__ __device__ long long operator()(const int& v) const { return static_cast<long long>(v); }
+};
+
+class NeighborBuilder {
+public:
+    DevBuf<double> d_pos;
+    DevBuf<int> bin_of, sorted_bins, sorted_atoms, iota, bin_start;
+    DevBuf<long long> first;
+    DevBuf<unsigned long long> keys;
+    DevBuf<unsigned char> tmp;
+
+    void build(int n, const double* pos, const int* d_types, const double* cell, const int* pbc, double r_cut, bool pos_on_device,
+               cudaStream_t stream, long& launches, DevBuf<int>& num_neigh, DevBuf<int>& neigh_indices, DevBuf<int>& neigh_types,
+               DevBuf<int>& shifts, DevBuf<double>& xyz, DevBuf<double>& r, long& num_edges) {
+        if (!(r_cut > 0.0)) throw ArgError("build_neighbors: r_cut must be positive");
+        NeighGrid g{};
+        for (int q = 0; q < 9; ++q) g.cell[q] = cell[q];
+        const double* a = cell;
+        const double det = a[0] * (a[4] * a[8] - a[5] * a[7]) - a[1] * (a[3] * a[8] - a[5] * a[6]) + a[2] * (a[3] * a[7] - a[4] * a[6]);
+        if (std::fabs(det) < 1e-300) throw ArgError("build_neighbors: singular cell");
+        g.inv[0] = (a[4] * a[8] - a[5] * a[7]) / det; g.inv[1] = (a[2] * a[7] - a[1] * a[8]) / det; g.inv[2] = (a[1] * a[5] - a[2] * a[4]) / det;
+        g.inv[3] = (a[5] * a[6] - a[3] * a[8]) / det; g.inv[4] = (a[0] * a[8] - a[2] * a[6]) / det; g.inv[5] = (a[2] * a[3] - a[0] * a[5]) / det;
+        g.inv[6] = (a[3] * a[7] - a[4] * a[6]) / det; g.inv[7] = (a[1] * a[6] - a[0] * a[7]) / det; g.inv[8] = (a[0] * a[4] - a[1] * a[3]) / det;
+        long long total_bins = 1;
+        for (int ax = 0; ax < 3; ++ax) {
+            const double* u = cell + 3 * ((ax + 1) % 3);
+            const double* v = cell + 3 * ((ax + 2) % 3);
+            const double cx = u[1] * v[2] - u[2] * v[1], cy = u[2] * v[0] - u[0] * v[2], cz = u[0] * v[1] - u[1] * v[0];
+            const double height = std::fabs(det) / std::sqrt(cx * cx + cy * cy + cz * cz);
+            const double rc = r_cut * (1.0 + 1e-9);
+            int nbins = static_cast<int>(std::floor(height / rc));
+            if (nbins < 1) nbins = 1;
+            if (nbins > 256) nbins = 256;
+            g.nb[ax] = nbins;
+            g.reach[ax] = static_cast<int>(std::ceil(rc / (height / nbins)));
+            if (!pbc[ax] && g.reach[ax] > nbins) g.reach[ax] = nbins;
+            if (g.reach[ax] > 63 * nbins) throw ArgError("build_neighbors: cell far smaller than r_cut");
+            g.pbc[ax] = pbc[ax] ? 1 : 0;
+            total_bins *= nbins;
+        }
+        g.rc2 = r_cut * r_cut;
+        const double* dpos = pos;
+        if (!pos_on_device) {
+            d_pos.resize(3 * static_cast<size_t>(n), stream);
+            if (n) SMX_CUDA(cudaMemcpyAsync(d_pos.p, pos, 3 * static_cast<size_t>(n) * sizeof(double), cudaMemcpyHostToDevice, stream));
+            dpos = d_pos.p;
+        }
+        num_neigh.resize(n, stream);
+        num_edges = 0;
+        if (n == 0) {
+            neigh_indices.resize(0, stream); neigh_types.resize(0, stream); shifts.resize(0, stream); xyz.resize(0, stream); r.resize(0, stream);
+            return;
+        }
+        const int nbins = static_cast<int>(total_bins);
+        const int blocks = std::min(4096, (n + 127) / 128);
+        bin_of.resize(n, stream); sorted_bins.resize(n, stream); sorted_atoms.resize(n, stream); iota.resize(n, stream);
+        bin_start.resize(static_cast<size_t>(nbins) + 1, stream);
+        neigh_bin_kernel<<<blocks, 128, 0, stream>>>(n, dpos, g, bin_of.p);
+        neigh_iota_kernel<<<blocks, 128, 0, stream>>>(n, iota.p);
+        launches += 2;
+        int bits = 1;
+        while ((1LL << bits) < total_bins) ++bits;
+        size_t bytes = 0;
+        SMX_CUDA(cub::DeviceRadixSort::SortPairs(nullptr, bytes, bin_of.p, sorted_bins.p, iota.p, sorted_atoms.p, n, 0, bits, stream));
+        tmp.resize(bytes, stream);
+        SMX_CUDA(cub::DeviceRadixSort::SortPairs(tmp.p, bytes, bin_of.p, sorted_bins.p, iota.p, sorted_atoms.p, n, 0, bits, stream));
+        neigh_offsets_kernel<<<std::min(1024, (nbins + 128) / 128), 128, 0, stream>>>(n, sorted_bins.p, nbins, bin_start.p);
+        launches += 2;
+        neigh_rows_kernel<true><<<blocks, 128, 0, stream>>>(n, dpos, d_types, g, bin_start.p, sorted_atoms.p, num_neigh.p, nullptr, nullptr,
+                                                          nullptr, nullptr, nullptr, nullptr, nullptr);
+        launches += 1;
+        first.resize(static_cast<size_t>(n) + 1, stream);
+        cub::TransformInputIterator<long long, NeighCast, const int*> it(num_neigh.p, NeighCast());
+        SMX_CUDA(cub::DeviceScan::ExclusiveSum(nullptr, bytes, it, first.p, n, stream));
+        tmp.resize(bytes, stream);
+        SMX_CUDA(cub::DeviceScan::ExclusiveSum(tmp.p, bytes, it, first.p, n, stream));
+        launches += 1;
+        long long last_first = 0;
+        int last_count = 0;
+        SMX_CUDA(cudaMemcpyAsync(&last_first, first.p + (n - 1), sizeof(long long), cudaMemcpyDeviceToHost, stream));
+        SMX_CUDA(cudaMemcpyAsync(&last_count, num_neigh.p + (n - 1), sizeof(int), cudaMemcpyDeviceToHost, stream));
+        SMX_CUDA(cudaStreamSynchronize(stream));
+        const long long total = last_first + last_count;
+        num_edges = static_cast<long>(total);
+        keys.resize(total, stream);
+        neigh_indices.resize(total, stream); neigh_types.resize(total, stream); shifts.resize(3 * total, stream);
+        xyz.resize(3 * total, stream); r.resize(total, stream);
+        if (total > 0) {
+            neigh_rows_kernel<false><<<blocks, 128, 0, stream>>>(n, dpos, d_types, g, bin_start.p, sorted_atoms.p, nullptr, first.p, keys.p,
+                                                               neigh_indices.p, neigh_types.p, shifts.p, xyz.p, r.p);
+            launches += 1;
+        }
+        cudaError_t err = cudaGetLastError();
+        if (err != cudaSuccess) throw CudaError(std::string("neighbour list: ") + cudaGetErrorString(err));
+    }
+};
+
+}  // namespace smx

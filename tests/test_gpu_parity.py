@@ -1,0 +1,300 @@
+"""Parity of the CUDA path (through the C ABI) with the oracle. All tests need a GPU."""
+import ctypes
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from oracle import ref as ref_driver
+from oracle.mace_numpy import MaceOracle
+from symmetrix_b200 import MACE, Symmetrix, SymmetrixError, _lib, structures as st
+from symmetrix_b200.modelgen.harmonics import random_rotation
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = Path(__file__).resolve().parent / "golden"
+INPUT_KEYS = ["num_nodes", "node_types", "num_neigh", "neigh_indices", "neigh_types", "xyz", "r"]
+FWD = ["A0", "M0", "H1", "Phi1", "A1", "M1", "H2"]
+ADJ = ["H2_adj", "M1_adj", "A1_adj", "Phi1_adj", "H1_adj", "M0_adj", "A0_adj"]
+
+# Tolerances: float64 results must agree with the reference CPU path to 1e-10 relative, float32 to 1e-4 relative
+# with a maximum absolute force error of 1e-3 eV/A.
+TOL = {"float64": dict(rel=1e-10, f_abs=1e-9), "float32": dict(rel=1e-4, f_abs=1e-3)}
+
+
+def run(ev, inp):
+    ev.compute_node_energies_forces(int(inp["num_nodes"]), inp["node_types"], inp["num_neigh"], inp["neigh_indices"],
+                                    inp["neigh_types"], inp["xyz"], inp["r"])
+    return ev.node_energies, ev.node_forces
+
+
+def rel_err(a, b):
+    return np.abs(a - b).max() / max(np.abs(b).max(), 1e-300)
+
+
+def check_against(ev_dtype, e, f, e_ref, f_ref, inputs=None, nl=None):
+    tol = TOL[ev_dtype]
+    assert abs(e.sum() - e_ref.sum()) <= tol["rel"] * abs(e_ref.sum())
+    assert rel_err(e, e_ref) <= 10 * tol["rel"]
+    assert rel_err(f, f_ref) <= 10 * tol["rel"]
+    assert np.abs(f - f_ref).max() <= tol["f_abs"]
+
+
+@pytest.fixture(scope="module")
+def tiny():
+    case = np.load(GOLDEN / "tiny_case.npz")
+    return case, {k: case[k] for k in INPUT_KEYS}
+
+
+@pytest.mark.parametrize("dtype", ["float64", "float32"])
+def test_tiny_golden_stagewise(tiny, dtype):
+    case, inputs = tiny
+    ev = MACE(GOLDEN / "tiny_model.json", dtype=dtype)
+    e, f = run(ev, inputs)
+    check_against(dtype, e, f, case["node_energies"], case["node_forces"])
+    rel = 1e-10 if dtype == "float64" else 2e-4
+    for name in FWD + ADJ:
+        want = case["stage_" + name]
+        got = getattr(ev, name)
+        assert got.size == want.size, name
+        assert rel_err(got, want) <= rel, (name, rel_err(got, want))
+
+
+@pytest.mark.parametrize("dtype", ["float64", "float32"])
+def test_config0_water64_golden(model_file, dtype):
+    path, model, spec = model_file("water64")
+    gold = np.load(GOLDEN / "water64_case.npz")
+    s = st.water_box(4, 12.42, seed=0)
+    nl = st.neighbor_list(s, spec.r_cut)
+    inputs = st.evaluator_inputs(s, nl, model["atomic_numbers"])
+    ev = MACE(path, dtype=dtype)
+    e, f = run(ev, inputs)
+    tol = TOL[dtype]
+    assert abs(e.sum() - gold["node_energies"].sum()) <= tol["rel"] * abs(gold["node_energies"].sum())
+    forces, virial, energy = ev.reduce_forces()
+    assert abs(energy - e.sum()) <= 1e-12 * abs(e.sum())
+    assert np.abs(forces - gold["atom_forces"]).max() <= max(tol["f_abs"], 10 * tol["rel"] * np.abs(gold["atom_forces"]).max())
+    assert rel_err(virial, gold["virial"]) <= 100 * tol["rel"]
+    f_np, v_np = st.atom_forces_and_virial(inputs, nl, f)
+    np.testing.assert_allclose(forces, f_np, rtol=0, atol=1e-11)
+    np.testing.assert_allclose(virial, v_np, rtol=1e-11, atol=1e-10)
+
+
+def _oracle_for(path, model):
+    """The compiled reference when it is here, else the numpy restatement."""
+    if ref_driver.available():
+        r = ref_driver.ReferenceMACE(path)
+        return lambda inp: r.compute_node_energies_forces(inp)
+    o = MaceOracle(model)
+    return lambda inp: o.compute_node_energies_forces(inp)
+
+
+@pytest.mark.parametrize("dtype", ["float64", "float32"])
+@pytest.mark.parametrize("name,channels,builder", [
+    ("fcc128", 32, lambda z: st.fcc_box(3, 3.6, z, seed=4)),                 # L_max = 1, 5 species, r_cut 6
+    ("fcc128", 128, lambda z: st.fcc_box(3, 3.6, z, seed=5)),                # benchmark width
+    ("large256", 32, lambda z: st.molecular_liquid(12, seed=6)),             # L_max = 2
+    ("organic128", 48, lambda z: st.water_box(3, 9.4, seed=7)),              # channel count not a multiple of 32
+    ("large256", 160, lambda z: st.molecular_liquid(8, seed=8)),             # more channels than one CTA pass
+])
+def test_downsized_benchmark_models(model_file, dtype, name, channels, builder):
+    path, model, spec = model_file(name, num_channels=channels, num_spline_points=32)
+    s = builder(model["atomic_numbers"])
+    nl = st.neighbor_list(s, spec.r_cut)
+    inputs = st.evaluator_inputs(s, nl, model["atomic_numbers"])
+    e_ref, f_ref = _oracle_for(path, model)(inputs)
+    ev = MACE(path, dtype=dtype)
+    e, f = run(ev, inputs)
+    check_against(dtype, e, f, e_ref, f_ref)
+
+
+def test_repeated_calls_are_bitwise_identical(tiny):
+    _, inputs = tiny
+    ev = MACE(GOLDEN / "tiny_model.json", dtype="float64")
+    e1, f1 = run(ev, inputs)
+    e2, f2 = run(ev, inputs)
+    np.testing.assert_array_equal(e1, e2)
+    np.testing.assert_array_equal(f1, f2)
+
+
+def test_rotation_invariance_and_force_equivariance(model_file):
+    path, model, spec = model_file("fcc128", num_channels=64, num_spline_points=64)
+    s = st.fcc_box(4, 3.6, model["atomic_numbers"], seed=11)
+    nl = st.neighbor_list(s, spec.r_cut)
+    inputs = st.evaluator_inputs(s, nl, model["atomic_numbers"])
+    ev = MACE(path, dtype="float64")
+    e0, f0 = run(ev, inputs)
+    rot = random_rotation(np.random.default_rng(5))
+    inp = dict(inputs); inp["xyz"] = (inputs["xyz"].reshape(-1, 3) @ rot.T).reshape(-1)
+    e1, f1 = run(ev, inp)
+    assert rel_err(e1, e0) < 1e-11
+    assert np.abs(f1.reshape(-1, 3) - f0.reshape(-1, 3) @ rot.T).max() < 1e-10 * max(1.0, np.abs(f0).max())
+
+
+def test_forces_are_energy_gradients_on_gpu(tiny):
+    _, inputs = tiny
+    ev = MACE(GOLDEN / "tiny_model.json", dtype="float64")
+    _, f = run(ev, inputs)
+    f = f.reshape(-1, 3)
+    xyz = inputs["xyz"].reshape(-1, 3).copy()
+    h = 1e-5
+    for e in (0, 17, 101):
+        for c in range(3):
+            vals = []
+            for sgn in (+1, -1):
+                x2 = xyz.copy(); x2[e, c] += sgn * h
+                inp = dict(inputs); inp["xyz"] = x2.reshape(-1); inp["r"] = np.linalg.norm(x2, axis=1)
+                en, _ = run(ev, inp)
+                vals.append(en.sum())
+            assert abs(-(vals[0] - vals[1]) / (2 * h) - f[e, c]) < 1e-6 * max(1.0, abs(f[e, c]))
+
+
+def test_device_resident_inputs_give_the_same_result(tiny):
+    import torch
+    _, inputs = tiny
+    ev = MACE(GOLDEN / "tiny_model.json", dtype="float64")
+    e0, f0 = run(ev, inputs)
+    dev = {k: torch.as_tensor(np.asarray(inputs[k])).cuda() for k in INPUT_KEYS if k != "num_nodes"}
+    ev.compute_node_energies_forces(int(inputs["num_nodes"]), dev["node_types"].int(), dev["num_neigh"].int(),
+                                    dev["neigh_indices"].int(), dev["neigh_types"].int(), dev["xyz"].double(), dev["r"].double())
+    np.testing.assert_array_equal(ev.node_energies, e0)
+    np.testing.assert_array_equal(ev.node_forces, f0)
+
+
+def test_empty_and_ragged_inputs(tiny):
+    _, inputs = tiny
+    ev = MACE(GOLDEN / "tiny_model.json", dtype="float64")
+    # no nodes at all
+    z = np.zeros(0, dtype=np.int32)
+    ev.compute_node_energies_forces(0, z, z, z, z, np.zeros(0), np.zeros(0))
+    assert ev.node_energies.size == 0 and ev.node_forces.size == 0
+    # nodes without any neighbour: energy is E0 + readouts of zero features
+    types = np.array([0, 1, 1], dtype=np.int32)
+    ev.compute_node_energies_forces(3, types, np.zeros(3, np.int32), z, z, np.zeros(0), np.zeros(0))
+    o = MaceOracle(GOLDEN / "tiny_model.json")
+    e_ref, _ = o.compute_node_energies_forces({"num_nodes": 3, "node_types": types, "num_neigh": np.zeros(3, np.int32),
+                                               "neigh_indices": z, "neigh_types": z, "xyz": np.zeros(0), "r": np.zeros(0)})
+    np.testing.assert_allclose(ev.node_energies, e_ref, rtol=1e-12)
+    # ragged: drop all edges of a few receivers (rows of length zero between populated rows)
+    nn = inputs["num_neigh"].copy()
+    first = np.concatenate([[0], np.cumsum(nn)])
+    keep = np.ones(inputs["r"].size, bool)
+    for i in (1, 2, 9):
+        keep[first[i]:first[i + 1]] = False
+        nn[i] = 0
+    inp = dict(inputs, num_neigh=nn, neigh_indices=inputs["neigh_indices"][keep], neigh_types=inputs["neigh_types"][keep],
+               xyz=inputs["xyz"].reshape(-1, 3)[keep].reshape(-1), r=inputs["r"][keep])
+    e_ref, f_ref = o.compute_node_energies_forces(inp)
+    e, f = run(ev, inp)
+    check_against("float64", e, f, e_ref, f_ref)
+
+
+def test_message_passing_stage_sequence_with_ghost_rows(model_file):
+    """The call sequence of the pair style's message-passing mode (pair_symmetrix_mace.cpp:444-495): layer 0 on local
+    nodes, H1 extended with rows for ghost atoms, layer 1 gathering from ghost rows, H1_adj folded back."""
+    path, model, spec = model_file("fcc128", num_channels=32, num_spline_points=32)
+    s = st.fcc_box(3, 3.6, model["atomic_numbers"], seed=21)
+    nl = st.neighbor_list(s, spec.r_cut)
+    full = st.evaluator_inputs(s, nl, model["atomic_numbers"])
+    n = s.num_atoms
+    # single-domain answer
+    ev = MACE(path, dtype="float64")
+    e_full, f_full = run(ev, full)
+    # message-passing form: every periodic image becomes its own ghost row (index >= n), as LAMMPS numbers ghosts
+    keys = {}
+    ghost_owner = []
+    j_mp = full["neigh_indices"].copy()
+    for e_idx, (j, sh) in enumerate(zip(nl["j"], nl["S"])):
+        if np.any(sh != 0):
+            key = (int(j), tuple(int(x) for x in sh))
+            if key not in keys:
+                keys[key] = n + len(ghost_owner)
+                ghost_owner.append(int(j))
+            j_mp[e_idx] = keys[key]
+    ghost_owner = np.array(ghost_owner)
+    rows = n + ghost_owner.size
+    mp = dict(full, neigh_indices=j_mp)
+    ev.begin(n, mp["node_types"], mp["num_neigh"], mp["neigh_indices"], mp["neigh_types"], mp["xyz"], mp["r"])
+    for stage in ["compute_Y", "compute_R0", "compute_A0", "compute_A0_scaled", "compute_M0", "compute_H1"]:
+        getattr(ev, stage)()
+    width = ev.num_LM * ev.num_channels
+    h1 = ev.H1.reshape(n, width)
+    ev.H1 = np.concatenate([h1, h1[ghost_owner]])             # forward_comm
+    for stage in ["compute_R1", "compute_Phi1", "compute_A1", "compute_A1_scaled", "compute_M1", "compute_H2", "compute_readouts"]:
+        getattr(ev, stage)()
+    ev.reverse_H2(zero_H1_adj=False); ev.reverse_M1(); ev.reverse_A1_scaled(); ev.reverse_A1()
+    ev.reverse_Phi1(zero_dxyz=False, zero_H1_adj=False)
+    adj = ev.H1_adj.reshape(rows, width)
+    folded = adj[:n].copy()
+    np.add.at(folded, ghost_owner, adj[n:])                   # reverse_comm
+    ev.H1_adj = folded
+    for stage in ["reverse_H1", "reverse_M0", "reverse_A0_scaled", "reverse_A0"]:
+        getattr(ev, stage)()
+    assert rel_err(ev.node_energies, e_full) < 1e-12
+    assert np.abs(ev.node_forces - f_full).max() < 1e-11 * max(1.0, np.abs(f_full).max())
+    # forces on ghost rows come back through reduce_forces with num_rows = locals + ghosts
+    forces, _, _ = ev.reduce_forces(num_rows=rows)
+    f_atoms = forces[:n].copy()
+    np.add.at(f_atoms, ghost_owner, forces[n:])
+    f_np, _ = st.atom_forces_and_virial(full, nl, f_full)
+    np.testing.assert_allclose(f_atoms, f_np, atol=1e-10)
+
+
+@pytest.mark.parametrize("builder,rc", [
+    (lambda: st.water_box(4, 12.42, seed=0), 5.0),
+    (lambda: st.fcc_box(5, 3.6, [29, 47, 79], seed=1), 6.0),
+    (lambda: st.Structure(np.array([[0.1, 0.2, 0.3], [1.0, 1.1, 0.9], [0.5, 1.7, 0.2]]), np.eye(3) * 1.9, np.array([1, 8, 1])), 4.0),
+    (lambda: st.Structure(np.random.default_rng(3).uniform(0, 1, (40, 3)) @ np.array([[7.0, 0, 0], [2.0, 6.5, 0], [1.0, -1.5, 8.0]]),
+                          np.array([[7.0, 0, 0], [2.0, 6.5, 0], [1.0, -1.5, 8.0]]), np.full(40, 1)), 3.3),
+    (lambda: st.Structure(np.random.default_rng(4).uniform(0, 9, (60, 3)), np.eye(3) * 9.0, np.full(60, 8), pbc=(True, False, True)), 3.0),
+])
+def test_neighbor_list_is_bit_exact(builder, rc):
+    s = builder()
+    nl = st.neighbor_list(s, rc)
+    ev = MACE(GOLDEN / "tiny_model.json", dtype="float64")
+    zmap = {1: 0, 8: 1}
+    types = np.array([zmap.get(int(z), 0) for z in s.numbers], dtype=np.int32)
+    n_edges = ev.build_neighbors(s.positions, types, s.cell, s.pbc, r_cut=rc)
+    assert n_edges == nl["i"].size
+    got = ev.get_edges()
+    np.testing.assert_array_equal(got["num_neigh"], np.bincount(nl["i"], minlength=s.num_atoms))
+    np.testing.assert_array_equal(got["neigh_indices"], nl["j"])
+    np.testing.assert_array_equal(got["shifts"], nl["S"])
+    np.testing.assert_array_equal(got["neigh_types"], types[nl["j"]])
+    assert got["xyz"].tobytes() == np.ascontiguousarray(nl["D"]).tobytes()     # identical float64 bits
+    assert got["r"].tobytes() == np.ascontiguousarray(nl["d"]).tobytes()
+
+
+def test_calculator_matches_oracle_energy_forces_stress(model_file):
+    path, model, spec = model_file("water64")
+    s = st.water_box(3, 9.4, seed=12)
+    calc = Symmetrix(path, dtype="float64")
+    res = calc.calculate(s.positions, s.cell, s.numbers, s.pbc)
+    nl = st.neighbor_list(s, spec.r_cut)
+    inputs = st.evaluator_inputs(s, nl, model["atomic_numbers"])
+    e_ref, f_ref = _oracle_for(path, model)(inputs)
+    forces, virial = st.atom_forces_and_virial(inputs, nl, f_ref)
+    assert abs(res["energy"] - e_ref.sum()) < 1e-10 * abs(e_ref.sum())
+    np.testing.assert_allclose(res["forces"], forces, atol=1e-9)
+    xyz = inputs["xyz"].reshape(-1, 3); nf = f_ref.reshape(-1, 3)
+    full = -(nf.T @ xyz) / np.linalg.det(s.cell)            # symmetrix_calc.py:102
+    voigt = np.array([full[0, 0], full[1, 1], full[2, 2], 0.5 * (full[1, 2] + full[2, 1]), 0.5 * (full[0, 2] + full[2, 0]),
+                      0.5 * (full[0, 1] + full[1, 0])])
+    np.testing.assert_allclose(res["stress"], voigt, atol=1e-10)
+
+
+def test_error_reporting(tiny):
+    _, inputs = tiny
+    ev = MACE(GOLDEN / "tiny_model.json", dtype="float64")
+    with pytest.raises(SymmetrixError):
+        ev.compute_A0()                    # no edge set yet
+    ev.begin(int(inputs["num_nodes"]), inputs["node_types"], inputs["num_neigh"], inputs["neigh_indices"],
+             inputs["neigh_types"], inputs["xyz"], inputs["r"])
+    with pytest.raises(SymmetrixError):
+        ev.compute_M0()                    # stage called out of order
+    with pytest.raises(SymmetrixError):
+        ev._stage("compute_everything")
+    with pytest.raises(SymmetrixError):
+        ev.get("R7")
+    with pytest.raises(SymmetrixError):
+        MACE(GOLDEN / "tiny_case.npz")     # not JSON
