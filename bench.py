@@ -1,0 +1,459 @@
+"""Benchmark of the MACE energy+force path: atom-steps/s on synthetic structures with random-init
+weights of the benchmark configurations.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME] [--dtype float64|float32]
+
+One JSON line on stdout (rank 0). A "step" is one full evaluation of one structure: edge arrays
+in, index building, all forward and reverse stages, per-atom force / virial / energy reduction.
+``value`` is measured with the edge arrays already resident in HBM, ``e2e`` with host (pinned)
+arrays in and host results out through the public Python/C-ABI call. ``--impl reference`` times the
+reference's own CPU evaluator (``oracle/_ref``) on the host cores instead.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "mace_energy_force_atom_steps_per_s"
+UNIT = "atom-steps/s"
+
+WORKLOADS = {
+    # name: (model spec name, structure builder, description)
+    "fcc4000": ("fcc128", lambda st, z, seed: st.fcc_box(10, 3.6, z, seed=seed),
+                "configs[1]: 4000-atom FCC (10x10x10 cells, a=3.6 A, 5 species, 0.1 A jitter), model 128x0e+128x1o, "
+                "l_max 3, correlation 3, r_cut 6 A, 10 radial functions, 89-element model exported for the 5 species present"),
+    "water192": ("water64", lambda st, z, seed: st.water_box(4, 12.42, seed=seed),
+                 "configs[0]: 64 H2O (192 atoms) in a 12.42 A cell, model 64x0e, r_cut 5 A"),
+}
+CPU_SAMPLE_CELLS = 4   # the CPU baseline evaluates a 4x4x4-cell (256-atom) box of the same construction
+
+
+def log(*a):
+    print(*a, file=sys.stderr, flush=True)
+
+
+def model_path(spec_name: str) -> tuple[Path, list[int]]:
+    """Model JSON regenerated from its seed into the temp directory (cached across runs on one machine)."""
+    from symmetrix_b200.modelgen.generate import generate_model, named_spec, write_json
+    cache = Path(os.environ.get("SMX_MODEL_CACHE", tempfile.gettempdir())) / f"smx_bench_{spec_name}.json"
+    spec = named_spec(spec_name)
+    if not cache.exists():
+        t0 = time.time()
+        model = generate_model(spec)
+        tmp = cache.with_suffix(f".{os.getpid()}.tmp")
+        write_json(model, tmp)
+        os.replace(tmp, cache)
+        log(f"[bench] generated {cache} in {time.time() - t0:.1f} s")
+    return cache, sorted(spec.atomic_numbers), spec
+
+
+def build_inputs(workload: str, seed: int):
+    from symmetrix_b200 import structures as st
+    spec_name, builder, _ = WORKLOADS[workload]
+    path, numbers, spec = model_path(spec_name)
+    s = builder(st, numbers, seed)
+    nl = st.neighbor_list(s, spec.r_cut)
+    return path, spec, s, nl, st.evaluator_inputs(s, nl, numbers)
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.proc = None
+        self.path = Path(tempfile.gettempdir()) / f"smx_clocks_{os.getpid()}.csv"
+        try:
+            self.fh = open(self.path, "w")
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-i", str(gpu_index), "-lms", "100"], stdout=self.fh, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.fh.close()
+        sm, mx, reasons = [], [], set()
+        for line in self.path.read_text().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1])); mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"], parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        try:
+            self.path.unlink()
+        except OSError:
+            pass
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        # median of the upper half: samples between steps (host-side gaps) idle the clocks
+        busy = sorted(sm)[len(sm) // 2:]
+        return {"sm_mhz": float(np.median(busy)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def measured_peaks() -> tuple[float, str]:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+def path_constants(L_max: int):
+    from symmetrix_b200.modelgen.generate import tp_paths
+    paths = tp_paths(3, L_max)
+    nz = sum((2 * l + 1) * (2 * l2 + 1) for l, _, l2 in paths)
+    q = sum(2 * l + 1 for l, _, _ in paths)
+    return len(paths), nz, q, (L_max + 1) ** 2
+
+
+def roofline_for(stage: str, ms: float, n_atoms: int, n_edges: int, K: int, L_max: int, dtype_bytes: int) -> dict:
+    """Algorithmic bytes and flops of the stage's dominant kernel for one launch (one full structure).
+
+    Per edge: xyz 24 B + sender index 4 B + sender type 4 B + r 8 B, one gathered sender feature row
+    nLM*K*s B, 24 B of partial force written (reverse). Per node: Q*K*s B of tensor-product output written
+    (forward) or of its adjoint read (reverse). Scratch the implementation adds (the per-edge adjoint
+    message buffer) and table reads served by L2 are not counted. Flops: forward (2 NZ + 2 Q + 8 P) K per
+    edge, reverse (8 NZ + 10 T2 + 14 P) K per edge with T2 = sum_p (2 l2 + 1).
+    """
+    from symmetrix_b200.modelgen.generate import tp_paths
+    P, NZ, Q, nLM = path_constants(L_max)
+    T2 = sum(2 * l2 + 1 for _, _, l2 in tp_paths(3, L_max))
+    s = dtype_bytes
+    if stage == "reverse_Phi1":
+        byts = n_edges * (40 + nLM * K * s + 24) + n_atoms * Q * K * s
+        flops = n_edges * K * (8 * NZ + 10 * T2 + 14 * P)
+        kernel = "tp_reverse_kernel"
+    elif stage == "compute_Phi1":
+        byts = n_edges * (40 + nLM * K * s) + n_atoms * Q * K * s
+        flops = n_edges * K * (2 * NZ + 2 * Q + 8 * P)
+        kernel = "tp_forward_kernel"
+    elif stage == "reverse_A0":
+        byts = n_edges * (40 + 24) + n_atoms * 16 * K * s
+        flops = n_edges * K * (8 * 16 + 14 * 4)
+        kernel = "layer0_reverse_kernel"
+    else:
+        byts = n_edges * 40 + n_atoms * 16 * K * s
+        flops = n_edges * K * (2 * 16 + 9 * 4)
+        kernel = "layer0_forward_kernel"
+    peak, how = measured_peaks()
+    achieved = byts / (ms * 1e-3) / 1e9
+    traffic = None
+    tfile = ROOT / "profiles" / "dram_traffic.json"
+    if tfile.exists():
+        try:
+            rec = json.loads(tfile.read_text()).get(kernel)
+            if rec:
+                # captured on a smaller box of the same construction; traffic grows with the edge count
+                traffic = rec["dram_bytes_per_edge"] * n_edges
+        except Exception:
+            traffic = None
+    return {"bound": "hbm", "kernel": kernel, "stage": stage, "achieved": achieved, "peak": peak, "unit": "GB/s",
+            "frac": achieved / peak, "peak_source": f"of {how}", "traffic": traffic, "launch_ms": ms,
+            "algorithmic_bytes": byts, "algorithmic_flops": flops, "achieved_tflops": flops / (ms * 1e-3) / 1e12}
+
+
+# ------------------------------------------------------------------------------------------- ours
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        log(f"[bench] WORLD_SIZE={world} differs from --gpus {args.gpus}; using WORLD_SIZE")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    from symmetrix_b200 import MACE, _lib
+
+    path, spec, s, nl, inputs = build_inputs(args.workload, seed=1 + rank)
+    n_atoms, n_edges = s.num_atoms, int(inputs["r"].size)
+    ev = MACE(path, dtype=args.dtype, device=local_rank)
+    dtype_bytes = 8 if args.dtype == "float64" else 4
+
+    keys = ["node_types", "num_neigh", "neigh_indices", "neigh_types", "xyz", "r"]
+    dev = {k: torch.as_tensor(np.ascontiguousarray(inputs[k])).cuda(local_rank) for k in keys}
+    pinned = {k: torch.as_tensor(np.ascontiguousarray(inputs[k])).pin_memory() for k in keys}
+    host = {k: pinned[k].numpy() for k in keys}
+    flush = torch.empty(256 * 1024 * 1024 // 4, dtype=torch.float32, device=f"cuda:{local_rank}")   # 256 MB > 126 MB L2
+    f_out = np.zeros((n_atoms, 3)); v_out = np.zeros(6)
+
+    def step_device():
+        ev.compute_node_energies_forces(n_atoms, *[dev[k] for k in keys])
+        return ev.reduce_forces()
+
+    def step_host():
+        ev.compute_node_energies_forces(n_atoms, *[host[k] for k in keys])
+        return ev.reduce_forces()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(step_fn, steps, warmup):
+        for _ in range(warmup):
+            step_fn()
+        barrier()
+        dev_ms, wall = 0.0, 0.0
+        for _ in range(steps):
+            flush.zero_()                      # L2 flush between timed iterations
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            ev.timer_start()
+            step_fn()
+            dev_ms += ev.timer_stop()
+            wall += time.perf_counter() - t0
+        barrier()
+        return dev_ms, wall
+
+    launches0 = ev.launch_count
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    dev_ms, wall_s = timed(step_device, args.steps, args.warmup)
+    clocks = sampler.stop() if sampler else None
+    launches = ev.launch_count - launches0
+    launches_per_step = launches // (args.steps + args.warmup)
+    e2e_ms, e2e_wall = timed(step_host, args.steps, max(1, args.warmup // 2))
+
+    # per-stage device time -> dominant kernel and its roofline
+    ev.set_profiling(True)
+    stage_acc: dict = {}
+    for _ in range(max(2, min(args.steps, 5))):
+        flush.zero_(); torch.cuda.synchronize()
+        ev.compute_node_energies_forces(n_atoms, *[dev[k] for k in keys])
+        for name, ms in ev.stage_times().items():
+            stage_acc.setdefault(name, []).append(ms)
+    ev.set_profiling(False)
+    stage_ms = {k: float(np.mean(v)) for k, v in stage_acc.items()}
+    dominant = max(stage_ms, key=stage_ms.get)
+    roof = roofline_for(dominant, stage_ms[dominant], n_atoms, n_edges, ev.num_channels, ev.L_max, dtype_bytes)
+    fma = ctypes_fma_peak(_lib, 32 if args.dtype == "float32" else 64, local_rank)
+    roof["fma_peak_tflops"] = fma
+    roof["fma_frac"] = roof["achieved_tflops"] / fma if fma else None
+
+    def reduce_max(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=f"cuda:{local_rank}")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    dev_ms_max = reduce_max(dev_ms)
+    e2e_ms_max = reduce_max(e2e_wall * 1e3)
+    total_atoms = n_atoms * world
+    value = total_atoms * args.steps / (dev_ms_max * 1e-3)
+    e2e_value = total_atoms * args.steps / (e2e_ms_max * 1e-3)
+    h2d = sum(host[k].nbytes for k in keys)
+    d2h = f_out.nbytes + v_out.nbytes + 8
+
+    out = None
+    if rank == 0:
+        out = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": dev_ms_max / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f64" if args.dtype == "float64" else "f32", "data": "synthetic",
+            "config": {"workload": args.workload, "description": WORKLOADS[args.workload][2], "atoms_per_gpu": n_atoms,
+                       "edges_per_gpu": n_edges, "parallelism": "single GPU" if world == 1 else f"{world} independent boxes (one per GPU, no halo exchange)",
+                       "l2": "256 MB buffer written between timed steps (L2 flush); per-step working set exceeds 126 MB",
+                       "timing": "CUDA events on the evaluator's stream around each step, summed over steps, max over ranks"},
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": e2e_ms_max / args.steps, "timing": "wall clock around the public call with pinned host arrays in, host forces/virial/energy out"},
+            "gpu_launches": launches, "gpu_launches_per_step": launches_per_step,
+            "clocks": clocks, "roofline": roof, "stage_ms": stage_ms,
+            "wall_ms_per_step": wall_s * 1e3 / args.steps,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            out["cpu_baseline"] = cpu_baseline(args.workload)
+        if world == 1 and not args.no_extra:
+            other = "float32" if args.dtype == "float64" else "float64"
+            ev2 = MACE(path, dtype=other, device=local_rank)
+            ev_saved = ev
+
+            def step2():
+                ev2.compute_node_energies_forces(n_atoms, *[dev[k] for k in keys])
+                return ev2.reduce_forces()
+            for _ in range(max(3, args.warmup)):
+                step2()
+            ms2 = 0.0
+            for _ in range(args.steps):
+                flush.zero_(); torch.cuda.synchronize()
+                ev2.timer_start(); step2(); ms2 += ev2.timer_stop()
+            e64 = ev_saved.reduce_forces()[2] if args.dtype == "float64" else ev2.reduce_forces()[2]
+            e32 = ev2.reduce_forces()[2] if args.dtype == "float64" else ev_saved.reduce_forces()[2]
+            out["extra"] = {other: {"value": n_atoms * args.steps / (ms2 * 1e-3), "ms_per_step": ms2 / args.steps},
+                            "fp32_vs_fp64_rel_energy_diff": abs(e32 - e64) / abs(e64)}
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return out
+
+
+def ctypes_fma_peak(_lib, precision: int, device: int) -> float | None:
+    import ctypes
+    lib = _lib.load()
+    t = ctypes.c_double(0.0)
+    if lib.smx_measure_fma_peak(precision, device, ctypes.byref(t)) != 0:
+        return None
+    return t.value
+
+
+# ------------------------------------------------------------------------------------------- CPU arms
+def _cpu_sample_inputs(workload: str, seed: int):
+    from symmetrix_b200 import structures as st
+    spec_name, _, _ = WORKLOADS[workload]
+    path, numbers, spec = model_path(spec_name)
+    if workload == "fcc4000":
+        s = st.fcc_box(CPU_SAMPLE_CELLS, 3.6, numbers, seed=seed)
+        sample = f"{CPU_SAMPLE_CELLS}x{CPU_SAMPLE_CELLS}x{CPU_SAMPLE_CELLS}-cell FCC box ({s.num_atoms} atoms) of the same construction and model"
+    else:
+        s = st.water_box(4, 12.42, seed=seed)
+        sample = "the full 192-atom structure"
+    nl = st.neighbor_list(s, spec.r_cut)
+    return path, s, st.evaluator_inputs(s, nl, numbers), sample
+
+
+def cpu_baseline(workload: str) -> dict:
+    """The reference CPU evaluator (serial, one core) on a bounded sample of the workload."""
+    from oracle import ref as ref_driver
+    path, s, inputs, sample = _cpu_sample_inputs(workload, seed=1)
+    if ref_driver.available("timed"):
+        r = ref_driver.ReferenceMACE(path, "timed")
+        kind = "reference"
+        fn = lambda: r.compute_node_energies_forces(inputs)   # noqa: E731
+    else:
+        from oracle.mace_numpy import MaceOracle
+        o = MaceOracle(path)
+        kind = "port"
+        fn = lambda: o.compute_node_energies_forces(inputs)   # noqa: E731
+    fn()                                   # first call sizes the evaluator's internal arrays
+    reps, t0 = 0, time.perf_counter()
+    while reps < 3 and (time.perf_counter() - t0) < 20.0:
+        fn(); reps += 1
+    dt = (time.perf_counter() - t0) / reps
+    return {"value": s.num_atoms / dt, "unit": UNIT, "cores": 1, "kind": kind,
+            "sample": f"{sample}; {reps} evaluations after one warm-up; -O3 -ffast-math -march=x86-64-v3, plain-loop BLAS",
+            "seconds_per_step": dt}
+
+
+def _replica_main(idx, workload, steps, warmup, barrier, times):
+    from oracle import ref as ref_driver
+    path, s, inputs, _ = _cpu_sample_inputs(workload, seed=100 + idx)
+    r = ref_driver.ReferenceMACE(path, "timed") if ref_driver.available("timed") else None
+    if r is None:
+        from oracle.mace_numpy import MaceOracle
+        o = MaceOracle(path)
+        fn = lambda: o.compute_node_energies_forces(inputs)   # noqa: E731
+    else:
+        fn = lambda: r.compute_node_energies_forces(inputs)   # noqa: E731
+    for _ in range(warmup):
+        fn()
+    barrier.wait()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        fn()
+    times[idx] = time.perf_counter() - t0
+    barrier.wait()
+
+
+def run_reference(args):
+    """The reference's own CPU implementation on all usable host cores: the evaluator is serial, so the host
+    is filled with independent replicas, each evaluating its own sample box per step."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return None
+    import multiprocessing as mp
+    from oracle import ref as ref_driver
+    try:
+        import psutil
+        mem_gb = psutil.virtual_memory().available / 2 ** 30
+    except Exception:
+        mem_gb = 64.0
+    cores = os.cpu_count() or 1
+    try:
+        cores = len(os.sched_getaffinity(0))
+    except Exception:
+        pass
+    replicas = int(max(1, min(cores, mem_gb // 4, 64)))
+    model_path(WORKLOADS[args.workload][0])            # generate once, before the replicas start
+    path, s, inputs, sample = _cpu_sample_inputs(args.workload, seed=100)
+    ctx = mp.get_context("spawn")
+    barrier = ctx.Barrier(replicas)
+    times = ctx.Array("d", replicas)
+    warmup = max(1, min(args.warmup, 2))
+    steps = max(1, min(args.steps, 5))
+    procs = [ctx.Process(target=_replica_main, args=(i, args.workload, steps, warmup, barrier, times)) for i in range(replicas)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join()
+    if any(p.exitcode != 0 for p in procs):
+        print(json.dumps({"impl": "reference", "unavailable": "a CPU replica of the reference evaluator exited with an error"}))
+        return None
+    t = max(times)
+    value = replicas * s.num_atoms * steps / t
+    kind = "reference" if ref_driver.available("timed") else "port"
+    out = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": steps, "warmup": warmup,
+        "ms_per_step": t * 1e3 / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f64",
+        "data": "synthetic",
+        "config": {"workload": args.workload, "description": WORKLOADS[args.workload][2],
+                   "parallelism": f"{replicas} independent serial replicas on the host cores (the reference CPU path has no threading)"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": replicas, "kind": kind,
+                         "sample": f"each replica evaluates a {sample} per step; requested steps/warmup {args.steps}/{args.warmup} "
+                                   f"bounded to {steps}/{warmup}"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(out), flush=True)
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="fcc4000", choices=sorted(WORKLOADS))
+    ap.add_argument("--dtype", default="float64", choices=["float64", "float32"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extra", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -130,6 +130,19 @@ int smx_last_device_ms(smx_handle h, double* ms);
 /* Number of kernels the evaluator launched since creation (for benchmark bookkeeping). */
 long smx_launch_count(smx_handle h);
 
+/* Measurement helpers; none has a counterpart in the reference (its Kokkos kernels only carry
+ * labels for external tools, e.g. mace_kokkos.cpp:866). smx_timer_start/stop bracket any sequence
+ * of calls with CUDA events on the evaluator's stream and return the elapsed device time.
+ * With profiling on, smx_compute additionally records one event per stage, and smx_stage_time
+ * returns the name and device time of stage `index` (0..14, in execution order) of the last
+ * smx_compute. smx_measure_fma_peak runs a register-only FMA loop and returns the SIMT
+ * fused-multiply-add rate in TFLOP/s, the roof of the FMA-bound edge kernels. */
+int smx_timer_start(smx_handle h);
+int smx_timer_stop(smx_handle h, double* ms);
+int smx_set_profiling(smx_handle h, int enabled);
+int smx_stage_time(smx_handle h, int index, char* name, int name_cap, double* ms);
+int smx_measure_fma_peak(int precision, int device, double* tflops);
+
 /* Neighbour list on the device -- replaces, for callers without their own, the external
  * builders the reference's callers rely on: ase/matscipy `neighbor_list('ijdD', atoms, r_cut)`
  * (symmetrix_calc.py:12-16,77) and the LAMMPS full list filtered by r^2 < r_cut^2

@@ -20,6 +20,7 @@ EXPORTED_SYMBOLS = [
     "smx_create", "smx_destroy", "smx_last_error", "smx_info", "smx_atomic_numbers", "smx_atomic_energies",
     "smx_compute", "smx_begin", "smx_stage", "smx_get_array", "smx_set_array", "smx_reduce_forces",
     "smx_last_device_ms", "smx_launch_count", "smx_build_neighbors", "smx_get_edges", "smx_compute_current",
+    "smx_timer_start", "smx_timer_stop", "smx_set_profiling", "smx_stage_time", "smx_measure_fma_peak",
 ]
 
 
@@ -66,5 +67,10 @@ def load():
     lib.smx_build_neighbors.argtypes = [vp, ctypes.c_int, dp, ip, dp, ip, ctypes.c_double, lp, ctypes.c_int]
     lib.smx_get_edges.argtypes = [vp, ip, ip, ip, ip, dp, dp, ctypes.c_int]
     lib.smx_compute_current.argtypes = [vp]
+    lib.smx_timer_start.argtypes = [vp]
+    lib.smx_timer_stop.argtypes = [vp, ctypes.POINTER(ctypes.c_double)]
+    lib.smx_set_profiling.argtypes = [vp, ctypes.c_int]
+    lib.smx_stage_time.argtypes = [vp, ctypes.c_int, ctypes.c_char_p, ctypes.c_int, ctypes.POINTER(ctypes.c_double)]
+    lib.smx_measure_fma_peak.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.POINTER(ctypes.c_double)]
     _lib = lib
     return lib

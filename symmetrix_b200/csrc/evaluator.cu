@@ -40,6 +40,10 @@ public:
     std::string last_error;
     long launches = 0;
     double last_ms = 0.0;
+    bool profiling = false;
+    std::vector<std::pair<std::string, double>> stage_ms;   // per-stage device time of the last compute (profiling on)
+    virtual void timer_start() = 0;
+    virtual double timer_stop() = 0;
 
     virtual void begin(int N, const int* node_types, const int* num_neigh, const int* neigh_indices,
                        const int* neigh_types, const double* xyz, const double* r, long E, int mem_space) = 0;
@@ -57,7 +61,8 @@ template <typename T>
 class Evaluator final : public EvaluatorBase {
 public:
     cudaStream_t stream = nullptr;
-    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr, evt0 = nullptr, evt1 = nullptr;
+    std::vector<cudaEvent_t> stage_events;
     int num_sms = 148;
 
     // model tables on the device
@@ -95,6 +100,8 @@ public:
         SMX_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
         SMX_CUDA(cudaEventCreate(&ev0));
         SMX_CUDA(cudaEventCreate(&ev1));
+        SMX_CUDA(cudaEventCreate(&evt0));
+        SMX_CUDA(cudaEventCreate(&evt1));
         cudaDeviceProp prop{};
         SMX_CUDA(cudaGetDeviceProperties(&prop, dev));
         num_sms = prop.multiProcessorCount;
@@ -105,6 +112,9 @@ public:
         if (stream) cudaStreamSynchronize(stream);
         if (ev0) cudaEventDestroy(ev0);
         if (ev1) cudaEventDestroy(ev1);
+        if (evt0) cudaEventDestroy(evt0);
+        if (evt1) cudaEventDestroy(evt1);
+        for (auto e : stage_events) cudaEventDestroy(e);
         if (stream) cudaStreamDestroy(stream);
     }
 
@@ -558,20 +568,54 @@ public:
         else throw ArgError("unknown stage '" + s + "'");
     }
 
+    void timer_start() override {
+        SMX_CUDA(cudaSetDevice(device));
+        SMX_CUDA(cudaEventRecord(evt0, stream));
+    }
+    double timer_stop() override {
+        SMX_CUDA(cudaSetDevice(device));
+        SMX_CUDA(cudaEventRecord(evt1, stream));
+        SMX_CUDA(cudaEventSynchronize(evt1));
+        float ms = 0.f;
+        SMX_CUDA(cudaEventElapsedTime(&ms, evt0, evt1));
+        return ms;
+    }
+
     void compute_all() override {   // order of MACE::compute_node_energies_forces, mace.cpp:17-64
         require_edges();
         SMX_CUDA(cudaSetDevice(device));
+        static const char* names[] = {"compute_A0", "compute_M0", "compute_H1", "compute_Phi1", "compute_A1", "compute_M1",
+                                      "compute_H2", "compute_readouts", "reverse_H2", "reverse_M1", "reverse_A1", "reverse_Phi1",
+                                      "reverse_H1", "reverse_M0", "reverse_A0"};
+        constexpr int kStages = 15;
+        if (profiling && stage_events.size() < kStages + 1) {
+            while (stage_events.size() < kStages + 1) {
+                cudaEvent_t e;
+                SMX_CUDA(cudaEventCreate(&e));
+                stage_events.push_back(e);
+            }
+        }
+        int mark = 0;
+        auto tick = [&]() { if (profiling) SMX_CUDA(cudaEventRecord(stage_events[mark++], stream)); };
         SMX_CUDA(cudaEventRecord(ev0, stream));
-        compute_A0(); compute_M0(); compute_H1();
-        compute_Phi1(); compute_A1(); compute_M1(); compute_H2();
-        compute_readouts();
-        reverse_H2(false); reverse_M1(); reverse_A1(); reverse_Phi1(false, false);
-        reverse_H1(); reverse_M0(); reverse_A0();
+        tick(); compute_A0(); tick(); compute_M0(); tick(); compute_H1();
+        tick(); compute_Phi1(); tick(); compute_A1(); tick(); compute_M1(); tick(); compute_H2();
+        tick(); compute_readouts();
+        tick(); reverse_H2(false); tick(); reverse_M1(); tick(); reverse_A1(); tick(); reverse_Phi1(false, false);
+        tick(); reverse_H1(); tick(); reverse_M0(); tick(); reverse_A0(); tick();
         SMX_CUDA(cudaEventRecord(ev1, stream));
         SMX_CUDA(cudaStreamSynchronize(stream));
         float ms = 0.f;
         SMX_CUDA(cudaEventElapsedTime(&ms, ev0, ev1));
         last_ms = ms;
+        if (profiling) {
+            stage_ms.clear();
+            for (int sidx = 0; sidx < kStages; ++sidx) {
+                float t = 0.f;
+                SMX_CUDA(cudaEventElapsedTime(&t, stage_events[sidx], stage_events[sidx + 1]));
+                stage_ms.emplace_back(names[sidx], t);
+            }
+        }
     }
 
     // ------------------------------------------------------------------ array access
@@ -713,6 +757,51 @@ public:
         SMX_CUDA(cudaStreamSynchronize(stream));
     }
 };
+
+// Peak fused-multiply-add rate of the SIMT pipes, measured with independent register chains.
+// The edge kernels are FMA-bound, so this is the roof they are compared with.
+template <typename T>
+__global__ void fma_peak_kernel(T* out, int iters) {
+    T a0 = T(threadIdx.x) * T(1e-3), a1 = a0 + T(1), a2 = a0 + T(2), a3 = a0 + T(3), a4 = a0 + T(4), a5 = a0 + T(5), a6 = a0 + T(6),
+      a7 = a0 + T(7);
+    const T b = T(0.999999), c = T(1e-7);
+    for (int i = 0; i < iters; ++i) {
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            a0 = a0 * b + c; a1 = a1 * b + c; a2 = a2 * b + c; a3 = a3 * b + c;
+            a4 = a4 * b + c; a5 = a5 * b + c; a6 = a6 * b + c; a7 = a7 * b + c;
+        }
+    }
+    out[blockIdx.x * blockDim.x + threadIdx.x] = a0 + a1 + a2 + a3 + a4 + a5 + a6 + a7;
+}
+
+template <typename T>
+double measure_fma_peak(int device) {
+    SMX_CUDA(cudaSetDevice(device));
+    cudaDeviceProp prop{};
+    SMX_CUDA(cudaGetDeviceProperties(&prop, device));
+    const int blocks = prop.multiProcessorCount * 8, threads = 256, iters = 4096;
+    T* out = nullptr;
+    SMX_CUDA(cudaMalloc(&out, sizeof(T) * blocks * threads));
+    cudaEvent_t e0, e1;
+    SMX_CUDA(cudaEventCreate(&e0));
+    SMX_CUDA(cudaEventCreate(&e1));
+    double best = 0.0;
+    for (int rep = 0; rep < 5; ++rep) {
+        SMX_CUDA(cudaEventRecord(e0));
+        fma_peak_kernel<T><<<blocks, threads>>>(out, iters);
+        SMX_CUDA(cudaEventRecord(e1));
+        SMX_CUDA(cudaEventSynchronize(e1));
+        float ms = 0.f;
+        SMX_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+        const double flops = 2.0 * 64.0 * iters * double(blocks) * threads;
+        best = std::max(best, flops / (ms * 1e-3) / 1e12);
+    }
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    cudaFree(out);
+    return best;
+}
 
 }  // namespace smx
 
@@ -857,6 +946,37 @@ int smx_last_device_ms(smx_handle h, double* ms) {
 }
 
 long smx_launch_count(smx_handle h) { return (h && h->impl) ? h->impl->launches : -1; }
+
+int smx_timer_start(smx_handle h) {
+    return guarded(h, [&](smx::EvaluatorBase& e) { e.timer_start(); });
+}
+int smx_timer_stop(smx_handle h, double* ms) {
+    return guarded(h, [&](smx::EvaluatorBase& e) { const double t = e.timer_stop(); if (ms) *ms = t; });
+}
+int smx_set_profiling(smx_handle h, int enabled) {
+    return guarded(h, [&](smx::EvaluatorBase& e) { e.profiling = enabled != 0; });
+}
+int smx_stage_time(smx_handle h, int index, char* name, int name_cap, double* ms) {
+    return guarded(h, [&](smx::EvaluatorBase& e) {
+        if (index < 0 || index >= static_cast<int>(e.stage_ms.size())) throw smx::ArgError("smx_stage_time: index out of range");
+        if (name && name_cap > 0) {
+            std::strncpy(name, e.stage_ms[index].first.c_str(), name_cap - 1);
+            name[name_cap - 1] = 0;
+        }
+        if (ms) *ms = e.stage_ms[index].second;
+    });
+}
+
+int smx_measure_fma_peak(int precision, int device, double* tflops) {
+    try {
+        if (!tflops) throw smx::ArgError("null output");
+        *tflops = precision == SMX_FP32 ? smx::measure_fma_peak<float>(device) : smx::measure_fma_peak<double>(device);
+        return SMX_OK;
+    } catch (const std::exception& e) {
+        g_create_error = e.what();
+        return SMX_ERR_CUDA;
+    }
+}
 
 int smx_build_neighbors(smx_handle h, int num_atoms, const double* positions, const int* types, const double* cell,
                         const int* pbc, double r_cut, long* num_edges, int mem_space) {

@@ -181,6 +181,28 @@ class MACE:
         self._check(self._lib.smx_last_device_ms(self._h, ctypes.byref(ms)))
         return ms.value
 
+    def timer_start(self) -> None:
+        self._check(self._lib.smx_timer_start(self._h))
+
+    def timer_stop(self) -> float:
+        ms = ctypes.c_double(0.0)
+        self._check(self._lib.smx_timer_stop(self._h, ctypes.byref(ms)))
+        return ms.value
+
+    def set_profiling(self, enabled: bool) -> None:
+        self._check(self._lib.smx_set_profiling(self._h, int(bool(enabled))))
+
+    def stage_times(self) -> dict:
+        """Device milliseconds of each stage of the last whole evaluation (profiling must be on)."""
+        out = {}
+        buf = ctypes.create_string_buffer(64)
+        ms = ctypes.c_double(0.0)
+        for idx in range(15):
+            if self._lib.smx_stage_time(self._h, idx, buf, 64, ctypes.byref(ms)) != _lib.SMX_OK:
+                break
+            out[buf.value.decode()] = ms.value
+        return out
+
     @property
     def launch_count(self) -> int:
         return int(self._lib.smx_launch_count(self._h))
