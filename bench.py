@@ -33,6 +33,8 @@ WORKLOADS = {
     "fcc4000": ("fcc128", lambda st, z, seed: st.fcc_box(10, 3.6, z, seed=seed),
                 "configs[1]: 4000-atom FCC (10x10x10 cells, a=3.6 A, 5 species, 0.1 A jitter), model 128x0e+128x1o, "
                 "l_max 3, correlation 3, r_cut 6 A, 10 radial functions, 89-element model exported for the 5 species present"),
+    "fcc1372": ("fcc128", lambda st, z, seed: st.fcc_box(7, 3.6, z, seed=seed),
+                "profiling case: 1372-atom FCC box (7x7x7 cells) of the configs[1] construction and model"),
     "water192": ("water64", lambda st, z, seed: st.water_box(4, 12.42, seed=seed),
                  "configs[0]: 64 H2O (192 atoms) in a 12.42 A cell, model 64x0e, r_cut 5 A"),
 }
@@ -163,16 +165,11 @@ def roofline_for(stage: str, ms: float, n_atoms: int, n_edges: int, K: int, L_ma
         kernel = "layer0_forward_kernel"
     peak, how = measured_peaks()
     achieved = byts / (ms * 1e-3) / 1e9
-    traffic = None
-    tfile = ROOT / "profiles" / "dram_traffic.json"
-    if tfile.exists():
-        try:
-            rec = json.loads(tfile.read_text()).get(kernel)
-            if rec:
-                # captured on a smaller box of the same construction; traffic grows with the edge count
-                traffic = rec["dram_bytes_per_edge"] * n_edges
-        except Exception:
-            traffic = None
+    # dram__bytes_read.sum + dram__bytes_write.sum per edge from the ncu capture summarised in
+    # profiles/edge_kernels_fcc1372_fp64.md (a smaller box of the same construction; traffic grows with the edge count)
+    per_edge = {("tp_reverse_kernel", 8): 11511.0, ("tp_forward_kernel", 8): 5121.0,
+                ("layer0_reverse_kernel", 8): 648.0, ("layer0_forward_kernel", 8): 429.0}.get((kernel, dtype_bytes))
+    traffic = per_edge * n_edges if per_edge and K == 128 and L_max == 1 else None
     return {"bound": "hbm", "kernel": kernel, "stage": stage, "achieved": achieved, "peak": peak, "unit": "GB/s",
             "frac": achieved / peak, "peak_source": f"of {how}", "traffic": traffic, "launch_ms": ms,
             "algorithmic_bytes": byts, "algorithmic_flops": flops, "achieved_tflops": flops / (ms * 1e-3) / 1e12}
@@ -331,7 +328,7 @@ def _cpu_sample_inputs(workload: str, seed: int):
     from symmetrix_b200 import structures as st
     spec_name, _, _ = WORKLOADS[workload]
     path, numbers, spec = model_path(spec_name)
-    if workload == "fcc4000":
+    if workload in ("fcc4000", "fcc1372"):
         s = st.fcc_box(CPU_SAMPLE_CELLS, 3.6, numbers, seed=seed)
         sample = f"{CPU_SAMPLE_CELLS}x{CPU_SAMPLE_CELLS}x{CPU_SAMPLE_CELLS}-cell FCC box ({s.num_atoms} atoms) of the same construction and model"
     else:
@@ -440,7 +437,7 @@ def run_reference(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=40)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="fcc4000", choices=sorted(WORKLOADS))

@@ -298,3 +298,30 @@ def test_error_reporting(tiny):
         ev.get("R7")
     with pytest.raises(SymmetrixError):
         MACE(GOLDEN / "tiny_case.npz")     # not JSON
+
+
+def test_cpp_facade_replays_pair_style_compute(tiny, tmp_path):
+    """tests/facade_harness.cpp: the reference pair style's single-domain loops against the C++ mirror class."""
+    import subprocess
+    case, inputs = tiny
+    root = Path(__file__).resolve().parents[1]
+    pkg = root / "symmetrix_b200"
+    exe = tmp_path / "facade_harness"
+    subprocess.run(["g++", "-std=c++20", f"-I{root / 'include'}", str(root / "tests" / "facade_harness.cpp"), "-o", str(exe),
+                    f"-L{pkg}", "-lsymmetrix_b200", f"-Wl,-rpath,{pkg}"], check=True)
+    with open(tmp_path / "case.bin", "wb") as f:
+        for key, dt in [("node_types", np.int32), ("num_neigh", np.int32), ("neigh_indices", np.int32), ("neigh_types", np.int32),
+                        ("xyz", np.float64), ("r", np.float64)]:
+            a = np.ascontiguousarray(inputs[key], dtype=dt).reshape(-1)
+            f.write(np.int64(a.size).tobytes()); f.write(a.tobytes())
+    subprocess.run([str(exe), str(GOLDEN / "tiny_model.json"), str(tmp_path / "case.bin"), str(tmp_path / "out.bin")], check=True)
+    out = np.fromfile(tmp_path / "out.bin", dtype=np.float64)
+    n = int(inputs["num_nodes"])
+    eng, eng2, f_loop, f_lib = out[0], out[1], out[2:2 + 3 * n], out[2 + 3 * n:]
+    assert abs(eng - case["node_energies"].sum()) < 1e-10 * abs(eng) and abs(eng - eng2) < 1e-12 * abs(eng)
+    nf = case["node_forces"].reshape(-1, 3)
+    recv = np.repeat(np.arange(n), inputs["num_neigh"])
+    want = np.zeros((n, 3))
+    np.add.at(want, recv, -nf); np.add.at(want, inputs["neigh_indices"], nf)
+    np.testing.assert_allclose(f_loop.reshape(n, 3), want, atol=1e-10)
+    np.testing.assert_allclose(f_lib.reshape(n, 3), want, atol=1e-10)

@@ -214,3 +214,15 @@ def test_structures_have_the_requested_shape():
     assert liq.num_atoms == 243
     nl = st.neighbor_list(liq, 0.8)
     assert np.all((nl["i"] // 9) == (nl["j"] // 9))   # no inter-molecular contact below 0.8 A
+
+
+def test_cpp_facade_compiles_and_reports_missing_device(tmp_path):
+    """The C++ mirror of the reference class compiles with g++ alone and links against the library."""
+    import subprocess
+    exe = tmp_path / "facade_harness"
+    pkg = ROOT / "symmetrix_b200"
+    subprocess.run(["g++", "-std=c++20", f"-I{ROOT / 'include'}", str(ROOT / "tests" / "facade_harness.cpp"), "-o", str(exe),
+                    f"-L{pkg}", "-lsymmetrix_b200", f"-Wl,-rpath,{pkg}"], check=True)
+    if not _has_gpu():
+        r = subprocess.run([str(exe), str(GOLDEN / "tiny_model.json"), "/dev/null", str(tmp_path / "o.bin")], capture_output=True, text=True)
+        assert r.returncode == 1 and "no CPU path" in r.stderr
