@@ -160,6 +160,24 @@ int smx_get_edges(smx_handle h, int* num_neigh, int* neigh_indices, int* neigh_t
 /* smx_compute on the current edge set (after smx_build_neighbors). */
 int smx_compute_current(smx_handle h);
 
+/* Energy + virial reduction for callers that cannot let the library allocate device memory: hosts
+ * that give the whole GPU to their own memory pool at start-up, jobs with a fixed device-memory
+ * budget, and step loops that cannot take the device-wide synchronisation of cudaMalloc / cudaFree.
+ * This entry point has no counterpart in the reference (its callers reduce on the host,
+ * pair_symmetrix_mace.cpp:324-368). It computes what smx_reduce_forces returns as `energy` and
+ * `virial` -- out7 = {sum of node_energies, virial xx, yy, zz, xy, xz, yz} -- from device arrays the
+ * caller passes (node_energies[num_nodes], xyz[3*num_edges], node_forces[3*num_edges], out7[7], all
+ * device pointers on the current GPU), asynchronously on `stream` (a cudaStream_t, may be NULL).
+ * It calls no cudaMalloc, cudaFree or allocating library routine: its scratch is a 229,376-byte
+ * array compiled into the library and resident on every GPU that loads it. Limits: at most
+ * 16,777,216 edges and as many nodes; larger inputs return SMX_ERR_INVALID_ARGUMENT with a message
+ * in `errbuf` (capacity `errbuf_len`, may be NULL). All calls on one GPU share the scratch array,
+ * which keeps the previous call's contents: calls whose kernels overlap on the device race. The first
+ * call on each GPU looks up the array's device address; make it before any stream capture starts. */
+int smx_energy_virial_noalloc(const double* node_energies, int num_nodes, const double* xyz,
+                              const double* node_forces, long num_edges, double* out7, void* stream,
+                              char* errbuf, int errbuf_len);
+
 #ifdef __cplusplus
 }
 #endif

@@ -21,6 +21,7 @@ EXPORTED_SYMBOLS = [
     "smx_compute", "smx_begin", "smx_stage", "smx_get_array", "smx_set_array", "smx_reduce_forces",
     "smx_last_device_ms", "smx_launch_count", "smx_build_neighbors", "smx_get_edges", "smx_compute_current",
     "smx_timer_start", "smx_timer_stop", "smx_set_profiling", "smx_stage_time", "smx_measure_fma_peak",
+    "smx_energy_virial_noalloc",
 ]
 
 
@@ -72,5 +73,6 @@ def load():
     lib.smx_set_profiling.argtypes = [vp, ctypes.c_int]
     lib.smx_stage_time.argtypes = [vp, ctypes.c_int, ctypes.c_char_p, ctypes.c_int, ctypes.POINTER(ctypes.c_double)]
     lib.smx_measure_fma_peak.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.POINTER(ctypes.c_double)]
+    lib.smx_energy_virial_noalloc.argtypes = [dp, ctypes.c_int, dp, dp, ctypes.c_long, dp, vp, ctypes.c_char_p, ctypes.c_int]
     _lib = lib
     return lib

@@ -15,7 +15,7 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "libsymmetrix_b200.so"
-SOURCES = [CSRC / "evaluator.cu"]
+SOURCES = [CSRC / "evaluator.cu", CSRC / "noalloc.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-shared", "-Xcudafe", "--diag_suppress=177",
