@@ -191,6 +191,8 @@ def run_ours(args):
 
     from symmetrix_b200 import MACE, _lib
 
+    if world > 1:
+        return run_decomposed(args, rank, world, local_rank, dist)
     path, spec, s, nl, inputs = build_inputs(args.workload, seed=1 + rank)
     n_atoms, n_edges = s.num_atoms, int(inputs["r"].size)
     ev = MACE(path, dtype=args.dtype, device=local_rank)
@@ -312,6 +314,109 @@ def run_ours(args):
         dist.barrier()
         dist.destroy_process_group()
     return out
+
+
+def run_decomposed(args, rank, world, local_rank, dist):
+    """N > 1: one structure, N times longer along x than the single-GPU workload (weak scaling), cut into N slabs
+    with a ghost shell of r_cut; H1 rows forward, H1_adj and force rows back between slab neighbours (NCCL
+    send/recv), energy + virial all-reduced."""
+    import torch
+    from symmetrix_b200 import MACE, structures as st
+    from symmetrix_b200.domain import SlabRank, evaluate_decomposed, make_slab_plan
+
+    spec_name = WORKLOADS[args.workload][0]
+    path, numbers, spec = model_path(spec_name) if rank == 0 else (None, None, None)
+    dist.barrier()
+    path, numbers, spec = model_path(spec_name)
+    cells = {"fcc4000": 10, "fcc1372": 7}.get(args.workload)
+    if cells is None:
+        raise SystemExit("decomposed runs are defined for the FCC workloads")
+    s = st.fcc_box((cells * world, cells, cells), 3.6, numbers, seed=1)
+    ev = MACE(path, dtype=args.dtype, device=local_rank)
+    rk = SlabRank(make_slab_plan(s, spec.r_cut, rank, world), ev, spec.r_cut, numbers)
+    rk.build_edges()
+    flush = torch.empty(256 * 1024 * 1024 // 4, dtype=torch.float32, device=f"cuda:{local_rank}")
+
+    def barrier():
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    def step_device():
+        return evaluate_decomposed([rk], dist=dist)
+
+    def step_host():
+        rk.build_edges()                       # positions from host memory, neighbour list rebuilt on the device
+        e, v, f = evaluate_decomposed([rk], dist=dist)
+        return e, v, f[0].cpu()
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        barrier()
+        total = 0.0
+        for _ in range(steps):
+            flush.zero_()
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            torch.cuda.synchronize()
+            e1.record()
+            e1.synchronize()
+            total += e0.elapsed_time(e1)
+        barrier()
+        return total
+
+    launches0 = ev.launch_count
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    ms = timed(step_device, args.steps, args.warmup)
+    clocks = sampler.stop() if sampler else None
+    launches = ev.launch_count - launches0
+    e2e_ms = timed(step_host, max(2, args.steps // 4), 1)
+    e2e_steps = max(2, args.steps // 4)
+
+    # per-stage device time on this rank (separate passes) -> roofline of the dominant kernel
+    rk.stage_ms = {}
+    prof_steps = 3
+    for _ in range(prof_steps):
+        step_device()
+    stage_ms = {k: v / prof_steps for k, v in rk.stage_ms.items()}
+    rk.stage_ms = None
+    dominant = max(stage_ms, key=stage_ms.get)
+    roof = roofline_for(dominant, stage_ms[dominant], rk.plan.n_own, rk.num_edges, ev.num_channels, ev.L_max,
+                        8 if args.dtype == "float64" else 4)
+    roof["scope"] = "rank 0's slab"
+
+    t = torch.tensor([ms, e2e_ms], dtype=torch.float64, device=f"cuda:{local_rank}")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_max, e2e_max = (float(x) for x in t.cpu())
+    counts = torch.tensor([rk.plan.n_own, rk.plan.n_ghost, rk.num_edges], dtype=torch.float64, device=f"cuda:{local_rank}")
+    dist.all_reduce(counts)
+    if rank == 0:
+        n_total = s.num_atoms
+        width = ev.num_LM * ev.num_channels * (8 if args.dtype == "float64" else 4)
+        out = {
+            "metric": METRIC, "value": n_total * args.steps / (ms_max * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_max / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f64" if args.dtype == "float64" else "f32", "data": "synthetic",
+            "config": {"workload": f"{args.workload} x {world} along x", "description": WORKLOADS[args.workload][2],
+                       "atoms_total": n_total, "atoms_per_gpu": n_total // world, "ghost_rows_total": int(counts[1].item()),
+                       "edges_total": int(counts[2].item()),
+                       "parallelism": f"{world} slabs along x, ghost shell r_cut, halo exchange of H1 / H1_adj / force rows by NCCL send/recv",
+                       "halo_bytes_per_rank_per_exchange": int(counts[1].item() / world * width),
+                       "l2": "256 MB buffer written between timed steps (L2 flush)",
+                       "timing": "CUDA events around each step with a barrier + synchronize on both sides, summed, max over ranks"},
+            "e2e": {"value": n_total * e2e_steps / (e2e_max * 1e-3), "unit": UNIT,
+                    "h2d_bytes_per_step": int((rk.plan.n_own + rk.plan.n_ghost) * 28 * world),
+                    "d2h_bytes_per_step": int(n_total * 24 + 56 * world), "ms_per_step": e2e_max / e2e_steps,
+                    "timing": "per step: local positions/types from host, neighbour list rebuilt on the device, evaluation, owned forces to host"},
+            "gpu_launches": launches * world, "gpu_launches_per_step": launches // (args.steps + args.warmup),
+            "clocks": clocks, "roofline": roof, "stage_ms": stage_ms,
+        }
+        print(json.dumps(out), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+    return None
 
 
 def ctypes_fma_peak(_lib, precision: int, device: int) -> float | None:

@@ -44,6 +44,10 @@ public:
     std::vector<std::pair<std::string, double>> stage_ms;   // per-stage device time of the last compute (profiling on)
     virtual void timer_start() = 0;
     virtual double timer_stop() = 0;
+    virtual void sync() = 0;
+    virtual long restrict_nodes(int num_nodes) = 0;
+    virtual void resize_rows(const std::string& name, int rows) = 0;
+    virtual void* device_ptr(const std::string& name, long* count, int* elem_bytes) = 0;
 
     virtual void begin(int N, const int* node_types, const int* num_neigh, const int* neigh_indices,
                        const int* neigh_types, const double* xyz, const double* r, long E, int mem_space) = 0;
@@ -568,6 +572,39 @@ public:
         else throw ArgError("unknown stage '" + s + "'");
     }
 
+    void sync() override {
+        SMX_CUDA(cudaSetDevice(device));
+        SMX_CUDA(cudaStreamSynchronize(stream));
+    }
+    // Keep only the first `num_nodes` receivers of the current edge set (their rows are a prefix of the edge arrays).
+    long restrict_nodes(int num_nodes) override {
+        require_edges();
+        SMX_CUDA(cudaSetDevice(device));
+        if (num_nodes < 0 || num_nodes > N) throw ArgError("restrict_nodes: num_nodes out of range");
+        long long e = 0;
+        SMX_CUDA(cudaMemcpyAsync(&e, first_neigh.p + num_nodes, sizeof(long long), cudaMemcpyDeviceToHost, stream));
+        SMX_CUDA(cudaStreamSynchronize(stream));
+        adopt_edges(num_nodes, static_cast<long>(e));
+        return static_cast<long>(e);
+    }
+    // Grow H1 / H1_adj to `rows` feature rows keeping the existing rows (ghost rows are appended by the caller).
+    void resize_rows(const std::string& name, int rows) override {
+        SMX_CUDA(cudaSetDevice(device));
+        if (name != "H1" && name != "H1_adj") throw ArgError("resize_rows: only H1 and H1_adj have ghost rows");
+        if (rows < N) throw ArgError("resize_rows: fewer rows than nodes");
+        DevBuf<T>& b = name == "H1" ? H1 : H1_adj;
+        const size_t old = b.n, want = static_cast<size_t>(rows) * model.num_LM * model.K;
+        b.resize(want, stream, true);
+        if (want > old) SMX_CUDA(cudaMemsetAsync(b.p + old, 0, (want - old) * sizeof(T), stream));
+        if (name == "H1") h1_rows = rows;
+        SMX_CUDA(cudaStreamSynchronize(stream));
+    }
+    void* device_ptr(const std::string& name, long* count, int* elem_bytes) override {
+        Field f = field(name);
+        if (count) *count = static_cast<long>(f.t ? f.t->n : f.d->n);
+        if (elem_bytes) *elem_bytes = f.t ? static_cast<int>(sizeof(T)) : 8;
+        return f.t ? static_cast<void*>(f.t->p) : static_cast<void*>(f.d->p);
+    }
     void timer_start() override {
         SMX_CUDA(cudaSetDevice(device));
         SMX_CUDA(cudaEventRecord(evt0, stream));
@@ -947,6 +984,24 @@ int smx_last_device_ms(smx_handle h, double* ms) {
 
 long smx_launch_count(smx_handle h) { return (h && h->impl) ? h->impl->launches : -1; }
 
+int smx_sync(smx_handle h) {
+    return guarded(h, [&](smx::EvaluatorBase& e) { e.sync(); });
+}
+int smx_restrict_nodes(smx_handle h, int num_nodes, long* num_edges) {
+    return guarded(h, [&](smx::EvaluatorBase& e) { const long n = e.restrict_nodes(num_nodes); if (num_edges) *num_edges = n; });
+}
+int smx_resize_rows(smx_handle h, const char* name, int rows) {
+    return guarded(h, [&](smx::EvaluatorBase& e) {
+        if (!name) throw smx::ArgError("smx_resize_rows: null name");
+        e.resize_rows(name, rows);
+    });
+}
+int smx_device_ptr(smx_handle h, const char* name, void** ptr, long* count, int* elem_bytes) {
+    return guarded(h, [&](smx::EvaluatorBase& e) {
+        if (!name || !ptr) throw smx::ArgError("smx_device_ptr: null argument");
+        *ptr = e.device_ptr(name, count, elem_bytes);
+    });
+}
 int smx_timer_start(smx_handle h) {
     return guarded(h, [&](smx::EvaluatorBase& e) { e.timer_start(); });
 }

@@ -1,0 +1,272 @@
+"""Slab domain decomposition of the MACE evaluation across ranks (one GPU per rank).
+
+The scheme is the reference pair style's message-passing mode (pair_symmetrix/pair_symmetrix_mace.cpp:
+376-547): every rank owns the atoms of one slab, sees ghost copies of the atoms within ``r_cut`` of its
+faces, evaluates layer 0 on its own atoms, receives ``H1`` rows for its ghosts, evaluates layer 1 and the
+reverse pass down to ``reverse_Phi1``, returns the ``H1_adj`` rows of its ghosts to their owners (who add
+them), finishes the reverse pass, and finally returns the force rows of its ghosts. What LAMMPS ``Comm``
+does there over MPI (``forward_comm`` / ``reverse_comm``, pack/unpack at pair_symmetrix_mace.cpp:194-238)
+is done here with point-to-point sends between slab neighbours (NCCL over NVLink on GPUs, gloo on CPU).
+
+The decomposition is 1-D along one cell axis; periodic images along the other two axes map to the same
+row (as the single-domain mode does with ``atom->map``, pair_symmetrix_mace.cpp:304-306), images along the
+slab axis are explicit ghost rows. Every rank derives the full plan from the same global structure, so no
+metadata has to be exchanged.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import numpy as np
+
+from .structures import Structure
+
+
+@dataclass
+class SlabPlan:
+    rank: int
+    world: int
+    axis: int
+    n_own: int
+    n_ghost: int
+    own_global: np.ndarray            # [n_own] global atom ids, ascending
+    ghost_global: np.ndarray          # [n_ghost]
+    ghost_owner: np.ndarray           # [n_ghost] owning rank
+    ghost_image: np.ndarray           # [n_ghost] cell shift along the slab axis (-1, 0, +1)
+    positions: np.ndarray             # [n_own + n_ghost, 3] local coordinates (ghosts at their image position)
+    numbers: np.ndarray               # [n_own + n_ghost]
+    cell: np.ndarray                  # [3, 3] cell used for the local neighbour list
+    pbc: tuple
+    peers: list = field(default_factory=list)        # ranks exchanged with, ascending
+    send_rows: dict = field(default_factory=dict)    # peer -> local owned rows, in the peer's ghost order
+    recv_rows: dict = field(default_factory=dict)    # peer -> local ghost rows (ascending)
+
+
+def _ghost_list(frac: np.ndarray, owner: np.ndarray, rank: int, world: int, shell: float):
+    """Ghost images of `rank`: (global id, image shift) of atoms whose image lies in the shell around its slab.
+
+    `frac` is the fractional coordinate along the slab axis, `shell` the ghost width in the same units."""
+    lo, hi = rank / world, (rank + 1) / world
+    out_g, out_n = [], []
+    for n in (-1, 0, 1):
+        x = frac + n
+        sel = ((x >= lo - shell) & (x < lo)) | ((x >= hi) & (x < hi + shell))
+        if n == 0:
+            sel &= owner != rank
+        idx = np.nonzero(sel)[0]
+        out_g.append(idx)
+        out_n.append(np.full(idx.size, n, dtype=np.int64))
+    g = np.concatenate(out_g)
+    n = np.concatenate(out_n)
+    order = np.lexsort((g, n, owner[g]))
+    return g[order], n[order]
+
+
+def make_slab_plan(s: Structure, r_cut: float, rank: int, world: int, axis: int = 0) -> SlabPlan:
+    """Plan of rank `rank` of `world` for structure `s` (positions inside the cell, orthogonal slab axis)."""
+    cell = np.asarray(s.cell, dtype=np.float64)
+    other = [a for a in range(3) if a != axis]
+    if any(abs(cell[axis, o]) > 1e-12 or abs(cell[o, axis]) > 1e-12 for o in other):
+        raise ValueError("the slab axis must be orthogonal to the other two cell vectors")
+    if not s.pbc[axis]:
+        raise ValueError("the slab axis must be periodic")
+    length = cell[axis, axis]
+    if world > 1 and length / world < r_cut:
+        raise ValueError(f"slabs of {length / world:.2f} A are thinner than r_cut = {r_cut} A")
+    pos = np.asarray(s.positions, dtype=np.float64)
+    frac = pos[:, axis] / length
+    owner = np.clip(np.floor(frac * world).astype(np.int64), 0, world - 1)
+    own = np.nonzero(owner == rank)[0]
+    if world == 1:
+        return SlabPlan(rank, world, axis, own.size, 0, own, np.zeros(0, np.int64), np.zeros(0, np.int64), np.zeros(0, np.int64),
+                        pos[own].copy(), np.asarray(s.numbers)[own], cell.copy(), tuple(s.pbc))
+    shell = r_cut / length
+    g, n = _ghost_list(frac, owner, rank, world, shell)
+    gpos = pos[g].copy()
+    gpos[:, axis] += n * length
+    positions = np.concatenate([pos[own], gpos])
+    # local cell: open along the slab axis (ghost images are explicit), periodic as given along the others
+    lcell = cell.copy()
+    lo = rank * length / world - r_cut
+    positions[:, axis] -= lo
+    lcell[axis, axis] = length / world + 2 * r_cut
+    pbc = tuple(False if a == axis else bool(s.pbc[a]) for a in range(3))
+    plan = SlabPlan(rank, world, axis, own.size, g.size, own, g, owner[g], n, positions,
+                    np.concatenate([np.asarray(s.numbers)[own], np.asarray(s.numbers)[g]]), lcell, pbc)
+    plan.peers = sorted(set(int(q) for q in owner[g]))
+    for q in plan.peers:
+        plan.recv_rows[q] = own.size + np.nonzero(owner[g] == q)[0]
+        # what I must send to q: q's ghost list restricted to atoms I own, in q's order
+        gq, _ = _ghost_list(frac, owner, q, world, shell)
+        mine = gq[owner[gq] == rank]
+        plan.send_rows[q] = np.searchsorted(own, mine)
+    return plan
+
+
+class LocalTransport:
+    """All ranks in one process: messages are handed over through a dictionary (tests, 1-GPU emulation)."""
+
+    def __init__(self):
+        self.box = {}
+
+    def post(self, src, dst, tag, tensor):
+        self.box[(src, dst, tag)] = tensor
+
+    def take(self, src, dst, tag):
+        return self.box.pop((src, dst, tag))
+
+
+class SlabRank:
+    """One rank's share of a decomposed evaluation, split into phases between which halos are exchanged.
+
+    `backend` is the evaluator of this rank (``symmetrix_b200.MACE`` on a GPU); `xp` is the array module
+    used for the halo buffers (torch).
+    """
+
+    def __init__(self, plan: SlabPlan, backend, r_cut: float, atomic_numbers):
+        import torch
+        self.torch = torch
+        self.plan = plan
+        self.ev = backend
+        self.rows = plan.n_own + plan.n_ghost
+        self.width = backend.num_LM * backend.num_channels
+        zmap = {int(z): t for t, z in enumerate(atomic_numbers)}
+        self.types = np.array([zmap[int(z)] for z in plan.numbers], dtype=np.int32)
+        self.r_cut = r_cut
+        self.device = self._device()
+        self.send_idx = {q: torch.as_tensor(np.ascontiguousarray(r), dtype=torch.long, device=self.device) for q, r in plan.send_rows.items()}
+        self.recv_idx = {q: torch.as_tensor(np.ascontiguousarray(r), dtype=torch.long, device=self.device) for q, r in plan.recv_rows.items()}
+        self.num_edges = 0
+        self.stage_ms = None          # set to {} to collect per-stage device times (adds a stream sync per stage)
+
+    def _run(self, stage, *flags):
+        if self.stage_ms is None:
+            self.ev._stage(stage, *flags)
+        else:
+            self.ev.timer_start()
+            self.ev._stage(stage, *flags)
+            self.stage_ms[stage] = self.stage_ms.get(stage, 0.0) + self.ev.timer_stop()
+
+    def _device(self):
+        dev = getattr(self.ev, "info", None)
+        return f"cuda:{dev.device}" if dev is not None else "cpu"
+
+    # ---------------------------------------------------------------- phases
+    def build_edges(self):
+        """Neighbour list of the local atoms (owned + ghosts); receivers are the owned atoms only."""
+        p = self.plan
+        self.ev.build_neighbors(p.positions, self.types, p.cell, p.pbc, r_cut=self.r_cut)
+        self.num_edges = self.ev.restrict_nodes(p.n_own)
+
+    def begin_step(self):
+        """Re-arm the current edge set (zero node energies / partial forces) for another evaluation."""
+        self.ev.restrict_nodes(self.plan.n_own)
+
+    def forward_layer0(self):
+        for stage in ("compute_A0", "compute_M0", "compute_H1"):
+            self._run(stage)
+        self.ev.resize_rows("H1", self.rows)
+
+    def _rows_view(self, name):
+        return self.ev.device_view(name).view(-1, self.width)
+
+    def pack_forward(self, peer):
+        self.ev.sync()
+        return self._rows_view("H1").index_select(0, self.send_idx[peer]).contiguous()
+
+    def unpack_forward(self, peer, buf):
+        self._rows_view("H1").index_copy_(0, self.recv_idx[peer], buf.to(self._rows_view("H1").dtype))
+
+    def layer1_and_reverse(self):
+        self._sync_torch()
+        for stage in ("compute_Phi1", "compute_A1", "compute_M1", "compute_H2", "compute_readouts"):
+            self._run(stage)
+        self._run("reverse_H2", True, False)
+        self._run("reverse_M1")
+        self._run("reverse_A1")
+        self._run("reverse_Phi1", False, False)
+
+    def pack_reverse(self, peer):
+        self.ev.sync()
+        return self._rows_view("H1_adj").index_select(0, self.recv_idx[peer]).contiguous()
+
+    def unpack_reverse(self, peer, buf):
+        v = self._rows_view("H1_adj")
+        v.index_add_(0, self.send_idx[peer], buf.to(v.dtype))
+
+    def reverse_layer0(self):
+        self._sync_torch()
+        for stage in ("reverse_H1", "reverse_M0", "reverse_A0"):
+            self._run(stage)
+        forces, virial, energy = self.ev.reduce_forces(num_rows=self.rows)
+        self.forces = self.torch.as_tensor(forces, device=self.device)
+        self.virial, self.energy = virial, energy
+
+    def pack_forces(self, peer):
+        return self.forces.index_select(0, self.recv_idx[peer]).contiguous()
+
+    def unpack_forces(self, peer, buf):
+        self.forces.index_add_(0, self.send_idx[peer], buf)
+
+    def owned_forces(self):
+        return self.forces[: self.plan.n_own]
+
+    def _sync_torch(self):
+        if self.device != "cpu":
+            self.torch.cuda.synchronize()
+
+
+def _exchange(ranks, transport_fn, pack, unpack, dist=None):
+    """One halo exchange. With `dist` (torch.distributed) there is exactly one local rank and messages go
+    point to point; without it `ranks` holds every rank and messages are handed over in memory."""
+    if dist is None:
+        box = {}
+        for r in ranks:
+            for q in r.plan.peers:
+                box[(r.plan.rank, q)] = pack(r, q)
+        for r in ranks:
+            for q in r.plan.peers:
+                unpack(r, q, box[(q, r.plan.rank)])
+        return
+    import torch
+    r = ranks[0]
+    ops, recvs = [], {}
+    sends = {q: pack(r, q) for q in r.plan.peers}
+    for q in r.plan.peers:
+        # the peer sends me what I unpack: shape = [rows I receive for this exchange, width of what I send]
+        n_recv = transport_fn(r, q)
+        recvs[q] = torch.empty((n_recv,) + tuple(sends[q].shape[1:]), dtype=sends[q].dtype, device=sends[q].device)
+        ops.append(dist.P2POp(dist.isend, sends[q], q))
+        ops.append(dist.P2POp(dist.irecv, recvs[q], q))
+    for req in dist.batch_isend_irecv(ops) if ops else []:
+        req.wait()
+    for q in r.plan.peers:
+        unpack(r, q, recvs[q])
+
+
+def evaluate_decomposed(ranks, dist=None):
+    """One energy+force evaluation over all slabs.
+
+    `ranks` is a list of :class:`SlabRank` -- all ranks of the decomposition when `dist` is None (single-
+    process emulation), or the single local rank when `dist` is an initialised ``torch.distributed``.
+    Returns (total energy, virial[6], list of owned-force tensors per local rank).
+    """
+    for r in ranks:
+        r.begin_step()
+        r.forward_layer0()
+    _exchange(ranks, lambda r, q: r.recv_idx[q].numel(), lambda r, q: r.pack_forward(q), lambda r, q, b: r.unpack_forward(q, b), dist)
+    for r in ranks:
+        r.layer1_and_reverse()
+    _exchange(ranks, lambda r, q: r.send_idx[q].numel(), lambda r, q: r.pack_reverse(q), lambda r, q, b: r.unpack_reverse(q, b), dist)
+    for r in ranks:
+        r.reverse_layer0()
+    _exchange(ranks, lambda r, q: r.send_idx[q].numel(), lambda r, q: r.pack_forces(q), lambda r, q, b: r.unpack_forces(q, b), dist)
+    energy = sum(r.energy for r in ranks)
+    virial = sum(np.asarray(r.virial) for r in ranks)
+    if dist is not None:
+        import torch
+        t = torch.tensor([energy, *virial], dtype=torch.float64, device=ranks[0].device)
+        dist.all_reduce(t)
+        vals = t.cpu().numpy()
+        energy, virial = float(vals[0]), vals[1:]
+    return energy, virial, [r.owned_forces() for r in ranks]

@@ -234,6 +234,33 @@ class MACE:
     def compute_current(self) -> None:
         self._check(self._lib.smx_compute_current(self._h))
 
+    # ------------------------------------------------------------------ helpers for decomposed drivers
+    def sync(self) -> None:
+        self._check(self._lib.smx_sync(self._h))
+
+    def restrict_nodes(self, num_nodes: int) -> int:
+        """Keep the first ``num_nodes`` receivers of the current edge set (owned atoms first); returns the edge count."""
+        n = ctypes.c_long(0)
+        self._check(self._lib.smx_restrict_nodes(self._h, int(num_nodes), ctypes.byref(n)))
+        self._num_nodes, self._num_edges = int(num_nodes), n.value
+        return n.value
+
+    def resize_rows(self, name: str, rows: int) -> None:
+        self._check(self._lib.smx_resize_rows(self._h, name.encode(), int(rows)))
+
+    def device_view(self, name: str):
+        """Zero-copy torch view (1-D, float32 or float64) of a named device array; valid until that array is resized."""
+        import torch
+        ptr, n, eb = ctypes.c_void_p(), ctypes.c_long(0), ctypes.c_int(0)
+        self._check(self._lib.smx_device_ptr(self._h, name.encode(), ctypes.byref(ptr), ctypes.byref(n), ctypes.byref(eb)))
+        if n.value == 0:
+            return torch.empty(0, dtype=torch.float64 if eb.value == 8 else torch.float32, device=f"cuda:{self.info.device}")
+
+        class _View:
+            __cuda_array_interface__ = {"shape": (n.value,), "typestr": "<f8" if eb.value == 8 else "<f4",
+                                        "data": (ptr.value, False), "version": 2}
+        return torch.as_tensor(_View(), device=f"cuda:{self.info.device}")
+
 
 def _array_property(name):
     def getter(self):

@@ -1,0 +1,67 @@
+"""Test infrastructure: the numpy oracle dressed as an evaluator backend for ``symmetrix_b200.domain``,
+so that the decomposition logic (plans, halo exchanges, multi-process runs over gloo) can be tested
+without a GPU. Never used by the product."""
+import numpy as np
+import torch
+
+from oracle.mace_numpy import MaceOracle
+from symmetrix_b200 import structures as st
+
+
+class OracleBackend:
+    def __init__(self, model):
+        self.o = MaceOracle(model)
+        self.num_LM = self.o.nLM
+        self.num_channels = self.o.K
+        self.atomic_numbers = self.o.atomic_numbers
+        self.inputs = None
+
+    def build_neighbors(self, positions, types, cell, pbc, r_cut):
+        s = st.Structure(np.asarray(positions), np.asarray(cell), np.asarray(types), tuple(pbc))
+        nl = st.neighbor_list(s, r_cut)
+        self.nl = nl
+        n = s.num_atoms
+        self.inputs = {"num_nodes": n, "node_types": np.asarray(types, np.int32),
+                       "num_neigh": np.bincount(nl["i"], minlength=n).astype(np.int32), "neigh_indices": nl["j"],
+                       "neigh_types": np.asarray(types, np.int32)[nl["j"]], "xyz": nl["D"].reshape(-1), "r": nl["d"]}
+        return nl["i"].size
+
+    def restrict_nodes(self, n_own):
+        inp = self.inputs
+        e = int(np.sum(inp["num_neigh"][:n_own]))
+        self.inputs = {"num_nodes": n_own, "node_types": inp["node_types"][:n_own], "num_neigh": inp["num_neigh"][:n_own],
+                       "neigh_indices": inp["neigh_indices"][:e], "neigh_types": inp["neigh_types"][:e],
+                       "xyz": inp["xyz"][:3 * e], "r": inp["r"][:e]}
+        self.o._edges(self.inputs)
+        self.o.node_forces = np.zeros((e, 3))
+        self.o.compute_Y(); self.o.compute_R0(); self.o.compute_R1()
+        return e
+
+    def _stage(self, name, zero_dxyz=True, zero_H1_adj=True):
+        getattr(self.o, name)()
+
+    def resize_rows(self, name, rows):
+        arr = getattr(self.o, name)
+        extra = rows - arr.shape[0]
+        setattr(self.o, name, np.ascontiguousarray(np.concatenate([arr, np.zeros((extra,) + arr.shape[1:])])))
+
+    def device_view(self, name):
+        arr = getattr(self.o, name)
+        assert arr.flags["C_CONTIGUOUS"]
+        return torch.from_numpy(arr.reshape(-1))
+
+    def sync(self):
+        pass
+
+    def reduce_forces(self, num_rows):
+        inp = self.inputs
+        nf = self.o.node_forces
+        recv = np.repeat(np.arange(inp["num_nodes"]), inp["num_neigh"])
+        f = np.zeros((num_rows, 3))
+        np.add.at(f, recv, -nf)
+        np.add.at(f, inp["neigh_indices"], nf)
+        x = inp["xyz"].reshape(-1, 3)
+        v = np.array([np.sum(x[:, 0] * nf[:, 0]), np.sum(x[:, 1] * nf[:, 1]), np.sum(x[:, 2] * nf[:, 2]),
+                      0.5 * np.sum(x[:, 0] * nf[:, 1] + x[:, 1] * nf[:, 0]), 0.5 * np.sum(x[:, 0] * nf[:, 2] + x[:, 2] * nf[:, 0]),
+                      0.5 * np.sum(x[:, 1] * nf[:, 2] + x[:, 2] * nf[:, 1])])
+        return f, v, float(self.o.node_energies.sum())
