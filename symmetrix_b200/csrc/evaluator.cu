@@ -70,9 +70,9 @@ public:
     int num_sms = 148;
 
     // model tables on the device
-    DevBuf<T> coef0, coef1, H0_w, A0_w, H1_w, A1_w, H2_w_H1, H2_w_M1, ro1, ro2_w1, ro2_w2, z_c, coefM0, coefM1;
+    DevBuf<T> coef0, coef1, H0_w, A0_w, H1_w, A1_w, H2_w_H1, H2_w_M1, ro1, ro2_w1, ro2_w2, coefM0, coefM1;
     DevBuf<double> E0;
-    DevBuf<int> z_ptr, z_lm1, prog0, prog0_off, mono0_off, prog1, prog1_off, mono1_off;
+    DevBuf<int> prog0, prog0_off, mono0_off, prog1, prog1_off, mono1_off;
     SplineMeta sm{};
 
     // current edge set
@@ -135,12 +135,9 @@ public:
         ro1.upload(cast_vec<T>(m.ro1), stream);
         ro2_w1.upload(cast_vec<T>(m.ro2_w1), stream);
         ro2_w2.upload(cast_vec<T>(m.ro2_w2), stream);
-        z_c.upload(cast_vec<T>(m.z_c), stream);
         coefM0.upload(cast_vec<T>(m.coef_M0), stream);
         coefM1.upload(cast_vec<T>(m.coef_M1), stream);
         E0.upload(m.atomic_energies, stream);
-        z_ptr.upload(m.z_ptr, stream);
-        z_lm1.upload(m.z_lm1, stream);
         {
             std::vector<int> words, offs;
             for (const auto& p : m.prog0) { offs.push_back(static_cast<int>(words.size())); words.insert(words.end(), p.words.begin(), p.words.end()); }
@@ -425,7 +422,6 @@ public:
         a.N = N; a.K = model.K;
         a.node_types = node_types; a.first_neigh = first_neigh.p; a.neigh_indices = neigh_indices; a.neigh_types = neigh_types;
         a.xyz = xyz; a.r = r; a.coef1 = coef1.p; a.sm = sm;
-        a.z_ptr = z_ptr.p; a.z_lm1 = z_lm1.p; a.z_c = z_c.p;
         a.H = H1.p; a.Phi1 = Phi1.p; a.dPhi1 = dPhi1.p; a.Hmsg = Hmsg.p; a.node_forces = node_forces.p;
         return a;
     }

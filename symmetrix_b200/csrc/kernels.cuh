@@ -22,8 +22,6 @@ namespace smx {
 constexpr int kEdgeBatch = 8;       // edges staged in shared memory per pass
 constexpr int kChannelBlock = 128;  // threads per CTA of the edge kernels; more channels are done in chunks
 constexpr int kMaxWarps = kChannelBlock / 32;
-// the coupling blocks of the L_max = 2 tensor product are three times larger: stage fewer edges
-constexpr int tp_edge_batch(int LF) { return LF >= 2 ? 4 : kEdgeBatch; }
 
 // Compile-time loop: f(std::integral_constant<int, 0>{}), ..., f(std::integral_constant<int, N-1>{}).
 // The tensor-product kernels index their register accumulators with path-dependent offsets, which
@@ -64,6 +62,54 @@ __device__ __forceinline__ T warp_sum(T v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     return v;
+}
+
+// Sum each of 16 per-lane values over the warp with 16 shuffles instead of 80: every step halves the
+// number of values a lane carries by exchanging the other half with its partner. On return the lane
+// holds the warp-wide sum of value `index` (lanes that differ only in bit 0 hold the same value).
+template <typename T>
+__device__ __forceinline__ T warp_reduce_scatter16(const T (&v)[16], int lane, int& index) {
+    const bool b4 = lane & 16, b3 = lane & 8, b2 = lane & 4, b1 = lane & 2;
+    T w8[8], w4[4], w2[2];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const T send = b4 ? v[i] : v[i + 8], keep = b4 ? v[i + 8] : v[i];
+        w8[i] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const T send = b3 ? w8[i] : w8[i + 4], keep = b3 ? w8[i + 4] : w8[i];
+        w4[i] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const T send = b2 ? w4[i] : w4[i + 2], keep = b2 ? w4[i + 2] : w4[i];
+        w2[i] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+    }
+    const T send = b1 ? w2[0] : w2[1], keep = b1 ? w2[1] : w2[0];
+    T w1 = keep + __shfl_xor_sync(0xffffffffu, send, 2);
+    w1 += __shfl_xor_sync(0xffffffffu, w1, 1);
+    index = (b4 ? 8 : 0) + (b3 ? 4 : 0) + (b2 ? 2 : 0) + (b1 ? 1 : 0);
+    return w1;
+}
+
+// Per-edge partial force from the warp-reduced adjoints, written by one thread per edge:
+//   nf -= xhat * dE/dr + sum_lm dE/dY_lm * grad Y_lm
+// red[w][e][0..15] = dE/dY_lm summed over the channels of warp w, red[w][e][16] = dE/dr.
+template <typename T, int EB>
+__device__ __forceinline__ void finish_edge_force(const T (*red)[EB][17], int nwarps, int e, const T* dY0, const T* dY1, const T* dY2,
+                                                  T ux, T uy, T uz, double* nf) {
+    double tr = 0, fx = 0, fy = 0, fz = 0;
+    for (int w = 0; w < nwarps; ++w) tr += red[w][e][16];
+#pragma unroll
+    for (int lm = 0; lm < kNumLm; ++lm) {
+        double wv = 0;
+        for (int w = 0; w < nwarps; ++w) wv += red[w][e][lm];
+        fx += wv * double(dY0[lm]); fy += wv * double(dY1[lm]); fz += wv * double(dY2[lm]);
+    }
+    nf[0] -= double(ux) * tr + fx;
+    nf[1] -= double(uy) * tr + fy;
+    nf[2] -= double(uz) * tr + fz;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -230,7 +276,7 @@ __global__ void __launch_bounds__(kChannelBlock) layer0_forward_kernel(const Lay
 template <typename T>
 __global__ void __launch_bounds__(kChannelBlock) layer0_reverse_kernel(const Layer0Args<T> a) {
     __shared__ EdgeStage<T> st[kEdgeBatch];
-    __shared__ T red[kMaxWarps][kEdgeBatch][4];
+    __shared__ T red[kMaxWarps][kEdgeBatch][17];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
     const int F = (kLmaxSH + 1) * a.K;
     for (int i = blockIdx.x; i < a.N; i += gridDim.x)
@@ -251,7 +297,9 @@ __global__ void __launch_bounds__(kChannelBlock) layer0_reverse_kernel(const Lay
             __syncthreads();
             for (int e = 0; e < nb; ++e) {
                 const EdgeStage<T>& s = st[e];
-                T fr = 0, fx = 0, fy = 0, fz = 0;
+                T W[kNumLm], fr = 0;     // adjoints of the harmonics and of the edge length, this channel
+#pragma unroll
+                for (int lm = 0; lm < kNumLm; ++lm) W[lm] = T(0);
                 if (active) {
                     const T h0 = a.H0_w[s.tj * a.K + k];
                     const T x = s.x;
@@ -261,42 +309,39 @@ __global__ void __launch_bounds__(kChannelBlock) layer0_reverse_kernel(const Lay
                         const Vec4<T> c = load4<T>(cb + 4 * l * a.K);
                         const T R = (c.x + x * (c.y + x * (c.z + x * c.w))) * h0;
                         const T Rd = (c.y + x * (T(2) * c.z + T(3) * x * c.w)) * h0;
-                        T sv = 0, gx = 0, gy = 0, gz = 0;
+                        T sv = 0;
 #pragma unroll
                         for (int lm = l * l; lm < (l + 1) * (l + 1); ++lm) {
                             sv += d[lm] * s.Y[lm];
-                            gx += d[lm] * s.dY[0][lm];
-                            gy += d[lm] * s.dY[1][lm];
-                            gz += d[lm] * s.dY[2][lm];
+                            W[lm] = R * d[lm];
                         }
-                        fr += Rd * sv; fx += R * gx; fy += R * gy; fz += R * gz;
+                        fr += Rd * sv;
                     }
                 }
-                fr = warp_sum(fr); fx = warp_sum(fx); fy = warp_sum(fy); fz = warp_sum(fz);
-                if (lane == 0) { red[warp][e][0] = fr; red[warp][e][1] = fx; red[warp][e][2] = fy; red[warp][e][3] = fz; }
+                int idx;
+                const T wsum = warp_reduce_scatter16(W, lane, idx);
+                fr = warp_sum(fr);
+                if ((lane & 1) == 0) red[warp][e][idx] = wsum;
+                if (lane == 0) red[warp][e][16] = fr;
             }
             __syncthreads();
             if (threadIdx.x < nb) {
                 const int e = threadIdx.x;
-                double tr = 0, tx = 0, ty = 0, tz = 0;
-                for (int w = 0; w < nwarps; ++w) { tr += red[w][e][0]; tx += red[w][e][1]; ty += red[w][e][2]; tz += red[w][e][3]; }
-                double* nf = a.node_forces + 3 * (e0 + e);
-                nf[0] -= double(st[e].ux) * tr + tx;
-                nf[1] -= double(st[e].uy) * tr + ty;
-                nf[2] -= double(st[e].uz) * tr + tz;
+                finish_edge_force<T, kEdgeBatch>(red, nwarps, e, st[e].dY[0], st[e].dY[1], st[e].dY[2], st[e].ux, st[e].uy, st[e].uz,
+                                                 a.node_forces + 3 * (e0 + e));
             }
         }
     }
 }
 
 // =============================================================================================
-// Layer 1 tensor product.
-// Per edge the CTA first builds, for every path p, the coupling block
-//     Z_p[m, m2] = sum_{m1} C^{l m}_{l1 m1, l2 m2} Y_ij[l1 m1]         (channel-independent)
-// and then every channel does
-//     Phi1[i, (l m e_p), k] += R1_p(r_ij)[k] * sum_{m2} Z_p[m, m2] H1[j, (l2 m2), k].
-// This equals the reference's two-step form (Phi1r, then the Clebsch-Gordan COO contraction,
-// mace.cpp:453-502) with the sums reordered; Phi1r is never formed.
+// Layer 1 tensor product. Per (edge, channel):
+//     Phi1[i, (l m e_p), k] += R1_p(r_ij)[k] * sum_{m1 m2} C^{l m}_{l1 m1, l2 m2} Y_ij[l1 m1] H1[j, (l2 m2), k]
+// which is the reference's two-step form (Phi1r, then the Clebsch-Gordan COO contraction,
+// mace.cpp:453-502) with the sums merged; Phi1r is never formed. The non-zeros of the coupling are
+// written out as straight-line code (generated/tp_L*_forward.inc), so the accumulators stay in
+// registers and the coupling constants are immediates; the only shared-memory traffic per edge is
+// the 16 harmonics. Any per-path scale of a model file's coupling table is folded into R1_p at load.
 // =============================================================================================
 template <typename T>
 struct TPArgs {
@@ -304,7 +349,6 @@ struct TPArgs {
     const int* node_types; const long long* first_neigh; const int* neigh_indices; const int* neigh_types;
     const double* xyz; const double* r;
     const T* coef1; SplineMeta sm;
-    const int* z_ptr; const int* z_lm1; const T* z_c;   // coupling entries per block entry
     const T* H;             // sender features [rows][nLM][K]
     T* Phi1;                // forward output [N][Q][K]
     const T* dPhi1;         // reverse input  [N][Q][K]
@@ -315,9 +359,7 @@ struct TPArgs {
 template <typename T, int LF>
 __global__ void __launch_bounds__(kChannelBlock) tp_forward_kernel(const TPArgs<T> a) {
     constexpr TPTable tp = make_tp_table(LF);
-    constexpr int kEdgeBatch = tp_edge_batch(LF);
     __shared__ EdgeStage<T> st[kEdgeBatch];
-    __shared__ T Z[kEdgeBatch][tp.NZ];
     const int F = tp.P * a.K;
     for (int i = blockIdx.x; i < a.N; i += gridDim.x)
     for (int kc = 0; kc < a.K; kc += blockDim.x) {
@@ -334,38 +376,29 @@ __global__ void __launch_bounds__(kChannelBlock) tp_forward_kernel(const TPArgs<
             if (threadIdx.x < nb)
                 stage_edge<T, false>(st[threadIdx.x], e0 + threadIdx.x, type_i, a.neigh_indices, a.neigh_types, a.xyz, a.r, a.sm, F);
             __syncthreads();
-            for (int w = threadIdx.x; w < nb * tp.NZ; w += blockDim.x) {
-                const int e = w / tp.NZ, z = w - e * tp.NZ;
-                T v = 0;
-                for (int n = a.z_ptr[z]; n < a.z_ptr[z + 1]; ++n) v += a.z_c[n] * st[e].Y[a.z_lm1[n]];
-                Z[e][z] = v;
-            }
-            __syncthreads();
             if (active) {
                 for (int e = 0; e < nb; ++e) {
                     const EdgeStage<T>& s = st[e];
                     const T x = s.x;
                     const T* cb = a.coef1 + s.coef_base + 4 * k;
                     const T* hrow = a.H + static_cast<size_t>(s.j) * tp.nLM * a.K + k;
-                    T h[tp.nLM];
+                    T h[tp.nLM], R[tp.P], Y[kNumLm];
 #pragma unroll
                     for (int lm2 = 0; lm2 < tp.nLM; ++lm2) h[lm2] = __ldg(hrow + static_cast<size_t>(lm2) * a.K);
-                    const T* zrow = Z[e];
-                    static_for<tp.P>([&](auto pc) {
-                        constexpr int p = decltype(pc)::value;
-                        constexpr int l = TPConst<LF>::t.l[p], l2 = TPConst<LF>::t.l2[p], n2 = 2 * l2 + 1, zo = TPConst<LF>::t.zoff[p];
+#pragma unroll
+                    for (int p = 0; p < tp.P; ++p) {
                         const Vec4<T> c = load4<T>(cb + 4 * p * a.K);
-                        const T R = c.x + x * (c.y + x * (c.z + x * c.w));
-                        static_for<2 * l + 1>([&](auto mc) {
-                            constexpr int m = decltype(mc)::value;
-                            T tmp = 0;
-                            static_for<n2>([&](auto m2c) {
-                                constexpr int m2 = decltype(m2c)::value;
-                                tmp += zrow[zo + m * n2 + m2] * h[l2 * l2 + m2];
-                            });
-                            acc[TPConst<LF>::t.lme(p, m)] += R * tmp;
-                        });
-                    });
+                        R[p] = c.x + x * (c.y + x * (c.z + x * c.w));
+                    }
+#pragma unroll
+                    for (int lm = 0; lm < kNumLm; ++lm) Y[lm] = s.Y[lm];
+                    if constexpr (LF == 0) {
+#include "generated/tp_L0_forward.inc"
+                    } else if constexpr (LF == 1) {
+#include "generated/tp_L1_forward.inc"
+                    } else {
+#include "generated/tp_L2_forward.inc"
+                    }
                 }
             }
         }
@@ -377,17 +410,17 @@ __global__ void __launch_bounds__(kChannelBlock) tp_forward_kernel(const TPArgs<
     }
 }
 
-// Reverse of the tensor product (MACE::reverse_Phi1, mace.cpp:504-605) for one receiver per CTA:
-//   message to the sender   Hmsg[ij, (l2 m2), k] = sum_p R1_p[k] sum_m Z_p[m, m2] dPhi1[i, (l m e_p), k]
-//   partial force           nf[ij] -= xhat * sum_{p,k} R1_p'[k] q_p[k] + sum_{p,k} R1_p[k] q^c_p[k]
-// with q_p = sum_{m,m2} Z_p[m,m2] dPhi1 H1_j and q^c_p the same with Z built from d Y / d xyz_c.
+// Reverse of the tensor product (MACE::reverse_Phi1, mace.cpp:504-605) for one receiver per CTA.
+// Per (edge, channel) the generated code (generated/tp_L*_reverse.inc) produces the three adjoints of
+// the trilinear form: msg = dE/dH1_j (written to Hmsg, summed per sender afterwards), W = dE/dY_ij and
+// fr = dE/dr_ij. W and fr are summed over channels (warp reduce-scatter, then across warps in shared
+// memory) and one thread per edge turns them into the partial force
+//   nf[ij] -= xhat * fr + sum_lm W[lm] * grad Y[lm].
 template <typename T, int LF>
 __global__ void __launch_bounds__(kChannelBlock) tp_reverse_kernel(const TPArgs<T> a) {
     constexpr TPTable tp = make_tp_table(LF);
-    constexpr int kEdgeBatch = tp_edge_batch(LF);
     __shared__ EdgeStage<T> st[kEdgeBatch];
-    __shared__ Vec4<T> Z4[kEdgeBatch][tp.NZ];     // {Z, Zx, Zy, Zz}
-    __shared__ T red[kMaxWarps][kEdgeBatch][4];
+    __shared__ T red[kMaxWarps][kEdgeBatch][17];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
     const int F = tp.P * a.K;
     for (int i = blockIdx.x; i < a.N; i += gridDim.x)
@@ -406,66 +439,48 @@ __global__ void __launch_bounds__(kChannelBlock) tp_reverse_kernel(const TPArgs<
             if (threadIdx.x < nb)
                 stage_edge<T, true>(st[threadIdx.x], e0 + threadIdx.x, type_i, a.neigh_indices, a.neigh_types, a.xyz, a.r, a.sm, F);
             __syncthreads();
-            for (int w = threadIdx.x; w < nb * tp.NZ; w += blockDim.x) {
-                const int e = w / tp.NZ, z = w - e * tp.NZ;
-                T v = 0, vx = 0, vy = 0, vz = 0;
-                for (int n = a.z_ptr[z]; n < a.z_ptr[z + 1]; ++n) {
-                    const T c = a.z_c[n];
-                    const int lm1 = a.z_lm1[n];
-                    v += c * st[e].Y[lm1]; vx += c * st[e].dY[0][lm1]; vy += c * st[e].dY[1][lm1]; vz += c * st[e].dY[2][lm1];
-                }
-                Z4[e][z] = {v, vx, vy, vz};
-            }
-            __syncthreads();
             for (int e = 0; e < nb; ++e) {
                 const EdgeStage<T>& s = st[e];
-                T fr = 0, fx = 0, fy = 0, fz = 0;
+                T W[kNumLm], fr = 0;
+#pragma unroll
+                for (int lm = 0; lm < kNumLm; ++lm) W[lm] = T(0);
                 if (active) {
                     const T x = s.x;
                     const T* cb = a.coef1 + s.coef_base + 4 * k;
                     const T* hrow = a.H + static_cast<size_t>(s.j) * tp.nLM * a.K + k;
-                    T h[tp.nLM], msg[tp.nLM];
+                    T h[tp.nLM], msg[tp.nLM], R[tp.P], Rd[tp.P], Y[kNumLm];
 #pragma unroll
                     for (int lm2 = 0; lm2 < tp.nLM; ++lm2) { h[lm2] = __ldg(hrow + static_cast<size_t>(lm2) * a.K); msg[lm2] = T(0); }
-                    const Vec4<T>* zrow = Z4[e];
-                    static_for<tp.P>([&](auto pc) {
-                        constexpr int p = decltype(pc)::value;
-                        constexpr int l = TPConst<LF>::t.l[p], l2 = TPConst<LF>::t.l2[p], n2 = 2 * l2 + 1, zo = TPConst<LF>::t.zoff[p];
+#pragma unroll
+                    for (int p = 0; p < tp.P; ++p) {
                         const Vec4<T> c = load4<T>(cb + 4 * p * a.K);
-                        const T R = c.x + x * (c.y + x * (c.z + x * c.w));
-                        const T Rd = c.y + x * (T(2) * c.z + T(3) * x * c.w);
-                        T q = 0, qx = 0, qy = 0, qz = 0;
-                        static_for<n2>([&](auto m2c) {
-                            constexpr int m2 = decltype(m2c)::value;
-                            T u = 0, ux = 0, uy = 0, uz = 0;
-                            static_for<2 * l + 1>([&](auto mc) {
-                                constexpr int m = decltype(mc)::value;
-                                const Vec4<T> zz = zrow[zo + m * n2 + m2];
-                                const T dv = d[TPConst<LF>::t.lme(p, m)];
-                                u += zz.x * dv; ux += zz.y * dv; uy += zz.z * dv; uz += zz.w * dv;
-                            });
-                            const T hv = h[l2 * l2 + m2];
-                            msg[l2 * l2 + m2] += R * u;
-                            q += hv * u; qx += hv * ux; qy += hv * uy; qz += hv * uz;
-                        });
-                        fr += Rd * q; fx += R * qx; fy += R * qy; fz += R * qz;
-                    });
+                        R[p] = c.x + x * (c.y + x * (c.z + x * c.w));
+                        Rd[p] = c.y + x * (T(2) * c.z + T(3) * x * c.w);
+                    }
+#pragma unroll
+                    for (int lm = 0; lm < kNumLm; ++lm) Y[lm] = s.Y[lm];
+                    if constexpr (LF == 0) {
+#include "generated/tp_L0_reverse.inc"
+                    } else if constexpr (LF == 1) {
+#include "generated/tp_L1_reverse.inc"
+                    } else {
+#include "generated/tp_L2_reverse.inc"
+                    }
                     T* mrow = a.Hmsg + static_cast<size_t>(e0 + e) * tp.nLM * a.K + k;
 #pragma unroll
                     for (int lm2 = 0; lm2 < tp.nLM; ++lm2) mrow[static_cast<size_t>(lm2) * a.K] = msg[lm2];
                 }
-                fr = warp_sum(fr); fx = warp_sum(fx); fy = warp_sum(fy); fz = warp_sum(fz);
-                if (lane == 0) { red[warp][e][0] = fr; red[warp][e][1] = fx; red[warp][e][2] = fy; red[warp][e][3] = fz; }
+                int idx;
+                const T wsum = warp_reduce_scatter16(W, lane, idx);
+                fr = warp_sum(fr);
+                if ((lane & 1) == 0) red[warp][e][idx] = wsum;
+                if (lane == 0) red[warp][e][16] = fr;
             }
             __syncthreads();
             if (threadIdx.x < nb) {
                 const int e = threadIdx.x;
-                double tr = 0, tx = 0, ty = 0, tz = 0;
-                for (int w = 0; w < nwarps; ++w) { tr += red[w][e][0]; tx += red[w][e][1]; ty += red[w][e][2]; tz += red[w][e][3]; }
-                double* nf = a.node_forces + 3 * (e0 + e);
-                nf[0] -= double(st[e].ux) * tr + tx;
-                nf[1] -= double(st[e].uy) * tr + ty;
-                nf[2] -= double(st[e].uz) * tr + tz;
+                finish_edge_force<T, kEdgeBatch>(red, nwarps, e, st[e].dY[0], st[e].dY[1], st[e].dY[2], st[e].ux, st[e].uy, st[e].uz,
+                                                 a.node_forces + 3 * (e0 + e));
             }
         }
     }

@@ -16,6 +16,7 @@
 
 #include "json_min.hpp"
 #include "tp_tables.hpp"
+#include "generated/cg_canon.hpp"
 
 namespace smx {
 
@@ -106,12 +107,12 @@ struct HostModel {
     std::vector<double> ro2_w2;      // [16]
     double ro2_scale = 1.0;
 
-    // tensor product: canonical table + coupling entries per (path block entry z): Z[z] = sum C * Y[lm1]
+    // tensor product: canonical path table; the file's Clebsch-Gordan COO must equal the canonical non-zeros
+    // (generated/cg_canon.hpp) up to one scale per path, which is folded into that path's radial functions
     TPTable tp{};
     std::vector<int> path_file_to_canon;   // index by the file's path number
     std::vector<int> lme_file_to_canon;    // output slot permutation (identity for canonical files)
-    std::vector<int> z_ptr, z_lm1;
-    std::vector<double> z_c;
+    std::vector<double> path_scale;        // per canonical path: file coupling / canonical coupling
 
     // symmetric contractions: programs per LM (M0) and one for M1; coefficients [element][monomial][K]
     std::vector<PolyProgram> prog0;
@@ -221,12 +222,20 @@ inline HostModel load_model_file(const std::string& filename) {
         for (int mm = 0; mm < 2 * l + 1; ++mm)
             m.lme_file_to_canon[file_lme_off[l] + mm * file_ne[l] + file_e[p]] = m.tp.lme(c, mm);
     }
-    {   // coupling entries grouped by block entry z
+    {   // compare the file's coupling entries with the canonical non-zeros, path by path
         const std::vector<int> cg_lme = file.at("Phi1_lme").flat_int(), cg_t = file.at("Phi1_lelm1lm2").flat_int();
         const std::vector<double> cg_c = file.at("Phi1_clebsch_gordan").flat();
         if (cg_lme.size() != cg_c.size() || cg_t.size() != cg_c.size())
             throw ModelError("model file: Clebsch-Gordan COO arrays differ in length");
-        std::vector<std::vector<std::pair<int, double>>> per_z(m.tp.NZ);
+        const CanonCG* canon = nullptr;
+        int n_canon = 0;
+        switch (m.L_max) {
+            case 0: canon = CanonCGTable<0>::e; n_canon = CanonCGTable<0>::n; break;
+            case 1: canon = CanonCGTable<1>::e; n_canon = CanonCGTable<1>::n; break;
+            default: canon = CanonCGTable<2>::e; n_canon = CanonCGTable<2>::n; break;
+        }
+        std::vector<double> file_val(n_canon, 0.0);
+        std::vector<int> hits(n_canon, 0);
         for (size_t n = 0; n < cg_c.size(); ++n) {
             const int t = cg_t[n], lme = cg_lme[n];
             if (t < 0 || t >= file_toff[P] || lme < 0 || lme >= m.tp.Q) throw ModelError("Clebsch-Gordan index out of range");
@@ -235,19 +244,31 @@ inline HostModel load_model_file(const std::string& filename) {
             const int l = pl[p], l1 = pl1[p], l2 = pl2[p];
             const int rem = t - file_toff[p];
             const int i1 = rem / (2 * l2 + 1), i2 = rem % (2 * l2 + 1);
-            // the output slot must belong to the same path
-            const int rel = lme - file_lme_off[l];
+            const int rel = lme - file_lme_off[l];   // the output slot must belong to the same path
             if (rel < 0 || rel >= (2 * l + 1) * file_ne[l] || rel % file_ne[l] != file_e[p])
                 throw ModelError("Clebsch-Gordan entry couples a path to another path's output slot");
             const int mm = rel / file_ne[l];
             const int c = m.path_file_to_canon[p];
-            const int z = m.tp.zoff[c] + mm * (2 * l2 + 1) + i2;
-            per_z[z].emplace_back(l1 * l1 + i1, cg_c[n]);
+            int found = -1;
+            for (int q = 0; q < n_canon; ++q)
+                if (canon[q].p == c && canon[q].m == mm && canon[q].lm1 == l1 * l1 + i1 && canon[q].lm2 == l2 * l2 + i2) { found = q; break; }
+            if (found < 0) {
+                if (std::fabs(cg_c[n]) < 1e-10) continue;
+                throw UnsupportedError("Clebsch-Gordan entry outside the real-harmonics coupling pattern of the evaluator");
+            }
+            file_val[found] += cg_c[n];
+            hits[found] += 1;
         }
-        m.z_ptr.push_back(0);
-        for (auto& lst : per_z) {
-            for (auto& en : lst) { m.z_lm1.push_back(en.first); m.z_c.push_back(en.second); }
-            m.z_ptr.push_back(static_cast<int>(m.z_lm1.size()));
+        m.path_scale.assign(m.tp.P, 0.0);
+        for (int c = 0; c < m.tp.P; ++c) {
+            double num = 0.0, den = 0.0;
+            for (int q = 0; q < n_canon; ++q)
+                if (canon[q].p == c) { num += file_val[q] * canon[q].c; den += canon[q].c * canon[q].c; }
+            const double scale = num / den;    // least-squares scale of this path
+            for (int q = 0; q < n_canon; ++q)
+                if (canon[q].p == c && std::fabs(file_val[q] - scale * canon[q].c) > 1e-9 * std::max(1.0, std::fabs(scale)))
+                    throw UnsupportedError("Clebsch-Gordan values of a path are not proportional to the evaluator's coupling table");
+            m.path_scale[c] = scale;
         }
     }
 
@@ -278,6 +299,16 @@ inline HostModel load_model_file(const std::string& filename) {
     for (int p = 0; p < P; ++p)
         for (int k = 0; k < K; ++k) fn_map[p * K + k] = m.path_file_to_canon[p] * K + k;
     load_splines("radial_spline_values_1", "radial_spline_derivs_1", m.F1, fn_map, m.coef1);
+    {   // fold the per-path coupling scale into the radial functions of that path
+        const size_t rows = static_cast<size_t>(m.num_pairs) * m.num_bins;
+        for (size_t row = 0; row < rows; ++row)
+            for (int c = 0; c < m.tp.P; ++c) {
+                const double sc = m.path_scale[c];
+                if (sc == 1.0) continue;
+                double* o = m.coef1.data() + (row * m.F1 + static_cast<size_t>(c) * K) * 4;
+                for (int q = 0; q < 4 * K; ++q) o[q] *= sc;
+            }
+    }
 
     // ---- dense weights
     auto expect = [&](const std::vector<double>& v, size_t n, const char* key) {
