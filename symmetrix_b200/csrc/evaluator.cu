@@ -71,8 +71,9 @@ public:
 
     // model tables on the device
     DevBuf<T> coef0, coef1, H0_w, A0_w, H1_w, A1_w, H2_w_H1, H2_w_M1, ro1, ro2_w1, ro2_w2, coefM0, coefM1;
+    bool poly_fixed = false;      // coefM0 / coefM1 hold the canonical order and the straight-line kernels are used
     DevBuf<double> E0;
-    DevBuf<int> prog0, prog0_off, mono0_off, prog1, prog1_off, mono1_off;
+    DevBuf<int> prog0, prog0_off, prog0_cnt, mono0_off, prog1, prog1_off, prog1_cnt, mono1_off;
     SplineMeta sm{};
 
     // current edge set
@@ -135,17 +136,25 @@ public:
         ro1.upload(cast_vec<T>(m.ro1), stream);
         ro2_w1.upload(cast_vec<T>(m.ro2_w1), stream);
         ro2_w2.upload(cast_vec<T>(m.ro2_w2), stream);
-        coefM0.upload(cast_vec<T>(m.coef_M0), stream);
-        coefM1.upload(cast_vec<T>(m.coef_M1), stream);
+        poly_fixed = m.poly_canonical;
+        coefM0.upload(cast_vec<T>(poly_fixed ? m.coef_M0_canon : m.coef_M0), stream);
+        coefM1.upload(cast_vec<T>(poly_fixed ? m.coef_M1_canon : m.coef_M1), stream);
         E0.upload(m.atomic_energies, stream);
         {
-            std::vector<int> words, offs;
-            for (const auto& p : m.prog0) { offs.push_back(static_cast<int>(words.size())); words.insert(words.end(), p.words.begin(), p.words.end()); }
+            // per output: [first word, number of operations to execute (without the trailing prefetch padding)]
+            std::vector<int> words, offs, counts;
+            for (const auto& p : m.prog0) {
+                offs.push_back(static_cast<int>(words.size()));
+                counts.push_back(static_cast<int>(p.words.size()) - kPolyPrefetch);
+                words.insert(words.end(), p.words.begin(), p.words.end());
+            }
             prog0.upload(words, stream);
             prog0_off.upload(offs, stream);
+            prog0_cnt.upload(counts, stream);
             mono0_off.upload(std::vector<int>(m.mono_off0.begin(), m.mono_off0.end() - 1), stream);
             prog1.upload(m.prog1.words, stream);
             prog1_off.upload(std::vector<int>{0}, stream);
+            prog1_cnt.upload(std::vector<int>{static_cast<int>(m.prog1.words.size()) - kPolyPrefetch}, stream);
             mono1_off.upload(std::vector<int>{0}, stream);
         }
         sm.h = m.spline_h;
@@ -156,6 +165,7 @@ public:
         model.coef0.clear(); model.coef0.shrink_to_fit();
         model.coef1.clear(); model.coef1.shrink_to_fit();
         model.coef_M0.clear(); model.coef_M0.shrink_to_fit();
+        model.coef_M0_canon.clear(); model.coef_M0_canon.shrink_to_fit();
     }
 
     // ------------------------------------------------------------------ launch helpers
@@ -281,7 +291,7 @@ public:
         SMX_CUDA(cudaStreamSynchronize(stream));  // `list` is a temporary of the caller
         dim3 grid(static_cast<unsigned>((max_rows + kGemmBM - 1) / kGemmBM), (max_cols + kGemmBN - 1) / kGemmBN,
                   static_cast<unsigned>(list.size()));
-        gemm_rows_kernel<T><<<grid, 256, 0, stream>>>(problems.p);
+        gemm_rows_kernel<T><<<grid, kGemmThreads, 0, stream>>>(problems.p);
         check_launch("gemm_rows_kernel");
     }
     GemmProblem<T> problem(const T* A, T* C, const T* B, bool by_type, int type, int sub_count, long long a_ns, long long a_off,
@@ -346,30 +356,50 @@ public:
 
     PolyArgs<T> poly_args(bool first) {
         PolyArgs<T> a{};
-        a.N = N; a.K = model.K; a.node_types = node_types;
+        a.N = N; a.K = model.K; a.node_types = node_types; a.perm = perm.p; a.type_seg = type_seg.p;
         if (first) {
-            a.num_out = model.num_LM; a.num_mono = model.num_mono0;
-            a.prog = prog0.p; a.prog_off = prog0_off.p; a.mono_off = mono0_off.p; a.coef = coefM0.p;
+            a.num_out = model.num_LM; a.num_mono = poly_fixed ? model.num_canon0 : model.num_mono0;
+            a.prog = prog0.p; a.prog_off = prog0_off.p; a.prog_cnt = prog0_cnt.p; a.mono_off = mono0_off.p; a.coef = coefM0.p;
             a.A = A0.p; a.M = M0.p; a.M_adj = M0_adj.p; a.A_adj = A0_adj.p;
         } else {
-            a.num_out = 1; a.num_mono = model.num_mono1;
-            a.prog = prog1.p; a.prog_off = prog1_off.p; a.mono_off = mono1_off.p; a.coef = coefM1.p;
+            a.num_out = 1; a.num_mono = poly_fixed ? model.num_canon1 : model.num_mono1;
+            a.prog = prog1.p; a.prog_off = prog1_off.p; a.prog_cnt = prog1_cnt.p; a.mono_off = mono1_off.p; a.coef = coefM1.p;
             a.A = A1.p; a.M = M1.p; a.M_adj = M1_adj.p; a.A_adj = A1_adj.p;
         }
         return a;
     }
+    template <int NOUT>
+    void launch_poly_fixed(bool first, bool reverse) {
+        const long long total = static_cast<long long>(N) * model.K;
+        const int grid = static_cast<int>((total + 127) / 128);
+        if (reverse) poly_fixed_reverse_kernel<T, NOUT><<<grid, 128, 0, stream>>>(poly_args(first));
+        else poly_fixed_forward_kernel<T, NOUT><<<grid, 128, 0, stream>>>(poly_args(first));
+        check_launch(reverse ? "poly_fixed_reverse_kernel" : "poly_fixed_forward_kernel");
+    }
     void run_poly(bool first, bool reverse) {
         if (N == 0) return;
-        const int block = 128;
-        const long long total = static_cast<long long>(N) * model.K;
-        const size_t smem = (reverse ? 2 : 1) * kNumLm * block * sizeof(T);
+        if (poly_fixed) {
+            const int nout = first ? model.num_LM : 1;
+            if (nout == 1) launch_poly_fixed<1>(first, reverse);
+            else if (nout == 4) launch_poly_fixed<4>(first, reverse);
+            else launch_poly_fixed<9>(first, reverse);
+            return;
+        }
+        // nodes per thread: as many as fit ~64 KB of shared memory (inputs, plus gradient accumulators in reverse)
+        constexpr int NBF = sizeof(T) == 8 ? 4 : 8, NBR = sizeof(T) == 8 ? 2 : 4;
+        const int block = std::min(128, ((model.K + 31) / 32) * 32);
+        const int chunks = (model.K + block - 1) / block;
         if (reverse) {
-            const int grid = static_cast<int>(std::min<long long>((total + block - 1) / block, 65535LL * 16));
-            poly_reverse_kernel<T><<<grid, block, smem, stream>>>(poly_args(first));
+            const size_t smem = 2 * static_cast<size_t>(NBR) * kNumLm * block * sizeof(T);
+            SMX_CUDA(cudaFuncSetAttribute(poly_reverse_kernel<T, NBR>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+            dim3 grid((N + NBR - 1) / NBR, model.num_elements, chunks);
+            poly_reverse_kernel<T, NBR><<<grid, block, smem, stream>>>(poly_args(first));
             check_launch("poly_reverse_kernel");
         } else {
-            const int grid = static_cast<int>(std::min<long long>((total + block - 1) / block, 65535LL * 16));
-            poly_forward_kernel<T><<<grid, block, smem, stream>>>(poly_args(first));
+            const size_t smem = static_cast<size_t>(NBF) * kNumLm * block * sizeof(T);
+            SMX_CUDA(cudaFuncSetAttribute(poly_forward_kernel<T, NBF>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+            dim3 grid((N + NBF - 1) / NBF, model.num_elements, chunks);
+            poly_forward_kernel<T, NBF><<<grid, block, smem, stream>>>(poly_args(first));
             check_launch("poly_forward_kernel");
         }
     }

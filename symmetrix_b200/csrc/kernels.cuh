@@ -16,6 +16,7 @@
 #include <utility>
 
 #include "tp_tables.hpp"
+#include "generated/poly_canon.hpp"
 
 namespace smx {
 
@@ -506,7 +507,7 @@ __global__ void sender_gather_kernel(int rows, int width, const long long* __res
 // =============================================================================================
 // Symmetric contraction (MACE::compute_M0 / compute_M1, mace.cpp:348-370,759-777, and their
 // reverses :372-395,779-794). One thread per (node, channel) walks the nested Horner program of
-// each output component; the 16 inputs of the thread live in shared memory, [variable][thread].
+// each output component; the 16 inputs of the thread live in shared memory.
 // =============================================================================================
 template <typename T>
 struct PolyArgs {
@@ -514,9 +515,12 @@ struct PolyArgs {
     int num_out;                 // output components (nLM for M0, 1 for M1)
     int num_mono;                // monomial rows per element in `coef`
     const int* node_types;
-    const int* prog;             // concatenated programs
-    const int* prog_off;         // [num_out] start of each program
-    const int* mono_off;         // [num_out] first coefficient row of each program
+    const int* perm;             // nodes sorted by element type
+    const int* type_seg;         // [E + 1] segment of each type in perm
+    const int* prog;             // concatenated operation streams (see compile_polynomial)
+    const int* prog_off;         // [num_out] first word of each stream
+    const int* prog_cnt;         // [num_out] operations to execute (a multiple of the prefetch distance)
+    const int* mono_off;         // [num_out] first coefficient row of each stream
     const T* coef;               // [E][num_mono][K]
     const T* A;                  // [N][16][K]
     T* M;                        // forward output [N][num_out][K]
@@ -524,104 +528,304 @@ struct PolyArgs {
     T* A_adj;                    // reverse output [N][16][K] (overwritten)
 };
 
+constexpr int kPolyAhead = 8;    // must equal kPolyPrefetch of the program builder
+
+__device__ __forceinline__ int poly_kind(int w) { return w & 7; }
+__device__ __forceinline__ int poly_var(int w) { return (w >> 3) & 31; }
 template <typename T>
+__device__ __forceinline__ T poly_coef(const T* c, int w, int K) {
+    const int row = (w >> 8) - 1;
+    return row >= 0 ? __ldg(c + static_cast<size_t>(row) * K) : T(0);
+}
+
+// One thread owns one channel of NB nodes of the same element type (blockIdx.y = type, blockIdx.x =
+// group of NB nodes in the type's segment of the sorted node list, blockIdx.z = channel chunk), so
+// every coefficient fetched from L2 is used NB times, and the operation words and coefficients of
+// the next kPolyAhead operations are already in flight while one executes. Inputs live in shared
+// memory as [node slot][variable][thread].
+template <typename T, int NB>
 __global__ void poly_forward_kernel(const PolyArgs<T> a) {
     extern __shared__ unsigned char smem_raw[];
-    T* As = reinterpret_cast<T*>(smem_raw);           // [16][blockDim.x]
-    const int nt = blockDim.x;
-    const long long total = static_cast<long long>(a.N) * a.K;
-    for (long long base = static_cast<long long>(blockIdx.x) * nt; base < total; base += static_cast<long long>(gridDim.x) * nt) {
-        const long long idx = base + threadIdx.x;
-        const bool active = idx < total;
-        const int i = active ? static_cast<int>(idx / a.K) : 0;
-        const int k = active ? static_cast<int>(idx - static_cast<long long>(i) * a.K) : 0;
-        if (active) {
+    T* As = reinterpret_cast<T*>(smem_raw);           // [NB][16][blockDim.x]
+    const int nt = blockDim.x, t = threadIdx.x;
+    const int type = blockIdx.y;
+    const int seg_begin = a.type_seg[type], seg_count = a.type_seg[type + 1] - seg_begin;
+    const int first = blockIdx.x * NB;
+    if (first >= seg_count) return;
+    const int k = blockIdx.z * nt + t;
+    if (k >= a.K) return;
+    int node[NB];
 #pragma unroll
-            for (int q = 0; q < kNumLm; ++q) As[q * nt + threadIdx.x] = a.A[(static_cast<size_t>(i) * kNumLm + q) * a.K + k];
-        }
-        if (active) {
-            const T* cf = a.coef + static_cast<size_t>(a.node_types[i]) * a.num_mono * a.K + k;
-            for (int o = 0; o < a.num_out; ++o) {
-                const int* w = a.prog + a.prog_off[o];
-                const T* c = cf + static_cast<size_t>(a.mono_off[o]) * a.K;
-                int pc = 0;
-                const int n1 = w[pc++];
-                T total_v = 0;
-                for (int g1 = 0; g1 < n1; ++g1) {
-                    const int q1 = w[pc], mu1 = w[pc + 1], n2 = w[pc + 2];
-                    pc += 3;
-                    T s1 = mu1 >= 0 ? c[static_cast<size_t>(mu1) * a.K] : T(0);
-                    for (int g2 = 0; g2 < n2; ++g2) {
-                        const int q2 = w[pc], mu2 = w[pc + 1], n3 = w[pc + 2];
-                        pc += 3;
-                        T s2 = mu2 >= 0 ? c[static_cast<size_t>(mu2) * a.K] : T(0);
-                        for (int g3 = 0; g3 < n3; ++g3) {
-                            s2 += c[static_cast<size_t>(w[pc + 1]) * a.K] * As[w[pc] * nt + threadIdx.x];
-                            pc += 2;
-                        }
-                        s1 += s2 * As[q2 * nt + threadIdx.x];
-                    }
-                    total_v += s1 * As[q1 * nt + threadIdx.x];
+    for (int n = 0; n < NB; ++n) {
+        const bool valid = first + n < seg_count;
+        node[n] = valid ? a.perm[seg_begin + first + n] : -1;
+#pragma unroll
+        for (int q = 0; q < kNumLm; ++q)
+            As[(n * kNumLm + q) * nt + t] = valid ? a.A[(static_cast<size_t>(node[n]) * kNumLm + q) * a.K + k] : T(0);
+    }
+    const T* cf = a.coef + static_cast<size_t>(type) * a.num_mono * a.K + k;
+    for (int o = 0; o < a.num_out; ++o) {
+        const int* w = a.prog + a.prog_off[o];
+        const int count = a.prog_cnt[o];
+        const T* c = cf + static_cast<size_t>(a.mono_off[o]) * a.K;
+        int wr[kPolyAhead];
+        T cr[kPolyAhead];
+#pragma unroll
+        for (int u = 0; u < kPolyAhead; ++u) { wr[u] = __ldg(w + u); cr[u] = poly_coef(c, wr[u], a.K); }
+        T total_v[NB], s1[NB], s2[NB];
+#pragma unroll
+        for (int n = 0; n < NB; ++n) total_v[n] = s1[n] = s2[n] = T(0);
+        for (int base = 0; base < count; base += kPolyAhead) {
+#pragma unroll
+            for (int u = 0; u < kPolyAhead; ++u) {
+                const int word = wr[u];
+                const T cv = cr[u];
+                wr[u] = __ldg(w + base + kPolyAhead + u);          // streams are padded, so this stays in bounds
+                cr[u] = poly_coef(c, wr[u], a.K);
+                const int kind = poly_kind(word), q = poly_var(word);
+                if (kind == 0) {
+#pragma unroll
+                    for (int n = 0; n < NB; ++n) s2[n] += cv * As[(n * kNumLm + q) * nt + t];
+                } else if (kind == 1) {
+#pragma unroll
+                    for (int n = 0; n < NB; ++n) s2[n] = cv;
+                } else if (kind == 2) {
+#pragma unroll
+                    for (int n = 0; n < NB; ++n) s1[n] += s2[n] * As[(n * kNumLm + q) * nt + t];
+                } else if (kind == 3) {
+#pragma unroll
+                    for (int n = 0; n < NB; ++n) s1[n] = cv;
+                } else if (kind == 4) {
+#pragma unroll
+                    for (int n = 0; n < NB; ++n) total_v[n] += s1[n] * As[(n * kNumLm + q) * nt + t];
                 }
-                a.M[(static_cast<size_t>(i) * a.num_out + o) * a.K + k] = total_v;
             }
+        }
+#pragma unroll
+        for (int n = 0; n < NB; ++n)
+            if (node[n] >= 0) a.M[(static_cast<size_t>(node[n]) * a.num_out + o) * a.K + k] = total_v[n];
+    }
+}
+
+template <typename T, int NB>
+__global__ void poly_reverse_kernel(const PolyArgs<T> a) {
+    extern __shared__ unsigned char smem_raw[];
+    const int nt = blockDim.x, t = threadIdx.x;
+    T* As = reinterpret_cast<T*>(smem_raw);           // [NB][16][nt]
+    T* Gs = As + NB * kNumLm * nt;                    // [NB][16][nt] gradient accumulators
+    const int type = blockIdx.y;
+    const int seg_begin = a.type_seg[type], seg_count = a.type_seg[type + 1] - seg_begin;
+    const int first = blockIdx.x * NB;
+    if (first >= seg_count) return;
+    const int k = blockIdx.z * nt + t;
+    if (k >= a.K) return;
+    int node[NB];
+#pragma unroll
+    for (int n = 0; n < NB; ++n) {
+        const bool valid = first + n < seg_count;
+        node[n] = valid ? a.perm[seg_begin + first + n] : -1;
+#pragma unroll
+        for (int q = 0; q < kNumLm; ++q) {
+            As[(n * kNumLm + q) * nt + t] = valid ? a.A[(static_cast<size_t>(node[n]) * kNumLm + q) * a.K + k] : T(0);
+            Gs[(n * kNumLm + q) * nt + t] = T(0);
+        }
+    }
+    const T* cf = a.coef + static_cast<size_t>(type) * a.num_mono * a.K + k;
+    for (int o = 0; o < a.num_out; ++o) {
+        T seed[NB];
+#pragma unroll
+        for (int n = 0; n < NB; ++n) seed[n] = node[n] >= 0 ? a.M_adj[(static_cast<size_t>(node[n]) * a.num_out + o) * a.K + k] : T(0);
+        const int* w = a.prog + a.prog_off[o];
+        const int count = a.prog_cnt[o];
+        const T* c = cf + static_cast<size_t>(a.mono_off[o]) * a.K;
+        int wr[kPolyAhead];
+        T cr[kPolyAhead];
+#pragma unroll
+        for (int u = 0; u < kPolyAhead; ++u) { wr[u] = __ldg(w + u); cr[u] = poly_coef(c, wr[u], a.K); }
+        // s1/s2: values of the open head / pair brackets; a2: A[q2]; adj1/adj2: adjoints of the brackets
+        T s1[NB], s2[NB], a2[NB], adj1[NB], adj2[NB];
+#pragma unroll
+        for (int n = 0; n < NB; ++n) s1[n] = s2[n] = a2[n] = adj1[n] = adj2[n] = T(0);
+        for (int base = 0; base < count; base += kPolyAhead) {
+#pragma unroll
+            for (int u = 0; u < kPolyAhead; ++u) {
+                const int word = wr[u];
+                const T cv = cr[u];
+                wr[u] = __ldg(w + base + kPolyAhead + u);
+                cr[u] = poly_coef(c, wr[u], a.K);
+                const int kind = poly_kind(word), q = poly_var(word);
+                if (kind == 0) {
+#pragma unroll
+                    for (int n = 0; n < NB; ++n) {
+                        s2[n] += cv * As[(n * kNumLm + q) * nt + t];
+                        Gs[(n * kNumLm + q) * nt + t] += adj2[n] * cv;
+                    }
+                } else if (kind == 1) {
+#pragma unroll
+                    for (int n = 0; n < NB; ++n) { a2[n] = As[(n * kNumLm + q) * nt + t]; s2[n] = cv; adj2[n] = adj1[n] * a2[n]; }
+                } else if (kind == 2) {
+#pragma unroll
+                    for (int n = 0; n < NB; ++n) { Gs[(n * kNumLm + q) * nt + t] += adj1[n] * s2[n]; s1[n] += s2[n] * a2[n]; }
+                } else if (kind == 3) {
+#pragma unroll
+                    for (int n = 0; n < NB; ++n) { s1[n] = cv; adj1[n] = seed[n] * As[(n * kNumLm + q) * nt + t]; }
+                } else if (kind == 4) {
+#pragma unroll
+                    for (int n = 0; n < NB; ++n) Gs[(n * kNumLm + q) * nt + t] += seed[n] * s1[n];
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int n = 0; n < NB; ++n)
+        if (node[n] >= 0)
+#pragma unroll
+            for (int q = 0; q < kNumLm; ++q) a.A_adj[(static_cast<size_t>(node[n]) * kNumLm + q) * a.K + k] = Gs[(n * kNumLm + q) * nt + t];
+}
+
+// Straight-line variant for models whose monomial lists are the symmetry-complete ones of
+// generated/poly_canon.hpp (l_max = 3, correlation 3): one thread per (node, channel), the 16 inputs and the
+// 16 gradient accumulators in registers, every coefficient one load at a compile-time offset. `coef` is then
+// ordered canonically, [element][canonical monomial][K]. NOUT = number of output components (1, 4 or 9).
+template <typename T, int NOUT>
+__global__ void __launch_bounds__(128) poly_fixed_forward_kernel(const PolyArgs<T> a) {
+    const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= static_cast<long long>(a.N) * a.K) return;
+    const int i = static_cast<int>(idx / a.K), k = static_cast<int>(idx - static_cast<long long>(i) * a.K);
+    T A[kNumLm];
+#pragma unroll
+    for (int q = 0; q < kNumLm; ++q) A[q] = a.A[(static_cast<size_t>(i) * kNumLm + q) * a.K + k];
+    const T* cf = a.coef + static_cast<size_t>(a.node_types[i]) * a.num_mono * a.K + k;
+    {
+        constexpr int kOff = kCanonPolyOffset[0];
+        auto C = [&](int slot) { return __ldg(cf + static_cast<size_t>(kOff + slot) * a.K); };
+#include "generated/poly_lm0_forward.inc"
+        a.M[(static_cast<size_t>(i) * NOUT + 0) * a.K + k] = total;
+    }
+    if constexpr (NOUT > 1) {
+        {
+            constexpr int kOff = kCanonPolyOffset[1];
+            auto C = [&](int slot) { return __ldg(cf + static_cast<size_t>(kOff + slot) * a.K); };
+#include "generated/poly_lm1_forward.inc"
+            a.M[(static_cast<size_t>(i) * NOUT + 1) * a.K + k] = total;
+        }
+        {
+            constexpr int kOff = kCanonPolyOffset[2];
+            auto C = [&](int slot) { return __ldg(cf + static_cast<size_t>(kOff + slot) * a.K); };
+#include "generated/poly_lm2_forward.inc"
+            a.M[(static_cast<size_t>(i) * NOUT + 2) * a.K + k] = total;
+        }
+        {
+            constexpr int kOff = kCanonPolyOffset[3];
+            auto C = [&](int slot) { return __ldg(cf + static_cast<size_t>(kOff + slot) * a.K); };
+#include "generated/poly_lm3_forward.inc"
+            a.M[(static_cast<size_t>(i) * NOUT + 3) * a.K + k] = total;
+        }
+    }
+    if constexpr (NOUT > 4) {
+        {
+            constexpr int kOff = kCanonPolyOffset[4];
+            auto C = [&](int slot) { return __ldg(cf + static_cast<size_t>(kOff + slot) * a.K); };
+#include "generated/poly_lm4_forward.inc"
+            a.M[(static_cast<size_t>(i) * NOUT + 4) * a.K + k] = total;
+        }
+        {
+            constexpr int kOff = kCanonPolyOffset[5];
+            auto C = [&](int slot) { return __ldg(cf + static_cast<size_t>(kOff + slot) * a.K); };
+#include "generated/poly_lm5_forward.inc"
+            a.M[(static_cast<size_t>(i) * NOUT + 5) * a.K + k] = total;
+        }
+        {
+            constexpr int kOff = kCanonPolyOffset[6];
+            auto C = [&](int slot) { return __ldg(cf + static_cast<size_t>(kOff + slot) * a.K); };
+#include "generated/poly_lm6_forward.inc"
+            a.M[(static_cast<size_t>(i) * NOUT + 6) * a.K + k] = total;
+        }
+        {
+            constexpr int kOff = kCanonPolyOffset[7];
+            auto C = [&](int slot) { return __ldg(cf + static_cast<size_t>(kOff + slot) * a.K); };
+#include "generated/poly_lm7_forward.inc"
+            a.M[(static_cast<size_t>(i) * NOUT + 7) * a.K + k] = total;
+        }
+        {
+            constexpr int kOff = kCanonPolyOffset[8];
+            auto C = [&](int slot) { return __ldg(cf + static_cast<size_t>(kOff + slot) * a.K); };
+#include "generated/poly_lm8_forward.inc"
+            a.M[(static_cast<size_t>(i) * NOUT + 8) * a.K + k] = total;
         }
     }
 }
 
-template <typename T>
-__global__ void poly_reverse_kernel(const PolyArgs<T> a) {
-    extern __shared__ unsigned char smem_raw[];
-    const int nt = blockDim.x;
-    T* As = reinterpret_cast<T*>(smem_raw);           // [16][nt]
-    T* Gs = As + kNumLm * nt;                         // [16][nt] gradient accumulators
-    const long long total = static_cast<long long>(a.N) * a.K;
-    for (long long base = static_cast<long long>(blockIdx.x) * nt; base < total; base += static_cast<long long>(gridDim.x) * nt) {
-        const long long idx = base + threadIdx.x;
-        if (idx >= total) continue;
-        const int i = static_cast<int>(idx / a.K);
-        const int k = static_cast<int>(idx - static_cast<long long>(i) * a.K);
-        const int t = threadIdx.x;
+template <typename T, int NOUT>
+__global__ void __launch_bounds__(128) poly_fixed_reverse_kernel(const PolyArgs<T> a) {
+    const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= static_cast<long long>(a.N) * a.K) return;
+    const int i = static_cast<int>(idx / a.K), k = static_cast<int>(idx - static_cast<long long>(i) * a.K);
+    T A[kNumLm], G[kNumLm];
 #pragma unroll
-        for (int q = 0; q < kNumLm; ++q) {
-            As[q * nt + t] = a.A[(static_cast<size_t>(i) * kNumLm + q) * a.K + k];
-            Gs[q * nt + t] = T(0);
-        }
-        const T* cf = a.coef + static_cast<size_t>(a.node_types[i]) * a.num_mono * a.K + k;
-        for (int o = 0; o < a.num_out; ++o) {
-            const T seed = a.M_adj[(static_cast<size_t>(i) * a.num_out + o) * a.K + k];
-            const int* w = a.prog + a.prog_off[o];
-            const T* c = cf + static_cast<size_t>(a.mono_off[o]) * a.K;
-            int pc = 0;
-            const int n1 = w[pc++];
-            for (int g1 = 0; g1 < n1; ++g1) {
-                const int q1 = w[pc], mu1 = w[pc + 1], n2 = w[pc + 2];
-                pc += 3;
-                const T a1 = As[q1 * nt + t];
-                T s1 = mu1 >= 0 ? c[static_cast<size_t>(mu1) * a.K] : T(0);
-                const T adj1 = seed * a1;                       // adjoint of the q1 bracket
-                for (int g2 = 0; g2 < n2; ++g2) {
-                    const int q2 = w[pc], mu2 = w[pc + 1], n3 = w[pc + 2];
-                    pc += 3;
-                    const T a2 = As[q2 * nt + t];
-                    T s2 = mu2 >= 0 ? c[static_cast<size_t>(mu2) * a.K] : T(0);
-                    const T adj2 = adj1 * a2;                   // adjoint of the (q1, q2) bracket
-                    for (int g3 = 0; g3 < n3; ++g3) {
-                        const T c3 = c[static_cast<size_t>(w[pc + 1]) * a.K];
-                        const int q3 = w[pc];
-                        s2 += c3 * As[q3 * nt + t];
-                        Gs[q3 * nt + t] += adj2 * c3;
-                        pc += 2;
-                    }
-                    Gs[q2 * nt + t] += adj1 * s2;
-                    s1 += s2 * a2;
-                }
-                Gs[q1 * nt + t] += seed * s1;
-            }
-        }
-#pragma unroll
-        for (int q = 0; q < kNumLm; ++q) a.A_adj[(static_cast<size_t>(i) * kNumLm + q) * a.K + k] = Gs[q * nt + t];
+    for (int q = 0; q < kNumLm; ++q) { A[q] = a.A[(static_cast<size_t>(i) * kNumLm + q) * a.K + k]; G[q] = T(0); }
+    const T* cf = a.coef + static_cast<size_t>(a.node_types[i]) * a.num_mono * a.K + k;
+    const T* seeds = a.M_adj + static_cast<size_t>(i) * NOUT * a.K + k;
+    {
+        constexpr int kOff = kCanonPolyOffset[0];
+        auto C = [&](int slot) { return __ldg(cf + static_cast<size_t>(kOff + slot) * a.K); };
+        const T seed = seeds[0];
+#include "generated/poly_lm0_reverse.inc"
     }
+    if constexpr (NOUT > 1) {
+        {
+            constexpr int kOff = kCanonPolyOffset[1];
+            auto C = [&](int slot) { return __ldg(cf + static_cast<size_t>(kOff + slot) * a.K); };
+            const T seed = seeds[static_cast<size_t>(1) * a.K];
+#include "generated/poly_lm1_reverse.inc"
+        }
+        {
+            constexpr int kOff = kCanonPolyOffset[2];
+            auto C = [&](int slot) { return __ldg(cf + static_cast<size_t>(kOff + slot) * a.K); };
+            const T seed = seeds[static_cast<size_t>(2) * a.K];
+#include "generated/poly_lm2_reverse.inc"
+        }
+        {
+            constexpr int kOff = kCanonPolyOffset[3];
+            auto C = [&](int slot) { return __ldg(cf + static_cast<size_t>(kOff + slot) * a.K); };
+            const T seed = seeds[static_cast<size_t>(3) * a.K];
+#include "generated/poly_lm3_reverse.inc"
+        }
+    }
+    if constexpr (NOUT > 4) {
+        {
+            constexpr int kOff = kCanonPolyOffset[4];
+            auto C = [&](int slot) { return __ldg(cf + static_cast<size_t>(kOff + slot) * a.K); };
+            const T seed = seeds[static_cast<size_t>(4) * a.K];
+#include "generated/poly_lm4_reverse.inc"
+        }
+        {
+            constexpr int kOff = kCanonPolyOffset[5];
+            auto C = [&](int slot) { return __ldg(cf + static_cast<size_t>(kOff + slot) * a.K); };
+            const T seed = seeds[static_cast<size_t>(5) * a.K];
+#include "generated/poly_lm5_reverse.inc"
+        }
+        {
+            constexpr int kOff = kCanonPolyOffset[6];
+            auto C = [&](int slot) { return __ldg(cf + static_cast<size_t>(kOff + slot) * a.K); };
+            const T seed = seeds[static_cast<size_t>(6) * a.K];
+#include "generated/poly_lm6_reverse.inc"
+        }
+        {
+            constexpr int kOff = kCanonPolyOffset[7];
+            auto C = [&](int slot) { return __ldg(cf + static_cast<size_t>(kOff + slot) * a.K); };
+            const T seed = seeds[static_cast<size_t>(7) * a.K];
+#include "generated/poly_lm7_reverse.inc"
+        }
+        {
+            constexpr int kOff = kCanonPolyOffset[8];
+            auto C = [&](int slot) { return __ldg(cf + static_cast<size_t>(kOff + slot) * a.K); };
+            const T seed = seeds[static_cast<size_t>(8) * a.K];
+#include "generated/poly_lm8_reverse.inc"
+        }
+    }
+#pragma unroll
+    for (int q = 0; q < kNumLm; ++q) a.A_adj[(static_cast<size_t>(i) * kNumLm + q) * a.K + k] = G[q];
 }
 
 // =============================================================================================
@@ -648,10 +852,120 @@ struct GemmProblem {
     int accumulate;          // 0: C = A.B ; 1: C += A.B
 };
 
-constexpr int kGemmBM = 64, kGemmBN = 64, kGemmBK = 16;
+constexpr int kGemmBM = 64, kGemmBN = 64, kGemmBK = 16, kGemmThreads = 128;
+
+// Tensor-core fragments. float64 uses the DMMA instruction mma.sync.m8n8k4 (sm_100a has no 5th-generation
+// tensor-core kind for float64); float32 uses TF32 mma.sync.m16n8k8 with the operands split into a TF32 head
+// and a TF32 remainder and three products per tile (head*head + head*rem + rem*head), which keeps float32-level
+// accuracy for the 1e-4 energy gate while running on the tensor pipe.
+__device__ __forceinline__ void dmma_m8n8k4(double& c0, double& c1, double a, double b) {
+    asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0,%1}, {%2}, {%3}, {%0,%1};" : "+d"(c0), "+d"(c1) : "d"(a), "d"(b));
+}
+__device__ __forceinline__ unsigned to_tf32(float x) {
+    unsigned r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return r;
+}
+__device__ __forceinline__ void mma_tf32_m16n8k8(float (&c)[4], const unsigned (&a)[4], const unsigned (&b)[2]) {
+    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+template <typename T> struct GemmSmem;
+template <> struct GemmSmem<double> { static constexpr int SA = kGemmBK + 4, SB = kGemmBN + 4; };   // conflict-free fragment reads
+template <> struct GemmSmem<float> { static constexpr int SA = kGemmBK + 4, SB = kGemmBN + 8; };
+
+// Warp tile 32 x 32 of the 64 x 64 CTA tile; accumulators and the k-loop body per precision.
+template <typename T> struct WarpTile;
+template <>
+struct WarpTile<double> {
+    double c[4][4][2];
+    __device__ __forceinline__ void zero() {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) c[i][j][0] = c[i][j][1] = 0.0;
+    }
+    __device__ __forceinline__ void step(const double* As, const double* Bs, int wm, int wn, int lane) {
+        constexpr int SA = GemmSmem<double>::SA, SB = GemmSmem<double>::SB;
+#pragma unroll
+        for (int kk = 0; kk < kGemmBK; kk += 4) {
+            double a[4], b[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a[i] = As[(wm * 32 + i * 8 + (lane >> 2)) * SA + kk + (lane & 3)];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) b[j] = Bs[(kk + (lane & 3)) * SB + wn * 32 + j * 8 + (lane >> 2)];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) dmma_m8n8k4(c[i][j][0], c[i][j][1], a[i], b[j]);
+        }
+    }
+    template <typename F>
+    __device__ __forceinline__ void for_each(int wm, int wn, int lane, F&& f) const {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) f(wm * 32 + i * 8 + (lane >> 2), wn * 32 + j * 8 + 2 * (lane & 3) + e, c[i][j][e]);
+    }
+};
+template <>
+struct WarpTile<float> {
+    float c[2][4][4];
+    __device__ __forceinline__ void zero() {
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) c[i][j][e] = 0.f;
+    }
+    __device__ __forceinline__ void step(const float* As, const float* Bs, int wm, int wn, int lane) {
+        constexpr int SA = GemmSmem<float>::SA, SB = GemmSmem<float>::SB;
+#pragma unroll
+        for (int kk = 0; kk < kGemmBK; kk += 8) {
+            unsigned ah[2][4], al[2][4], bh[4][2], bl[4][2];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int r = wm * 32 + i * 16 + (lane >> 2), cidx = kk + (lane & 3);
+                const float v[4] = {As[r * SA + cidx], As[(r + 8) * SA + cidx], As[r * SA + cidx + 4], As[(r + 8) * SA + cidx + 4]};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) { ah[i][e] = to_tf32(v[e]); al[i][e] = to_tf32(v[e] - __uint_as_float(ah[i][e])); }
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int n = wn * 32 + j * 8 + (lane >> 2);
+                const float v[2] = {Bs[(kk + (lane & 3)) * SB + n], Bs[(kk + 4 + (lane & 3)) * SB + n]};
+#pragma unroll
+                for (int e = 0; e < 2; ++e) { bh[j][e] = to_tf32(v[e]); bl[j][e] = to_tf32(v[e] - __uint_as_float(bh[j][e])); }
+            }
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    mma_tf32_m16n8k8(c[i][j], al[i], bh[j]);
+                    mma_tf32_m16n8k8(c[i][j], ah[i], bl[j]);
+                    mma_tf32_m16n8k8(c[i][j], ah[i], bh[j]);
+                }
+        }
+    }
+    template <typename F>
+    __device__ __forceinline__ void for_each(int wm, int wn, int lane, F&& f) const {
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    f(wm * 32 + i * 16 + (lane >> 2) + (e >> 1) * 8, wn * 32 + j * 8 + 2 * (lane & 3) + (e & 1), c[i][j][e]);
+    }
+};
 
 template <typename T>
-__global__ void __launch_bounds__(256) gemm_rows_kernel(const GemmProblem<T>* __restrict__ problems) {
+__global__ void __launch_bounds__(kGemmThreads) gemm_rows_kernel(const GemmProblem<T>* __restrict__ problems) {
     const GemmProblem<T> pb = problems[blockIdx.z];
     int node_begin = 0, node_count = pb.num_nodes;
     if (pb.seg) { node_begin = pb.seg[pb.seg_index]; node_count = pb.seg[pb.seg_index + 1] - node_begin; }
@@ -660,11 +974,13 @@ __global__ void __launch_bounds__(256) gemm_rows_kernel(const GemmProblem<T>* __
     const int col0 = blockIdx.y * kGemmBN;
     if (row0 >= M || col0 >= pb.Nc) return;
 
-    __shared__ T As[kGemmBK][kGemmBM + 1];
-    __shared__ T Bs[kGemmBK][kGemmBN + 1];
+    constexpr int SA = GemmSmem<T>::SA, SB = GemmSmem<T>::SB;
+    __shared__ T As[kGemmBM * SA];
+    __shared__ T Bs[kGemmBK * SB];
     __shared__ long long a_base[kGemmBM];
     __shared__ long long c_base[kGemmBM];
-    const int tid = threadIdx.x;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int wm = warp >> 1, wn = warp & 1;
     if (tid < kGemmBM) {
         const long long r = row0 + tid;
         if (r < M) {
@@ -679,66 +995,52 @@ __global__ void __launch_bounds__(256) gemm_rows_kernel(const GemmProblem<T>* __
         }
     }
     __syncthreads();
-    const int tx = tid & 15, ty = tid >> 4;     // 16 x 16 threads, 4 x 4 outputs each
-    T acc[4][4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) acc[i][j] = T(0);
 
-    for (int k0 = 0; k0 < pb.Kd; k0 += kGemmBK) {
-        // A tile: 64 rows x 16 k; thread loads 4 elements (coalesced along k within a row)
+    constexpr int kPer = kGemmBM * kGemmBK / kGemmThreads;   // 8 elements of each tile per thread
+    T ra[kPer], rb[kPer];
+    auto fetch = [&](int k0) {
 #pragma unroll
-        for (int it = 0; it < 4; ++it) {
-            const int lin = tid + it * 256;
+        for (int it = 0; it < kPer; ++it) {
+            const int lin = tid + it * kGemmThreads;
             const int rr = lin >> 4, kk = lin & 15;
-            T v = T(0);
-            if (a_base[rr] >= 0 && k0 + kk < pb.Kd) v = pb.A[a_base[rr] + k0 + kk];
-            As[kk][rr] = v;
-        }
-        // B tile: 16 k x 64 cols
-#pragma unroll
-        for (int it = 0; it < 4; ++it) {
-            const int lin = tid + it * 256;
-            T v = T(0);
+            ra[it] = (a_base[rr] >= 0 && k0 + kk < pb.Kd) ? pb.A[a_base[rr] + k0 + kk] : T(0);
             if (!pb.transB) {
-                const int kk = lin >> 6, cc = lin & 63;
-                if (k0 + kk < pb.Kd && col0 + cc < pb.Nc) v = pb.B[static_cast<size_t>(k0 + kk) * pb.ldb + col0 + cc];
-                Bs[kk][cc] = v;
+                const int kb = lin >> 6, cc = lin & 63;
+                rb[it] = (k0 + kb < pb.Kd && col0 + cc < pb.Nc) ? pb.B[static_cast<size_t>(k0 + kb) * pb.ldb + col0 + cc] : T(0);
             } else {
-                const int cc = lin >> 4, kk = lin & 15;
-                if (k0 + kk < pb.Kd && col0 + cc < pb.Nc) v = pb.B[static_cast<size_t>(col0 + cc) * pb.ldb + k0 + kk];
-                Bs[kk][cc] = v;
+                const int cc = lin >> 4, kb = lin & 15;
+                rb[it] = (k0 + kb < pb.Kd && col0 + cc < pb.Nc) ? pb.B[static_cast<size_t>(col0 + cc) * pb.ldb + k0 + kb] : T(0);
             }
         }
-        __syncthreads();
+    };
+    auto stash = [&]() {
 #pragma unroll
-        for (int kk = 0; kk < kGemmBK; ++kk) {
-            T av[4], bv[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) av[i] = As[kk][ty * 4 + i];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) bv[j] = Bs[kk][tx + 16 * j];
-#pragma unroll
-            for (int i = 0; i < 4; ++i)
-#pragma unroll
-                for (int j = 0; j < 4; ++j) acc[i][j] += av[i] * bv[j];
+        for (int it = 0; it < kPer; ++it) {
+            const int lin = tid + it * kGemmThreads;
+            As[(lin >> 4) * SA + (lin & 15)] = ra[it];
+            if (!pb.transB) Bs[(lin >> 6) * SB + (lin & 63)] = rb[it];
+            else Bs[(lin & 15) * SB + (lin >> 4)] = rb[it];
         }
+    };
+
+    WarpTile<T> acc;
+    acc.zero();
+    fetch(0);
+    for (int k0 = 0; k0 < pb.Kd; k0 += kGemmBK) {
+        stash();
+        __syncthreads();
+        if (k0 + kGemmBK < pb.Kd) fetch(k0 + kGemmBK);     // next tile's global loads overlap the tensor-core work
+        acc.step(As, Bs, wm, wn, lane);
         __syncthreads();
     }
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const long long cb = c_base[ty * 4 + i];
-        if (cb < 0) continue;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int col = col0 + tx + 16 * j;
-            if (col < pb.Nc) {
-                T* dst = pb.C + cb + col;
-                *dst = pb.accumulate ? (*dst + acc[i][j]) : acc[i][j];
-            }
+    acc.for_each(wm, wn, lane, [&](int r, int cidx, T v) {
+        const long long cb = c_base[r];
+        const int col = col0 + cidx;
+        if (cb >= 0 && col < pb.Nc) {
+            T* dst = pb.C + cb + col;
+            *dst = pb.accumulate ? (*dst + v) : v;
         }
-    }
+    });
 }
 
 // =============================================================================================

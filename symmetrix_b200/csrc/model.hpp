@@ -17,6 +17,7 @@
 #include "json_min.hpp"
 #include "tp_tables.hpp"
 #include "generated/cg_canon.hpp"
+#include "generated/poly_canon.hpp"
 
 namespace smx {
 
@@ -28,17 +29,24 @@ struct UnsupportedError : std::runtime_error {
 };
 
 // A sparse polynomial of degree <= 3 in the 16 variables A[i, :, k], shared by all channels and
-// element types (which only change the coefficients), compiled to a nested Horner program:
-//   P = sum_q1 A[q1] (c1 + sum_{q2} A[q2] (c2 + sum_{q3} c3 A[q3]))
-// Word stream: [n1] then per q1 group [q1, mu1, n2], per q2 group [q2, mu2, n3], per leaf [q3, mu3];
-// mu is the row of the coefficient in the model's monomial order (-1: no such monomial).
-// Takes the place of the product DAG the reference builds per (element, LM, channel)
+// element types (which only change the coefficients), compiled to a flat operation stream for the
+// nested Horner form
+//   P = sum_q1 A[q1] (c1 + sum_{q2} A[q2] (c2 + sum_{q3} c3 A[q3])).
+// One 32-bit word per operation: kind | variable << 3 | (coefficient row + 1) << 8, where the row
+// is the monomial's position in the model's monomial list (0: no such monomial, coefficient zero).
+// A flat stream lets the kernels fetch the coefficients of later operations while executing the
+// current one. Takes the place of the product DAG the reference builds per (element, LM, channel)
 // (libsymmetrix/source/multivariate_polynomial.cpp:10-101).
+enum PolyOp : int { kPolyLeaf = 0, kPolyPairBegin = 1, kPolyPairEnd = 2, kPolyHeadBegin = 3, kPolyHeadEnd = 4, kPolyNop = 5 };
+constexpr int kPolyPrefetch = 8;     // operations fetched ahead; streams are padded with this many no-ops
+
 struct PolyProgram {
     std::vector<int> words;
     int num_monomials = 0;
     int num_leaves = 0, num_pairs = 0;
 };
+
+inline int poly_word(int kind, int q, int mu) { return kind | (q << 3) | ((mu + 1) << 8); }
 
 inline PolyProgram compile_polynomial(const std::vector<std::vector<int>>& monomials, int num_vars) {
     struct Pair { int mu = -1; std::vector<std::pair<int, int>> leaves; };
@@ -60,23 +68,21 @@ inline PolyProgram compile_polynomial(const std::vector<std::vector<int>>& monom
     }
     PolyProgram prog;
     prog.num_monomials = static_cast<int>(monomials.size());
-    prog.words.push_back(static_cast<int>(heads.size()));
     for (auto& [q1, h] : heads) {
-        prog.words.push_back(q1);
-        prog.words.push_back(h.mu);
-        prog.words.push_back(static_cast<int>(h.pairs.size()));
+        prog.words.push_back(poly_word(kPolyHeadBegin, q1, h.mu));
         for (auto& [q2, p] : h.pairs) {
-            prog.words.push_back(q2);
-            prog.words.push_back(p.mu);
-            prog.words.push_back(static_cast<int>(p.leaves.size()));
+            prog.words.push_back(poly_word(kPolyPairBegin, q2, p.mu));
             prog.num_pairs += 1;
             for (auto& lf : p.leaves) {
-                prog.words.push_back(lf.first);
-                prog.words.push_back(lf.second);
+                prog.words.push_back(poly_word(kPolyLeaf, lf.first, lf.second));
                 prog.num_leaves += 1;
             }
+            prog.words.push_back(poly_word(kPolyPairEnd, q2, -1));
         }
+        prog.words.push_back(poly_word(kPolyHeadEnd, q1, -1));
     }
+    while (prog.words.size() % kPolyPrefetch) prog.words.push_back(poly_word(kPolyNop, 0, -1));
+    for (int i = 0; i < kPolyPrefetch; ++i) prog.words.push_back(poly_word(kPolyNop, 0, -1));
     return prog;
 }
 
@@ -122,7 +128,29 @@ struct HostModel {
     PolyProgram prog1;
     int num_mono1 = 0;
     std::vector<double> coef_M1;
+    // the same coefficients re-ordered to the canonical monomial lists (generated/poly_canon.hpp) used by the
+    // straight-line kernels; `poly_canonical` is false if the file has monomials outside those lists
+    bool poly_canonical = true;
+    int num_canon0 = 0, num_canon1 = 0;
+    std::vector<double> coef_M0_canon, coef_M1_canon;
 };
+
+namespace detail {
+// slot of each of the file's monomials of output component `lm` in the canonical list, or -1
+inline std::vector<int> canonical_slots(const std::vector<std::vector<int>>& monomials, int lm) {
+    std::vector<int> out(monomials.size(), -1);
+    for (size_t mu = 0; mu < monomials.size(); ++mu) {
+        std::vector<int> m = monomials[mu];
+        std::sort(m.begin(), m.end());
+        m.resize(3, -1);
+        for (int s = 0; s < kCanonPolyCount[lm]; ++s) {
+            const CanonMonomial& c = kCanonMonomials[kCanonPolyOffset[lm] + s];
+            if (c.q[0] == m[0] && c.q[1] == m[1] && c.q[2] == m[2]) { out[mu] = s; break; }
+        }
+    }
+    return out;
+}
+}  // namespace detail
 
 namespace detail {
 
@@ -357,6 +385,13 @@ inline HostModel load_model_file(const std::string& filename) {
         }
         m.num_mono0 = m.mono_off0[m.num_LM];
         m.coef_M0.assign(size_t(E) * m.num_mono0 * K, 0.0);
+        m.num_canon0 = kCanonPolyOffset[m.num_LM];
+        m.coef_M0_canon.assign(size_t(E) * m.num_canon0 * K, 0.0);
+        std::vector<std::vector<int>> slots0;
+        for (int lm = 0; lm < m.num_LM; ++lm) {
+            slots0.push_back(detail::canonical_slots(detail::int_lists(monos.at(std::to_string(lm))), lm));
+            for (int sl : slots0.back()) if (sl < 0) m.poly_canonical = false;
+        }
         for (int a = 0; a < E; ++a) {
             const JsonValue& wa = weights.at(std::to_string(a));
             for (int lm = 0; lm < m.num_LM; ++lm) {
@@ -365,8 +400,11 @@ inline HostModel load_model_file(const std::string& filename) {
                 for (int k = 0; k < K; ++k) {
                     const JsonValue& wk = wl.at(std::to_string(k));
                     if (static_cast<int>(wk.size()) != nm) throw ModelError("M0_weights row length differs from M0_monomials");
-                    for (int mu = 0; mu < nm; ++mu)
+                    for (int mu = 0; mu < nm; ++mu) {
                         m.coef_M0[(size_t(a) * m.num_mono0 + m.mono_off0[lm] + mu) * K + k] = wk.nums[mu];
+                        if (slots0[lm][mu] >= 0)
+                            m.coef_M0_canon[(size_t(a) * m.num_canon0 + kCanonPolyOffset[lm] + slots0[lm][mu]) * K + k] += wk.nums[mu];
+                    }
                 }
             }
         }
@@ -377,13 +415,19 @@ inline HostModel load_model_file(const std::string& filename) {
         m.num_mono1 = static_cast<int>(lists.size());
         const JsonValue& weights = file.at("M1_weights");
         m.coef_M1.assign(size_t(E) * m.num_mono1 * K, 0.0);
+        m.num_canon1 = kCanonPolyCount[0];
+        m.coef_M1_canon.assign(size_t(E) * m.num_canon1 * K, 0.0);
+        const std::vector<int> slots1 = detail::canonical_slots(lists, 0);
+        for (int sl : slots1) if (sl < 0) m.poly_canonical = false;
         for (int a = 0; a < E; ++a) {
             const JsonValue& wa = weights.at(std::to_string(a));
             for (int k = 0; k < K; ++k) {
                 const JsonValue& wk = wa.at(std::to_string(k));
                 if (static_cast<int>(wk.size()) != m.num_mono1) throw ModelError("M1_weights row length differs from M1_monomials");
-                for (int mu = 0; mu < m.num_mono1; ++mu)
+                for (int mu = 0; mu < m.num_mono1; ++mu) {
                     m.coef_M1[(size_t(a) * m.num_mono1 + mu) * K + k] = wk.nums[mu];
+                    if (slots1[mu] >= 0) m.coef_M1_canon[(size_t(a) * m.num_canon1 + slots1[mu]) * K + k] += wk.nums[mu];
+                }
             }
         }
     }

@@ -325,3 +325,27 @@ def test_cpp_facade_replays_pair_style_compute(tiny, tmp_path):
     np.add.at(want, recv, -nf); np.add.at(want, inputs["neigh_indices"], nf)
     np.testing.assert_allclose(f_loop.reshape(n, 3), want, atol=1e-10)
     np.testing.assert_allclose(f_lib.reshape(n, 3), want, atol=1e-10)
+
+
+@pytest.mark.parametrize("dtype", ["float64", "float32"])
+def test_models_with_unusual_monomials_use_the_table_driven_contraction(tiny, tmp_path, dtype):
+    """A model file whose monomial lists are not the symmetry-complete ones (here: extra, symmetry-breaking monomials in
+    both contractions) cannot use the generated straight-line contraction code and runs the interpreter instead."""
+    import json
+    _, inputs = tiny
+    model = json.loads((GOLDEN / "tiny_model.json").read_text())
+    rng = np.random.default_rng(5)
+    model["M1_monomials"] = model["M1_monomials"] + [[1], [2, 7], [0, 3, 11]]
+    for a in model["M1_weights"]:
+        for k in model["M1_weights"][a]:
+            model["M1_weights"][a][k] = model["M1_weights"][a][k] + (0.3 * rng.standard_normal(3)).tolist()
+    model["M0_monomials"]["2"] = model["M0_monomials"]["2"] + [[5, 5]]
+    for a in model["M0_weights"]:
+        for k in model["M0_weights"][a]["2"]:
+            model["M0_weights"][a]["2"][k] = model["M0_weights"][a]["2"][k] + [0.2 * float(rng.standard_normal())]
+    path = tmp_path / "odd.json"
+    path.write_text(json.dumps(model))
+    e_ref, f_ref = MaceOracle(model).compute_node_energies_forces(inputs)
+    ev = MACE(path, dtype=dtype)
+    e, f = run(ev, inputs)
+    check_against(dtype, e, f, e_ref, f_ref)
