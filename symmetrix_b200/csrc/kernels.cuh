@@ -20,7 +20,7 @@
 
 namespace smx {
 
-constexpr int kEdgeBatch = 8;       // edges staged in shared memory per pass
+constexpr int kEdgeBatch = 32;      // edges staged in shared memory per pass (one staging latency and two barriers per batch)
 constexpr int kChannelBlock = 128;  // threads per CTA of the edge kernels; more channels are done in chunks
 constexpr int kMaxWarps = kChannelBlock / 32;
 
@@ -357,8 +357,16 @@ struct TPArgs {
     double* node_forces;    // reverse: accumulated into
 };
 
+// Resident CTAs per SM the compiler is asked to allow for (register budget): measured best on B200 for the
+// configs[1] model -- float64 forward 3 (168 registers), reverse 1 (no spills); float32 forward 5, reverse 4.
+// For L_max = 2 the register demand is about twice as high and the budgets are relaxed to avoid spills.
+template <typename T> constexpr int tp_min_blocks(int LF, bool reverse) {
+    if (LF >= 2) return sizeof(T) == 8 ? 1 : (reverse ? 2 : 3);
+    return sizeof(T) == 8 ? (reverse ? 1 : 3) : (reverse ? 4 : 5);
+}
+
 template <typename T, int LF>
-__global__ void __launch_bounds__(kChannelBlock) tp_forward_kernel(const TPArgs<T> a) {
+__global__ void __launch_bounds__(kChannelBlock, tp_min_blocks<T>(LF, false)) tp_forward_kernel(const TPArgs<T> a) {
     constexpr TPTable tp = make_tp_table(LF);
     __shared__ EdgeStage<T> st[kEdgeBatch];
     const int F = tp.P * a.K;
@@ -418,7 +426,7 @@ __global__ void __launch_bounds__(kChannelBlock) tp_forward_kernel(const TPArgs<
 // memory) and one thread per edge turns them into the partial force
 //   nf[ij] -= xhat * fr + sum_lm W[lm] * grad Y[lm].
 template <typename T, int LF>
-__global__ void __launch_bounds__(kChannelBlock) tp_reverse_kernel(const TPArgs<T> a) {
+__global__ void __launch_bounds__(kChannelBlock, tp_min_blocks<T>(LF, true)) tp_reverse_kernel(const TPArgs<T> a) {
     constexpr TPTable tp = make_tp_table(LF);
     __shared__ EdgeStage<T> st[kEdgeBatch];
     __shared__ T red[kMaxWarps][kEdgeBatch][17];
