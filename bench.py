@@ -35,6 +35,12 @@ WORKLOADS = {
                 "l_max 3, correlation 3, r_cut 6 A, 10 radial functions, 89-element model exported for the 5 species present"),
     "fcc1372": ("fcc128", lambda st, z, seed: st.fcc_box(7, 3.6, z, seed=seed),
                 "profiling case: 1372-atom FCC box (7x7x7 cells) of the configs[1] construction and model"),
+    "fcc256k": ("fcc128", lambda st, z, seed: st.fcc_box((10, 80, 80), 3.6, z, seed=seed),
+                "configs[3] per-GPU share: 256,000-atom FCC slab (10x80x80 cells) of the configs[1] construction and model; "
+                "8 of these side by side are the 2,048,000-atom box"),
+    "water98304": ("organic128_HO", lambda st, z, seed: st.water_box_density(32, 1.0, seed=seed),
+                   "configs[2]: 98,304-atom water box (32,768 H2O, 1.0 g/cm^3), organic-liquid model 128x0e+128x1o, r_cut 5 A, "
+                   "10-element model exported for the species present (H, O)"),
     "water192": ("water64", lambda st, z, seed: st.water_box(4, 12.42, seed=seed),
                  "configs[0]: 64 H2O (192 atoms) in a 12.42 A cell, model 64x0e, r_cut 5 A"),
 }
@@ -49,7 +55,7 @@ def model_path(spec_name: str) -> tuple[Path, list[int]]:
     """Model JSON regenerated from its seed into the temp directory (cached across runs on one machine)."""
     from symmetrix_b200.modelgen.generate import generate_model, named_spec, write_json
     cache = Path(os.environ.get("SMX_MODEL_CACHE", tempfile.gettempdir())) / f"smx_bench_{spec_name}.json"
-    spec = named_spec(spec_name)
+    spec = named_spec("organic128", atomic_numbers=[1, 8]) if spec_name == "organic128_HO" else named_spec(spec_name)
     if not cache.exists():
         t0 = time.time()
         model = generate_model(spec)
@@ -126,34 +132,32 @@ def measured_peaks() -> tuple[float, str]:
     return 6650.0, "fallback"
 
 
-def path_constants(L_max: int):
-    from symmetrix_b200.modelgen.generate import tp_paths
-    paths = tp_paths(3, L_max)
-    nz = sum((2 * l + 1) * (2 * l2 + 1) for l, _, l2 in paths)
-    q = sum(2 * l + 1 for l, _, _ in paths)
-    return len(paths), nz, q, (L_max + 1) ** 2
-
-
 def roofline_for(stage: str, ms: float, n_atoms: int, n_edges: int, K: int, L_max: int, dtype_bytes: int) -> dict:
     """Algorithmic bytes and flops of the stage's dominant kernel for one launch (one full structure).
 
     Per edge: xyz 24 B + sender index 4 B + sender type 4 B + r 8 B, one gathered sender feature row
     nLM*K*s B, 24 B of partial force written (reverse). Per node: Q*K*s B of tensor-product output written
     (forward) or of its adjoint read (reverse). Scratch the implementation adds (the per-edge adjoint
-    message buffer) and table reads served by L2 are not counted. Flops: forward (2 NZ + 2 Q + 8 P) K per
-    edge, reverse (8 NZ + 10 T2 + 14 P) K per edge with T2 = sum_p (2 l2 + 1).
+    message buffer) and table reads served by L2 are not counted. Flops are the operation counts of the
+    generated straight-line code per (edge, channel), an FMA counting 2.
     """
-    from symmetrix_b200.modelgen.generate import tp_paths
-    P, NZ, Q, nLM = path_constants(L_max)
-    T2 = sum(2 * l2 + 1 for _, _, l2 in tp_paths(3, L_max))
+    from symmetrix_b200.modelgen.gen_tp_code import tables
+    paths, nz, _ = tables(L_max)
+    P, Q, nLM = len(paths), sum(2 * p[0] + 1 for p in paths), (L_max + 1) ** 2
+    T1, T2 = sum(2 * p[1] + 1 for p in paths), sum(2 * p[2] + 1 for p in paths)
+    nnz = len(nz)
+    n_yh = len({(a, b) for (_, _, a, b, _) in nz})
+    # operation counts of the generated straight-line code, per (edge, channel); an FMA counts 2
+    fwd_flops = n_yh + 2 * nnz + 2 * Q + 6 * P
+    rev_flops = nnz + 2 * nnz + 2 * nnz + 2 * T1 + 2 * T2 + 2 * T2 + 2 * P + 11 * P
     s = dtype_bytes
     if stage == "reverse_Phi1":
         byts = n_edges * (40 + nLM * K * s + 24) + n_atoms * Q * K * s
-        flops = n_edges * K * (8 * NZ + 10 * T2 + 14 * P)
+        flops = n_edges * K * rev_flops
         kernel = "tp_reverse_kernel"
     elif stage == "compute_Phi1":
         byts = n_edges * (40 + nLM * K * s) + n_atoms * Q * K * s
-        flops = n_edges * K * (2 * NZ + 2 * Q + 8 * P)
+        flops = n_edges * K * fwd_flops
         kernel = "tp_forward_kernel"
     elif stage == "reverse_A0":
         byts = n_edges * (40 + 24) + n_atoms * 16 * K * s
@@ -328,10 +332,10 @@ def run_decomposed(args, rank, world, local_rank, dist):
     path, numbers, spec = model_path(spec_name) if rank == 0 else (None, None, None)
     dist.barrier()
     path, numbers, spec = model_path(spec_name)
-    cells = {"fcc4000": 10, "fcc1372": 7}.get(args.workload)
+    cells = {"fcc4000": (10, 10, 10), "fcc1372": (7, 7, 7), "fcc256k": (10, 80, 80)}.get(args.workload)
     if cells is None:
         raise SystemExit("decomposed runs are defined for the FCC workloads")
-    s = st.fcc_box((cells * world, cells, cells), 3.6, numbers, seed=1)
+    s = st.fcc_box((cells[0] * world, cells[1], cells[2]), 3.6, numbers, seed=1)
     ev = MACE(path, dtype=args.dtype, device=local_rank)
     rk = SlabRank(make_slab_plan(s, spec.r_cut, rank, world), ev, spec.r_cut, numbers)
     rk.build_edges()
@@ -433,7 +437,7 @@ def _cpu_sample_inputs(workload: str, seed: int):
     from symmetrix_b200 import structures as st
     spec_name, _, _ = WORKLOADS[workload]
     path, numbers, spec = model_path(spec_name)
-    if workload in ("fcc4000", "fcc1372"):
+    if workload in ("fcc4000", "fcc1372", "fcc256k"):
         s = st.fcc_box(CPU_SAMPLE_CELLS, 3.6, numbers, seed=seed)
         sample = f"{CPU_SAMPLE_CELLS}x{CPU_SAMPLE_CELLS}x{CPU_SAMPLE_CELLS}-cell FCC box ({s.num_atoms} atoms) of the same construction and model"
     else:
@@ -546,10 +550,12 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="fcc4000", choices=sorted(WORKLOADS))
-    ap.add_argument("--dtype", default="float64", choices=["float64", "float32"])
+    ap.add_argument("--dtype", default=None, choices=["float64", "float32"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extra", action="store_true")
     args = ap.parse_args()
+    if args.dtype is None:   # configs[0] and [1] are quoted in float64 (the reference CPU precision), the larger ones in float32
+        args.dtype = "float32" if args.workload in ("fcc256k", "water98304") else "float64"
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference(args)

@@ -452,7 +452,7 @@ public:
         a.N = N; a.K = model.K;
         a.node_types = node_types; a.first_neigh = first_neigh.p; a.neigh_indices = neigh_indices; a.neigh_types = neigh_types;
         a.xyz = xyz; a.r = r; a.coef1 = coef1.p; a.sm = sm;
-        a.H = H1.p; a.Phi1 = Phi1.p; a.dPhi1 = dPhi1.p; a.Hmsg = Hmsg.p; a.node_forces = node_forces.p;
+        a.H = H1.p; a.Phi1 = Phi1.p; a.dPhi1 = dPhi1.p; a.Hmsg = Hmsg.p; a.H_adj = H1_adj.p; a.node_forces = node_forces.p;
         return a;
     }
     template <int LF>
@@ -492,6 +492,10 @@ public:
         if (zero_dxyz) node_forces.zero(stream);
         if (zero_H1_adj) H1_adj.zero(stream);
         if (N == 0) return;
+        if (sizeof(T) == 4) {      // float32: messages are accumulated in place by the kernel
+            dispatch_tp(true);
+            return;
+        }
         Hmsg.resize(static_cast<size_t>(E) * nLM * K, stream);
         dispatch_tp(true);
         ensure_sender_lists(std::max(h1_rows, N));

@@ -353,7 +353,8 @@ struct TPArgs {
     const T* H;             // sender features [rows][nLM][K]
     T* Phi1;                // forward output [N][Q][K]
     const T* dPhi1;         // reverse input  [N][Q][K]
-    T* Hmsg;                // reverse output [num_edges][nLM][K]: adjoint message of each edge to its sender
+    T* Hmsg;                // reverse output [num_edges][nLM][K]: adjoint message of each edge to its sender (float64)
+    T* H_adj;               // float32: the messages are added straight into H_adj[sender] with red.global.add
     double* node_forces;    // reverse: accumulated into
 };
 
@@ -475,9 +476,17 @@ __global__ void __launch_bounds__(kChannelBlock, tp_min_blocks<T>(LF, true)) tp_
                     } else {
 #include "generated/tp_L2_reverse.inc"
                     }
-                    T* mrow = a.Hmsg + static_cast<size_t>(e0 + e) * tp.nLM * a.K + k;
+                    if constexpr (sizeof(T) == 8) {
+                        // float64: deterministic two-step scatter (per-edge message, then a fixed-order sum per sender)
+                        T* mrow = a.Hmsg + static_cast<size_t>(e0 + e) * tp.nLM * a.K + k;
 #pragma unroll
-                    for (int lm2 = 0; lm2 < tp.nLM; ++lm2) mrow[static_cast<size_t>(lm2) * a.K] = msg[lm2];
+                        for (int lm2 = 0; lm2 < tp.nLM; ++lm2) mrow[static_cast<size_t>(lm2) * a.K] = msg[lm2];
+                    } else {
+                        // float32: one reduction per value directly into the sender's row (no message buffer)
+                        T* arow = a.H_adj + static_cast<size_t>(s.j) * tp.nLM * a.K + k;
+#pragma unroll
+                        for (int lm2 = 0; lm2 < tp.nLM; ++lm2) atomicAdd(arow + static_cast<size_t>(lm2) * a.K, msg[lm2]);
+                    }
                 }
                 int idx;
                 const T wsum = warp_reduce_scatter16(W, lane, idx);
