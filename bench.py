@@ -47,6 +47,15 @@ WORKLOADS = {
 CPU_SAMPLE_CELLS = 4   # the CPU baseline evaluates a 4x4x4-cell (256-atom) box of the same construction
 
 
+_REAL_STDOUT = None
+
+
+def emit(obj):
+    stream = _REAL_STDOUT or sys.stdout
+    stream.write(json.dumps(obj) + "\n")
+    stream.flush()
+
+
 def log(*a):
     print(*a, file=sys.stderr, flush=True)
 
@@ -313,7 +322,7 @@ def run_ours(args):
             e32 = ev2.reduce_forces()[2] if args.dtype == "float64" else ev_saved.reduce_forces()[2]
             out["extra"] = {other: {"value": n_atoms * args.steps / (ms2 * 1e-3), "ms_per_step": ms2 / args.steps},
                             "fp32_vs_fp64_rel_energy_diff": abs(e32 - e64) / abs(e64)}
-        print(json.dumps(out), flush=True)
+        emit(out)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -417,7 +426,7 @@ def run_decomposed(args, rank, world, local_rank, dist):
             "gpu_launches": launches * world, "gpu_launches_per_step": launches // (args.steps + args.warmup),
             "clocks": clocks, "roofline": roof, "stage_ms": stage_ms,
         }
-        print(json.dumps(out), flush=True)
+        emit(out)
     dist.barrier()
     dist.destroy_process_group()
     return None
@@ -522,7 +531,7 @@ def run_reference(args):
     for p in procs:
         p.join()
     if any(p.exitcode != 0 for p in procs):
-        print(json.dumps({"impl": "reference", "unavailable": "a CPU replica of the reference evaluator exited with an error"}))
+        emit({"impl": "reference", "unavailable": "a CPU replica of the reference evaluator exited with an error"})
         return None
     t = max(times)
     value = replicas * s.num_atoms * steps / t
@@ -539,11 +548,15 @@ def run_reference(args):
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(out), flush=True)
+    emit(out)
     return out
 
 
 def main():
+    # Libraries (NCCL among them) may print to stdout; the one JSON line goes to the real stdout, everything else to stderr.
+    global _REAL_STDOUT
+    _REAL_STDOUT = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=40)
