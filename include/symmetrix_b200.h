@@ -92,9 +92,11 @@ int smx_compute(smx_handle h, int num_nodes, const int* node_types, const int* n
  * one by one (mace.hpp:40-164; call sequence pair_symmetrix/pair_symmetrix_mace.cpp:444-495):
  * name is one of compute_Y, compute_R0, compute_A0, compute_M0, compute_H1, compute_R1,
  * compute_Phi1, compute_A1, compute_M1, compute_H2, compute_readouts, reverse_H2, reverse_M1,
- * reverse_A1, reverse_Phi1, reverse_H1, reverse_M0, reverse_A0 (the *_scaled stages are accepted
- * and do nothing, as in the reference when the model has no density normalisation).
- * `zero_dxyz` / `zero_H1_adj` carry the flags of reverse_Phi1 / reverse_H2 (mace.hpp:118,159).
+ * reverse_A1, reverse_Phi1, reverse_H1, reverse_M0, reverse_A0, compute_ZBL (ZBL::compute_ZBL,
+ * zbl.hpp:29-37, a no-op for models without pair repulsion) and compute_A0_scaled, compute_A1_scaled,
+ * reverse_A0_scaled, reverse_A1_scaled (no-ops for models without density normalisation, as in the
+ * reference). `zero_dxyz` / `zero_H1_adj` carry the flags of reverse_Phi1 / reverse_H2 /
+ * reverse_A1_scaled (mace.hpp:118,145,159).
  * Radial functions and harmonics are recomputed inside the edge kernels, so compute_Y /
  * compute_R0 / compute_R1 only record the edge arrays they are given. A sequence of stage calls
  * must start with smx_begin, which replaces the zero-fill of node_energies / node_forces that

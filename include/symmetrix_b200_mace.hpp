@@ -51,6 +51,12 @@ public:
     std::vector<double> atomic_energies;
     bool has_zbl = false;
 
+    // The pair style calls mace->zbl.compute_ZBL(...) by hand in its staged modes (pair_symmetrix_mace.cpp:441-444).
+    struct ZBLStage {
+        MACE* owner = nullptr;
+        template <typename... A> void compute_ZBL(A&&...) { owner->stage("compute_ZBL"); }
+    } zbl{this};
+
     // Host mirrors of the public vectors the callers read or swap (mace.hpp:28,104)
     std::vector<double> node_energies, node_forces, H1, H1_adj;
 
@@ -96,7 +102,8 @@ public:
     void reverse_Phi1(const int, std::span<const int>, std::span<const int>, std::span<const double>, std::span<const double>,
                       bool zero_dxyz = true, bool zero_H1_adj = true) { stage("reverse_Phi1", zero_dxyz, zero_H1_adj); }
     void reverse_H2(const int, std::span<const int>, bool zero_H1_adj = true) { stage("reverse_H2", true, zero_H1_adj); }
-    template <typename... A> void reverse_A1_scaled(A&&...) { stage("reverse_A1_scaled"); }
+    void reverse_A1_scaled(const int, std::span<const int>, std::span<const int>, std::span<const int>, std::span<const double>,
+                           std::span<const double>, bool zero_dxyz = true) { stage("reverse_A1_scaled", zero_dxyz, true); }
 
     // Device <-> host mirrors: pull("H1") after compute_H1, push("H1") after a forward halo exchange, etc.
     std::vector<double>& pull(const std::string& name) {

@@ -97,13 +97,20 @@ class SplineSet:
 
 
 class MaceOracle:
-    """Restatement of ``class MACE`` (mace.hpp:12-169) for models without ZBL / density scaling."""
+    """Restatement of ``class MACE`` (mace.hpp:12-169), including ZBL and density normalisation."""
 
     def __init__(self, model):
         m = load_model(model)
         self.model = m
-        if m.get("has_zbl") or m.get("A0_scaled") or m.get("A1_scaled"):
-            raise NotImplementedError("ZBL and density-normalised interactions are outside this restatement")
+        self.has_zbl = bool(m.get("has_zbl"))
+        self.A0_scaled, self.A1_scaled = bool(m.get("A0_scaled")), bool(m.get("A1_scaled"))
+        if self.has_zbl:
+            self.zbl = dict(a_exp=float(m["zbl_a_exp"]), a_prefactor=float(m["zbl_a_prefactor"]), c=np.asarray(m["zbl_c"], dtype=np.float64),
+                            radii=np.asarray(m["zbl_covalent_radii"], dtype=np.float64), p=int(m["zbl_p"]))
+        if self.A0_scaled:
+            self.A0_spl = [SplineSet(m["A0_spline_h"], [v], [d]) for v, d in zip(m["A0_spline_values"], m["A0_spline_derivs"])]
+        if self.A1_scaled:
+            self.A1_spl = [SplineSet(m["A1_spline_h"], [v], [d]) for v, d in zip(m["A1_spline_values"], m["A1_spline_derivs"])]
         self.num_elements = int(m["num_elements"]); self.K = int(m["num_channels"])
         self.r_cut = float(m["r_cut"]); self.l_max = int(m["l_max"]); self.L_max = int(m["L_max"])
         self.nlm = (self.l_max + 1) ** 2; self.nLM = (self.L_max + 1) ** 2
@@ -279,6 +286,66 @@ class MaceOracle:
         self.node_energies += act @ self.ro2_w2
         self.H2_adj = (dact * self.ro2_w2[None, :]) @ self.ro2_w1
 
+    # ---------------------------------------------------------------- ZBL and density normalisation
+    def compute_ZBL(self):                                          # zbl.cpp:22-125
+        if not self.has_zbl:
+            return
+        z = self.zbl
+        Z = np.asarray(self.atomic_numbers)
+        Zu = Z[self.node_types[self.recv]].astype(np.float64); Zv = Z[self.neigh_types].astype(np.float64)
+        r = self.r
+        r_max = z["radii"][Zu.astype(int)] + z["radii"][Zv.astype(int)]
+        a = z["a_prefactor"] * 0.529 / (Zu ** z["a_exp"] + Zv ** z["a_exp"])
+        ce = np.array([-3.2, -0.9423, -0.4028, -0.2016])
+        terms = z["c"][None, :] * np.exp(ce[None, :] * (r / a)[:, None])
+        phi = terms.sum(axis=1); dphi = (terms * ce[None, :]).sum(axis=1) / a
+        v = 14.3996 * Zu * Zv / r * phi
+        dv = 14.3996 * Zu * Zv * (r * dphi - phi) / (r * r)
+        p = z["p"]; x = r / r_max
+        env = 1.0 - ((p + 1.0) * (p + 2.0) / 2.0) * x ** p + p * (p + 2.0) * x ** (p + 1) - (p * (p + 1.0) / 2.0) * x ** (p + 2)
+        denv = (-((p + 1.0) * (p + 2.0) / 2.0) * p * x ** (p - 1) + p * (p + 2.0) * (p + 1.0) * x ** p
+                - (p * (p + 1.0) / 2.0) * (p + 2.0) * x ** (p + 1)) / r_max
+        inside = r < r_max
+        env = np.where(inside, env, 0.0); denv = np.where(inside, denv, 0.0)
+        np.add.at(self.node_energies, self.recv, 0.5 * v * env)
+        g = 0.5 * (v * denv + dv * env)
+        self.node_forces -= self.xyz / r[:, None] * g[:, None]
+
+    def _density(self, splines):
+        f = np.zeros(self.r.size); d = np.zeros(self.r.size)
+        for p, spl in enumerate(splines):
+            sel = np.nonzero(self.pair == p)[0]
+            if sel.size:
+                v, dv = spl.evaluate_derivs(self.r[sel])
+                f[sel], d[sel] = v[:, 0], dv[:, 0]
+        factor = 1.0 + np.bincount(self.recv, weights=f, minlength=self.N)
+        return factor, d
+
+    def compute_A0_scaled(self):                                    # mace.cpp:273-298
+        if self.A0_scaled:
+            factor, _ = self._density(self.A0_spl)
+            self.A0 = self.A0 / factor[:, None, None]
+
+    def compute_A1_scaled(self):                                    # mace.cpp:681-706
+        if self.A1_scaled:
+            factor, _ = self._density(self.A1_spl)
+            self.A1 = self.A1 / factor[:, None, None]
+
+    def _reverse_scaled(self, splines, A, A_adj):                   # mace.cpp:300-346, 708-757
+        factor, d = self._density(splines)
+        dot = np.einsum("nqk,nqk->n", A_adj, A)
+        g = (dot / factor)[self.recv] * d / self.r
+        self.node_forces += self.xyz * g[:, None]
+        return A_adj / factor[:, None, None]
+
+    def reverse_A0_scaled(self):
+        if self.A0_scaled:
+            self.A0_adj = self._reverse_scaled(self.A0_spl, self.A0, self.A0_adj)
+
+    def reverse_A1_scaled(self):
+        if self.A1_scaled:
+            self.A1_adj = self._reverse_scaled(self.A1_spl, self.A1, self.A1_adj)
+
     # ---------------------------------------------------------------- reverse stages
     def reverse_H2(self):                                           # mace.cpp:834-874
         self.H1_adj[:self.N, 0] += np.einsum("nkj,nj->nk", self.H2_w_H1[self.node_types], self.H2_adj)
@@ -335,9 +402,10 @@ class MaceOracle:
     def compute_node_energies_forces(self, inp):                    # mace.cpp:17-64
         self._edges(inp)
         self.node_forces = np.zeros((self.r.size, 3))
-        self.compute_Y(); self.compute_R0(); self.compute_A0(); self.compute_M0(); self.compute_H1()
-        self.compute_R1(); self.compute_Phi1(); self.compute_A1(); self.compute_M1(); self.compute_H2()
+        self.compute_Y(); self.compute_R0(); self.compute_A0(); self.compute_A0_scaled(); self.compute_M0(); self.compute_H1()
+        self.compute_R1(); self.compute_Phi1(); self.compute_A1(); self.compute_A1_scaled(); self.compute_M1(); self.compute_H2()
         self.compute_readouts()
-        self.reverse_H2(); self.reverse_M1(); self.reverse_A1(); self.reverse_Phi1()
-        self.reverse_H1(); self.reverse_M0(); self.reverse_A0()
+        self.compute_ZBL()        # the reference adds it first (mace.cpp:32-35); the sums commute
+        self.reverse_H2(); self.reverse_M1(); self.reverse_A1_scaled(); self.reverse_A1(); self.reverse_Phi1()
+        self.reverse_H1(); self.reverse_M0(); self.reverse_A0_scaled(); self.reverse_A0()
         return self.node_energies.copy(), self.node_forces.reshape(-1).copy()

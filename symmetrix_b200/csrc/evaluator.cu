@@ -72,7 +72,8 @@ public:
     // model tables on the device
     DevBuf<T> coef0, coef1, H0_w, A0_w, H1_w, A1_w, H2_w_H1, H2_w_M1, ro1, ro2_w1, ro2_w2, coefM0, coefM1;
     bool poly_fixed = false;      // coefM0 / coefM1 hold the canonical order and the straight-line kernels are used
-    DevBuf<double> E0;
+    DevBuf<double> E0, zbl_radii, A0_spl, A1_spl;
+    DevBuf<int> zbl_numbers;
     DevBuf<int> prog0, prog0_off, prog0_cnt, mono0_off, prog1, prog1_off, prog1_cnt, mono1_off;
     SplineMeta sm{};
 
@@ -140,6 +141,9 @@ public:
         coefM0.upload(cast_vec<T>(poly_fixed ? m.coef_M0_canon : m.coef_M0), stream);
         coefM1.upload(cast_vec<T>(poly_fixed ? m.coef_M1_canon : m.coef_M1), stream);
         E0.upload(m.atomic_energies, stream);
+        if (m.has_zbl) { zbl_radii.upload(m.zbl_covalent_radii, stream); zbl_numbers.upload(m.atomic_numbers, stream); }
+        if (m.A0_scaled) A0_spl.upload(m.A0_spline_coef, stream);
+        if (m.A1_scaled) A1_spl.upload(m.A1_spline_coef, stream);
         {
             // per output: [first word, number of operations to execute (without the trailing prefetch padding)]
             std::vector<int> words, offs, counts;
@@ -318,6 +322,43 @@ public:
         a.xyz = xyz; a.r = r; a.coef0 = coef0.p; a.sm = sm; a.H0_w = H0_w.p;
         a.Phi0 = Phi0.p; a.Phi0_adj = Phi0_adj.p; a.node_forces = node_forces.p;
         return a;
+    }
+
+    void compute_ZBL() {   // ZBL::compute_ZBL, zbl.cpp:96-125
+        if (!model.has_zbl || N == 0) return;
+        ZblParams z{};
+        z.a_exp = model.zbl_a_exp; z.a_prefactor = model.zbl_a_prefactor; z.p = model.zbl_p;
+        for (int q = 0; q < 4; ++q) z.c[q] = model.zbl_c[q];
+        z.covalent_radii = zbl_radii.p; z.atomic_numbers = zbl_numbers.p;
+        zbl_kernel<<<std::min((N + 127) / 128, num_sms * 8), 128, 0, stream>>>(N, node_types, first_neigh.p, neigh_types, xyz, r, z,
+                                                                              node_energies.p, node_forces.p);
+        check_launch("zbl_kernel");
+    }
+    ScalarSplines density_splines(bool first) const {
+        ScalarSplines sp{};
+        sp.coef = first ? A0_spl.p : A1_spl.p;
+        sp.h = first ? model.A0_spline_h : model.A1_spline_h;
+        sp.bins = first ? model.A0_spline_bins : model.A1_spline_bins;
+        sp.num_elements = model.num_elements;
+        return sp;
+    }
+    void compute_A_scaled(bool first) {   // MACE::compute_A0_scaled / compute_A1_scaled, mace.cpp:273-298, 681-706
+        if (!(first ? model.A0_scaled : model.A1_scaled) || N == 0) return;
+        DevBuf<T>& A = first ? A0 : A1;
+        if (A.n != static_cast<size_t>(N) * kNumLm * model.K) throw ArgError("compute_A_scaled: A has not been computed");
+        density_scale_forward_kernel<T><<<std::min(N, num_sms * 8), 128, 0, stream>>>(N, model.K, node_types, first_neigh.p, neigh_types, r,
+                                                                                    density_splines(first), A.p);
+        check_launch("density_scale_forward_kernel");
+    }
+    void reverse_A_scaled(bool first, bool zero_dxyz) {   // MACE::reverse_A0_scaled / reverse_A1_scaled, mace.cpp:300-346, 708-757
+        if (!(first ? model.A0_scaled : model.A1_scaled) || N == 0) return;
+        DevBuf<T>& A = first ? A0 : A1;
+        DevBuf<T>& A_adj = first ? A0_adj : A1_adj;
+        if (A_adj.n != static_cast<size_t>(N) * kNumLm * model.K) throw ArgError("reverse_A_scaled: the adjoint has not been computed");
+        if (zero_dxyz) node_forces.zero(stream);
+        density_scale_reverse_kernel<T><<<std::min(N, num_sms * 8), 128, 0, stream>>>(N, model.K, node_types, first_neigh.p, neigh_types, xyz, r,
+                                                                                    density_splines(first), A.p, A_adj.p, node_forces.p);
+        check_launch("density_scale_reverse_kernel");
     }
 
     void compute_A0() {   // MACE::compute_A0, mace.cpp:150-201
@@ -583,8 +624,12 @@ public:
         require_edges();
         SMX_CUDA(cudaSetDevice(device));
         if (s == "compute_Y" || s == "compute_R0" || s == "compute_R1") return;  // fused into the edge kernels
-        if (s == "compute_A0_scaled" || s == "compute_A1_scaled" || s == "reverse_A0_scaled" || s == "reverse_A1_scaled") return;
         if (s == "compute_A0") compute_A0();
+        else if (s == "compute_ZBL") compute_ZBL();
+        else if (s == "compute_A0_scaled") compute_A_scaled(true);
+        else if (s == "compute_A1_scaled") compute_A_scaled(false);
+        else if (s == "reverse_A0_scaled") reverse_A_scaled(true, false);
+        else if (s == "reverse_A1_scaled") reverse_A_scaled(false, zero_dxyz);
         else if (s == "compute_M0") compute_M0();
         else if (s == "compute_H1") compute_H1();
         else if (s == "compute_Phi1") compute_Phi1();
@@ -665,11 +710,12 @@ public:
         int mark = 0;
         auto tick = [&]() { if (profiling) SMX_CUDA(cudaEventRecord(stage_events[mark++], stream)); };
         SMX_CUDA(cudaEventRecord(ev0, stream));
-        tick(); compute_A0(); tick(); compute_M0(); tick(); compute_H1();
-        tick(); compute_Phi1(); tick(); compute_A1(); tick(); compute_M1(); tick(); compute_H2();
+        compute_ZBL();
+        tick(); compute_A0(); compute_A_scaled(true); tick(); compute_M0(); tick(); compute_H1();
+        tick(); compute_Phi1(); tick(); compute_A1(); compute_A_scaled(false); tick(); compute_M1(); tick(); compute_H2();
         tick(); compute_readouts();
-        tick(); reverse_H2(false); tick(); reverse_M1(); tick(); reverse_A1(); tick(); reverse_Phi1(false, false);
-        tick(); reverse_H1(); tick(); reverse_M0(); tick(); reverse_A0(); tick();
+        tick(); reverse_H2(false); tick(); reverse_M1(); reverse_A_scaled(false, false); tick(); reverse_A1(); tick(); reverse_Phi1(false, false);
+        tick(); reverse_H1(); tick(); reverse_M0(); reverse_A_scaled(true, false); tick(); reverse_A0(); tick();
         SMX_CUDA(cudaEventRecord(ev1, stream));
         SMX_CUDA(cudaStreamSynchronize(stream));
         float ms = 0.f;

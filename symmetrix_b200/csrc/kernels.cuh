@@ -1118,6 +1118,144 @@ __global__ void readout_kernel(const ReadoutArgs<T> a) {
 }
 
 // =============================================================================================
+// ZBL pair repulsion (ZBL::compute_ZBL, zbl.cpp:96-125 with compute / compute_gradient / envelope :22-94):
+// screened Coulomb term times a polynomial envelope that vanishes at the sum of the covalent radii. Half of each
+// pair energy goes to the receiver's node energy, the radial derivative to the edge's partial force. One thread
+// per node walks its row, so the energy sum needs no atomics. Always float64.
+// =============================================================================================
+struct ZblParams {
+    double a_exp, a_prefactor, c[4];
+    int p;
+    const double* covalent_radii;   // indexed by atomic number
+    const int* atomic_numbers;      // per model type
+};
+
+__global__ void zbl_kernel(int N, const int* __restrict__ node_types, const long long* __restrict__ first_neigh,
+                           const int* __restrict__ neigh_types, const double* __restrict__ xyz, const double* __restrict__ r,
+                           ZblParams z, double* __restrict__ node_energies, double* __restrict__ node_forces) {
+    const double ce[4] = {-3.2, -0.9423, -0.4028, -0.2016};     // screening exponents, zbl.hpp:49-52
+    const double v_prefactor = 14.3996;                          // zbl.hpp:53
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < N; i += gridDim.x * blockDim.x) {
+        const int Zi = z.atomic_numbers[node_types[i]];
+        double e_sum = 0.0;
+        for (long long e = first_neigh[i]; e < first_neigh[i + 1]; ++e) {
+            const int Zj = z.atomic_numbers[neigh_types[e]];
+            const double rr = r[e];
+            const double r_max = z.covalent_radii[Zi] + z.covalent_radii[Zj];
+            if (rr >= r_max) continue;                           // envelope and its gradient vanish (zbl.cpp:76,86)
+            const double Zu = Zi, Zv = Zj;
+            const double a = z.a_prefactor * 0.529 / (pow(Zu, z.a_exp) + pow(Zv, z.a_exp));
+            const double roa = rr / a;
+            double phi = 0.0, dphi = 0.0;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const double t = z.c[q] * exp(ce[q] * roa);
+                phi += t;
+                dphi += ce[q] * t;
+            }
+            dphi /= a;
+            const double v = v_prefactor * Zu * Zv / rr * phi;
+            const double dv = v_prefactor * Zu * Zv * (rr * dphi - phi) / (rr * rr);
+            const double x = rr / r_max, p = z.p;
+            const double env = 1.0 - ((p + 1.0) * (p + 2.0) / 2.0) * pow(x, p) + p * (p + 2.0) * pow(x, p + 1.0) - (p * (p + 1.0) / 2.0) * pow(x, p + 2.0);
+            const double denv = (-((p + 1.0) * (p + 2.0) / 2.0) * p * pow(x, p - 1.0) + p * (p + 2.0) * (p + 1.0) * pow(x, p)
+                                 - (p * (p + 1.0) / 2.0) * (p + 2.0) * pow(x, p + 1.0)) / r_max;
+            e_sum += 0.5 * v * env;
+            const double g = 0.5 * (v * denv + dv * env);
+            node_forces[3 * e] -= xyz[3 * e] / rr * g;
+            node_forces[3 * e + 1] -= xyz[3 * e + 1] / rr * g;
+            node_forces[3 * e + 2] -= xyz[3 * e + 2] / rr * g;
+        }
+        node_energies[i] += e_sum;
+    }
+}
+
+// =============================================================================================
+// Density normalisation of a layer's A features (MACE::compute_A0_scaled / reverse_A0_scaled and the A1 twins,
+// mace.cpp:273-346, 681-757): A[i] /= 1 + sum_j f_ab(r_ij) with one scalar cubic spline per element pair.
+// One CTA per node. The reverse pass recomputes the factor, adds dE/dr of the factor to the edge forces and
+// scales the adjoint.
+// =============================================================================================
+struct ScalarSplines {
+    const double* coef;   // [pair][bin][4]
+    double h;
+    int bins, num_elements;
+};
+
+__device__ __forceinline__ void scalar_spline(const ScalarSplines& sp, int type_i, int type_j, double rr, double& f, double& d) {
+    const int lo = type_i <= type_j ? type_i : type_j, hi = type_i <= type_j ? type_j : type_i;
+    const int pair = lo * (2 * sp.num_elements - lo - 1) / 2 + hi;
+    int bin = static_cast<int>(rr / sp.h);
+    bin = bin < 0 ? 0 : (bin > sp.bins - 1 ? sp.bins - 1 : bin);
+    const double x = rr - sp.h * bin;
+    const double* c = sp.coef + (static_cast<size_t>(pair) * sp.bins + bin) * 4;
+    f = c[0] + c[1] * x + c[2] * x * x + c[3] * x * x * x;
+    d = c[1] + 2 * c[2] * x + 3 * c[3] * x * x;
+}
+
+__device__ __forceinline__ double block_sum(double v, double* sh) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) sh[warp] = v;
+    __syncthreads();
+    double t = 0;
+    for (int w = 0; w < nw; ++w) t += sh[w];
+    return t;
+}
+
+template <typename T>
+__global__ void density_scale_forward_kernel(int N, int K, const int* __restrict__ node_types, const long long* __restrict__ first_neigh,
+                                             const int* __restrict__ neigh_types, const double* __restrict__ r, ScalarSplines sp,
+                                             T* __restrict__ A) {
+    __shared__ double sh[32];
+    for (int i = blockIdx.x; i < N; i += gridDim.x) {
+        const int ti = node_types[i];
+        double part = 0;
+        for (long long e = first_neigh[i] + threadIdx.x; e < first_neigh[i + 1]; e += blockDim.x) {
+            double f, d;
+            scalar_spline(sp, ti, neigh_types[e], r[e], f, d);
+            part += f;
+        }
+        const double factor = 1.0 + block_sum(part, sh);
+        T* row = A + static_cast<size_t>(i) * kNumLm * K;
+        for (int c = threadIdx.x; c < kNumLm * K; c += blockDim.x) row[c] = static_cast<T>(double(row[c]) / factor);
+    }
+}
+
+template <typename T>
+__global__ void density_scale_reverse_kernel(int N, int K, const int* __restrict__ node_types, const long long* __restrict__ first_neigh,
+                                             const int* __restrict__ neigh_types, const double* __restrict__ xyz, const double* __restrict__ r,
+                                             ScalarSplines sp, const T* __restrict__ A, T* __restrict__ A_adj, double* __restrict__ node_forces) {
+    __shared__ double sh[32];
+    for (int i = blockIdx.x; i < N; i += gridDim.x) {
+        const int ti = node_types[i];
+        double part = 0;
+        for (long long e = first_neigh[i] + threadIdx.x; e < first_neigh[i + 1]; e += blockDim.x) {
+            double f, d;
+            scalar_spline(sp, ti, neigh_types[e], r[e], f, d);
+            part += f;
+        }
+        const double factor = 1.0 + block_sum(part, sh);
+        const T* arow = A + static_cast<size_t>(i) * kNumLm * K;
+        T* grow = A_adj + static_cast<size_t>(i) * kNumLm * K;
+        double dot = 0;
+        for (int c = threadIdx.x; c < kNumLm * K; c += blockDim.x) dot += double(grow[c]) * double(arow[c]);
+        dot = block_sum(dot, sh);
+        for (long long e = first_neigh[i] + threadIdx.x; e < first_neigh[i + 1]; e += blockDim.x) {
+            double f, d;
+            scalar_spline(sp, ti, neigh_types[e], r[e], f, d);
+            const double g = dot / factor * d / r[e];
+            node_forces[3 * e] += g * xyz[3 * e];
+            node_forces[3 * e + 1] += g * xyz[3 * e + 1];
+            node_forces[3 * e + 2] += g * xyz[3 * e + 2];
+        }
+        __syncthreads();
+        for (int c = threadIdx.x; c < kNumLm * K; c += blockDim.x) grow[c] = static_cast<T>(double(grow[c]) / factor);
+    }
+}
+
+// =============================================================================================
 // Small helpers
 // =============================================================================================
 __global__ void iota_kernel(int n, int* out) {

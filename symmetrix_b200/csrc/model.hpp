@@ -93,6 +93,17 @@ struct HostModel {
     std::vector<int> atomic_numbers;
     std::vector<double> atomic_energies;
     bool has_zbl = false;
+    // ZBL pair repulsion (zbl.hpp:43-56): exponent / prefactor of the screening length, 4 screening coefficients,
+    // covalent radii indexed by atomic number, envelope order
+    double zbl_a_exp = 0.0, zbl_a_prefactor = 0.0;
+    std::vector<double> zbl_c, zbl_covalent_radii;
+    int zbl_p = 0;
+    // density normalisation of the two interaction layers (mace.cpp:273-346, 681-757): scalar cubic splines per
+    // unordered element pair, coefficients [pair][bin][4] (cubic_spline.cpp:55-71)
+    bool A0_scaled = false, A1_scaled = false;
+    double A0_spline_h = 0.0, A1_spline_h = 0.0;
+    int A0_spline_bins = 0, A1_spline_bins = 0;
+    std::vector<double> A0_spline_coef, A1_spline_coef;
 
     // radial splines: coefficient tables [pair][bin][function][4] (cubic_spline_set.cpp:5-25)
     double spline_h = 0.0;
@@ -214,9 +225,44 @@ inline HostModel load_model_file(const std::string& filename) {
     if (m.l_max != kLmaxSH) throw UnsupportedError("only l_max == 3 is supported (as in the reference exporter)");
     if (m.L_max < 0 || m.L_max > 2) throw UnsupportedError("hidden features up to L_max == 2 are supported");
     if (K < 1 || K > 1024) throw UnsupportedError("num_channels must be in 1..1024");
-    if (m.has_zbl) throw UnsupportedError("ZBL pair repulsion is not covered by this build");
-    if (file.at("A0_scaled").as_bool() || file.at("A1_scaled").as_bool())
-        throw UnsupportedError("density-normalised interactions (A0_scaled / A1_scaled) are not covered by this build");
+    if (m.has_zbl) {
+        m.zbl_a_exp = file.at("zbl_a_exp").as_double();
+        m.zbl_a_prefactor = file.at("zbl_a_prefactor").as_double();
+        m.zbl_c = file.at("zbl_c").flat();
+        m.zbl_covalent_radii = file.at("zbl_covalent_radii").flat();
+        m.zbl_p = file.at("zbl_p").as_int();
+        if (m.zbl_c.size() != 4) throw ModelError("model file: zbl_c needs 4 coefficients");
+        for (int z : m.atomic_numbers)
+            if (z < 0 || z >= static_cast<int>(m.zbl_covalent_radii.size())) throw ModelError("model file: zbl_covalent_radii does not cover the model's elements");
+    }
+    auto load_scalar_splines = [&](const char* hkey, const char* vkey, const char* dkey, double& h, int& bins, std::vector<double>& coef) {
+        h = file.at(hkey).as_double();
+        const JsonValue& vals = file.at(vkey);
+        const JsonValue& ders = file.at(dkey);
+        const int pairs = E * (E + 1) / 2;
+        if (vals.type != JsonValue::Array || static_cast<int>(vals.size()) != pairs || static_cast<int>(ders.size()) != pairs)
+            throw ModelError(std::string("model file: ") + vkey + " must have one spline per unordered element pair");
+        const int G = static_cast<int>(vals.arr[0].size());
+        if (G < 2) throw ModelError("model file: density splines need at least two nodes");
+        bins = G - 1;
+        coef.assign(static_cast<size_t>(pairs) * bins * 4, 0.0);
+        for (int pr = 0; pr < pairs; ++pr) {
+            const auto& v = vals.arr[pr].nums;
+            const auto& d = ders.arr[pr].nums;
+            if (static_cast<int>(v.size()) != G || static_cast<int>(d.size()) != G) throw ModelError("model file: ragged density spline table");
+            for (int i = 0; i < bins; ++i) {   // CubicSpline::generate_coefficients, cubic_spline.cpp:61-69
+                double* o = coef.data() + (static_cast<size_t>(pr) * bins + i) * 4;
+                o[0] = v[i];
+                o[1] = d[i];
+                o[2] = (-3 * o[0] - 2 * h * o[1] + 3 * v[i + 1] - h * d[i + 1]) / (h * h);
+                o[3] = (2 * o[0] + h * o[1] - 2 * v[i + 1] + h * d[i + 1]) / (h * h * h);
+            }
+        }
+    };
+    m.A0_scaled = file.at("A0_scaled").as_bool();
+    m.A1_scaled = file.at("A1_scaled").as_bool();
+    if (m.A0_scaled) load_scalar_splines("A0_spline_h", "A0_spline_values", "A0_spline_derivs", m.A0_spline_h, m.A0_spline_bins, m.A0_spline_coef);
+    if (m.A1_scaled) load_scalar_splines("A1_spline_h", "A1_spline_values", "A1_spline_derivs", m.A1_spline_h, m.A1_spline_bins, m.A1_spline_coef);
 
     // ---- tensor-product paths: map the file's order onto the canonical table
     m.tp = make_tp_table(m.L_max);

@@ -122,6 +122,7 @@ class MACE:
 
     # Stage methods. They take the reference's argument lists for source compatibility, but the
     # edge arrays in effect are those of the last begin() / compute_node_energies_forces().
+    def compute_ZBL(self, *a): self._stage("compute_ZBL")
     def compute_Y(self, *a): self._stage("compute_Y")
     def compute_R0(self, *a): self._stage("compute_R0")
     def compute_R1(self, *a): self._stage("compute_R1")
@@ -137,7 +138,7 @@ class MACE:
     def compute_readouts(self, *a): self._stage("compute_readouts")
     def reverse_M1(self, *a): self._stage("reverse_M1")
     def reverse_A1(self, *a): self._stage("reverse_A1")
-    def reverse_A1_scaled(self, *a): self._stage("reverse_A1_scaled")
+    def reverse_A1_scaled(self, *a, zero_dxyz=True): self._stage("reverse_A1_scaled", zero_dxyz, True)
     def reverse_H1(self, *a): self._stage("reverse_H1")
     def reverse_M0(self, *a): self._stage("reverse_M0")
     def reverse_A0_scaled(self, *a): self._stage("reverse_A0_scaled")

@@ -38,6 +38,8 @@ class ModelSpec:
     avg_num_neighbors: float = 40.0
     seed: int = 0
     correlation: int = 3
+    zbl: bool = False          # add a ZBL pair repulsion (MACE "pair_repulsion")
+    density: bool = False      # density-normalised interaction blocks (A0_scaled / A1_scaled)
     extra: dict = field(default_factory=dict)
 
 
@@ -239,7 +241,14 @@ def generate_model(spec: ModelSpec) -> dict:
     out["atomic_numbers"] = sorted(int(z) for z in spec.atomic_numbers)
     out["num_elements"] = n_el
     out["atomic_energies"] = rng.uniform(-5.0, -1.0, size=n_el)
-    out["has_zbl"] = False
+    out["has_zbl"] = bool(spec.zbl)
+    if spec.zbl:
+        # universal ZBL screening coefficients; synthetic covalent radii (the envelope vanishes at r_u + r_v)
+        out["zbl_a_exp"] = 0.3
+        out["zbl_a_prefactor"] = 0.4543
+        out["zbl_c"] = [0.1818, 0.5099, 0.2802, 0.02817]
+        out["zbl_covalent_radii"] = [0.2] + [0.6 + 0.35 * math.sqrt(z) / (1.0 + 0.02 * z) for z in range(1, 119)]
+        out["zbl_p"] = 6
 
     paths, lme, t_idx, cg = tp_tables(l_max, L_max)
     h, v0, d0, mlp0, _ = radial_mlp_tables(spec, rng, (l_max + 1) * k, gain=1.0)
@@ -251,7 +260,23 @@ def generate_model(spec: ModelSpec) -> dict:
     out["radial_spline_derivs_1"] = d1
 
     out["H0_weights"] = rng.standard_normal(n_el * k)
-    out["A0_scaled"] = False
+    def density_tables():
+        """tanh(f(r)^2) per element pair, f a random combination of the radial basis, tabulated like the radial functions."""
+        g = spec.num_spline_points
+        rr, hh = np.linspace(1e-12, spec.r_cut, g, retstep=True)
+        basis = bessel_cutoff_basis(rr, spec.r_cut, spec.num_bessel, spec.poly_p)
+        vals, ders = [], []
+        for a in range(n_el):
+            for b in range(a, n_el):
+                w = rng.standard_normal(spec.num_bessel)
+                y = np.tanh((basis @ w) ** 2)
+                spl = CubicSpline(rr, y, bc_type=("not-a-knot", "clamped"))
+                vals.append(spl(rr)); ders.append(spl.derivative()(rr))
+        return float(hh), np.stack(vals), np.stack(ders)
+
+    out["A0_scaled"] = bool(spec.density)
+    if spec.density:
+        out["A0_spline_h"], out["A0_spline_values"], out["A0_spline_derivs"] = density_tables()
     out["A0_weights"] = rng.standard_normal((n_el, l_max + 1, k * k)) / (math.sqrt(k) * math.sqrt(spec.avg_num_neighbors))
 
     def contraction_weights(L_list):
@@ -286,7 +311,9 @@ def generate_model(spec: ModelSpec) -> dict:
     out["Phi1_clebsch_gordan"] = cg
     out["Phi1_lelm1lm2"] = t_idx
 
-    out["A1_scaled"] = False
+    out["A1_scaled"] = bool(spec.density)
+    if spec.density:
+        out["A1_spline_h"], out["A1_spline_values"], out["A1_spline_derivs"] = density_tables()
     num_e = [sum(1 for p in paths if p[0] == l) for l in range(l_max + 1)]
     out["A1_weights"] = [
         (rng.standard_normal(num_e[l] * k * k) / (math.sqrt(num_e[l] * k) * math.sqrt(spec.avg_num_neighbors)))

@@ -349,3 +349,31 @@ def test_models_with_unusual_monomials_use_the_table_driven_contraction(tiny, tm
     ev = MACE(path, dtype=dtype)
     e, f = run(ev, inputs)
     check_against(dtype, e, f, e_ref, f_ref)
+
+
+@pytest.mark.parametrize("dtype", ["float64", "float32"])
+@pytest.mark.parametrize("flags", [dict(zbl=True), dict(density=True), dict(zbl=True, density=True)])
+def test_zbl_and_density_normalised_models(model_file, dtype, flags):
+    """Models of the MACE-MP kind: ZBL pair repulsion (zbl.cpp) and density-normalised interaction blocks
+    (mace.cpp:273-346, 681-757), against the compiled reference (or its restatement)."""
+    path, model, spec = model_file("fcc128", num_channels=32, num_spline_points=32, **flags)
+    s = st.fcc_box(3, 3.2, model["atomic_numbers"], seed=9, jitter=0.25)       # some pairs inside the ZBL envelope
+    nl = st.neighbor_list(s, spec.r_cut)
+    inputs = st.evaluator_inputs(s, nl, model["atomic_numbers"])
+    e_ref, f_ref = _oracle_for(path, model)(inputs)
+    ev = MACE(path, dtype=dtype)
+    assert ev.has_zbl == bool(flags.get("zbl"))
+    e, f = run(ev, inputs)
+    check_against(dtype, e, f, e_ref, f_ref)
+    # the same through the staged call sequence of the pair style, ZBL first (pair_symmetrix_mace.cpp:441-495)
+    ev.begin(int(inputs["num_nodes"]), inputs["node_types"], inputs["num_neigh"], inputs["neigh_indices"], inputs["neigh_types"],
+             inputs["xyz"], inputs["r"])
+    ev.compute_ZBL()
+    for stage in ["compute_Y", "compute_R0", "compute_A0", "compute_A0_scaled", "compute_M0", "compute_H1", "compute_R1", "compute_Phi1",
+                  "compute_A1", "compute_A1_scaled", "compute_M1", "compute_H2", "compute_readouts"]:
+        getattr(ev, stage)()
+    ev.reverse_H2(zero_H1_adj=False); ev.reverse_M1(); ev.reverse_A1_scaled(zero_dxyz=False); ev.reverse_A1()
+    ev.reverse_Phi1(zero_dxyz=False, zero_H1_adj=False)
+    for stage in ["reverse_H1", "reverse_M0", "reverse_A0_scaled", "reverse_A0"]:
+        getattr(ev, stage)()
+    check_against(dtype, ev.node_energies, ev.node_forces, e_ref, f_ref)

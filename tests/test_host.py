@@ -63,12 +63,18 @@ def test_create_reports_missing_and_malformed_files(tmp_path):
 
 def test_create_rejects_models_outside_the_supported_set(tmp_path):
     model = json.loads((GOLDEN / "tiny_model.json").read_text())
-    for key, val, expect in [("has_zbl", True, "ZBL"), ("A0_scaled", True, "density"), ("l_max", 2, "l_max")]:
+    for key, val, expect in [("l_max", 2, "l_max"), ("L_max", 3, "L_max")]:
         m = dict(model); m[key] = val
         p = tmp_path / f"{key}.json"
         p.write_text(json.dumps(m))
         status, msg = _create(p)
         assert status == _lib.SMX_ERR_UNSUPPORTED and expect in msg, (key, status, msg)
+    for key, expect in [("has_zbl", "zbl_a_exp"), ("A0_scaled", "A0_spline_h")]:    # switched on without their tables
+        m = dict(model); m[key] = True
+        p = tmp_path / f"{key}.json"
+        p.write_text(json.dumps(m))
+        status, msg = _create(p)
+        assert status == _lib.SMX_ERR_MODEL and expect in msg, (key, status, msg)
     m = dict(model); m["H1_weights"] = model["H1_weights"][:-1]
     p = tmp_path / "short.json"; p.write_text(json.dumps(m))
     status, msg = _create(p)

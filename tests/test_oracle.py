@@ -121,3 +121,38 @@ def test_energy_is_rotation_invariant(tiny):
     e1, f1 = o.compute_node_energies_forces(inp)
     np.testing.assert_allclose(e1, e0, rtol=1e-11, atol=1e-12)
     np.testing.assert_allclose(f1.reshape(-1, 3), f0.reshape(-1, 3) @ rot.T, atol=1e-11)
+
+
+@pytest.mark.skipif(not ref_driver.available(), reason="oracle/_ref not built (needs the reference checkout)")
+def test_port_matches_compiled_reference_with_zbl_and_density_normalisation(model_file):
+    path, model, spec = model_file("tiny", zbl=True, density=True)
+    s = st.water_box(2, 8.0, seed=3)
+    nl = st.neighbor_list(s, spec.r_cut)
+    inputs = st.evaluator_inputs(s, nl, model["atomic_numbers"])
+    e_ref, f_ref = ref_driver.ReferenceMACE(path).compute_node_energies_forces(inputs)
+    e, f = MaceOracle(model).compute_node_energies_forces(inputs)
+    np.testing.assert_allclose(e, e_ref, rtol=1e-12, atol=1e-13)
+    np.testing.assert_allclose(f, f_ref, rtol=1e-10, atol=1e-12)
+    plain_path, plain_model, _ = model_file("tiny")
+    e_plain, _ = MaceOracle(plain_model).compute_node_energies_forces(inputs)
+    assert abs(e.sum() - e_plain.sum()) > 1.0      # the two extra terms are not negligible in this test
+
+
+def test_port_forces_with_zbl_and_density_are_energy_gradients(model_file):
+    path, model, spec = model_file("tiny", zbl=True, density=True)
+    s = st.water_box(2, 8.0, seed=3)
+    nl = st.neighbor_list(s, spec.r_cut)
+    inputs = st.evaluator_inputs(s, nl, model["atomic_numbers"])
+    o = MaceOracle(model)
+    _, f = o.compute_node_energies_forces(inputs)
+    f = f.reshape(-1, 3)
+    xyz = inputs["xyz"].reshape(-1, 3).copy()
+    h = 1e-5
+    for e in (3, 40, 77):
+        for c in range(3):
+            vals = []
+            for sgn in (+1, -1):
+                x2 = xyz.copy(); x2[e, c] += sgn * h
+                inp = dict(inputs); inp["xyz"] = x2.reshape(-1); inp["r"] = np.linalg.norm(x2, axis=1)
+                vals.append(o.compute_node_energies_forces(inp)[0].sum())
+            assert abs(-(vals[0] - vals[1]) / (2 * h) - f[e, c]) < 2e-6 * max(1.0, abs(f[e, c]))
