@@ -165,13 +165,17 @@ int smx_compute_current(smx_handle h);
 /* Helpers for callers that decompose a structure across GPUs and exchange halo rows on the device
  * (the role LAMMPS' Comm plays for the reference's message-passing mode, pair_symmetrix_mace.cpp:
  * 194-238,463-490 -- there the rows travel through host vectors and MPI).
- * smx_sync waits for the evaluator's stream. smx_restrict_nodes keeps only the first `num_nodes`
+ * smx_sync waits for the evaluator's stream; smx_set_stream makes the evaluator issue all further work on the
+ * caller's cudaStream_t when `external` is non-zero (a NULL handle then means the legacy default stream) and
+ * returns to its own stream when `external` is zero, so that pack / unpack kernels and NCCL calls of the
+ * caller are ordered with the evaluator's kernels without host synchronisation. smx_restrict_nodes keeps only the first `num_nodes`
  * receivers of the current edge set (owned atoms first, ghost atoms after them) and returns the
  * remaining edge count. smx_resize_rows grows "H1" or "H1_adj" to `rows` feature rows, keeping the
  * computed rows and zero-filling the appended ghost rows. smx_device_ptr returns the device address,
  * element count and element size (4 or 8 bytes) of a named array so that pack / unpack kernels and
  * NCCL can work on it in place; the pointer is valid until the next call that resizes that array. */
 int smx_sync(smx_handle h);
+int smx_set_stream(smx_handle h, void* stream, int external);
 int smx_restrict_nodes(smx_handle h, int num_nodes, long* num_edges);
 int smx_resize_rows(smx_handle h, const char* name, int rows);
 int smx_device_ptr(smx_handle h, const char* name, void** ptr, long* count, int* elem_bytes);

@@ -45,6 +45,7 @@ public:
     virtual void timer_start() = 0;
     virtual double timer_stop() = 0;
     virtual void sync() = 0;
+    virtual void set_stream(void* s, bool external) = 0;
     virtual long restrict_nodes(int num_nodes) = 0;
     virtual void resize_rows(const std::string& name, int rows) = 0;
     virtual void* device_ptr(const std::string& name, long* count, int* elem_bytes) = 0;
@@ -94,8 +95,14 @@ public:
     // per-call arrays
     DevBuf<T> Phi0, A0, A0_adj, Phi0_adj, M0, M0_adj, H1, H1_adj, Phi1, dPhi1, A1, A1_adj, M1, M1_adj, H2, H2_adj, Hmsg;
     DevBuf<double> node_energies, node_forces, scratch_d, partials, out7, atom_f;
-    DevBuf<GemmProblem<T>> problems;
-    std::vector<GemmProblem<T>> host_problems;
+    // GEMM problem lists travel through a pinned host ring and a device ring, so launches need no host synchronisation;
+    // the rings hold far more entries than one evaluation uses (a slot is reused only thousands of launches later)
+    static constexpr size_t kProblemRing = 8192;
+    GemmProblem<T>* host_ring = nullptr;
+    DevBuf<GemmProblem<T>> dev_ring;
+    size_t ring_pos = 0;
+    bool own_stream = true;
+    cudaStream_t own_stream_handle = nullptr;
     NeighborBuilder nb;
 
     explicit Evaluator(HostModel&& m, int dev) {
@@ -104,6 +111,8 @@ public:
         precision = sizeof(T) == 4 ? 32 : 64;
         SMX_CUDA(cudaSetDevice(dev));
         SMX_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
+        SMX_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&host_ring), kProblemRing * sizeof(GemmProblem<T>), cudaHostAllocDefault));
+        dev_ring.resize(kProblemRing, stream);
         SMX_CUDA(cudaEventCreate(&ev0));
         SMX_CUDA(cudaEventCreate(&ev1));
         SMX_CUDA(cudaEventCreate(&evt0));
@@ -121,7 +130,9 @@ public:
         if (evt0) cudaEventDestroy(evt0);
         if (evt1) cudaEventDestroy(evt1);
         for (auto e : stage_events) cudaEventDestroy(e);
-        if (stream) cudaStreamDestroy(stream);
+        if (host_ring) cudaFreeHost(host_ring);
+        if (!own_stream && own_stream_handle) cudaStreamDestroy(own_stream_handle);
+        if (stream && own_stream) cudaStreamDestroy(stream);
     }
 
     void upload_model() {
@@ -290,13 +301,15 @@ public:
     // ------------------------------------------------------------------ GEMM plumbing
     void run_gemms(const std::vector<GemmProblem<T>>& list, long long max_rows, int max_cols) {
         if (list.empty() || max_rows <= 0) return;
-        problems.resize(list.size(), stream);
-        SMX_CUDA(cudaMemcpyAsync(problems.p, list.data(), list.size() * sizeof(GemmProblem<T>), cudaMemcpyHostToDevice, stream));
-        SMX_CUDA(cudaStreamSynchronize(stream));  // `list` is a temporary of the caller
+        if (list.size() > kProblemRing) throw UnsupportedError("too many element types for one GEMM launch");
+        if (ring_pos + list.size() > kProblemRing) ring_pos = 0;
+        std::copy(list.begin(), list.end(), host_ring + ring_pos);
+        SMX_CUDA(cudaMemcpyAsync(dev_ring.p + ring_pos, host_ring + ring_pos, list.size() * sizeof(GemmProblem<T>), cudaMemcpyHostToDevice, stream));
         dim3 grid(static_cast<unsigned>((max_rows + kGemmBM - 1) / kGemmBM), (max_cols + kGemmBN - 1) / kGemmBN,
                   static_cast<unsigned>(list.size()));
-        gemm_rows_kernel<T><<<grid, kGemmThreads, 0, stream>>>(problems.p);
+        gemm_rows_kernel<T><<<grid, kGemmThreads, 0, stream>>>(dev_ring.p + ring_pos);
         check_launch("gemm_rows_kernel");
+        ring_pos += list.size();
     }
     GemmProblem<T> problem(const T* A, T* C, const T* B, bool by_type, int type, int sub_count, long long a_ns, long long a_off,
                            long long a_ss, long long c_ns, long long c_off, long long c_ss, int Kd, int Nc, int ldb, bool transB,
@@ -650,6 +663,20 @@ public:
     void sync() override {
         SMX_CUDA(cudaSetDevice(device));
         SMX_CUDA(cudaStreamSynchronize(stream));
+    }
+    // Issue all further work on the caller's stream (`external`), or go back to the evaluator's own stream.
+    // A null handle with `external` set means the legacy default stream.
+    void set_stream(void* s, bool external) override {
+        SMX_CUDA(cudaSetDevice(device));
+        SMX_CUDA(cudaStreamSynchronize(stream));
+        if (external) {
+            if (own_stream) own_stream_handle = stream;
+            stream = static_cast<cudaStream_t>(s);
+            own_stream = false;
+        } else if (!own_stream) {
+            stream = own_stream_handle;
+            own_stream = true;
+        }
     }
     // Keep only the first `num_nodes` receivers of the current edge set (their rows are a prefix of the edge arrays).
     long restrict_nodes(int num_nodes) override {
@@ -1062,6 +1089,9 @@ long smx_launch_count(smx_handle h) { return (h && h->impl) ? h->impl->launches 
 
 int smx_sync(smx_handle h) {
     return guarded(h, [&](smx::EvaluatorBase& e) { e.sync(); });
+}
+int smx_set_stream(smx_handle h, void* stream, int external) {
+    return guarded(h, [&](smx::EvaluatorBase& e) { e.set_stream(stream, external != 0); });
 }
 int smx_restrict_nodes(smx_handle h, int num_nodes, long* num_edges) {
     return guarded(h, [&](smx::EvaluatorBase& e) { const long n = e.restrict_nodes(num_nodes); if (num_edges) *num_edges = n; });

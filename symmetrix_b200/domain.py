@@ -137,6 +137,11 @@ class SlabRank:
         self.send_idx = {q: torch.as_tensor(np.ascontiguousarray(r), dtype=torch.long, device=self.device) for q, r in plan.send_rows.items()}
         self.recv_idx = {q: torch.as_tensor(np.ascontiguousarray(r), dtype=torch.long, device=self.device) for q, r in plan.recv_rows.items()}
         self.num_edges = 0
+        # on a GPU the evaluator shares torch's current stream: pack / unpack kernels, NCCL and the evaluator's kernels are
+        # then ordered by the stream and no host synchronisation is needed between phases
+        self.shared_stream = self.device != "cpu" and hasattr(self.ev, "use_torch_stream")
+        if self.shared_stream:
+            self.ev.use_torch_stream(True)
         self.stage_ms = None          # set to {} to collect per-stage device times (adds a stream sync per stage)
 
     def _run(self, stage, *flags):
@@ -171,7 +176,8 @@ class SlabRank:
         return self.ev.device_view(name).view(-1, self.width)
 
     def pack_forward(self, peer):
-        self.ev.sync()
+        if not self.shared_stream:
+            self.ev.sync()
         return self._rows_view("H1").index_select(0, self.send_idx[peer]).contiguous()
 
     def unpack_forward(self, peer, buf):
@@ -187,7 +193,8 @@ class SlabRank:
         self._run("reverse_Phi1", False, False)
 
     def pack_reverse(self, peer):
-        self.ev.sync()
+        if not self.shared_stream:
+            self.ev.sync()
         return self._rows_view("H1_adj").index_select(0, self.recv_idx[peer]).contiguous()
 
     def unpack_reverse(self, peer, buf):
@@ -212,7 +219,7 @@ class SlabRank:
         return self.forces[: self.plan.n_own]
 
     def _sync_torch(self):
-        if self.device != "cpu":
+        if self.device != "cpu" and not self.shared_stream:
             self.torch.cuda.synchronize()
 
 

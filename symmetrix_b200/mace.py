@@ -239,6 +239,12 @@ class MACE:
     def sync(self) -> None:
         self._check(self._lib.smx_sync(self._h))
 
+    def use_torch_stream(self, enable: bool = True) -> None:
+        """Issue the evaluator's work on torch's current CUDA stream, so torch kernels and NCCL calls are ordered with it."""
+        import torch
+        ptr = torch.cuda.current_stream(self.info.device).cuda_stream if enable else None
+        self._check(self._lib.smx_set_stream(self._h, ctypes.c_void_p(ptr), 1 if enable else 0))
+
     def restrict_nodes(self, num_nodes: int) -> int:
         """Keep the first ``num_nodes`` receivers of the current edge set (owned atoms first); returns the edge count."""
         n = ctypes.c_long(0)
