@@ -16,6 +16,7 @@
 #include "../../include/symmetrix_b200.h"
 #include "common.cuh"
 #include "kernels.cuh"
+#include "gemm_tcgen05.cuh"
 #include "model.hpp"
 #include "neighbors.cuh"
 
@@ -102,6 +103,8 @@ public:
     DevBuf<GemmProblem<T>> dev_ring;
     size_t ring_pos = 0;
     bool own_stream = true;
+    DevBuf<int> tc5_status;       // non-zero if a bounded wait of the tcgen05 GEMM ran out
+    bool use_tc5 = false;
     cudaStream_t own_stream_handle = nullptr;
     NeighborBuilder nb;
 
@@ -113,6 +116,13 @@ public:
         SMX_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
         SMX_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&host_ring), kProblemRing * sizeof(GemmProblem<T>), cudaHostAllocDefault));
         dev_ring.resize(kProblemRing, stream);
+        tc5_status.resize(1, stream);
+        tc5_status.zero(stream);
+        if constexpr (sizeof(T) == 4) {
+            const char* g = std::getenv("SMX_GEMM");
+            use_tc5 = g && std::string(g) == "tcgen05";
+            SMX_CUDA(cudaFuncSetAttribute(gemm_rows_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTc5SmemBytes));
+        }
         SMX_CUDA(cudaEventCreate(&ev0));
         SMX_CUDA(cudaEventCreate(&ev1));
         SMX_CUDA(cudaEventCreate(&evt0));
@@ -307,6 +317,15 @@ public:
         SMX_CUDA(cudaMemcpyAsync(dev_ring.p + ring_pos, host_ring + ring_pos, list.size() * sizeof(GemmProblem<T>), cudaMemcpyHostToDevice, stream));
         dim3 grid(static_cast<unsigned>((max_rows + kGemmBM - 1) / kGemmBM), (max_cols + kGemmBN - 1) / kGemmBN,
                   static_cast<unsigned>(list.size()));
+        if constexpr (sizeof(T) == 4) {
+            if (use_tc5) {
+                dim3 g5(static_cast<unsigned>((max_rows + kTc5BM - 1) / kTc5BM), (max_cols + kTc5BN - 1) / kTc5BN, static_cast<unsigned>(list.size()));
+                gemm_rows_tcgen05_kernel<<<g5, kTc5Threads, kTc5SmemBytes, stream>>>(dev_ring.p + ring_pos, tc5_status.p);
+                check_launch("gemm_rows_tcgen05_kernel");
+                ring_pos += list.size();
+                return;
+            }
+        }
         gemm_rows_kernel<T><<<grid, kGemmThreads, 0, stream>>>(dev_ring.p + ring_pos);
         check_launch("gemm_rows_kernel");
         ring_pos += list.size();
@@ -707,6 +726,13 @@ public:
         if (elem_bytes) *elem_bytes = f.t ? static_cast<int>(sizeof(T)) : 8;
         return f.t ? static_cast<void*>(f.t->p) : static_cast<void*>(f.d->p);
     }
+    // Synchronises the stream and reports a tcgen05 GEMM whose bounded mbarrier wait ran out.
+    void check_tensor_core_status() {
+        int code = 0;
+        if (use_tc5) SMX_CUDA(cudaMemcpyAsync(&code, tc5_status.p, sizeof(int), cudaMemcpyDeviceToHost, stream));
+        SMX_CUDA(cudaStreamSynchronize(stream));
+        if (code != 0) throw CudaError("tensor-core GEMM: a bounded mbarrier wait ran out (code " + std::to_string(code) + ")");
+    }
     void timer_start() override {
         SMX_CUDA(cudaSetDevice(device));
         SMX_CUDA(cudaEventRecord(evt0, stream));
@@ -744,7 +770,7 @@ public:
         tick(); reverse_H2(false); tick(); reverse_M1(); reverse_A_scaled(false, false); tick(); reverse_A1(); tick(); reverse_Phi1(false, false);
         tick(); reverse_H1(); tick(); reverse_M0(); reverse_A_scaled(true, false); tick(); reverse_A0(); tick();
         SMX_CUDA(cudaEventRecord(ev1, stream));
-        SMX_CUDA(cudaStreamSynchronize(stream));
+        check_tensor_core_status();
         float ms = 0.f;
         SMX_CUDA(cudaEventElapsedTime(&ms, ev0, ev1));
         last_ms = ms;
@@ -800,7 +826,7 @@ public:
         }
         SMX_CUDA(cudaMemcpyAsync(dst, src, ncopy * sizeof(double),
                                  mem_space == SMX_DEVICE ? cudaMemcpyDeviceToDevice : cudaMemcpyDeviceToHost, stream));
-        SMX_CUDA(cudaStreamSynchronize(stream));
+        check_tensor_core_status();
         return static_cast<long>(n);
     }
 
@@ -861,7 +887,7 @@ public:
             if (energy) SMX_CUDA(cudaMemcpyAsync(energy, out7.p, sizeof(double), kind, stream));
             if (virial) SMX_CUDA(cudaMemcpyAsync(virial, out7.p + 1, 6 * sizeof(double), kind, stream));
         }
-        SMX_CUDA(cudaStreamSynchronize(stream));
+        check_tensor_core_status();
     }
 
     // ------------------------------------------------------------------ neighbour list
