@@ -17,6 +17,8 @@
 #include "common.cuh"
 #include "kernels.cuh"
 #include "gemm_tcgen05.cuh"
+#include <type_traits>
+
 #include "model.hpp"
 #include "neighbors.cuh"
 
@@ -27,6 +29,27 @@ static std::vector<T> cast_vec(const std::vector<double>& v) {
     std::vector<T> o(v.size());
     for (size_t i = 0; i < v.size(); ++i) o[i] = static_cast<T>(v[i]);
     return o;
+}
+
+// Spline tables for the device: rows of 4*K values per (pair, bin, function block). float keeps the host
+// order [K][4]; double splits every row into [2][K][2] so that both 16-byte loads of a warp are contiguous
+// (see load_coef).
+template <typename T>
+static std::vector<T> spline_rows(const std::vector<double>& v, int K) {
+    if constexpr (std::is_same<T, float>::value) {
+        return cast_vec<T>(v);
+    } else {
+        std::vector<T> o(v.size());
+        const size_t row = static_cast<size_t>(4) * K;
+        for (size_t r0 = 0; r0 + row <= v.size(); r0 += row)
+            for (int k = 0; k < K; ++k) {
+                o[r0 + 2 * k] = v[r0 + 4 * k];
+                o[r0 + 2 * k + 1] = v[r0 + 4 * k + 1];
+                o[r0 + 2 * K + 2 * k] = v[r0 + 4 * k + 2];
+                o[r0 + 2 * K + 2 * k + 1] = v[r0 + 4 * k + 3];
+            }
+        return o;
+    }
 }
 
 struct CastToLL {
@@ -147,8 +170,9 @@ public:
 
     void upload_model() {
         const HostModel& m = model;
-        coef0.upload(cast_vec<T>(m.coef0), stream);
-        coef1.upload(cast_vec<T>(m.coef1), stream);
+        coef0.upload(spline_rows<T>(m.coef0, m.K), stream);
+        coef1.upload(spline_rows<T>(m.coef1, m.K), stream);
+
         H0_w.upload(cast_vec<T>(m.H0_w), stream);
         A0_w.upload(cast_vec<T>(m.A0_w), stream);
         H1_w.upload(cast_vec<T>(m.H1_w), stream);

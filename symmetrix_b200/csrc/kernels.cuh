@@ -2,7 +2,8 @@
 //
 // Data layout in HBM (all row-major, channel index fastest, one arithmetic type T per evaluator):
 //   node features  A0/A1 [N][16][K], M0/H1 [rows][nLM][K], Phi1 [N][Q][K], M1/H2 [N][K]
-//   spline tables  [pair][bin][function][4]  (one 16/32-byte vector load per function and edge)
+//   spline tables  [pair][bin][function block][K][4] in float, [pair][bin][function block][2][K][2] in double
+//                  (16-byte vector loads that a warp issues over contiguous 512-byte spans)
 //   contraction    coefficients [element][monomial][K]
 // One thread owns one channel k of one receiver node, so every global access is a contiguous
 // run of K values across the CTA. Per-edge quantities that do not depend on the channel
@@ -44,17 +45,22 @@ template <typename T> struct Vec4;
 template <> struct alignas(16) Vec4<float> { float x, y, z, w; };
 template <> struct alignas(32) Vec4<double> { double x, y, z, w; };
 
+// The four cubic coefficients of channel k from one (pair, bin, function-block) row of 4*K values.
+// float rows are [K][4]: one 16-byte load per thread, a warp reads 512 contiguous bytes.
+// double rows are [2][K][2] (c0,c1 of every channel, then c2,c3 of every channel): each of the two 16-byte
+// loads of a warp is again 512 contiguous bytes, i.e. 4 L1 wavefronts instead of the 8 an interleaved
+// [K][4] row of doubles (32-byte stride between lanes) costs.
 template <typename T>
-__device__ __forceinline__ Vec4<T> load4(const T* p);
+__device__ __forceinline__ Vec4<T> load_coef(const T* row, int k, int K);
 template <>
-__device__ __forceinline__ Vec4<float> load4<float>(const float* p) {
-    const float4 v = __ldg(reinterpret_cast<const float4*>(p));
+__device__ __forceinline__ Vec4<float> load_coef<float>(const float* row, int k, int) {
+    const float4 v = __ldg(reinterpret_cast<const float4*>(row) + k);
     return {v.x, v.y, v.z, v.w};
 }
 template <>
-__device__ __forceinline__ Vec4<double> load4<double>(const double* p) {
-    const double2 a = __ldg(reinterpret_cast<const double2*>(p));
-    const double2 b = __ldg(reinterpret_cast<const double2*>(p) + 1);
+__device__ __forceinline__ Vec4<double> load_coef<double>(const double* row, int k, int K) {
+    const double2 a = __ldg(reinterpret_cast<const double2*>(row) + k);
+    const double2 b = __ldg(reinterpret_cast<const double2*>(row) + K + k);
     return {a.x, a.y, b.x, b.y};
 }
 
@@ -250,10 +256,10 @@ __global__ void __launch_bounds__(kChannelBlock) layer0_forward_kernel(const Lay
                     const EdgeStage<T>& s = st[e];
                     const T h0 = a.H0_w[s.tj * a.K + k];
                     const T x = s.x;
-                    const T* cb = a.coef0 + s.coef_base + 4 * k;
+                    const T* cb = a.coef0 + s.coef_base;
 #pragma unroll
                     for (int l = 0; l <= kLmaxSH; ++l) {
-                        const Vec4<T> c = load4<T>(cb + 4 * l * a.K);
+                        const Vec4<T> c = load_coef<T>(cb + 4 * l * a.K, k, a.K);
                         const T R = (c.x + x * (c.y + x * (c.z + x * c.w))) * h0;
 #pragma unroll
                         for (int lm = l * l; lm < (l + 1) * (l + 1); ++lm) acc[lm] += R * s.Y[lm];
@@ -304,10 +310,10 @@ __global__ void __launch_bounds__(kChannelBlock) layer0_reverse_kernel(const Lay
                 if (active) {
                     const T h0 = a.H0_w[s.tj * a.K + k];
                     const T x = s.x;
-                    const T* cb = a.coef0 + s.coef_base + 4 * k;
+                    const T* cb = a.coef0 + s.coef_base;
 #pragma unroll
                     for (int l = 0; l <= kLmaxSH; ++l) {
-                        const Vec4<T> c = load4<T>(cb + 4 * l * a.K);
+                        const Vec4<T> c = load_coef<T>(cb + 4 * l * a.K, k, a.K);
                         const T R = (c.x + x * (c.y + x * (c.z + x * c.w))) * h0;
                         const T Rd = (c.y + x * (T(2) * c.z + T(3) * x * c.w)) * h0;
                         T sv = 0;
@@ -390,14 +396,14 @@ __global__ void __launch_bounds__(kChannelBlock, tp_min_blocks<T>(LF, false)) tp
                 for (int e = 0; e < nb; ++e) {
                     const EdgeStage<T>& s = st[e];
                     const T x = s.x;
-                    const T* cb = a.coef1 + s.coef_base + 4 * k;
+                    const T* cb = a.coef1 + s.coef_base;
                     const T* hrow = a.H + static_cast<size_t>(s.j) * tp.nLM * a.K + k;
                     T h[tp.nLM], R[tp.P], Y[kNumLm];
 #pragma unroll
                     for (int lm2 = 0; lm2 < tp.nLM; ++lm2) h[lm2] = __ldg(hrow + static_cast<size_t>(lm2) * a.K);
 #pragma unroll
                     for (int p = 0; p < tp.P; ++p) {
-                        const Vec4<T> c = load4<T>(cb + 4 * p * a.K);
+                        const Vec4<T> c = load_coef<T>(cb + 4 * p * a.K, k, a.K);
                         R[p] = c.x + x * (c.y + x * (c.z + x * c.w));
                     }
 #pragma unroll
@@ -456,14 +462,14 @@ __global__ void __launch_bounds__(kChannelBlock, tp_min_blocks<T>(LF, true)) tp_
                 for (int lm = 0; lm < kNumLm; ++lm) W[lm] = T(0);
                 if (active) {
                     const T x = s.x;
-                    const T* cb = a.coef1 + s.coef_base + 4 * k;
+                    const T* cb = a.coef1 + s.coef_base;
                     const T* hrow = a.H + static_cast<size_t>(s.j) * tp.nLM * a.K + k;
                     T h[tp.nLM], msg[tp.nLM], R[tp.P], Rd[tp.P], Y[kNumLm];
 #pragma unroll
                     for (int lm2 = 0; lm2 < tp.nLM; ++lm2) { h[lm2] = __ldg(hrow + static_cast<size_t>(lm2) * a.K); msg[lm2] = T(0); }
 #pragma unroll
                     for (int p = 0; p < tp.P; ++p) {
-                        const Vec4<T> c = load4<T>(cb + 4 * p * a.K);
+                        const Vec4<T> c = load_coef<T>(cb + 4 * p * a.K, k, a.K);
                         R[p] = c.x + x * (c.y + x * (c.z + x * c.w));
                         Rd[p] = c.y + x * (T(2) * c.z + T(3) * x * c.w);
                     }
