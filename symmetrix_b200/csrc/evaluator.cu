@@ -6,9 +6,11 @@
 
 #include <cstdio>
 #include <cstring>
+#include <map>
 #include <memory>
 #include <stdexcept>
 #include <string>
+#include <tuple>
 #include <vector>
 
 #include <cub/cub.cuh>
@@ -93,6 +95,7 @@ public:
     cudaEvent_t ev0 = nullptr, ev1 = nullptr, evt0 = nullptr, evt1 = nullptr;
     std::vector<cudaEvent_t> stage_events;
     int num_sms = 148;
+    int max_dynamic_smem = 0;     // sharedMemPerBlockOptin of the device
 
     // model tables on the device
     DevBuf<T> coef0, coef1, H0_w, A0_w, H1_w, A1_w, H2_w_H1, H2_w_M1, ro1, ro2_w1, ro2_w2, coefM0, coefM1;
@@ -126,8 +129,12 @@ public:
     DevBuf<GemmProblem<T>> dev_ring;
     size_t ring_pos = 0;
     bool own_stream = true;
-    DevBuf<int> tc5_status;       // non-zero if a bounded wait of the tcgen05 GEMM ran out
+    DevBuf<int> kernel_status;    // non-zero if a bounded mbarrier wait ran out (1, 2: tcgen05 GEMM; 3, 4: staged tensor-product reverse)
+    bool staged_reverse = false;  // spline rows of the tensor-product reverse through bulk copies into shared memory
+                                  // (SMX_TP_STAGED=1; measured equal in float64 and 15 % slower in float32 on B200)
+    bool waits_in_flight = false; // a kernel with bounded waits has been launched since the last status check
     bool use_tc5 = false;
+    std::map<std::tuple<const void*, int, int, int, int>, std::unique_ptr<DevBuf<float>>> weight_images;
     cudaStream_t own_stream_handle = nullptr;
     NeighborBuilder nb;
 
@@ -139,11 +146,13 @@ public:
         SMX_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
         SMX_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&host_ring), kProblemRing * sizeof(GemmProblem<T>), cudaHostAllocDefault));
         dev_ring.resize(kProblemRing, stream);
-        tc5_status.resize(1, stream);
-        tc5_status.zero(stream);
+        kernel_status.resize(1, stream);
+        kernel_status.zero(stream);
+        if (const char* t = std::getenv("SMX_TP_STAGED")) staged_reverse = std::string(t) != "0";
         if constexpr (sizeof(T) == 4) {
+            // float32 GEMMs run on tcgen05 unless SMX_GEMM=mma asks for the mma.sync kernel
             const char* g = std::getenv("SMX_GEMM");
-            use_tc5 = g && std::string(g) == "tcgen05";
+            use_tc5 = !(g && std::string(g) == "mma");
             SMX_CUDA(cudaFuncSetAttribute(gemm_rows_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTc5SmemBytes));
         }
         SMX_CUDA(cudaEventCreate(&ev0));
@@ -153,6 +162,7 @@ public:
         cudaDeviceProp prop{};
         SMX_CUDA(cudaGetDeviceProperties(&prop, dev));
         num_sms = prop.multiProcessorCount;
+        max_dynamic_smem = static_cast<int>(prop.sharedMemPerBlockOptin);
         upload_model();
     }
     ~Evaluator() override {
@@ -338,22 +348,42 @@ public:
         if (list.size() > kProblemRing) throw UnsupportedError("too many element types for one GEMM launch");
         if (ring_pos + list.size() > kProblemRing) ring_pos = 0;
         std::copy(list.begin(), list.end(), host_ring + ring_pos);
-        SMX_CUDA(cudaMemcpyAsync(dev_ring.p + ring_pos, host_ring + ring_pos, list.size() * sizeof(GemmProblem<T>), cudaMemcpyHostToDevice, stream));
         dim3 grid(static_cast<unsigned>((max_rows + kGemmBM - 1) / kGemmBM), (max_cols + kGemmBN - 1) / kGemmBN,
                   static_cast<unsigned>(list.size()));
         if constexpr (sizeof(T) == 4) {
             if (use_tc5) {
+                for (size_t q = 0; q < list.size(); ++q) host_ring[ring_pos + q].B_image = weight_image(list[q]);
+                SMX_CUDA(cudaMemcpyAsync(dev_ring.p + ring_pos, host_ring + ring_pos, list.size() * sizeof(GemmProblem<T>), cudaMemcpyHostToDevice, stream));
                 dim3 g5(static_cast<unsigned>((max_rows + kTc5BM - 1) / kTc5BM), (max_cols + kTc5BN - 1) / kTc5BN, static_cast<unsigned>(list.size()));
-                gemm_rows_tcgen05_kernel<<<g5, kTc5Threads, kTc5SmemBytes, stream>>>(dev_ring.p + ring_pos, tc5_status.p);
+                waits_in_flight = true;
+                gemm_rows_tcgen05_kernel<<<g5, kTc5Threads, kTc5SmemBytes, stream>>>(dev_ring.p + ring_pos, kernel_status.p);
                 check_launch("gemm_rows_tcgen05_kernel");
                 ring_pos += list.size();
                 return;
             }
         }
+        SMX_CUDA(cudaMemcpyAsync(dev_ring.p + ring_pos, host_ring + ring_pos, list.size() * sizeof(GemmProblem<T>), cudaMemcpyHostToDevice, stream));
         gemm_rows_kernel<T><<<grid, kGemmThreads, 0, stream>>>(dev_ring.p + ring_pos);
         check_launch("gemm_rows_kernel");
         ring_pos += list.size();
     }
+    // Operand image of a problem's weight matrix for the tcgen05 kernel, built on first use (the weights are
+    // constant after the model upload) by a small kernel on the evaluator's stream.
+    const float* weight_image(const GemmProblem<float>& p) {
+        const auto key = std::make_tuple(static_cast<const void*>(p.B), p.Kd, p.Nc, p.ldb, p.transB);
+        auto it = weight_images.find(key);
+        if (it == weight_images.end()) {
+            auto buf = std::make_unique<DevBuf<float>>();
+            buf->resize(tc5_image_floats(p.Kd, p.Nc), stream);
+            const long long groups = static_cast<long long>(tc5_image_floats(p.Kd, p.Nc) / 8);
+            const int grid = static_cast<int>(std::min<long long>((groups + 255) / 256, 4096));
+            gemm_tc5_prepare_b_kernel<<<grid, 256, 0, stream>>>(p.B, p.Kd, p.Nc, p.ldb, p.transB, buf->p);
+            check_launch("gemm_tc5_prepare_b_kernel");
+            it = weight_images.emplace(key, std::move(buf)).first;
+        }
+        return it->second->p;
+    }
+    const double* weight_image(const GemmProblem<double>&) { return nullptr; }
     GemmProblem<T> problem(const T* A, T* C, const T* B, bool by_type, int type, int sub_count, long long a_ns, long long a_off,
                            long long a_ss, long long c_ns, long long c_off, long long c_ss, int Kd, int Nc, int ldb, bool transB,
                            bool acc) {
@@ -550,14 +580,31 @@ public:
         a.node_types = node_types; a.first_neigh = first_neigh.p; a.neigh_indices = neigh_indices; a.neigh_types = neigh_types;
         a.xyz = xyz; a.r = r; a.coef1 = coef1.p; a.sm = sm;
         a.H = H1.p; a.Phi1 = Phi1.p; a.dPhi1 = dPhi1.p; a.Hmsg = Hmsg.p; a.H_adj = H1_adj.p; a.node_forces = node_forces.p;
+        a.status = kernel_status.p;
         return a;
     }
     template <int LF>
     void launch_tp(bool reverse) {
         const int block = channel_block();
         if (reverse) {
-            const int grid = persistent_grid(tp_reverse_kernel<T, LF>, block, 0, N);
-            tp_reverse_kernel<T, LF><<<grid, block, 0, stream>>>(tp_args());
+            // two slots of one spline-row chunk each; staged only if that costs no resident CTA
+            const size_t slots = 2 * sizeof(T) * 4 * make_tp_table(LF).P * static_cast<size_t>(std::min(model.K, block));
+            bool staged = staged_reverse && slots <= static_cast<size_t>(max_dynamic_smem);
+            int plain_per_sm = 0, staged_per_sm = 0;
+            if (staged) {
+                SMX_CUDA(cudaFuncSetAttribute(tp_reverse_kernel<T, LF, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(slots)));
+                SMX_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&plain_per_sm, tp_reverse_kernel<T, LF, false>, block, 0));
+                SMX_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&staged_per_sm, tp_reverse_kernel<T, LF, true>, block, slots));
+                staged = staged_per_sm >= 1 && staged_per_sm >= plain_per_sm;
+            }
+            if (staged) {
+                const int grid = persistent_grid(tp_reverse_kernel<T, LF, true>, block, slots, N);
+                waits_in_flight = true;
+                tp_reverse_kernel<T, LF, true><<<grid, block, slots, stream>>>(tp_args());
+            } else {
+                const int grid = persistent_grid(tp_reverse_kernel<T, LF, false>, block, 0, N);
+                tp_reverse_kernel<T, LF, false><<<grid, block, 0, stream>>>(tp_args());
+            }
             check_launch("tp_reverse_kernel");
         } else {
             const int grid = persistent_grid(tp_forward_kernel<T, LF>, block, 0, N);
@@ -750,12 +797,13 @@ public:
         if (elem_bytes) *elem_bytes = f.t ? static_cast<int>(sizeof(T)) : 8;
         return f.t ? static_cast<void*>(f.t->p) : static_cast<void*>(f.d->p);
     }
-    // Synchronises the stream and reports a tcgen05 GEMM whose bounded mbarrier wait ran out.
-    void check_tensor_core_status() {
+    // Synchronises the stream and reports a kernel whose bounded mbarrier wait ran out.
+    void check_kernel_status() {
         int code = 0;
-        if (use_tc5) SMX_CUDA(cudaMemcpyAsync(&code, tc5_status.p, sizeof(int), cudaMemcpyDeviceToHost, stream));
+        if (waits_in_flight) SMX_CUDA(cudaMemcpyAsync(&code, kernel_status.p, sizeof(int), cudaMemcpyDeviceToHost, stream));
         SMX_CUDA(cudaStreamSynchronize(stream));
-        if (code != 0) throw CudaError("tensor-core GEMM: a bounded mbarrier wait ran out (code " + std::to_string(code) + ")");
+        waits_in_flight = false;
+        if (code != 0) throw CudaError("a bounded mbarrier wait ran out in a device kernel (code " + std::to_string(code) + "); results are invalid");
     }
     void timer_start() override {
         SMX_CUDA(cudaSetDevice(device));
@@ -794,7 +842,7 @@ public:
         tick(); reverse_H2(false); tick(); reverse_M1(); reverse_A_scaled(false, false); tick(); reverse_A1(); tick(); reverse_Phi1(false, false);
         tick(); reverse_H1(); tick(); reverse_M0(); reverse_A_scaled(true, false); tick(); reverse_A0(); tick();
         SMX_CUDA(cudaEventRecord(ev1, stream));
-        check_tensor_core_status();
+        check_kernel_status();
         float ms = 0.f;
         SMX_CUDA(cudaEventElapsedTime(&ms, ev0, ev1));
         last_ms = ms;
@@ -850,7 +898,7 @@ public:
         }
         SMX_CUDA(cudaMemcpyAsync(dst, src, ncopy * sizeof(double),
                                  mem_space == SMX_DEVICE ? cudaMemcpyDeviceToDevice : cudaMemcpyDeviceToHost, stream));
-        check_tensor_core_status();
+        check_kernel_status();
         return static_cast<long>(n);
     }
 
@@ -911,7 +959,7 @@ public:
             if (energy) SMX_CUDA(cudaMemcpyAsync(energy, out7.p, sizeof(double), kind, stream));
             if (virial) SMX_CUDA(cudaMemcpyAsync(virial, out7.p + 1, 6 * sizeof(double), kind, stream));
         }
-        check_tensor_core_status();
+        check_kernel_status();
     }
 
     // ------------------------------------------------------------------ neighbour list

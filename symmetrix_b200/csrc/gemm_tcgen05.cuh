@@ -2,14 +2,19 @@
 //
 // Same problem list as gemm_rows_kernel (rows gathered through (node, sub-row) strides and the type-sorted
 // permutation). One CTA of 128 threads owns a 128 x 128 output tile whose accumulator lives in 128 columns of
-// TMEM. The k dimension is walked in chunks of 32 floats (one 128-byte swizzle atom per row); for every chunk all
-// threads load the A rows and the B columns with ordinary loads, split each float into a TF32 head and a TF32
-// remainder (x = hi + lo), and store four operand tiles (A_hi, A_lo, B_hi, B_lo) into shared memory in the
-// K-major, 128-byte-swizzled layout the tensor core reads. One thread then issues three MMAs per 8-wide k step
-// (lo*hi + hi*lo + hi*hi), which keeps float32-level accuracy, and commits them to an mbarrier. Two shared-memory
-// stages are used, so the loads of chunk i+1 overlap the MMAs of chunk i; a stage is rewritten only after the
-// commit of its previous use has arrived. Every wait is bounded: if an mbarrier does not flip within the spin
-// budget the CTA records an error code, skips further tensor-core work, frees its TMEM and returns.
+// TMEM; three CTAs are resident per SM (64 KB of operand tiles each), so the loads, tensor-core work and
+// epilogues of different tiles overlap. float32 accuracy comes from the 3xTF32 split x = hi + lo
+// (hi = x with the 13 low mantissa bits cleared): per 8-wide k step the tensor core runs lo*hi + hi*lo + hi*hi.
+//
+// The k dimension is walked in chunks of 32 floats (one 128-byte swizzle atom per row). Per chunk
+//   * B (the weights) comes from an operand image prepared once per weight matrix by gemm_tc5_prepare_b_kernel:
+//     per (128-column block, k chunk) a hi tile and a lo tile already in the K-major, 128-byte-swizzled
+//     shared-memory layout, so one thread brings both in with one bulk asynchronous copy (TMA) on an mbarrier;
+//   * A (the gathered rows) is read with 16-byte loads, split in registers and stored as two swizzled tiles;
+//     the loads of chunk i + 1 are issued before the CTA waits for the tensor core to finish chunk i;
+//   * one thread issues the 12 MMAs of the chunk and commits them to an mbarrier.
+// Every wait is bounded: if an mbarrier does not flip within the spin budget the CTA records an error code, skips
+// further tensor-core work, frees its TMEM and returns.
 #pragma once
 
 #include <cuda_runtime.h>
@@ -20,20 +25,48 @@
 
 namespace smx {
 
-constexpr int kTc5BM = 128, kTc5BN = 128, kTc5BK = 32, kTc5Threads = 128, kTc5Stages = 2;
+constexpr int kTc5BM = 128, kTc5BN = 128, kTc5BK = 32, kTc5Threads = 128;
 constexpr int kTc5TileBytes = kTc5BM * kTc5BK * 4;                       // 16 KB per operand tile
-constexpr int kTc5StageBytes = 4 * kTc5TileBytes;                        // A_hi, A_lo, B_hi, B_lo
-constexpr int kTc5SmemBytes = kTc5Stages * kTc5StageBytes + 1024;        // + slack for 1024-byte alignment
-constexpr unsigned kTc5SpinLimit = 1u << 24;
+constexpr int kTc5TileFloats = kTc5TileBytes / 4;
+constexpr int kTc5SmemBytes = 4 * kTc5TileBytes + 1024;                  // A_hi, A_lo, B_hi, B_lo + slack for 1024-byte alignment
+constexpr unsigned kTc5HiMask = 0xFFFFE000u;
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
-
-// byte offset of float (row, col) in a K-major tile of 32 floats per row with the 128-byte swizzle:
-// rows in groups of 8 (1024 bytes), 16-byte chunk index XOR-ed with the row index inside the group
-__device__ __forceinline__ int tc5_swizzled_offset(int row, int col) {
+// byte offset of the 16-byte group `c4` (4 floats) of row `row` in a K-major tile of 32 floats per row with the
+// 128-byte swizzle: rows in groups of 8 (1024 bytes), 16-byte group index XOR-ed with the row index inside the group
+__host__ __device__ __forceinline__ int tc5_swizzled_group(int row, int c4) {
     const int r8 = row & 7;
-    const int chunk = (col >> 2) ^ r8;
-    return (row >> 3) * 1024 + r8 * 128 + chunk * 16 + (col & 3) * 4;
+    return (row >> 3) * 1024 + r8 * 128 + ((c4 ^ r8) << 4);
+}
+
+// floats of the operand image of a [Kd] x [Nc] weight matrix: [column block][k chunk][hi, lo][tile]
+inline size_t tc5_image_floats(int Kd, int Nc) {
+    return static_cast<size_t>((Nc + kTc5BN - 1) / kTc5BN) * ((Kd + kTc5BK - 1) / kTc5BK) * 2 * kTc5TileFloats;
+}
+
+// One thread per (column block, k chunk, column n, 16-byte group): reads four weights, zero beyond the matrix,
+// and writes the hi and lo values where the tensor core expects column n of the K-major B tile.
+__global__ void gemm_tc5_prepare_b_kernel(const float* __restrict__ B, int Kd, int Nc, int ldb, int transB, float* __restrict__ image) {
+    const int k_chunks = (Kd + kTc5BK - 1) / kTc5BK, n_blocks = (Nc + kTc5BN - 1) / kTc5BN;
+    const long long total = static_cast<long long>(n_blocks) * k_chunks * kTc5BN * (kTc5BK / 4);
+    for (long long t = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; t < total; t += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int c4 = static_cast<int>(t & 7);
+        const int n = static_cast<int>((t >> 3) & (kTc5BN - 1));
+        const long long tile = t >> 10;                     // column block * k_chunks + k chunk
+        const int kc = static_cast<int>(tile % k_chunks), nb = static_cast<int>(tile / k_chunks);
+        float hi[4], lo[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int k = kc * kTc5BK + c4 * 4 + q, col = nb * kTc5BN + n;
+            float v = 0.f;
+            if (k < Kd && col < Nc) v = transB ? B[static_cast<size_t>(col) * ldb + k] : B[static_cast<size_t>(k) * ldb + col];
+            hi[q] = __uint_as_float(__float_as_uint(v) & kTc5HiMask);
+            lo[q] = v - hi[q];
+        }
+        float* base = image + static_cast<size_t>(tile) * 2 * kTc5TileFloats;
+        const int off = tc5_swizzled_group(n, c4) >> 2;
+        *reinterpret_cast<float4*>(base + off) = make_float4(hi[0], hi[1], hi[2], hi[3]);
+        *reinterpret_cast<float4*>(base + kTc5TileFloats + off) = make_float4(lo[0], lo[1], lo[2], lo[3]);
+    }
 }
 
 // shared-memory matrix descriptor: K-major, 128-byte swizzle, 8-row groups 1024 bytes apart
@@ -62,24 +95,22 @@ __device__ __forceinline__ void tc5_mma(uint32_t tmem_d, uint64_t a_desc, uint64
         : "memory");
 }
 
-__device__ __forceinline__ bool tc5_wait(uint32_t mbar, uint32_t parity) {
-    for (unsigned spin = 0; spin < kTc5SpinLimit; ++spin) {
-        uint32_t done;
-        asm volatile(
-            "{\n\t"
-            ".reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t"
-            "}\n"
-            : "=r"(done)
-            : "r"(mbar), "r"(parity)
-            : "memory");
-        if (done) return true;
-    }
-    return false;
+__device__ __forceinline__ void tc5_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
+          "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]),
+          "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
+          "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-// `status` receives a non-zero code if a bounded wait ran out (1: stage reuse, 2: final drain).
+// `status` receives a non-zero code if a bounded wait ran out (1: tensor core, 2: weight tile copy).
+// Every problem carries the operand image of its weight matrix in B_image.
 __global__ void __launch_bounds__(kTc5Threads) gemm_rows_tcgen05_kernel(const GemmProblem<float>* __restrict__ problems, int* __restrict__ status) {
     const GemmProblem<float> pb = problems[blockIdx.z];
     int node_begin = 0, node_count = pb.num_nodes;
@@ -87,11 +118,14 @@ __global__ void __launch_bounds__(kTc5Threads) gemm_rows_tcgen05_kernel(const Ge
     const long long M = static_cast<long long>(node_count) * pb.sub_count;
     const long long row0 = static_cast<long long>(blockIdx.x) * kTc5BM;
     const int col0 = blockIdx.y * kTc5BN;
-    if (row0 >= M || col0 >= pb.Nc) return;
+    if (row0 >= M || col0 >= pb.Nc || pb.Kd <= 0) return;
 
     extern __shared__ unsigned char tc5_smem_raw[];
     unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tc5_smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-    __shared__ __align__(8) unsigned long long mbar[kTc5Stages];
+    unsigned char* sA_hi = tiles;
+    unsigned char* sA_lo = sA_hi + kTc5TileBytes;
+    unsigned char* sB = sA_lo + kTc5TileBytes;                // B_hi then B_lo, contiguous as in the image
+    __shared__ __align__(8) unsigned long long mma_bar, b_bar;
     __shared__ uint32_t tmem_base_slot;
     __shared__ long long a_base[kTc5BM];
     __shared__ long long c_base[kTc5BM];
@@ -113,8 +147,8 @@ __global__ void __launch_bounds__(kTc5Threads) gemm_rows_tcgen05_kernel(const Ge
     }
     if (tid == 0) {
         failed = 0;
-        for (int s = 0; s < kTc5Stages; ++s)
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&mbar[s])) : "memory");
+        mbar_init(&mma_bar, 1);
+        mbar_init(&b_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
@@ -128,108 +162,130 @@ __global__ void __launch_bounds__(kTc5Threads) gemm_rows_tcgen05_kernel(const Ge
     const uint32_t idesc = tc5_instr_desc();
 
     const int num_chunks = (pb.Kd + kTc5BK - 1) / kTc5BK;
-    uint32_t phase[kTc5Stages] = {0, 0};
-    int uses[kTc5Stages] = {0, 0};
+    const float* image = pb.B_image + static_cast<size_t>(blockIdx.y) * num_chunks * 2 * kTc5TileFloats;
+    // 16-byte loads need rows that start on a 16-byte boundary and a k extent that is a multiple of 4 (true for
+    // every problem the evaluator builds when K is a multiple of 4); otherwise the loads are scalar
+    const bool vec_ok = (pb.Kd & 3) == 0 && ((pb.a_node_stride | pb.a_off | pb.a_sub_stride) & 3) == 0 &&
+                        (reinterpret_cast<uintptr_t>(pb.A) & 15) == 0;
+
+    float4 pre[8];
+    auto load_chunk = [&](int ch) {
+        const int k0 = ch * kTc5BK;
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+            const int lin = tid + it * kTc5Threads;
+            const int rr = lin >> 3, kk = k0 + ((lin & 7) << 2);
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            const long long ab = a_base[rr];
+            if (ab >= 0) {
+                if (vec_ok && kk + 3 < pb.Kd) {
+                    v = *reinterpret_cast<const float4*>(pb.A + ab + kk);
+                } else {
+                    if (kk < pb.Kd) v.x = pb.A[ab + kk];
+                    if (kk + 1 < pb.Kd) v.y = pb.A[ab + kk + 1];
+                    if (kk + 2 < pb.Kd) v.z = pb.A[ab + kk + 2];
+                    if (kk + 3 < pb.Kd) v.w = pb.A[ab + kk + 3];
+                }
+            }
+            pre[it] = v;
+        }
+    };
+    load_chunk(0);
+    unsigned mma_par = 0, b_par = 0;
     for (int ch = 0; ch < num_chunks; ++ch) {
-        const int stage = ch % kTc5Stages;
-        unsigned char* sA_hi = tiles + stage * kTc5StageBytes;
-        unsigned char* sA_lo = sA_hi + kTc5TileBytes;
-        unsigned char* sB_hi = sA_lo + kTc5TileBytes;
-        unsigned char* sB_lo = sB_hi + kTc5TileBytes;
-        // the MMAs that read this stage two chunks ago must have completed before it is overwritten
-        if (uses[stage] > 0 && !failed) {
-            if (!tc5_wait(smem_u32(&mbar[stage]), phase[stage])) { failed = 1; }
-            phase[stage] ^= 1;
+        // the MMAs of the previous chunk read the tiles: wait for them before overwriting
+        if (ch > 0) {
+            if (!*reinterpret_cast<volatile int*>(&failed) && !mbar_wait(&mma_bar, mma_par)) failed = 1;
+            mma_par ^= 1u;
         }
         __syncthreads();
-        const int k0 = ch * kTc5BK;
-        // A tile: 128 rows x 32 k, coalesced along k
-#pragma unroll 4
-        for (int it = 0; it < (kTc5BM * kTc5BK) / kTc5Threads; ++it) {
-            const int lin = tid + it * kTc5Threads;
-            const int rr = lin >> 5, kk = lin & 31;
-            float v = 0.f;
-            if (a_base[rr] >= 0 && k0 + kk < pb.Kd) v = pb.A[a_base[rr] + k0 + kk];
-            const float hi = __uint_as_float(__float_as_uint(v) & 0xFFFFE000u);
-            const int off = tc5_swizzled_offset(rr, kk);
-            *reinterpret_cast<float*>(sA_hi + off) = hi;
-            *reinterpret_cast<float*>(sA_lo + off) = v - hi;
+        if (tid == 0 && !failed) {
+            mbar_expect_tx(&b_bar, 2 * kTc5TileBytes);
+            bulk_copy_g2s(sB, image + static_cast<size_t>(ch) * 2 * kTc5TileFloats, 2 * kTc5TileBytes, &b_bar);
         }
-        // B tile as [n][k] (K-major): 128 n x 32 k
-#pragma unroll 4
-        for (int it = 0; it < (kTc5BN * kTc5BK) / kTc5Threads; ++it) {
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
             const int lin = tid + it * kTc5Threads;
-            int nn, kk;
-            float v = 0.f;
-            if (!pb.transB) {          // B is [Kd][Nc]: read coalesced along n
-                kk = lin >> 7; nn = lin & 127;
-                if (k0 + kk < pb.Kd && col0 + nn < pb.Nc) v = pb.B[static_cast<size_t>(k0 + kk) * pb.ldb + col0 + nn];
-            } else {                   // B is [Nc][Kd]: read coalesced along k
-                nn = lin >> 5; kk = lin & 31;
-                if (k0 + kk < pb.Kd && col0 + nn < pb.Nc) v = pb.B[static_cast<size_t>(col0 + nn) * pb.ldb + k0 + kk];
-            }
-            const float hi = __uint_as_float(__float_as_uint(v) & 0xFFFFE000u);
-            const int off = tc5_swizzled_offset(nn, kk);
-            *reinterpret_cast<float*>(sB_hi + off) = hi;
-            *reinterpret_cast<float*>(sB_lo + off) = v - hi;
+            const int off = tc5_swizzled_group(lin >> 3, lin & 7);
+            const float4 v = pre[it];
+            float4 hi, lo;
+            hi.x = __uint_as_float(__float_as_uint(v.x) & kTc5HiMask); lo.x = v.x - hi.x;
+            hi.y = __uint_as_float(__float_as_uint(v.y) & kTc5HiMask); lo.y = v.y - hi.y;
+            hi.z = __uint_as_float(__float_as_uint(v.z) & kTc5HiMask); lo.z = v.z - hi.z;
+            hi.w = __uint_as_float(__float_as_uint(v.w) & kTc5HiMask); lo.w = v.w - hi.w;
+            *reinterpret_cast<float4*>(sA_hi + off) = hi;
+            *reinterpret_cast<float4*>(sA_lo + off) = lo;
         }
+        if (ch + 1 < num_chunks) load_chunk(ch + 1);            // in flight while the tensor core works on this chunk
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic-proxy stores -> visible to the tensor core
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncthreads();
         if (tid == 0 && !failed) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t a_hi = smem_u32(sA_hi), a_lo = smem_u32(sA_lo), b_hi = smem_u32(sB_hi), b_lo = smem_u32(sB_lo);
+            if (!mbar_wait(&b_bar, b_par)) {
+                failed = 2;
+            } else {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t a_hi = smem_u32(sA_hi), a_lo = smem_u32(sA_lo), b_hi = smem_u32(sB), b_lo = smem_u32(sB + kTc5TileBytes);
 #pragma unroll
-            for (int ks = 0; ks < kTc5BK / 8; ++ks) {
-                const uint32_t adv = ks * 32;        // 8 TF32 values = 32 bytes inside the swizzle atom
-                const uint32_t first = (ch == 0 && ks == 0) ? 0u : 1u;
-                tc5_mma(tmem_d, tc5_smem_desc(a_lo + adv), tc5_smem_desc(b_hi + adv), idesc, first);
-                tc5_mma(tmem_d, tc5_smem_desc(a_hi + adv), tc5_smem_desc(b_lo + adv), idesc, 1u);
-                tc5_mma(tmem_d, tc5_smem_desc(a_hi + adv), tc5_smem_desc(b_hi + adv), idesc, 1u);
+                for (int ks = 0; ks < kTc5BK / 8; ++ks) {
+                    const uint32_t adv = ks * 32;        // 8 TF32 values = 32 bytes inside the swizzle atom
+                    const uint32_t first = (ch == 0 && ks == 0) ? 0u : 1u;
+                    tc5_mma(tmem_d, tc5_smem_desc(a_lo + adv), tc5_smem_desc(b_hi + adv), idesc, first);
+                    tc5_mma(tmem_d, tc5_smem_desc(a_hi + adv), tc5_smem_desc(b_lo + adv), idesc, 1u);
+                    tc5_mma(tmem_d, tc5_smem_desc(a_hi + adv), tc5_smem_desc(b_hi + adv), idesc, 1u);
+                }
+                asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&mma_bar)) : "memory");
             }
-            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&mbar[stage])) : "memory");
         }
-        uses[stage] += 1;
+        b_par ^= 1u;
     }
-    // drain: the last commit of every stage that was used
-    for (int s = 0; s < kTc5Stages; ++s) {
-        if (uses[s] > 0 && !failed) {
-            if (!tc5_wait(smem_u32(&mbar[s]), phase[s])) failed = 2;
-        }
-    }
+    __syncthreads();                                             // `failed` as thread 0 left it
+    if (!*reinterpret_cast<volatile int*>(&failed) && !mbar_wait(&mma_bar, mma_par)) failed = 1;
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     if (!failed) {
-        const long long cb = c_base[warp * 32 + lane];
-#pragma unroll
+        // Epilogue. A thread holds one output row (its TMEM lane); writing rows straight from registers would make
+        // every store instruction touch 32 different rows. The warp therefore passes its 32 x 128 block through the
+        // (now idle) operand tiles, 16-byte groups XOR-swizzled by the row so that both the row-wise writes and the
+        // column-wise reads are free of bank conflicts, and then stores whole 512-byte rows per instruction.
+        float* stage = reinterpret_cast<float*>(tiles) + warp * (32 * kTc5BN);
+#pragma unroll 1
         for (int cc = 0; cc < kTc5BN / 32; ++cc) {
             uint32_t v[32];
-            const uint32_t taddr = tmem_d + (static_cast<uint32_t>(warp * 32) << 16) + cc * 32;
-            asm volatile(
-                "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
-                  "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]),
-                  "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
-                  "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-                : "r"(taddr)
-                : "memory");
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-            if (cb >= 0) {
+            tc5_ld32(tmem_d + (static_cast<uint32_t>(warp * 32) << 16) + cc * 32, v);
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const int col = col0 + cc * 32 + j;
-                    if (col < pb.Nc) {
-                        float* dst = pb.C + cb + col;
-                        const float val = __uint_as_float(v[j]);
-                        *dst = pb.accumulate ? (*dst + val) : val;
-                    }
+            for (int j = 0; j < 8; ++j) {
+                const int g = cc * 8 + j;
+                *reinterpret_cast<float4*>(stage + lane * kTc5BN + ((g ^ lane) << 2)) =
+                    make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+            }
+        }
+        __syncwarp();
+        const bool cvec = ((pb.c_node_stride | pb.c_off | pb.c_sub_stride) & 3) == 0 && (reinterpret_cast<uintptr_t>(pb.C) & 15) == 0;
+        const int col = col0 + lane * 4;
+#pragma unroll 4
+        for (int r = 0; r < 32; ++r) {
+            const long long cb = c_base[warp * 32 + r];
+            if (cb < 0) continue;
+            float4 o = *reinterpret_cast<const float4*>(stage + r * kTc5BN + ((lane ^ r) << 2));
+            float* dst = pb.C + cb + col;
+            if (cvec && col + 3 < pb.Nc) {
+                if (pb.accumulate) {
+                    const float4 old = *reinterpret_cast<const float4*>(dst);
+                    o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
                 }
+                *reinterpret_cast<float4*>(dst) = o;
+            } else {
+                const float ov[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                    if (col + q < pb.Nc) dst[q] = pb.accumulate ? (dst[q] + ov[q]) : ov[q];
             }
         }
     } else if (tid == 0) {
         atomicMax(status, failed);
+        // a weight-tile copy that may still be in flight gets one more bounded wait before the CTA exits
+        mbar_wait(&b_bar, b_par ^ 1u);
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();

@@ -14,6 +14,8 @@
 
 #include <cuda_runtime.h>
 
+#include <cstdint>
+
 #include <utility>
 
 #include "tp_tables.hpp"
@@ -62,6 +64,70 @@ __device__ __forceinline__ Vec4<double> load_coef<double>(const double* row, int
     const double2 a = __ldg(reinterpret_cast<const double2*>(row) + k);
     const double2 b = __ldg(reinterpret_cast<const double2*>(row) + K + k);
     return {a.x, a.y, b.x, b.y};
+}
+
+// ---------------------------------------------------------------------------------------------
+// Bulk asynchronous copies (TMA, cp.async.bulk) of spline rows into shared memory, completed on an
+// mbarrier. Every wait is bounded: a wait that runs out returns false and the caller records it.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
+    asm volatile("{\n\t.reg .b64 t;\n\tmbarrier.arrive.shared::cta.b64 t, [%0];\n\t}" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
+    asm volatile("{\n\t.reg .b64 t;\n\tmbarrier.arrive.expect_tx.shared::cta.b64 t, [%0], %1;\n\t}" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+constexpr unsigned kMbarSpinLimit = 1u << 22;
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
+    const uint32_t addr = smem_u32(bar);
+    for (unsigned spin = 0; spin < kMbarSpinLimit; ++spin) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+// global -> shared, both addresses 16-byte aligned, bytes a multiple of 16
+__device__ __forceinline__ void bulk_copy_g2s(void* dst, const void* src, unsigned bytes, unsigned long long* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+
+// Channel `kl` of a staged row chunk of `Kc` channels: same layouts as load_coef with K = Kc.
+template <typename T>
+__device__ __forceinline__ Vec4<T> lds_coef(const T* slot, int p, int kl, int Kc);
+template <>
+__device__ __forceinline__ Vec4<float> lds_coef<float>(const float* slot, int p, int kl, int Kc) {
+    const float4 v = reinterpret_cast<const float4*>(slot)[p * Kc + kl];
+    return {v.x, v.y, v.z, v.w};
+}
+template <>
+__device__ __forceinline__ Vec4<double> lds_coef<double>(const double* slot, int p, int kl, int Kc) {
+    const double2 a = reinterpret_cast<const double2*>(slot)[(2 * p) * Kc + kl];
+    const double2 b = reinterpret_cast<const double2*>(slot)[(2 * p + 1) * Kc + kl];
+    return {a.x, a.y, b.x, b.y};
+}
+
+// One thread: start the copy of the chunk [kc, kc + Kc) of all P function blocks of a spline row into a slot.
+template <typename T>
+__device__ __forceinline__ void issue_row_copy(T* slot, const T* row, int P, int K, int kc, int Kc, unsigned long long* bar) {
+    const unsigned bytes = 4u * P * Kc * sizeof(T);
+    mbar_expect_tx(bar, bytes);
+    if (Kc == K) {
+        bulk_copy_g2s(slot, row, bytes, bar);
+    } else if constexpr (sizeof(T) == 4) {
+        for (int p = 0; p < P; ++p) bulk_copy_g2s(slot + 4 * p * Kc, row + 4 * (p * K + kc), 16u * Kc, bar);
+    } else {
+        for (int q = 0; q < 2 * P; ++q) bulk_copy_g2s(slot + 2 * q * Kc, row + 2 * (q * K + kc), 16u * Kc, bar);
+    }
 }
 
 template <typename T>
@@ -362,6 +428,7 @@ struct TPArgs {
     T* Hmsg;                // reverse output [num_edges][nLM][K]: adjoint message of each edge to its sender (float64)
     T* H_adj;               // float32: the messages are added straight into H_adj[sender] with red.global.add
     double* node_forces;    // reverse: accumulated into
+    int* status;            // set non-zero by a bounded wait that ran out (staged reverse kernel)
 };
 
 // Resident CTAs per SM the compiler is asked to allow for (register budget): measured best on B200 for the
@@ -432,46 +499,105 @@ __global__ void __launch_bounds__(kChannelBlock, tp_min_blocks<T>(LF, false)) tp
 // fr = dE/dr_ij. W and fr are summed over channels (warp reduce-scatter, then across warps in shared
 // memory) and one thread per edge turns them into the partial force
 //   nf[ij] -= xhat * fr + sum_lm W[lm] * grad Y[lm].
-template <typename T, int LF>
+//
+// STAGED = true: the spline row of every edge (4*P*K values, 40 KB in float64 for K = 128, L_max = 1) is brought
+// into shared memory by one bulk asynchronous copy (TMA) that a single thread starts one edge ahead of its use,
+// through two slots guarded by a full/empty mbarrier pair each, so the coefficient reads are shared-memory loads
+// instead of global loads that only 8 resident warps per SM would have to cover. A bounded wait that runs out
+// sets *status, stops further copies and waits, and the kernel finishes (with results the host discards).
+template <typename T, bool STAGED> constexpr int tp_reverse_batch() { return STAGED ? (sizeof(T) == 8 ? 24 : 16) : kEdgeBatch; }
+
+template <typename T, int LF, bool STAGED>
 __global__ void __launch_bounds__(kChannelBlock, tp_min_blocks<T>(LF, true)) tp_reverse_kernel(const TPArgs<T> a) {
     constexpr TPTable tp = make_tp_table(LF);
-    __shared__ EdgeStage<T> st[kEdgeBatch];
-    __shared__ T red[kMaxWarps][kEdgeBatch][17];
+    constexpr int EB = tp_reverse_batch<T, STAGED>();
+    __shared__ EdgeStage<T> st[EB];
+    __shared__ T red[kMaxWarps][EB][17];
+    __shared__ __align__(8) unsigned long long full_bar[2], empty_bar[2];
+    __shared__ int failed;
+    extern __shared__ __align__(128) unsigned char tp_dyn_smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
     const int F = tp.P * a.K;
+    unsigned full_par = 0, empty_par = 0;     // bit s: parity of the phase slot s is in
+    if constexpr (STAGED) {
+        if (threadIdx.x == 0) {
+            failed = 0;
+            mbar_init(&full_bar[0], 1); mbar_init(&full_bar[1], 1);
+            mbar_init(&empty_bar[0], blockDim.x); mbar_init(&empty_bar[1], blockDim.x);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        }
+        __syncthreads();
+    }
     for (int i = blockIdx.x; i < a.N; i += gridDim.x)
     for (int kc = 0; kc < a.K; kc += blockDim.x) {
         const int k = kc + threadIdx.x;
         const bool active = k < a.K;
+        const int Kc = a.K - kc < static_cast<int>(blockDim.x) ? a.K - kc : static_cast<int>(blockDim.x);
+        T* const slot0 = reinterpret_cast<T*>(tp_dyn_smem);
+        T* const slot1 = slot0 + 4 * tp.P * Kc;
         const long long e_begin = a.first_neigh[i], e_end = a.first_neigh[i + 1];
         const int type_i = a.node_types[i];
         T d[tp.Q];
 #pragma unroll
         for (int q = 0; q < tp.Q; ++q)
             d[q] = active ? a.dPhi1[(static_cast<size_t>(i) * tp.Q + q) * a.K + k] : T(0);
-        for (long long e0 = e_begin; e0 < e_end; e0 += kEdgeBatch) {
-            const int nb = static_cast<int>(e_end - e0 < kEdgeBatch ? e_end - e0 : kEdgeBatch);
+        for (long long e0 = e_begin; e0 < e_end; e0 += EB) {
+            const int nb = static_cast<int>(e_end - e0 < EB ? e_end - e0 : EB);
             __syncthreads();
             if (threadIdx.x < nb)
                 stage_edge<T, true>(st[threadIdx.x], e0 + threadIdx.x, type_i, a.neigh_indices, a.neigh_types, a.xyz, a.r, a.sm, F);
             __syncthreads();
+            if constexpr (STAGED) {
+                if (threadIdx.x == 0 && !failed) {
+                    issue_row_copy<T>(slot0, a.coef1 + st[0].coef_base, tp.P, a.K, kc, Kc, &full_bar[0]);
+                    if (nb > 1) issue_row_copy<T>(slot1, a.coef1 + st[1].coef_base, tp.P, a.K, kc, Kc, &full_bar[1]);
+                }
+            }
             for (int e = 0; e < nb; ++e) {
                 const EdgeStage<T>& s = st[e];
                 T W[kNumLm], fr = 0;
 #pragma unroll
                 for (int lm = 0; lm < kNumLm; ++lm) W[lm] = T(0);
+                const int sl = e & 1;
+                T R[tp.P], Rd[tp.P];
+                if constexpr (STAGED) {
+                    if (!*reinterpret_cast<volatile int*>(&failed)) {
+                        if (!mbar_wait(&full_bar[sl], (full_par >> sl) & 1u)) { failed = 1; atomicMax(a.status, 3); }
+                    }
+                    full_par ^= 1u << sl;
+                    const T* slot = sl ? slot1 : slot0;
+                    const T x = s.x;
+                    if (active) {
+#pragma unroll
+                        for (int p = 0; p < tp.P; ++p) {
+                            const Vec4<T> c = lds_coef<T>(slot, p, threadIdx.x, Kc);
+                            R[p] = c.x + x * (c.y + x * (c.z + x * c.w));
+                            Rd[p] = c.y + x * (T(2) * c.z + T(3) * x * c.w);
+                        }
+                    }
+                    mbar_arrive(&empty_bar[sl]);                 // this thread has read its part of the slot
+                    if (threadIdx.x == 0) {
+                        if (e + 2 < nb && !failed) {
+                            if (!mbar_wait(&empty_bar[sl], (empty_par >> sl) & 1u)) { failed = 1; atomicMax(a.status, 4); }
+                            else issue_row_copy<T>(sl ? slot1 : slot0, a.coef1 + st[e + 2].coef_base, tp.P, a.K, kc, Kc, &full_bar[sl]);
+                        }
+                    }
+                    empty_par ^= 1u << sl;
+                }
                 if (active) {
                     const T x = s.x;
-                    const T* cb = a.coef1 + s.coef_base;
                     const T* hrow = a.H + static_cast<size_t>(s.j) * tp.nLM * a.K + k;
-                    T h[tp.nLM], msg[tp.nLM], R[tp.P], Rd[tp.P], Y[kNumLm];
+                    T h[tp.nLM], msg[tp.nLM], Y[kNumLm];
 #pragma unroll
                     for (int lm2 = 0; lm2 < tp.nLM; ++lm2) { h[lm2] = __ldg(hrow + static_cast<size_t>(lm2) * a.K); msg[lm2] = T(0); }
+                    if constexpr (!STAGED) {
+                        const T* cb = a.coef1 + s.coef_base;
 #pragma unroll
-                    for (int p = 0; p < tp.P; ++p) {
-                        const Vec4<T> c = load_coef<T>(cb + 4 * p * a.K, k, a.K);
-                        R[p] = c.x + x * (c.y + x * (c.z + x * c.w));
-                        Rd[p] = c.y + x * (T(2) * c.z + T(3) * x * c.w);
+                        for (int p = 0; p < tp.P; ++p) {
+                            const Vec4<T> c = load_coef<T>(cb + 4 * p * a.K, k, a.K);
+                            R[p] = c.x + x * (c.y + x * (c.z + x * c.w));
+                            Rd[p] = c.y + x * (T(2) * c.z + T(3) * x * c.w);
+                        }
                     }
 #pragma unroll
                     for (int lm = 0; lm < kNumLm; ++lm) Y[lm] = s.Y[lm];
@@ -503,9 +629,17 @@ __global__ void __launch_bounds__(kChannelBlock, tp_min_blocks<T>(LF, true)) tp_
             __syncthreads();
             if (threadIdx.x < nb) {
                 const int e = threadIdx.x;
-                finish_edge_force<T, kEdgeBatch>(red, nwarps, e, st[e].dY[0], st[e].dY[1], st[e].dY[2], st[e].ux, st[e].uy, st[e].uz,
-                                                 a.node_forces + 3 * (e0 + e));
+                finish_edge_force<T, EB>(red, nwarps, e, st[e].dY[0], st[e].dY[1], st[e].dY[2], st[e].ux, st[e].uy, st[e].uz,
+                                         a.node_forces + 3 * (e0 + e));
             }
+        }
+    }
+    if constexpr (STAGED) {
+        // after a failed wait: give copies that may still be in flight one more bounded wait before the CTA exits
+        __syncthreads();
+        if (threadIdx.x == 0 && failed) {
+            mbar_wait(&full_bar[0], (full_par & 1u) ^ 1u);
+            mbar_wait(&full_bar[1], ((full_par >> 1) & 1u) ^ 1u);
         }
     }
 }
@@ -873,6 +1007,7 @@ struct GemmProblem {
     int ldb;                 // leading dimension of B
     int transB;              // 0: B is [Kd][Nc]; 1: B is [Nc][Kd] and used transposed
     int accumulate;          // 0: C = A.B ; 1: C += A.B
+    const T* B_image;        // float32 tcgen05 path: B as pre-split, pre-swizzled operand tiles (gemm_tcgen05.cuh)
 };
 
 constexpr int kGemmBM = 64, kGemmBN = 64, kGemmBK = 16, kGemmThreads = 128;

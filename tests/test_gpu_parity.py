@@ -108,6 +108,29 @@ def test_downsized_benchmark_models(model_file, dtype, name, channels, builder):
     check_against(dtype, e, f, e_ref, f_ref)
 
 
+@pytest.mark.parametrize("dtype,env", [
+    ("float32", {"SMX_GEMM": "mma"}),           # mma.sync 3xTF32 GEMM instead of the tcgen05 kernel
+    ("float64", {"SMX_TP_STAGED": "1"}),        # spline rows of the tensor-product reverse through TMA bulk copies
+    ("float32", {"SMX_TP_STAGED": "1"}),
+])
+@pytest.mark.parametrize("name,channels,builder", [
+    ("fcc128", 128, lambda z: st.fcc_box(3, 3.6, z, seed=5)),
+    ("large256", 160, lambda z: st.molecular_liquid(8, seed=8)),             # L_max = 2, two channel chunks per CTA
+])
+def test_alternative_kernel_paths(model_file, monkeypatch, dtype, env, name, channels, builder):
+    """The kernel variants an environment variable selects at evaluator creation meet the same gates."""
+    path, model, spec = model_file(name, num_channels=channels, num_spline_points=32)
+    s = builder(model["atomic_numbers"])
+    nl = st.neighbor_list(s, spec.r_cut)
+    inputs = st.evaluator_inputs(s, nl, model["atomic_numbers"])
+    e_ref, f_ref = _oracle_for(path, model)(inputs)
+    for k, v in env.items():
+        monkeypatch.setenv(k, v)
+    ev = MACE(path, dtype=dtype)
+    e, f = run(ev, inputs)
+    check_against(dtype, e, f, e_ref, f_ref)
+
+
 def test_repeated_calls_are_bitwise_identical(tiny):
     _, inputs = tiny
     ev = MACE(GOLDEN / "tiny_model.json", dtype="float64")
