@@ -270,6 +270,7 @@ def run_ours(args):
     fma = ctypes_fma_peak(_lib, 32 if args.dtype == "float32" else 64, local_rank)
     roof["fma_peak_tflops"] = fma
     roof["fma_frac"] = roof["achieved_tflops"] / fma if fma else None
+    roof["l2_stream"] = l2_stream_floor(ev, dominant, roof["launch_ms"])
 
     def reduce_max(x):
         if world == 1:
@@ -430,6 +431,16 @@ def run_decomposed(args, rank, world, local_rank, dist):
     dist.barrier()
     dist.destroy_process_group()
     return None
+
+
+def l2_stream_floor(ev, stage: str, launch_ms: float) -> dict:
+    """The edge kernels read one spline row per edge (4 * P * K values) out of a table larger than L2 that no
+    SM reuses from L1; this measures, on the evaluator's current edge set, a kernel that does only those reads.
+    `frac` = probe time / kernel time: how close the kernel is to the floor the L2 -> SM path sets."""
+    layer = 0 if stage.endswith("A0") else 1
+    ms, nbytes = ev.measure_row_stream(layer)
+    return {"bytes": nbytes, "probe_ms": ms, "probe_gbs": nbytes / (ms * 1e-3) / 1e9 if ms > 0 else None,
+            "kernel_gbs": nbytes / (launch_ms * 1e-3) / 1e9, "frac": ms / launch_ms if launch_ms > 0 else None}
 
 
 def ctypes_fma_peak(_lib, precision: int, device: int) -> float | None:

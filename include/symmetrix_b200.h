@@ -138,12 +138,17 @@ long smx_launch_count(smx_handle h);
  * With profiling on, smx_compute additionally records one event per stage, and smx_stage_time
  * returns the name and device time of stage `index` (0..14, in execution order) of the last
  * smx_compute. smx_measure_fma_peak runs a register-only FMA loop and returns the SIMT
- * fused-multiply-add rate in TFLOP/s, the roof of the FMA-bound edge kernels. */
+ * fused-multiply-add rate in TFLOP/s, the roof of the FMA-bound edge kernels.
+ * smx_measure_row_stream runs, over the evaluator's current edge set, a kernel that only reads the
+ * spline row of every edge from the table of interaction layer `layer` (0 or 1) the way the edge
+ * kernels do; it returns its device time and the bytes read, the floor that streaming the
+ * coefficients from L2 sets for one pass of an edge kernel. */
 int smx_timer_start(smx_handle h);
 int smx_timer_stop(smx_handle h, double* ms);
 int smx_set_profiling(smx_handle h, int enabled);
 int smx_stage_time(smx_handle h, int index, char* name, int name_cap, double* ms);
 int smx_measure_fma_peak(int precision, int device, double* tflops);
+int smx_measure_row_stream(smx_handle h, int layer, double* ms, double* bytes);
 
 /* Neighbour list on the device -- replaces, for callers without their own, the external
  * builders the reference's callers rely on: ase/matscipy `neighbor_list('ijdD', atoms, r_cut)`

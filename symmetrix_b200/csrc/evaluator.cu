@@ -71,6 +71,7 @@ public:
     virtual void timer_start() = 0;
     virtual double timer_stop() = 0;
     virtual void sync() = 0;
+    virtual void measure_row_stream(int layer, double* ms, double* bytes) = 0;
     virtual void set_stream(void* s, bool external) = 0;
     virtual long restrict_nodes(int num_nodes) = 0;
     virtual void resize_rows(const std::string& name, int rows) = 0;
@@ -805,6 +806,32 @@ public:
         waits_in_flight = false;
         if (code != 0) throw CudaError("a bounded mbarrier wait ran out in a device kernel (code " + std::to_string(code) + "); results are invalid");
     }
+    // Duration of one pass of row_stream_probe_kernel over the current edge set (best of three after a warm-up)
+    // and the bytes it moves from the spline table of interaction layer `layer`.
+    void measure_row_stream(int layer, double* ms, double* bytes) override {
+        require_edges();
+        if (layer != 0 && layer != 1) throw ArgError("measure_row_stream: layer must be 0 or 1");
+        SMX_CUDA(cudaSetDevice(device));
+        const int K = model.K, P = layer == 0 ? kLmaxSH + 1 : model.tp.P;
+        const T* table = layer == 0 ? coef0.p : coef1.p;
+        DevBuf<T> sink;
+        sink.resize(1, stream);
+        const int block = channel_block();
+        const int grid = persistent_grid(row_stream_probe_kernel<T>, block, 0, N);
+        float best = 0.f;
+        for (int rep = 0; rep < 4; ++rep) {
+            SMX_CUDA(cudaEventRecord(evt0, stream));
+            row_stream_probe_kernel<T><<<grid, block, 0, stream>>>(N, K, P, node_types, first_neigh.p, neigh_types, r, table, sm, sink.p);
+            check_launch("row_stream_probe_kernel");
+            SMX_CUDA(cudaEventRecord(evt1, stream));
+            SMX_CUDA(cudaEventSynchronize(evt1));
+            float t = 0.f;
+            SMX_CUDA(cudaEventElapsedTime(&t, evt0, evt1));
+            if (rep > 0 && (best == 0.f || t < best)) best = t;
+        }
+        if (ms) *ms = best;
+        if (bytes) *bytes = static_cast<double>(E) * 4.0 * P * K * sizeof(T);
+    }
     void timer_start() override {
         SMX_CUDA(cudaSetDevice(device));
         SMX_CUDA(cudaEventRecord(evt0, stream));
@@ -1235,6 +1262,10 @@ int smx_measure_fma_peak(int precision, int device, double* tflops) {
         g_create_error = e.what();
         return SMX_ERR_CUDA;
     }
+}
+
+int smx_measure_row_stream(smx_handle h, int layer, double* ms, double* bytes) {
+    return guarded(h, [&](smx::EvaluatorBase& e) { e.measure_row_stream(layer, ms, bytes); });
 }
 
 int smx_build_neighbors(smx_handle h, int num_atoms, const double* positions, const int* types, const double* cell,

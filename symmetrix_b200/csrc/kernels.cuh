@@ -644,6 +644,35 @@ __global__ void __launch_bounds__(kChannelBlock, tp_min_blocks<T>(LF, true)) tp_
     }
 }
 
+// Measurement probe: streams, for every edge of the current edge set, the spline row the edge kernels read
+// (same (pair, bin) addressing, same per-thread 16-byte loads) and does nothing else; its duration is the
+// floor the L2 -> SM path sets for one pass of an edge kernel over the edge set. No barriers and few
+// registers, so the SMs run it at full occupancy.
+template <typename T>
+__global__ void row_stream_probe_kernel(int N, int K, int P, const int* __restrict__ node_types, const long long* __restrict__ first_neigh,
+                                        const int* __restrict__ neigh_types, const double* __restrict__ r, const T* __restrict__ coef,
+                                        SplineMeta sm, T* __restrict__ sink) {
+    T acc = T(0);
+    for (int i = blockIdx.x; i < N; i += gridDim.x) {
+        const int type_i = node_types[i];
+        const long long e_begin = first_neigh[i], e_end = first_neigh[i + 1];
+        for (int k = threadIdx.x; k < K; k += blockDim.x)
+            for (long long e = e_begin; e < e_end; ++e) {
+                int bin = static_cast<int>(r[e] / sm.h);
+                bin = bin < 0 ? 0 : (bin > sm.num_bins - 1 ? sm.num_bins - 1 : bin);
+                const int tj = neigh_types[e];
+                const int lo = type_i <= tj ? type_i : tj, hi = type_i <= tj ? tj : type_i;
+                const int pair = lo * (2 * sm.num_elements - lo - 1) / 2 + hi;
+                const T* row = coef + (static_cast<long long>(pair) * sm.num_bins + bin) * P * K * 4;
+                for (int p = 0; p < P; ++p) {
+                    const Vec4<T> c = load_coef<T>(row + 4 * p * K, k, K);
+                    acc += (c.x + c.y) + (c.z + c.w);
+                }
+            }
+    }
+    if (acc == T(1.2345e30)) *sink = acc;     // never true for real tables; keeps the loads alive
+}
+
 // Sum of the adjoint messages of all edges that have row j as their sender, in the fixed order
 // of the sender-sorted edge list (deterministic; takes the place of the atomic scatter the
 // reference's device code uses, mace_kokkos.cpp:1008-1010):

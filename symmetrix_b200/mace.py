@@ -190,6 +190,13 @@ class MACE:
         self._check(self._lib.smx_timer_stop(self._h, ctypes.byref(ms)))
         return ms.value
 
+    def measure_row_stream(self, layer: int):
+        """(device ms, bytes) of a kernel that only streams the spline row of every current edge from the table of
+        interaction layer `layer`: the floor the L2 -> SM path sets for one pass of an edge kernel."""
+        ms, nbytes = ctypes.c_double(0.0), ctypes.c_double(0.0)
+        self._check(self._lib.smx_measure_row_stream(self._h, int(layer), ctypes.byref(ms), ctypes.byref(nbytes)))
+        return ms.value, nbytes.value
+
     def set_profiling(self, enabled: bool) -> None:
         self._check(self._lib.smx_set_profiling(self._h, int(bool(enabled))))
 
