@@ -121,7 +121,9 @@ int smx_set_array(smx_handle h, const char* name, const double* src, long n, int
  * forces: f[i] -= nf_ij, f[j] += nf_ij, virial += sym(xyz_ij (x) nf_ij), energy = sum of node
  * energies (pair_symmetrix/pair_symmetrix_mace.cpp:324-368; symmetrix_calc.py:85-102).
  * `atom_forces` has 3*num_rows doubles with num_rows >= 1 + max(neigh_indices); `virial` has 6
- * (xx, yy, zz, xy, xz, yz). Any output pointer may be NULL. Deterministic (no atomics). */
+ * (xx, yy, zz, xy, xz, yz). Any output pointer may be NULL. Deterministic (no atomics). With
+ * host destinations the call returns when the results are there; with device destinations it is
+ * asynchronous on the evaluator's stream. */
 int smx_reduce_forces(smx_handle h, int num_rows, double* atom_forces, double* virial,
                       double* energy, int mem_space);
 

@@ -753,7 +753,7 @@ public:
 
     void sync() override {
         SMX_CUDA(cudaSetDevice(device));
-        SMX_CUDA(cudaStreamSynchronize(stream));
+        check_kernel_status();
     }
     // Issue all further work on the caller's stream (`external`), or go back to the evaluator's own stream.
     // A null handle with `external` set means the legacy default stream.
@@ -790,7 +790,6 @@ public:
         b.resize(want, stream, true);
         if (want > old) SMX_CUDA(cudaMemsetAsync(b.p + old, 0, (want - old) * sizeof(T), stream));
         if (name == "H1") h1_rows = rows;
-        SMX_CUDA(cudaStreamSynchronize(stream));
     }
     void* device_ptr(const std::string& name, long* count, int* elem_bytes) override {
         Field f = field(name);
@@ -986,7 +985,7 @@ public:
             if (energy) SMX_CUDA(cudaMemcpyAsync(energy, out7.p, sizeof(double), kind, stream));
             if (virial) SMX_CUDA(cudaMemcpyAsync(virial, out7.p + 1, 6 * sizeof(double), kind, stream));
         }
-        check_kernel_status();
+        if (mem_space != SMX_DEVICE) check_kernel_status();   // device destinations: asynchronous on the stream
     }
 
     // ------------------------------------------------------------------ neighbour list

@@ -205,9 +205,13 @@ class SlabRank:
         self._sync_torch()
         for stage in ("reverse_H1", "reverse_M0", "reverse_A0"):
             self._run(stage)
-        forces, virial, energy = self.ev.reduce_forces(num_rows=self.rows)
-        self.forces = self.torch.as_tensor(forces, device=self.device)
-        self.virial, self.energy = virial, energy
+        if self.shared_stream:
+            # results stay on the device: no host synchronisation before the force-row exchange
+            self.forces, self.virial, self.energy = self.ev.reduce_forces(num_rows=self.rows, device=True)
+        else:
+            forces, virial, energy = self.ev.reduce_forces(num_rows=self.rows)
+            self.forces = self.torch.as_tensor(forces, device=self.device)
+            self.virial, self.energy = virial, energy
 
     def pack_forces(self, peer):
         return self.forces.index_select(0, self.recv_idx[peer]).contiguous()
@@ -268,6 +272,13 @@ def evaluate_decomposed(ranks, dist=None):
     for r in ranks:
         r.reverse_layer0()
     _exchange(ranks, lambda r, q: r.send_idx[q].numel(), lambda r, q: r.pack_forces(q), lambda r, q, b: r.unpack_forces(q, b), dist)
+    if ranks[0].shared_stream:
+        import torch
+        t = sum(torch.cat([r.energy, r.virial]) for r in ranks)      # seven float64 values on the device
+        if dist is not None:
+            dist.all_reduce(t)
+        vals = t.cpu().numpy()                                      # the only host synchronisation of the step
+        return float(vals[0]), vals[1:], [r.owned_forces() for r in ranks]
     energy = sum(r.energy for r in ranks)
     virial = sum(np.asarray(r.virial) for r in ranks)
     if dist is not None:

@@ -164,9 +164,22 @@ class MACE:
         a = np.ascontiguousarray(values, dtype=np.float64).reshape(-1)
         self._check(self._lib.smx_set_array(self._h, name.encode(), ctypes.c_void_p(a.ctypes.data), a.size, _lib.SMX_HOST))
 
-    def reduce_forces(self, num_rows=None, want_forces=True, want_virial=True):
-        """Per-atom forces ``[num_rows, 3]``, virial ``[6]`` (xx, yy, zz, xy, xz, yz) and total energy."""
+    def reduce_forces(self, num_rows=None, want_forces=True, want_virial=True, device=False):
+        """Per-atom forces ``[num_rows, 3]``, virial ``[6]`` (xx, yy, zz, xy, xz, yz) and total energy.
+
+        With ``device=True`` the three results are float64 torch tensors on the evaluator's GPU (the energy has
+        shape ``[1]``), written asynchronously on the evaluator's stream: no host synchronisation happens."""
         rows = self._num_nodes if num_rows is None else int(num_rows)
+        if device:
+            import torch
+            dev = f"cuda:{self.info.device}"
+            f = torch.zeros((rows, 3), dtype=torch.float64, device=dev) if want_forces else None
+            v = torch.zeros(6, dtype=torch.float64, device=dev) if want_virial else None
+            e = torch.zeros(1, dtype=torch.float64, device=dev)
+            self._check(self._lib.smx_reduce_forces(
+                self._h, rows, ctypes.c_void_p(f.data_ptr()) if want_forces else None,
+                ctypes.c_void_p(v.data_ptr()) if want_virial else None, ctypes.c_void_p(e.data_ptr()), _lib.SMX_DEVICE))
+            return f, v, e
         f = np.zeros((rows, 3)) if want_forces else None
         v = np.zeros(6) if want_virial else None
         e = ctypes.c_double(0.0)
