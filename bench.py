@@ -347,7 +347,7 @@ def run_decomposed(args, rank, world, local_rank, dist):
         raise SystemExit("decomposed runs are defined for the FCC workloads")
     s = st.fcc_box((cells[0] * world, cells[1], cells[2]), 3.6, numbers, seed=1)
     ev = MACE(path, dtype=args.dtype, device=local_rank)
-    rk = SlabRank(make_slab_plan(s, spec.r_cut, rank, world), ev, spec.r_cut, numbers)
+    rk = SlabRank(make_slab_plan(s, spec.r_cut, rank, world, mode=args.dd_mode), ev, spec.r_cut, numbers)
     rk.build_edges()
     flush = torch.empty(256 * 1024 * 1024 // 4, dtype=torch.float32, device=f"cuda:{local_rank}")
 
@@ -416,7 +416,9 @@ def run_decomposed(args, rank, world, local_rank, dist):
             "config": {"workload": f"{args.workload} x {world} along x", "description": WORKLOADS[args.workload][2],
                        "atoms_total": n_total, "atoms_per_gpu": n_total // world, "ghost_rows_total": int(counts[1].item()),
                        "edges_total": int(counts[2].item()),
-                       "parallelism": f"{world} slabs along x, ghost shell r_cut, halo exchange of H1 / H1_adj / force rows by NCCL send/recv",
+                       "parallelism": (f"{world} slabs along x, ghost shell r_cut, halo exchange of H1 / H1_adj / force rows by NCCL send/recv"
+                                       if args.dd_mode == "message_passing" else
+                                       f"{world} slabs along x, ghost shell 2 r_cut, layer 0 recomputed on ghosts, force rows by NCCL send/recv"),
                        "halo_bytes_per_rank_per_exchange": int(counts[1].item() / world * width),
                        "l2": "256 MB buffer written between timed steps (L2 flush)",
                        "timing": "CUDA events around each step with a barrier + synchronize on both sides, summed, max over ranks"},
@@ -575,6 +577,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="fcc4000", choices=sorted(WORKLOADS))
     ap.add_argument("--dtype", default=None, choices=["float64", "float32"])
+    ap.add_argument("--dd-mode", default="message_passing", choices=["message_passing", "recompute"],
+                    help="N > 1: exchange H1 / H1_adj rows (ghost shell r_cut) or recompute layer 0 on a 2 r_cut shell")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extra", action="store_true")
     args = ap.parse_args()

@@ -177,13 +177,20 @@ int smx_compute_current(smx_handle h);
  * returns to its own stream when `external` is zero, so that pack / unpack kernels and NCCL calls of the
  * caller are ordered with the evaluator's kernels without host synchronisation. smx_restrict_nodes keeps only the first `num_nodes`
  * receivers of the current edge set (owned atoms first, ghost atoms after them) and returns the
- * remaining edge count. smx_resize_rows grows "H1" or "H1_adj" to `rows` feature rows, keeping the
+ * remaining edge count; it starts a new evaluation (outputs zero-filled) and `num_nodes` may be anything up to
+ * the receiver count the edge set was given or built with. smx_set_active_nodes changes the active
+ * receivers the same way but in the middle of an evaluation: node energies, partial forces and feature
+ * rows beyond the active nodes are kept. That is the reference's recompute mode
+ * (pair_symmetrix_mace.cpp:551-748), where layer 0 and its reverse run on owned + ghost atoms
+ * (MACE::compute_* called with `nlocal + nghost`-sized lists there) and layer 1 on owned atoms only.
+ * smx_resize_rows grows "H1" or "H1_adj" to `rows` feature rows, keeping the
  * computed rows and zero-filling the appended ghost rows. smx_device_ptr returns the device address,
  * element count and element size (4 or 8 bytes) of a named array so that pack / unpack kernels and
  * NCCL can work on it in place; the pointer is valid until the next call that resizes that array. */
 int smx_sync(smx_handle h);
 int smx_set_stream(smx_handle h, void* stream, int external);
 int smx_restrict_nodes(smx_handle h, int num_nodes, long* num_edges);
+int smx_set_active_nodes(smx_handle h, int num_nodes, long* num_edges);
 int smx_resize_rows(smx_handle h, const char* name, int rows);
 int smx_device_ptr(smx_handle h, const char* name, void** ptr, long* count, int* elem_bytes);
 

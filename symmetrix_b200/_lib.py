@@ -21,7 +21,7 @@ EXPORTED_SYMBOLS = [
     "smx_compute", "smx_begin", "smx_stage", "smx_get_array", "smx_set_array", "smx_reduce_forces",
     "smx_last_device_ms", "smx_launch_count", "smx_build_neighbors", "smx_get_edges", "smx_compute_current",
     "smx_timer_start", "smx_timer_stop", "smx_set_profiling", "smx_stage_time", "smx_measure_fma_peak", "smx_measure_row_stream",
-    "smx_energy_virial_noalloc", "smx_sync", "smx_set_stream", "smx_restrict_nodes", "smx_resize_rows", "smx_device_ptr",
+    "smx_energy_virial_noalloc", "smx_sync", "smx_set_stream", "smx_restrict_nodes", "smx_set_active_nodes", "smx_resize_rows", "smx_device_ptr",
 ]
 
 
@@ -77,6 +77,7 @@ def load():
     lib.smx_sync.argtypes = [vp]
     lib.smx_set_stream.argtypes = [vp, vp, ctypes.c_int]
     lib.smx_restrict_nodes.argtypes = [vp, ctypes.c_int, lp]
+    lib.smx_set_active_nodes.argtypes = [vp, ctypes.c_int, lp]
     lib.smx_resize_rows.argtypes = [vp, ctypes.c_char_p, ctypes.c_int]
     lib.smx_device_ptr.argtypes = [vp, ctypes.c_char_p, ctypes.POINTER(ctypes.c_void_p), lp, ctypes.POINTER(ctypes.c_int)]
     lib.smx_energy_virial_noalloc.argtypes = [dp, ctypes.c_int, dp, dp, ctypes.c_long, dp, vp, ctypes.c_char_p, ctypes.c_int]

@@ -73,7 +73,7 @@ public:
     virtual void sync() = 0;
     virtual void measure_row_stream(int layer, double* ms, double* bytes) = 0;
     virtual void set_stream(void* s, bool external) = 0;
-    virtual long restrict_nodes(int num_nodes) = 0;
+    virtual long restrict_nodes(int num_nodes, bool keep_outputs) = 0;
     virtual void resize_rows(const std::string& name, int rows) = 0;
     virtual void* device_ptr(const std::string& name, long* count, int* elem_bytes) = 0;
 
@@ -109,6 +109,7 @@ public:
     // current edge set
     int N = 0;
     long E = 0;
+    int N_built = 0;              // receivers of the edge set as given or built; N <= N_built are active
     int h1_rows = 0;
     bool have_edges = false;
     DevBuf<int> in_node_types, in_num_neigh, in_neigh_indices, in_neigh_types, in_shifts;
@@ -267,27 +268,33 @@ public:
         neigh_types = stage_input(et, n_edges, in_neigh_types, mem_space);
         xyz = stage_input(x, 3 * static_cast<size_t>(n_edges), in_xyz, mem_space);
         r = stage_input(rr, n_edges, in_r, mem_space);
+        N_built = n_nodes;
         adopt_edges(n_nodes, n_edges);
     }
 
     // Derived index arrays of the current edge set: CSR offsets and nodes sorted by element type.
-    void adopt_edges(int n_nodes, long n_edges) {
+    // `keep`: change the active receivers in the middle of an evaluation -- the outputs accumulated so far and the
+    // feature rows beyond the active nodes stay as they are.
+    void adopt_edges(int n_nodes, long n_edges, bool keep = false, bool rescan = true) {
         N = n_nodes;
         E = n_edges;
-        h1_rows = N;
+        if (!keep) h1_rows = N;
         sender_rows = -1;
         have_edges = true;
-        first_neigh.resize(static_cast<size_t>(N) + 1, stream);
-        if (N > 0) {
-            cub::TransformInputIterator<long long, CastToLL, const int*> it(num_neigh, CastToLL());
-            size_t bytes = 0;
-            SMX_CUDA(cub::DeviceScan::ExclusiveSum(nullptr, bytes, it, first_neigh.p, N, stream));
-            cub_tmp.resize(bytes, stream);
-            SMX_CUDA(cub::DeviceScan::ExclusiveSum(cub_tmp.p, bytes, it, first_neigh.p, N, stream));
-            launches += 1;
+        if (rescan) {
+            // offsets of all receivers; a restricted set uses a prefix of this scan (entry n = edges of the first n)
+            first_neigh.resize(static_cast<size_t>(N) + 1, stream);
+            if (N > 0) {
+                cub::TransformInputIterator<long long, CastToLL, const int*> it(num_neigh, CastToLL());
+                size_t bytes = 0;
+                SMX_CUDA(cub::DeviceScan::ExclusiveSum(nullptr, bytes, it, first_neigh.p, N, stream));
+                cub_tmp.resize(bytes, stream);
+                SMX_CUDA(cub::DeviceScan::ExclusiveSum(cub_tmp.p, bytes, it, first_neigh.p, N, stream));
+                launches += 1;
+            }
+            const long long total = E;
+            SMX_CUDA(cudaMemcpyAsync(first_neigh.p + N, &total, sizeof(long long), cudaMemcpyHostToDevice, stream));
         }
-        const long long total = E;
-        SMX_CUDA(cudaMemcpyAsync(first_neigh.p + N, &total, sizeof(long long), cudaMemcpyHostToDevice, stream));
         // nodes sorted by element type (stable), and the segment of each type
         perm.resize(N, stream);
         sorted_types.resize(N, stream);
@@ -307,6 +314,12 @@ public:
         segment_offsets_int_kernel<<<1, 128, 0, stream>>>(N, sorted_types.p, model.num_elements, type_seg.p);
         check_launch("type segments");
         // outputs the caller zero-fills in the reference (mace.cpp:27-30)
+        if (keep) {
+            // the arrays only ever grow and were zero-filled at their largest extent when the step began
+            node_energies.resize(N, stream, true);
+            node_forces.resize(3 * static_cast<size_t>(E), stream, true);
+            return;
+        }
         node_energies.resize(N, stream);
         node_energies.zero(stream);
         node_forces.resize(3 * static_cast<size_t>(E), stream);
@@ -770,14 +783,16 @@ public:
         }
     }
     // Keep only the first `num_nodes` receivers of the current edge set (their rows are a prefix of the edge arrays).
-    long restrict_nodes(int num_nodes) override {
+    // Make the first `num_nodes` receivers of the edge set the active ones. Without `keep_outputs` this starts a new
+    // evaluation (outputs zero-filled); with it the evaluation in progress continues on the other receiver set.
+    long restrict_nodes(int num_nodes, bool keep_outputs) override {
         require_edges();
         SMX_CUDA(cudaSetDevice(device));
-        if (num_nodes < 0 || num_nodes > N) throw ArgError("restrict_nodes: num_nodes out of range");
+        if (num_nodes < 0 || num_nodes > N_built) throw ArgError("restrict_nodes: num_nodes out of range");
         long long e = 0;
         SMX_CUDA(cudaMemcpyAsync(&e, first_neigh.p + num_nodes, sizeof(long long), cudaMemcpyDeviceToHost, stream));
         SMX_CUDA(cudaStreamSynchronize(stream));
-        adopt_edges(num_nodes, static_cast<long>(e));
+        adopt_edges(num_nodes, static_cast<long>(e), keep_outputs, false);
         return static_cast<long>(e);
     }
     // Grow H1 / H1_adj to `rows` feature rows keeping the existing rows (ghost rows are appended by the caller).
@@ -1000,6 +1015,7 @@ public:
         node_types = d_types;
         num_neigh = in_num_neigh.p; neigh_indices = in_neigh_indices.p; neigh_types = in_neigh_types.p;
         xyz = in_xyz.p; r = in_r.p;
+        N_built = natoms;
         adopt_edges(natoms, n_edges);
         SMX_CUDA(cudaStreamSynchronize(stream));
         return n_edges;
@@ -1218,7 +1234,11 @@ int smx_set_stream(smx_handle h, void* stream, int external) {
     return guarded(h, [&](smx::EvaluatorBase& e) { e.set_stream(stream, external != 0); });
 }
 int smx_restrict_nodes(smx_handle h, int num_nodes, long* num_edges) {
-    return guarded(h, [&](smx::EvaluatorBase& e) { const long n = e.restrict_nodes(num_nodes); if (num_edges) *num_edges = n; });
+    return guarded(h, [&](smx::EvaluatorBase& e) { const long n = e.restrict_nodes(num_nodes, false); if (num_edges) *num_edges = n; });
+}
+
+int smx_set_active_nodes(smx_handle h, int num_nodes, long* num_edges) {
+    return guarded(h, [&](smx::EvaluatorBase& e) { const long n = e.restrict_nodes(num_nodes, true); if (num_edges) *num_edges = n; });
 }
 int smx_resize_rows(smx_handle h, const char* name, int rows) {
     return guarded(h, [&](smx::EvaluatorBase& e) {

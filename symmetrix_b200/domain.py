@@ -8,6 +8,11 @@ them), finishes the reverse pass, and finally returns the force rows of its ghos
 does there over MPI (``forward_comm`` / ``reverse_comm``, pack/unpack at pair_symmetrix_mace.cpp:194-238)
 is done here with point-to-point sends between slab neighbours (NCCL over NVLink on GPUs, gloo on CPU).
 
+A second mode, "recompute" (the pair style's ``no_mpi_message_passing`` branch, pair_symmetrix_mace.cpp:551-748),
+trades the two feature exchanges for redundant work: the ghost shell is ``2 r_cut`` wide, layer 0 and its reverse run
+on the owned atoms and on the ghosts within ``r_cut`` (whose neighbourhoods the wider shell completes), layer 1 on the
+owned atoms, and only the force rows of the ghosts travel. Both modes give the same energies and forces.
+
 The decomposition is 1-D along one cell axis; periodic images along the other two axes map to the same
 row (as the single-domain mode does with ``atom->map``, pair_symmetrix_mace.cpp:304-306), images along the
 slab axis are explicit ghost rows. Every rank derives the full plan from the same global structure, so no
@@ -40,14 +45,17 @@ class SlabPlan:
     peers: list = field(default_factory=list)        # ranks exchanged with, ascending
     send_rows: dict = field(default_factory=dict)    # peer -> local owned rows, in the peer's ghost order
     recv_rows: dict = field(default_factory=dict)    # peer -> local ghost rows (ascending)
+    mode: str = "message_passing"                    # or "recompute"
+    n_inner: int = 0                                 # recompute mode: ghosts within r_cut of the slab (they come first)
 
 
-def _ghost_list(frac: np.ndarray, owner: np.ndarray, rank: int, world: int, shell: float):
+def _ghost_list(frac: np.ndarray, owner: np.ndarray, rank: int, world: int, shell: float, inner: float = None):
     """Ghost images of `rank`: (global id, image shift) of atoms whose image lies in the shell around its slab.
 
-    `frac` is the fractional coordinate along the slab axis, `shell` the ghost width in the same units."""
+    `frac` is the fractional coordinate along the slab axis, `shell` the ghost width in the same units. With `inner`
+    (a narrower width) the images inside that narrower shell come first and their count is returned as well."""
     lo, hi = rank / world, (rank + 1) / world
-    out_g, out_n = [], []
+    out_g, out_n, out_far = [], [], []
     for n in (-1, 0, 1):
         x = frac + n
         sel = ((x >= lo - shell) & (x < lo)) | ((x >= hi) & (x < hi + shell))
@@ -56,14 +64,23 @@ def _ghost_list(frac: np.ndarray, owner: np.ndarray, rank: int, world: int, shel
         idx = np.nonzero(sel)[0]
         out_g.append(idx)
         out_n.append(np.full(idx.size, n, dtype=np.int64))
+        if inner is not None:
+            xi = x[idx]
+            out_far.append(~(((xi >= lo - inner) & (xi < lo)) | ((xi >= hi) & (xi < hi + inner))))
     g = np.concatenate(out_g)
     n = np.concatenate(out_n)
-    order = np.lexsort((g, n, owner[g]))
-    return g[order], n[order]
+    if inner is None:
+        order = np.lexsort((g, n, owner[g]))
+        return g[order], n[order]
+    far = np.concatenate(out_far)
+    order = np.lexsort((g, n, owner[g], far))
+    return g[order], n[order], int(np.count_nonzero(~far))
 
 
-def make_slab_plan(s: Structure, r_cut: float, rank: int, world: int, axis: int = 0) -> SlabPlan:
+def make_slab_plan(s: Structure, r_cut: float, rank: int, world: int, axis: int = 0, mode: str = "message_passing") -> SlabPlan:
     """Plan of rank `rank` of `world` for structure `s` (positions inside the cell, orthogonal slab axis)."""
+    if mode not in ("message_passing", "recompute"):
+        raise ValueError(f"unknown decomposition mode {mode!r}")
     cell = np.asarray(s.cell, dtype=np.float64)
     other = [a for a in range(3) if a != axis]
     if any(abs(cell[axis, o]) > 1e-12 or abs(cell[o, axis]) > 1e-12 for o in other):
@@ -80,40 +97,35 @@ def make_slab_plan(s: Structure, r_cut: float, rank: int, world: int, axis: int 
     if world == 1:
         return SlabPlan(rank, world, axis, own.size, 0, own, np.zeros(0, np.int64), np.zeros(0, np.int64), np.zeros(0, np.int64),
                         pos[own].copy(), np.asarray(s.numbers)[own], cell.copy(), tuple(s.pbc))
-    shell = r_cut / length
-    g, n = _ghost_list(frac, owner, rank, world, shell)
+    width = r_cut if mode == "message_passing" else 2.0 * r_cut
+    if 2.0 * width > length + 1e-9 and mode == "recompute":
+        raise ValueError(f"a {width:.2f} A ghost shell on both sides does not fit into a cell of {length:.2f} A")
+    shell = width / length
+    n_inner = 0
+    if mode == "recompute":
+        g, n, n_inner = _ghost_list(frac, owner, rank, world, shell, inner=r_cut / length)
+    else:
+        g, n = _ghost_list(frac, owner, rank, world, shell)
     gpos = pos[g].copy()
     gpos[:, axis] += n * length
     positions = np.concatenate([pos[own], gpos])
     # local cell: open along the slab axis (ghost images are explicit), periodic as given along the others
     lcell = cell.copy()
-    lo = rank * length / world - r_cut
+    lo = rank * length / world - width
     positions[:, axis] -= lo
-    lcell[axis, axis] = length / world + 2 * r_cut
+    lcell[axis, axis] = length / world + 2 * width
     pbc = tuple(False if a == axis else bool(s.pbc[a]) for a in range(3))
     plan = SlabPlan(rank, world, axis, own.size, g.size, own, g, owner[g], n, positions,
                     np.concatenate([np.asarray(s.numbers)[own], np.asarray(s.numbers)[g]]), lcell, pbc)
+    plan.mode, plan.n_inner = mode, n_inner
     plan.peers = sorted(set(int(q) for q in owner[g]))
     for q in plan.peers:
         plan.recv_rows[q] = own.size + np.nonzero(owner[g] == q)[0]
         # what I must send to q: q's ghost list restricted to atoms I own, in q's order
-        gq, _ = _ghost_list(frac, owner, q, world, shell)
+        gq = _ghost_list(frac, owner, q, world, shell, inner=r_cut / length if mode == "recompute" else None)[0]
         mine = gq[owner[gq] == rank]
         plan.send_rows[q] = np.searchsorted(own, mine)
     return plan
-
-
-class LocalTransport:
-    """All ranks in one process: messages are handed over through a dictionary (tests, 1-GPU emulation)."""
-
-    def __init__(self):
-        self.box = {}
-
-    def post(self, src, dst, tag, tensor):
-        self.box[(src, dst, tag)] = tensor
-
-    def take(self, src, dst, tag):
-        return self.box.pop((src, dst, tag))
 
 
 class SlabRank:
@@ -129,6 +141,9 @@ class SlabRank:
         self.plan = plan
         self.ev = backend
         self.rows = plan.n_own + plan.n_ghost
+        self.recompute = plan.mode == "recompute"
+        # receivers of layer 0: owned atoms, plus (recompute mode) the ghosts within r_cut of the slab
+        self.n_layer0 = plan.n_own + (plan.n_inner if self.recompute else 0)
         self.width = backend.num_LM * backend.num_channels
         zmap = {int(z): t for t, z in enumerate(atomic_numbers)}
         self.types = np.array([zmap[int(z)] for z in plan.numbers], dtype=np.int32)
@@ -161,16 +176,19 @@ class SlabRank:
         """Neighbour list of the local atoms (owned + ghosts); receivers are the owned atoms only."""
         p = self.plan
         self.ev.build_neighbors(p.positions, self.types, p.cell, p.pbc, r_cut=self.r_cut)
-        self.num_edges = self.ev.restrict_nodes(p.n_own)
+        self.num_edges = self.ev.restrict_nodes(self.n_layer0)
 
     def begin_step(self):
         """Re-arm the current edge set (zero node energies / partial forces) for another evaluation."""
-        self.ev.restrict_nodes(self.plan.n_own)
+        self.ev.restrict_nodes(self.n_layer0)
 
     def forward_layer0(self):
         for stage in ("compute_A0", "compute_M0", "compute_H1"):
             self._run(stage)
-        self.ev.resize_rows("H1", self.rows)
+        if self.recompute:
+            self.ev.set_active_nodes(self.plan.n_own)      # layer 1 on the owned atoms; H1 keeps its ghost rows
+        else:
+            self.ev.resize_rows("H1", self.rows)
 
     def _rows_view(self, name):
         return self.ev.device_view(name).view(-1, self.width)
@@ -203,6 +221,8 @@ class SlabRank:
 
     def reverse_layer0(self):
         self._sync_torch()
+        if self.recompute:
+            self.ev.set_active_nodes(self.n_layer0)        # the partial H1_adj of the ghosts goes through layer 0 here
         for stage in ("reverse_H1", "reverse_M0", "reverse_A0"):
             self._run(stage)
         if self.shared_stream:
@@ -262,13 +282,16 @@ def evaluate_decomposed(ranks, dist=None):
     process emulation), or the single local rank when `dist` is an initialised ``torch.distributed``.
     Returns (total energy, virial[6], list of owned-force tensors per local rank).
     """
+    recompute = ranks[0].recompute
     for r in ranks:
         r.begin_step()
         r.forward_layer0()
-    _exchange(ranks, lambda r, q: r.recv_idx[q].numel(), lambda r, q: r.pack_forward(q), lambda r, q, b: r.unpack_forward(q, b), dist)
+    if not recompute:
+        _exchange(ranks, lambda r, q: r.recv_idx[q].numel(), lambda r, q: r.pack_forward(q), lambda r, q, b: r.unpack_forward(q, b), dist)
     for r in ranks:
         r.layer1_and_reverse()
-    _exchange(ranks, lambda r, q: r.send_idx[q].numel(), lambda r, q: r.pack_reverse(q), lambda r, q, b: r.unpack_reverse(q, b), dist)
+    if not recompute:
+        _exchange(ranks, lambda r, q: r.send_idx[q].numel(), lambda r, q: r.pack_reverse(q), lambda r, q, b: r.unpack_reverse(q, b), dist)
     for r in ranks:
         r.reverse_layer0()
     _exchange(ranks, lambda r, q: r.send_idx[q].numel(), lambda r, q: r.pack_forces(q), lambda r, q, b: r.unpack_forces(q, b), dist)

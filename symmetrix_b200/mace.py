@@ -272,6 +272,15 @@ class MACE:
         self._num_nodes, self._num_edges = int(num_nodes), n.value
         return n.value
 
+    def set_active_nodes(self, num_nodes: int) -> int:
+        """Like :meth:`restrict_nodes`, but in the middle of an evaluation: the outputs accumulated so far and the feature
+        rows beyond the active nodes are kept (recompute mode of the pair style: layer 0 on owned + ghost atoms, layer 1 on
+        owned atoms)."""
+        n = ctypes.c_long(0)
+        self._check(self._lib.smx_set_active_nodes(self._h, int(num_nodes), ctypes.byref(n)))
+        self._num_nodes, self._num_edges = int(num_nodes), n.value
+        return n.value
+
     def resize_rows(self, name: str, rows: int) -> None:
         self._check(self._lib.smx_resize_rows(self._h, name.encode(), int(rows)))
 

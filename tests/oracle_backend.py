@@ -24,17 +24,36 @@ class OracleBackend:
         self.inputs = {"num_nodes": n, "node_types": np.asarray(types, np.int32),
                        "num_neigh": np.bincount(nl["i"], minlength=n).astype(np.int32), "neigh_indices": nl["j"],
                        "neigh_types": np.asarray(types, np.int32)[nl["j"]], "xyz": nl["D"].reshape(-1), "r": nl["d"]}
+        self.full_inputs = self.inputs
         return nl["i"].size
 
-    def restrict_nodes(self, n_own):
-        inp = self.inputs
-        e = int(np.sum(inp["num_neigh"][:n_own]))
-        self.inputs = {"num_nodes": n_own, "node_types": inp["node_types"][:n_own], "num_neigh": inp["num_neigh"][:n_own],
+    def _activate(self, n):
+        inp = self.full_inputs
+        e = int(np.sum(inp["num_neigh"][:n]))
+        self.inputs = {"num_nodes": n, "node_types": inp["node_types"][:n], "num_neigh": inp["num_neigh"][:n],
                        "neigh_indices": inp["neigh_indices"][:e], "neigh_types": inp["neigh_types"][:e],
                        "xyz": inp["xyz"][:3 * e], "r": inp["r"][:e]}
         self.o._edges(self.inputs)
-        self.o.node_forces = np.zeros((e, 3))
         self.o.compute_Y(); self.o.compute_R0(); self.o.compute_R1()
+        return e
+
+    def restrict_nodes(self, n_own):
+        """New evaluation on the first n_own receivers: outputs zero-filled."""
+        self._nf_full = np.zeros((self.full_inputs["r"].size, 3))
+        self._en_full = np.zeros(self.full_inputs["num_nodes"])
+        e = self._activate(n_own)
+        self.o.node_forces = np.zeros((e, 3))
+        self.o.node_energies = np.zeros(n_own)
+        return e
+
+    def set_active_nodes(self, n):
+        """Other receiver set, same evaluation: partial forces and node energies are carried over."""
+        nf, en = self.o.node_forces, self.o.node_energies
+        self._nf_full[: nf.shape[0]] = nf
+        self._en_full[: en.shape[0]] = en
+        e = self._activate(n)
+        self.o.node_forces = self._nf_full[:e].copy()
+        self.o.node_energies = self._en_full[:n].copy()
         return e
 
     def _stage(self, name, zero_dxyz=True, zero_H1_adj=True):

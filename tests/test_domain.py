@@ -30,10 +30,12 @@ def _single_domain():
     return s, e.sum(), forces, virial
 
 
-def test_plans_are_consistent_between_ranks():
+@pytest.mark.parametrize("mode", ["message_passing", "recompute"])
+def test_plans_are_consistent_between_ranks(mode):
     s = _structure()
+    shell = R_CUT if mode == "message_passing" else 2 * R_CUT
     for world in (2, 3, 4, 6):
-        plans = [make_slab_plan(s, R_CUT, r, world) for r in range(world)]
+        plans = [make_slab_plan(s, R_CUT, r, world, mode=mode) for r in range(world)]
         assert sum(p.n_own for p in plans) == s.num_atoms
         assert np.array_equal(np.sort(np.concatenate([p.own_global for p in plans])), np.arange(s.num_atoms))
         for p in plans:
@@ -45,8 +47,12 @@ def test_plans_are_consistent_between_ranks():
             # ghost images sit inside the shell around the slab
             x = p.positions[p.n_own:, 0]
             w = s.cell[0, 0] / world
-            assert np.all((x >= 0) & (x < w + 2 * R_CUT))
-            assert np.all((p.positions[:p.n_own, 0] >= R_CUT - 1e-9) & (p.positions[:p.n_own, 0] < R_CUT + w + 1e-9))
+            assert np.all((x >= 0) & (x < w + 2 * shell))
+            assert np.all((p.positions[:p.n_own, 0] >= shell - 1e-9) & (p.positions[:p.n_own, 0] < shell + w + 1e-9))
+            if mode == "recompute":
+                # the ghosts within r_cut of the slab come first: they are receivers of layer 0
+                near = (x >= shell - R_CUT) & (x < shell + w + R_CUT)
+                assert np.all(near[:p.n_inner]) and not np.any(near[p.n_inner:])
 
 
 def test_plan_rejects_slabs_thinner_than_the_cutoff():
@@ -55,13 +61,14 @@ def test_plan_rejects_slabs_thinner_than_the_cutoff():
         make_slab_plan(s, R_CUT, 0, 7)
 
 
+@pytest.mark.parametrize("mode", ["message_passing", "recompute"])
 @pytest.mark.parametrize("world", [1, 2, 3, 5])
-def test_decomposed_evaluation_equals_single_domain(world):
+def test_decomposed_evaluation_equals_single_domain(world, mode):
     s, e_ref, f_ref, v_ref = _single_domain()
     ranks = []
     for r in range(world):
         b = OracleBackend(GOLDEN / "tiny_model.json")
-        rk = SlabRank(make_slab_plan(s, R_CUT, r, world), b, R_CUT, b.atomic_numbers)
+        rk = SlabRank(make_slab_plan(s, R_CUT, r, world, mode=mode), b, R_CUT, b.atomic_numbers)
         rk.build_edges()
         ranks.append(rk)
     for _ in range(2):   # a second evaluation on the same edge sets must give the same answer
@@ -74,13 +81,13 @@ def test_decomposed_evaluation_equals_single_domain(world):
         np.testing.assert_allclose(virial, v_ref, atol=1e-10)
 
 
-def _gloo_worker(rank, world, port, out_dir):
+def _gloo_worker(rank, world, port, out_dir, mode="message_passing"):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
     import torch.distributed as dist
     dist.init_process_group("gloo", rank=rank, world_size=world)
     s = _structure()
     b = OracleBackend(GOLDEN / "tiny_model.json")
-    rk = SlabRank(make_slab_plan(s, R_CUT, rank, world), b, R_CUT, b.atomic_numbers)
+    rk = SlabRank(make_slab_plan(s, R_CUT, rank, world, mode=mode), b, R_CUT, b.atomic_numbers)
     rk.build_edges()
     energy, virial, owned = evaluate_decomposed([rk], dist=dist)
     np.savez(Path(out_dir) / f"rank{rank}.npz", energy=energy, virial=virial, forces=owned[0].numpy(), own=rk.plan.own_global)
@@ -88,12 +95,12 @@ def _gloo_worker(rank, world, port, out_dir):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world", [2, 3])
-def test_decomposed_evaluation_over_gloo(world, tmp_path):
+@pytest.mark.parametrize("world,mode", [(2, "message_passing"), (3, "message_passing"), (2, "recompute")])
+def test_decomposed_evaluation_over_gloo(world, mode, tmp_path):
     import torch.multiprocessing as mp
     s, e_ref, f_ref, v_ref = _single_domain()
-    port = 29500 + (os.getpid() % 2000) + world
-    mp.spawn(_gloo_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    port = 29500 + (os.getpid() % 2000) + world + (10 if mode == "recompute" else 0)
+    mp.spawn(_gloo_worker, args=(world, port, str(tmp_path), mode), nprocs=world, join=True)
     forces = np.zeros_like(f_ref)
     for r in range(world):
         d = np.load(tmp_path / f"rank{r}.npz")

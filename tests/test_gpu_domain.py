@@ -24,15 +24,17 @@ def _single(path, s, dtype="float64"):
     return ev.reduce_forces()
 
 
-@pytest.mark.parametrize("dtype,world", [("float64", 2), ("float64", 3), ("float32", 2)])
-def test_emulated_ranks_on_one_gpu_match_single_domain(model_file, dtype, world):
+@pytest.mark.parametrize("dtype,world,mode", [("float64", 2, "message_passing"), ("float64", 3, "message_passing"),
+                                              ("float32", 2, "message_passing"), ("float64", 2, "recompute"),
+                                              ("float64", 3, "recompute"), ("float32", 3, "recompute")])
+def test_emulated_ranks_on_one_gpu_match_single_domain(model_file, dtype, world, mode):
     path, model, spec = model_file("fcc128", num_channels=32, num_spline_points=32)
     s = st.fcc_box((4 * world, 3, 3), 3.6, model["atomic_numbers"], seed=17, jitter=0.12)
     f_ref, v_ref, e_ref = _single(path, s)
     ranks = []
     for r in range(world):
         ev = MACE(path, dtype=dtype)
-        rk = SlabRank(make_slab_plan(s, spec.r_cut, r, world), ev, spec.r_cut, ev.atomic_numbers)
+        rk = SlabRank(make_slab_plan(s, spec.r_cut, r, world, mode=mode), ev, spec.r_cut, ev.atomic_numbers)
         rk.build_edges()
         ranks.append(rk)
     rel, fabs = (1e-10, 1e-9) if dtype == "float64" else (1e-4, 1e-3)
@@ -51,8 +53,8 @@ def _gpu_count():
     return torch.cuda.device_count()
 
 
-@pytest.mark.parametrize("dtype", ["float64", "float32"])
-def test_ranks_over_nccl_match_single_domain(model_file, dtype, tmp_path):
+@pytest.mark.parametrize("dtype,mode", [("float64", "message_passing"), ("float32", "message_passing"), ("float64", "recompute")])
+def test_ranks_over_nccl_match_single_domain(model_file, dtype, mode, tmp_path):
     world = min(_gpu_count(), 4)
     if world < 2:
         pytest.skip("needs at least two GPUs")
@@ -60,7 +62,7 @@ def test_ranks_over_nccl_match_single_domain(model_file, dtype, tmp_path):
     out = tmp_path / "dd.npz"
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
-           "--master-port", str(29400 + os.getpid() % 500), str(ROOT / "tests" / "dd_nccl_worker.py"), str(path), dtype, str(out)]
+           "--master-port", str(29400 + os.getpid() % 500), str(ROOT / "tests" / "dd_nccl_worker.py"), str(path), dtype, str(out), mode]
     subprocess.run(cmd, check=True, env=env, timeout=600)
     d = np.load(out)
     rel, fabs = (1e-10, 1e-9) if dtype == "float64" else (1e-4, 1e-3)
