@@ -122,6 +122,12 @@ public:
     void reduce_forces(int num_rows, double* atom_forces, double* virial6, double* energy) {
         check(smx_reduce_forces(h_, num_rows, atom_forces, virial6, energy, SMX_HOST));
     }
+    // Receiver count of the stage calls that follow. The reference passes `num_nodes` to every stage; its recompute
+    // branch (pair_symmetrix_mace.cpp:551-748) runs layer 0 on nlocal + nghost receivers and layer 1 on nlocal. Here the
+    // edge set is given once to begin() with all receivers (owned first); restrict_nodes starts an evaluation on the
+    // first `num_nodes`, set_active_nodes changes the count in the middle of one and keeps the accumulated outputs.
+    long restrict_nodes(int num_nodes) { long e = 0; check(smx_restrict_nodes(h_, num_nodes, &e)); return e; }
+    long set_active_nodes(int num_nodes) { long e = 0; check(smx_set_active_nodes(h_, num_nodes, &e)); return e; }
     smx_handle handle() const { return h_; }
 
 private:
