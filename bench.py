@@ -343,9 +343,14 @@ def run_decomposed(args, rank, world, local_rank, dist):
     dist.barrier()
     path, numbers, spec = model_path(spec_name)
     cells = {"fcc4000": (10, 10, 10), "fcc1372": (7, 7, 7), "fcc256k": (10, 80, 80)}.get(args.workload)
-    if cells is None:
-        raise SystemExit("decomposed runs are defined for the FCC workloads")
-    s = st.fcc_box((cells[0] * world, cells[1], cells[2]), 3.6, numbers, seed=1)
+    if cells is not None:
+        # weak scaling: the box grows along x with the number of GPUs
+        s = st.fcc_box((cells[0] * world, cells[1], cells[2]), 3.6, numbers, seed=1)
+        scaling, label = "weak", f"{args.workload} x {world} along x"
+    else:
+        # strong scaling: the same box (configs[2]: the 98,304-atom water box) cut into `world` slabs
+        s = WORKLOADS[args.workload][1](st, numbers, 1)
+        scaling, label = "strong", f"{args.workload} in {world} slabs along x"
     ev = MACE(path, dtype=args.dtype, device=local_rank)
     rk = SlabRank(make_slab_plan(s, spec.r_cut, rank, world, mode=args.dd_mode), ev, spec.r_cut, numbers)
     rk.build_edges()
@@ -411,9 +416,9 @@ def run_decomposed(args, rank, world, local_rank, dist):
         width = ev.num_LM * ev.num_channels * (8 if args.dtype == "float64" else 4)
         out = {
             "metric": METRIC, "value": n_total * args.steps / (ms_max * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms_max / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "warmup": args.warmup, "ms_per_step": ms_max / args.steps, "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
             "dtype": "f64" if args.dtype == "float64" else "f32", "data": "synthetic",
-            "config": {"workload": f"{args.workload} x {world} along x", "description": WORKLOADS[args.workload][2],
+            "config": {"workload": label, "description": WORKLOADS[args.workload][2],
                        "atoms_total": n_total, "atoms_per_gpu": n_total // world, "ghost_rows_total": int(counts[1].item()),
                        "edges_total": int(counts[2].item()),
                        "parallelism": (f"{world} slabs along x, ghost shell r_cut, halo exchange of H1 / H1_adj / force rows by NCCL send/recv"
