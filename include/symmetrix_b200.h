@@ -52,6 +52,7 @@ typedef struct smx_model_info {
     int has_zbl;        /* MACE::has_zbl       (mace.hpp:39)  */
     int precision;      /* SMX_FP32 or SMX_FP64: arithmetic type of features and weights     */
     int device;         /* CUDA device ordinal the evaluator lives on                        */
+    int num_interactions; /* 2 (every model the reference can export) or 3 (file key "num_interactions") */
 } smx_model_info;
 
 /* Replaces the constructor MACE::MACE(std::string filename) -> load_from_json

@@ -31,6 +31,7 @@ class ModelInfo(ctypes.Structure):
         ("l_max", ctypes.c_int), ("num_lm", ctypes.c_int), ("L_max", ctypes.c_int), ("num_LM", ctypes.c_int),
         ("num_paths", ctypes.c_int), ("num_lelm1lm2", ctypes.c_int), ("num_lme", ctypes.c_int),
         ("has_zbl", ctypes.c_int), ("precision", ctypes.c_int), ("device", ctypes.c_int),
+        ("num_interactions", ctypes.c_int),
     ]
 
 

@@ -100,6 +100,8 @@ public:
 
     // model tables on the device
     DevBuf<T> coef0, coef1, H0_w, A0_w, H1_w, A1_w, H2_w_H1, H2_w_M1, ro1, ro2_w1, ro2_w2, coefM0, coefM1;
+    DevBuf<T> coefm, Am_w, Hm_w, Hm_res, ro_m, coefMm;    // middle interaction block (models with three blocks)
+    DevBuf<int> progm, progm_off, progm_cnt, monom_off;
     bool poly_fixed = false;      // coefM0 / coefM1 hold the canonical order and the straight-line kernels are used
     DevBuf<double> E0, zbl_radii, A0_spl, A1_spl;
     DevBuf<int> zbl_numbers;
@@ -111,6 +113,7 @@ public:
     long E = 0;
     int N_built = 0;              // receivers of the edge set as given or built; N <= N_built are active
     int h1_rows = 0;
+    int hm_rows = 0;              // rows of Hm / Hm_adj (three-block models), as h1_rows for H1
     bool have_edges = false;
     DevBuf<int> in_node_types, in_num_neigh, in_neigh_indices, in_neigh_types, in_shifts;
     DevBuf<double> in_xyz, in_r;
@@ -123,6 +126,7 @@ public:
 
     // per-call arrays
     DevBuf<T> Phi0, A0, A0_adj, Phi0_adj, M0, M0_adj, H1, H1_adj, Phi1, dPhi1, A1, A1_adj, M1, M1_adj, H2, H2_adj, Hmsg;
+    DevBuf<T> Phim, dPhim, Am, Am_adj, Mm, Mm_adj, Hm, Hm_adj;
     DevBuf<double> node_energies, node_forces, scratch_d, partials, out7, atom_f;
     // GEMM problem lists travel through a pinned host ring and a device ring, so launches need no host synchronisation;
     // the rings hold far more entries than one evaluation uses (a slot is reused only thousands of launches later)
@@ -197,6 +201,24 @@ public:
         poly_fixed = m.poly_canonical;
         coefM0.upload(cast_vec<T>(poly_fixed ? m.coef_M0_canon : m.coef_M0), stream);
         coefM1.upload(cast_vec<T>(poly_fixed ? m.coef_M1_canon : m.coef_M1), stream);
+        if (m.num_interactions == 3) {
+            coefm.upload(spline_rows<T>(m.coefm, m.K), stream);
+            Am_w.upload(cast_vec<T>(m.Am_w), stream);
+            Hm_w.upload(cast_vec<T>(m.Hm_w), stream);
+            Hm_res.upload(cast_vec<T>(m.Hm_res), stream);
+            ro_m.upload(cast_vec<T>(m.ro_m), stream);
+            coefMm.upload(cast_vec<T>(poly_fixed ? m.coef_Mm_canon : m.coef_Mm), stream);
+            std::vector<int> words, offs, counts;
+            for (const auto& p : m.progm) {
+                offs.push_back(static_cast<int>(words.size()));
+                counts.push_back(static_cast<int>(p.words.size()) - kPolyPrefetch);
+                words.insert(words.end(), p.words.begin(), p.words.end());
+            }
+            progm.upload(words, stream);
+            progm_off.upload(offs, stream);
+            progm_cnt.upload(counts, stream);
+            monom_off.upload(std::vector<int>(m.mono_offm.begin(), m.mono_offm.end() - 1), stream);
+        }
         E0.upload(m.atomic_energies, stream);
         if (m.has_zbl) { zbl_radii.upload(m.zbl_covalent_radii, stream); zbl_numbers.upload(m.atomic_numbers, stream); }
         if (m.A0_scaled) A0_spl.upload(m.A0_spline_coef, stream);
@@ -278,7 +300,7 @@ public:
     void adopt_edges(int n_nodes, long n_edges, bool keep = false, bool rescan = true) {
         N = n_nodes;
         E = n_edges;
-        if (!keep) h1_rows = N;
+        if (!keep) { h1_rows = N; hm_rows = N; }
         sender_rows = -1;
         have_edges = true;
         if (rescan) {
@@ -495,10 +517,15 @@ public:
         check_launch("layer0_reverse_kernel");
     }
 
-    PolyArgs<T> poly_args(bool first) {
+    // which: 0 = contraction of block 0 (M0), 1 = of the last block (M1, one output), 2 = of the middle block (Mm)
+    PolyArgs<T> poly_args(int which) {
         PolyArgs<T> a{};
         a.N = N; a.K = model.K; a.node_types = node_types; a.perm = perm.p; a.type_seg = type_seg.p;
-        if (first) {
+        if (which == 2) {
+            a.num_out = model.num_LM; a.num_mono = poly_fixed ? model.num_canonm : model.num_monom;
+            a.prog = progm.p; a.prog_off = progm_off.p; a.prog_cnt = progm_cnt.p; a.mono_off = monom_off.p; a.coef = coefMm.p;
+            a.A = Am.p; a.M = Mm.p; a.M_adj = Mm_adj.p; a.A_adj = Am_adj.p;
+        } else if (which == 0) {
             a.num_out = model.num_LM; a.num_mono = poly_fixed ? model.num_canon0 : model.num_mono0;
             a.prog = prog0.p; a.prog_off = prog0_off.p; a.prog_cnt = prog0_cnt.p; a.mono_off = mono0_off.p; a.coef = coefM0.p;
             a.A = A0.p; a.M = M0.p; a.M_adj = M0_adj.p; a.A_adj = A0_adj.p;
@@ -510,17 +537,17 @@ public:
         return a;
     }
     template <int NOUT>
-    void launch_poly_fixed(bool first, bool reverse) {
+    void launch_poly_fixed(int first, bool reverse) {
         const long long total = static_cast<long long>(N) * model.K;
         const int grid = static_cast<int>((total + 127) / 128);
         if (reverse) poly_fixed_reverse_kernel<T, NOUT><<<grid, 128, 0, stream>>>(poly_args(first));
         else poly_fixed_forward_kernel<T, NOUT><<<grid, 128, 0, stream>>>(poly_args(first));
         check_launch(reverse ? "poly_fixed_reverse_kernel" : "poly_fixed_forward_kernel");
     }
-    void run_poly(bool first, bool reverse) {
+    void run_poly(int first, bool reverse) {
         if (N == 0) return;
         if (poly_fixed) {
-            const int nout = first ? model.num_LM : 1;
+            const int nout = first != 1 ? model.num_LM : 1;
             if (nout == 1) launch_poly_fixed<1>(first, reverse);
             else if (nout == 4) launch_poly_fixed<4>(first, reverse);
             else launch_poly_fixed<9>(first, reverse);
@@ -548,22 +575,22 @@ public:
     void compute_M0() {   // MACE::compute_M0, mace.cpp:348-370
         if (A0.n != static_cast<size_t>(N) * kNumLm * model.K) throw ArgError("compute_M0: A0 has not been computed");
         M0.resize(static_cast<size_t>(N) * model.num_LM * model.K, stream);
-        run_poly(true, false);
+        run_poly(0, false);
     }
     void reverse_M0() {   // MACE::reverse_M0, mace.cpp:372-395
         if (M0_adj.n != static_cast<size_t>(N) * model.num_LM * model.K) throw ArgError("reverse_M0: M0_adj has not been computed");
         A0_adj.resize(static_cast<size_t>(N) * kNumLm * model.K, stream);
-        run_poly(true, true);
+        run_poly(0, true);
     }
     void compute_M1() {   // MACE::compute_M1, mace.cpp:759-777
         if (A1.n != static_cast<size_t>(N) * kNumLm * model.K) throw ArgError("compute_M1: A1 has not been computed");
         M1.resize(static_cast<size_t>(N) * model.K, stream);
-        run_poly(false, false);
+        run_poly(1, false);
     }
     void reverse_M1() {   // MACE::reverse_M1, mace.cpp:779-794
         if (M1_adj.n != static_cast<size_t>(N) * model.K) throw ArgError("reverse_M1: M1_adj has not been computed");
         A1_adj.resize(static_cast<size_t>(N) * kNumLm * model.K, stream);
-        run_poly(false, true);
+        run_poly(1, true);
     }
 
     void compute_H1() {   // MACE::compute_H1, mace.cpp:397-423
@@ -588,17 +615,24 @@ public:
         run_gemms(list, static_cast<long long>(2 * model.L_max + 1) * N, K);
     }
 
-    TPArgs<T> tp_args() {
+    bool deep() const { return model.num_interactions == 3; }
+    // which: 1 = last block (features of the previous block: Hm in three-block models, else H1), 2 = middle block (H1)
+    TPArgs<T> tp_args(int which) {
         TPArgs<T> a{};
         a.N = N; a.K = model.K;
         a.node_types = node_types; a.first_neigh = first_neigh.p; a.neigh_indices = neigh_indices; a.neigh_types = neigh_types;
-        a.xyz = xyz; a.r = r; a.coef1 = coef1.p; a.sm = sm;
-        a.H = H1.p; a.Phi1 = Phi1.p; a.dPhi1 = dPhi1.p; a.Hmsg = Hmsg.p; a.H_adj = H1_adj.p; a.node_forces = node_forces.p;
+        a.xyz = xyz; a.r = r; a.sm = sm;
+        if (which == 2) {
+            a.coef1 = coefm.p; a.H = H1.p; a.Phi1 = Phim.p; a.dPhi1 = dPhim.p; a.H_adj = H1_adj.p;
+        } else {
+            a.coef1 = coef1.p; a.H = deep() ? Hm.p : H1.p; a.Phi1 = Phi1.p; a.dPhi1 = dPhi1.p; a.H_adj = deep() ? Hm_adj.p : H1_adj.p;
+        }
+        a.Hmsg = Hmsg.p; a.node_forces = node_forces.p;
         a.status = kernel_status.p;
         return a;
     }
     template <int LF>
-    void launch_tp(bool reverse) {
+    void launch_tp(bool reverse, int which) {
         const int block = channel_block();
         if (reverse) {
             // two slots of one spline-row chunk each; staged only if that costs no resident CTA
@@ -614,83 +648,158 @@ public:
             if (staged) {
                 const int grid = persistent_grid(tp_reverse_kernel<T, LF, true>, block, slots, N);
                 waits_in_flight = true;
-                tp_reverse_kernel<T, LF, true><<<grid, block, slots, stream>>>(tp_args());
+                tp_reverse_kernel<T, LF, true><<<grid, block, slots, stream>>>(tp_args(which));
             } else {
                 const int grid = persistent_grid(tp_reverse_kernel<T, LF, false>, block, 0, N);
-                tp_reverse_kernel<T, LF, false><<<grid, block, 0, stream>>>(tp_args());
+                tp_reverse_kernel<T, LF, false><<<grid, block, 0, stream>>>(tp_args(which));
             }
             check_launch("tp_reverse_kernel");
         } else {
             const int grid = persistent_grid(tp_forward_kernel<T, LF>, block, 0, N);
-            tp_forward_kernel<T, LF><<<grid, block, 0, stream>>>(tp_args());
+            tp_forward_kernel<T, LF><<<grid, block, 0, stream>>>(tp_args(which));
             check_launch("tp_forward_kernel");
         }
     }
-    void dispatch_tp(bool reverse) {
+    void dispatch_tp(bool reverse, int which = 1) {
         switch (model.L_max) {
-            case 0: launch_tp<0>(reverse); break;
-            case 1: launch_tp<1>(reverse); break;
-            case 2: launch_tp<2>(reverse); break;
+            case 0: launch_tp<0>(reverse, which); break;
+            case 1: launch_tp<1>(reverse, which); break;
+            case 2: launch_tp<2>(reverse, which); break;
             default: throw UnsupportedError("L_max > 2");
         }
     }
 
-    void compute_Phi1() {   // MACE::compute_Phi1, mace.cpp:453-502
+    // Tensor product of block `which` (1: last, 2: middle). Sender features / their adjoints: see tp_args.
+    void tp_forward_stage(int which, const char* what) {   // MACE::compute_Phi1, mace.cpp:453-502
         const int K = model.K;
-        if (H1.n < static_cast<size_t>(N) * model.num_LM * K) throw ArgError("compute_Phi1: H1 has not been computed");
-        Phi1.resize(static_cast<size_t>(N) * model.tp.Q * K, stream);
+        const DevBuf<T>& feat = (which == 2 || !deep()) ? H1 : Hm;
+        if (feat.n < static_cast<size_t>(N) * model.num_LM * K) throw ArgError(std::string(what) + ": the sender features have not been computed");
+        DevBuf<T>& out = which == 2 ? Phim : Phi1;
+        out.resize(static_cast<size_t>(N) * model.tp.Q * K, stream);
         if (N == 0) return;
-        dispatch_tp(false);
+        dispatch_tp(false, which);
     }
-    void reverse_Phi1(bool zero_dxyz, bool zero_H1_adj) {   // MACE::reverse_Phi1, mace.cpp:504-605
+    void tp_reverse_stage(int which, bool zero_dxyz, bool zero_adj, const char* what) {   // MACE::reverse_Phi1, mace.cpp:504-605
         const int K = model.K, nLM = model.num_LM;
-        if (dPhi1.n != static_cast<size_t>(N) * model.tp.Q * K) throw ArgError("reverse_Phi1: Phi1_adj has not been computed");
-        const size_t hsize = static_cast<size_t>(h1_rows) * nLM * K;
-        if (H1_adj.n != hsize) { H1_adj.resize(hsize, stream, true); }
+        const DevBuf<T>& dphi = which == 2 ? dPhim : dPhi1;
+        if (dphi.n != static_cast<size_t>(N) * model.tp.Q * K) throw ArgError(std::string(what) + ": the adjoint of the tensor product has not been computed");
+        const bool to_h1 = which == 2 || !deep();
+        DevBuf<T>& adj = to_h1 ? H1_adj : Hm_adj;
+        const int rows = to_h1 ? h1_rows : hm_rows;
+        const size_t hsize = static_cast<size_t>(rows) * nLM * K;
+        if (adj.n != hsize) { adj.resize(hsize, stream, true); }
         if (zero_dxyz) node_forces.zero(stream);
-        if (zero_H1_adj) H1_adj.zero(stream);
+        if (zero_adj) adj.zero(stream);
         if (N == 0) return;
         if (sizeof(T) == 4) {      // float32: messages are accumulated in place by the kernel
-            dispatch_tp(true);
+            dispatch_tp(true, which);
             return;
         }
         Hmsg.resize(static_cast<size_t>(E) * nLM * K, stream);
-        dispatch_tp(true);
-        ensure_sender_lists(std::max(h1_rows, N));
+        dispatch_tp(true, which);
+        ensure_sender_lists(std::max(rows, N));
         if (E > 0) {
             const int width = nLM * K;
             const int block = std::min(256, ((width + 31) / 32) * 32);
-            const int grid = std::min(h1_rows, num_sms * 16);
-            sender_gather_kernel<T><<<grid, block, 0, stream>>>(h1_rows, width, in_ptr.p, in_edge.p, Hmsg.p, H1_adj.p);
+            const int grid = std::min(rows, num_sms * 16);
+            sender_gather_kernel<T><<<grid, block, 0, stream>>>(rows, width, in_ptr.p, in_edge.p, Hmsg.p, adj.p);
             check_launch("sender_gather_kernel");
         }
     }
+    void compute_Phi1() { tp_forward_stage(1, "compute_Phi1"); }
+    void reverse_Phi1(bool zero_dxyz, bool zero_H1_adj) { tp_reverse_stage(1, zero_dxyz, zero_H1_adj, "reverse_Phi1"); }
 
-    void compute_A1() {   // MACE::compute_A1, mace.cpp:607-642
+    void linear_A_forward(int which, const char* what) {   // MACE::compute_A1, mace.cpp:607-642
         const int K = model.K;
         const TPTable& tp = model.tp;
-        if (Phi1.n != static_cast<size_t>(N) * tp.Q * K) throw ArgError("compute_A1: Phi1 has not been computed");
-        A1.resize(static_cast<size_t>(N) * kNumLm * K, stream);
+        DevBuf<T>& phi = which == 2 ? Phim : Phi1;
+        DevBuf<T>& out = which == 2 ? Am : A1;
+        const T* w = which == 2 ? Am_w.p : A1_w.p;
+        const auto& off = which == 2 ? model.Am_w_off : model.A1_w_off;
+        if (phi.n != static_cast<size_t>(N) * tp.Q * K) throw ArgError(std::string(what) + ": the tensor product has not been computed");
+        out.resize(static_cast<size_t>(N) * kNumLm * K, stream);
         std::vector<GemmProblem<T>> list;
         for (int l = 0; l <= kLmaxSH; ++l)
-            list.push_back(problem(Phi1.p, A1.p, A1_w.p + model.A1_w_off[l], false, 0, 2 * l + 1, 1LL * tp.Q * K, 1LL * tp.lme_off[l] * K,
+            list.push_back(problem(phi.p, out.p, w + off[l], false, 0, 2 * l + 1, 1LL * tp.Q * K, 1LL * tp.lme_off[l] * K,
                                    1LL * tp.n_e[l] * K, 16LL * K, 1LL * l * l * K, K, tp.n_e[l] * K, K, K, false, false));
         run_gemms(list, 7LL * N, K);
     }
-    void reverse_A1() {   // MACE::reverse_A1, mace.cpp:644-679
+    void linear_A_reverse(int which, const char* what) {   // MACE::reverse_A1, mace.cpp:644-679
         const int K = model.K;
         const TPTable& tp = model.tp;
-        if (A1_adj.n != static_cast<size_t>(N) * kNumLm * K) throw ArgError("reverse_A1: A1_adj has not been computed");
-        dPhi1.resize(static_cast<size_t>(N) * tp.Q * K, stream);
+        DevBuf<T>& adj = which == 2 ? Am_adj : A1_adj;
+        DevBuf<T>& dphi = which == 2 ? dPhim : dPhi1;
+        const T* w = which == 2 ? Am_w.p : A1_w.p;
+        const auto& off = which == 2 ? model.Am_w_off : model.A1_w_off;
+        if (adj.n != static_cast<size_t>(N) * kNumLm * K) throw ArgError(std::string(what) + ": the adjoint of A has not been computed");
+        dphi.resize(static_cast<size_t>(N) * tp.Q * K, stream);
         std::vector<GemmProblem<T>> list;
         int max_cols = K;
         for (int l = 0; l <= kLmaxSH; ++l) {
-            list.push_back(problem(A1_adj.p, dPhi1.p, A1_w.p + model.A1_w_off[l], false, 0, 2 * l + 1, 16LL * K, 1LL * l * l * K, K,
+            list.push_back(problem(adj.p, dphi.p, w + off[l], false, 0, 2 * l + 1, 16LL * K, 1LL * l * l * K, K,
                                    1LL * tp.Q * K, 1LL * tp.lme_off[l] * K, 1LL * tp.n_e[l] * K, K, tp.n_e[l] * K, K, true, false));
             max_cols = std::max(max_cols, tp.n_e[l] * K);
         }
         run_gemms(list, 7LL * N, max_cols);
     }
+    void compute_A1() { linear_A_forward(1, "compute_A1"); }
+    void reverse_A1() { linear_A_reverse(1, "reverse_A1"); }
+
+    // ---- middle interaction block (three-block models): Phim -> Am -> Mm -> Hm, the generalisation of the last block's
+    // stages to a contraction with every (L, M) (as compute_M0) and features Hm = Mm . W_L + H1 . W_res[type][L]
+    void require_deep(const char* what) const {
+        if (!deep()) throw ArgError(std::string(what) + ": the model has two interaction blocks");
+    }
+    void compute_Phim() { require_deep("compute_Phim"); tp_forward_stage(2, "compute_Phim"); }
+    void compute_Am() { require_deep("compute_Am"); linear_A_forward(2, "compute_Am"); }
+    void compute_Mm() {
+        require_deep("compute_Mm");
+        if (Am.n != static_cast<size_t>(N) * kNumLm * model.K) throw ArgError("compute_Mm: Am has not been computed");
+        Mm.resize(static_cast<size_t>(N) * model.num_LM * model.K, stream);
+        run_poly(2, false);
+    }
+    void compute_Hm() {
+        require_deep("compute_Hm");
+        const int K = model.K, nLM = model.num_LM;
+        if (Mm.n != static_cast<size_t>(N) * nLM * K) throw ArgError("compute_Hm: Mm has not been computed");
+        Hm.resize(static_cast<size_t>(N) * nLM * K, stream);
+        hm_rows = N;
+        std::vector<GemmProblem<T>> list;
+        for (int l = 0; l <= model.L_max; ++l)
+            list.push_back(problem(Mm.p, Hm.p, Hm_w.p + static_cast<size_t>(l) * K * K, false, 0, 2 * l + 1, 1LL * nLM * K,
+                                   1LL * l * l * K, K, 1LL * nLM * K, 1LL * l * l * K, K, K, K, K, false, false));
+        run_gemms(list, static_cast<long long>(2 * model.L_max + 1) * N, K);
+        list.clear();
+        for (int a = 0; a < model.num_elements; ++a)
+            for (int l = 0; l <= model.L_max; ++l)
+                list.push_back(problem(H1.p, Hm.p, Hm_res.p + (static_cast<size_t>(a) * (model.L_max + 1) + l) * K * K, true, a, 2 * l + 1,
+                                       1LL * nLM * K, 1LL * l * l * K, K, 1LL * nLM * K, 1LL * l * l * K, K, K, K, K, false, true));
+        run_gemms(list, static_cast<long long>(2 * model.L_max + 1) * N, K);
+    }
+    void reverse_Hm() {
+        require_deep("reverse_Hm");
+        const int K = model.K, nLM = model.num_LM;
+        if (Hm_adj.n < static_cast<size_t>(N) * nLM * K) throw ArgError("reverse_Hm: Hm_adj has not been computed");
+        if (H1_adj.n < static_cast<size_t>(N) * nLM * K) throw ArgError("reverse_Hm: H1_adj has not been computed");
+        Mm_adj.resize(static_cast<size_t>(N) * nLM * K, stream);
+        std::vector<GemmProblem<T>> list;
+        for (int l = 0; l <= model.L_max; ++l)
+            list.push_back(problem(Hm_adj.p, Mm_adj.p, Hm_w.p + static_cast<size_t>(l) * K * K, false, 0, 2 * l + 1, 1LL * nLM * K,
+                                   1LL * l * l * K, K, 1LL * nLM * K, 1LL * l * l * K, K, K, K, K, true, false));
+        for (int a = 0; a < model.num_elements; ++a)
+            for (int l = 0; l <= model.L_max; ++l)
+                list.push_back(problem(Hm_adj.p, H1_adj.p, Hm_res.p + (static_cast<size_t>(a) * (model.L_max + 1) + l) * K * K, true, a,
+                                       2 * l + 1, 1LL * nLM * K, 1LL * l * l * K, K, 1LL * nLM * K, 1LL * l * l * K, K, K, K, K, true, true));
+        run_gemms(list, static_cast<long long>(2 * model.L_max + 1) * N, K);
+    }
+    void reverse_Mm() {
+        require_deep("reverse_Mm");
+        if (Mm_adj.n != static_cast<size_t>(N) * model.num_LM * model.K) throw ArgError("reverse_Mm: Mm_adj has not been computed");
+        Am_adj.resize(static_cast<size_t>(N) * kNumLm * model.K, stream);
+        run_poly(2, true);
+    }
+    void reverse_Am() { require_deep("reverse_Am"); linear_A_reverse(2, "reverse_Am"); }
+    void reverse_Phim(bool zero_dxyz, bool zero_H1_adj) { require_deep("reverse_Phim"); tp_reverse_stage(2, zero_dxyz, zero_H1_adj, "reverse_Phim"); }
 
     void compute_H2() {   // MACE::compute_H2, mace.cpp:796-832
         const int K = model.K, nLM = model.num_LM;
@@ -698,8 +807,8 @@ public:
         H2.resize(static_cast<size_t>(N) * K, stream);
         std::vector<GemmProblem<T>> list;
         for (int a = 0; a < model.num_elements; ++a)
-            list.push_back(problem(H1.p, H2.p, H2_w_H1.p + static_cast<size_t>(a) * K * K, true, a, 1, 1LL * nLM * K, 0, 0, K, 0, 0, K, K, K,
-                                   false, false));
+            list.push_back(problem(deep() ? Hm.p : H1.p, H2.p, H2_w_H1.p + static_cast<size_t>(a) * K * K, true, a, 1, 1LL * nLM * K, 0, 0, K, 0, 0, K, K, K,
+                                   false, false));   // residual of the previous block's scalar features
         run_gemms(list, N, K);
         list.clear();
         list.push_back(problem(M1.p, H2.p, H2_w_M1.p, false, 0, 1, K, 0, 0, K, 0, 0, K, K, K, false, true));
@@ -708,13 +817,14 @@ public:
     void reverse_H2(bool zero_H1_adj) {   // MACE::reverse_H2, mace.cpp:834-874
         const int K = model.K, nLM = model.num_LM;
         if (H2_adj.n != static_cast<size_t>(N) * K) throw ArgError("reverse_H2: H2_adj has not been computed");
-        const size_t hsize = static_cast<size_t>(h1_rows) * nLM * K;
-        if (H1_adj.n != hsize) H1_adj.resize(hsize, stream, true);
+        DevBuf<T>& prev_adj = deep() ? Hm_adj : H1_adj;
+        const size_t hsize = static_cast<size_t>(deep() ? hm_rows : h1_rows) * nLM * K;
+        if (prev_adj.n != hsize) prev_adj.resize(hsize, stream, true);
         M1_adj.resize(static_cast<size_t>(N) * K, stream);
-        if (zero_H1_adj) H1_adj.zero(stream);
+        if (zero_H1_adj) prev_adj.zero(stream);
         std::vector<GemmProblem<T>> list;
         for (int a = 0; a < model.num_elements; ++a)
-            list.push_back(problem(H2_adj.p, H1_adj.p, H2_w_H1.p + static_cast<size_t>(a) * K * K, true, a, 1, K, 0, 0, 1LL * nLM * K, 0, 0, K, K,
+            list.push_back(problem(H2_adj.p, prev_adj.p, H2_w_H1.p + static_cast<size_t>(a) * K * K, true, a, 1, K, 0, 0, 1LL * nLM * K, 0, 0, K, K,
                                    K, true, true));
         list.push_back(problem(H2_adj.p, M1_adj.p, H2_w_M1.p, false, 0, 1, K, 0, 0, K, 0, 0, K, K, K, true, false));
         run_gemms(list, N, K);
@@ -726,11 +836,16 @@ public:
         H1_adj.resize(static_cast<size_t>(h1_rows) * nLM * K, stream);
         H1_adj.zero(stream);
         H2_adj.resize(static_cast<size_t>(N) * K, stream);
+        if (deep()) {
+            Hm_adj.resize(static_cast<size_t>(hm_rows) * nLM * K, stream);
+            Hm_adj.zero(stream);
+        }
         if (N == 0) return;
         ReadoutArgs<T> a{};
         a.N = N; a.K = K; a.nLM = nLM; a.node_types = node_types; a.E0 = E0.p;
         a.ro1 = ro1.p; a.W1 = ro2_w1.p; a.w2 = ro2_w2.p; a.scale = static_cast<T>(model.ro2_scale);
         a.H1 = H1.p; a.H2 = H2.p; a.node_energies = node_energies.p; a.H1_adj = H1_adj.p; a.H2_adj = H2_adj.p;
+        if (deep()) { a.ro_m = ro_m.p; a.Hm = Hm.p; a.Hm_adj = Hm_adj.p; }
         const int block = 128;
         const int grid = std::min((N + 3) / 4, num_sms * 16);
         readout_kernel<T><<<grid, block, 0, stream>>>(a);
@@ -761,6 +876,15 @@ public:
         else if (s == "reverse_H1") reverse_H1();
         else if (s == "reverse_M0") reverse_M0();
         else if (s == "reverse_A0") reverse_A0();
+        else if (s == "compute_Rm") return;   // fused, like compute_R1
+        else if (s == "compute_Phim") compute_Phim();
+        else if (s == "compute_Am") compute_Am();
+        else if (s == "compute_Mm") compute_Mm();
+        else if (s == "compute_Hm") compute_Hm();
+        else if (s == "reverse_Hm") reverse_Hm();
+        else if (s == "reverse_Mm") reverse_Mm();
+        else if (s == "reverse_Am") reverse_Am();
+        else if (s == "reverse_Phim") reverse_Phim(zero_dxyz, zero_H1_adj);
         else throw ArgError("unknown stage '" + s + "'");
     }
 
@@ -798,13 +922,15 @@ public:
     // Grow H1 / H1_adj to `rows` feature rows keeping the existing rows (ghost rows are appended by the caller).
     void resize_rows(const std::string& name, int rows) override {
         SMX_CUDA(cudaSetDevice(device));
-        if (name != "H1" && name != "H1_adj") throw ArgError("resize_rows: only H1 and H1_adj have ghost rows");
+        if (name != "H1" && name != "H1_adj" && name != "Hm" && name != "Hm_adj")
+            throw ArgError("resize_rows: only H1, Hm and their adjoints have ghost rows");
         if (rows < N) throw ArgError("resize_rows: fewer rows than nodes");
-        DevBuf<T>& b = name == "H1" ? H1 : H1_adj;
+        DevBuf<T>& b = name == "H1" ? H1 : name == "H1_adj" ? H1_adj : name == "Hm" ? Hm : Hm_adj;
         const size_t old = b.n, want = static_cast<size_t>(rows) * model.num_LM * model.K;
         b.resize(want, stream, true);
         if (want > old) SMX_CUDA(cudaMemsetAsync(b.p + old, 0, (want - old) * sizeof(T), stream));
         if (name == "H1") h1_rows = rows;
+        if (name == "Hm") hm_rows = rows;
     }
     void* device_ptr(const std::string& name, long* count, int* elem_bytes) override {
         Field f = field(name);
@@ -862,12 +988,17 @@ public:
     void compute_all() override {   // order of MACE::compute_node_energies_forces, mace.cpp:17-64
         require_edges();
         SMX_CUDA(cudaSetDevice(device));
-        static const char* names[] = {"compute_A0", "compute_M0", "compute_H1", "compute_Phi1", "compute_A1", "compute_M1",
-                                      "compute_H2", "compute_readouts", "reverse_H2", "reverse_M1", "reverse_A1", "reverse_Phi1",
-                                      "reverse_H1", "reverse_M0", "reverse_A0"};
-        constexpr int kStages = 15;
-        if (profiling && stage_events.size() < kStages + 1) {
-            while (stage_events.size() < kStages + 1) {
+        static const char* names2[] = {"compute_A0", "compute_M0", "compute_H1", "compute_Phi1", "compute_A1", "compute_M1",
+                                       "compute_H2", "compute_readouts", "reverse_H2", "reverse_M1", "reverse_A1", "reverse_Phi1",
+                                       "reverse_H1", "reverse_M0", "reverse_A0"};
+        static const char* names3[] = {"compute_A0", "compute_M0", "compute_H1", "compute_Phim", "compute_Am", "compute_Mm", "compute_Hm",
+                                       "compute_Phi1", "compute_A1", "compute_M1", "compute_H2", "compute_readouts", "reverse_H2",
+                                       "reverse_M1", "reverse_A1", "reverse_Phi1", "reverse_Hm", "reverse_Mm", "reverse_Am", "reverse_Phim",
+                                       "reverse_H1", "reverse_M0", "reverse_A0"};
+        const char* const* names = deep() ? names3 : names2;
+        const int kStages = deep() ? 23 : 15;
+        if (profiling && static_cast<int>(stage_events.size()) < kStages + 1) {
+            while (static_cast<int>(stage_events.size()) < kStages + 1) {
                 cudaEvent_t e;
                 SMX_CUDA(cudaEventCreate(&e));
                 stage_events.push_back(e);
@@ -878,9 +1009,11 @@ public:
         SMX_CUDA(cudaEventRecord(ev0, stream));
         compute_ZBL();
         tick(); compute_A0(); compute_A_scaled(true); tick(); compute_M0(); tick(); compute_H1();
+        if (deep()) { tick(); compute_Phim(); tick(); compute_Am(); tick(); compute_Mm(); tick(); compute_Hm(); }
         tick(); compute_Phi1(); tick(); compute_A1(); compute_A_scaled(false); tick(); compute_M1(); tick(); compute_H2();
         tick(); compute_readouts();
         tick(); reverse_H2(false); tick(); reverse_M1(); reverse_A_scaled(false, false); tick(); reverse_A1(); tick(); reverse_Phi1(false, false);
+        if (deep()) { tick(); reverse_Hm(); tick(); reverse_Mm(); tick(); reverse_Am(); tick(); reverse_Phim(false, false); }
         tick(); reverse_H1(); tick(); reverse_M0(); reverse_A_scaled(true, false); tick(); reverse_A0(); tick();
         SMX_CUDA(cudaEventRecord(ev1, stream));
         check_kernel_status();
@@ -917,6 +1050,14 @@ public:
         else if (s == "M1_adj") f.t = &M1_adj;
         else if (s == "H2") f.t = &H2;
         else if (s == "H2_adj") f.t = &H2_adj;
+        else if (s == "Phim") f.t = &Phim;
+        else if (s == "Phim_adj") f.t = &dPhim;
+        else if (s == "Am") f.t = &Am;
+        else if (s == "Am_adj") f.t = &Am_adj;
+        else if (s == "Mm") f.t = &Mm;
+        else if (s == "Mm_adj") f.t = &Mm_adj;
+        else if (s == "Hm") f.t = &Hm;
+        else if (s == "Hm_adj") f.t = &Hm_adj;
         else throw ArgError("unknown array '" + s + "'");
         return f;
     }
@@ -964,11 +1105,12 @@ public:
                 check_launch("convert_kernel");
             }
         }
-        if (name == "H1" || name == "H1_adj") {
+        if (name == "H1" || name == "H1_adj" || name == "Hm" || name == "Hm_adj") {
             const size_t row = static_cast<size_t>(model.num_LM) * model.K;
-            if (static_cast<size_t>(n) % row != 0) throw ArgError("set_array: H1 length is not a multiple of num_LM * num_channels");
+            if (static_cast<size_t>(n) % row != 0) throw ArgError("set_array: feature array length is not a multiple of num_LM * num_channels");
             const int rows = static_cast<int>(static_cast<size_t>(n) / row);
             if (name == "H1") h1_rows = rows;
+            if (name == "Hm") hm_rows = rows;
         }
         SMX_CUDA(cudaStreamSynchronize(stream));
     }
@@ -1159,6 +1301,7 @@ int smx_info(smx_handle h, smx_model_info* info) {
         info->num_elements = m.num_elements; info->num_channels = m.K; info->r_cut = m.r_cut;
         info->l_max = m.l_max; info->num_lm = m.num_lm; info->L_max = m.L_max; info->num_LM = m.num_LM;
         info->num_paths = m.tp.P; info->num_lelm1lm2 = m.tp.T; info->num_lme = m.tp.Q;
+        info->num_interactions = m.num_interactions;
         info->has_zbl = m.has_zbl ? 1 : 0; info->precision = e.precision; info->device = e.device;
     });
 }

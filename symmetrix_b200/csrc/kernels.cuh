@@ -1246,6 +1246,8 @@ struct ReadoutArgs {
     const T* H1; const T* H2;
     double* node_energies;
     T* H1_adj; T* H2_adj;
+    // three-block models: linear readout of the middle block's scalar features (null otherwise)
+    const T* ro_m; const T* Hm; T* Hm_adj;
 };
 
 template <typename T>
@@ -1263,6 +1265,10 @@ __global__ void readout_kernel(const ReadoutArgs<T> a) {
         for (int k = lane; k < a.K; k += 32) {
             lin += a.ro1[k] * h1[k];
             a.H1_adj[static_cast<size_t>(i) * a.nLM * a.K + k] = a.ro1[k];
+            if (a.ro_m) {
+                lin += a.ro_m[k] * a.Hm[static_cast<size_t>(i) * a.nLM * a.K + k];
+                a.Hm_adj[static_cast<size_t>(i) * a.nLM * a.K + k] = a.ro_m[k];
+            }
             const T v = h2[k];
 #pragma unroll
             for (int h = 0; h < 16; ++h) z[h] += a.W1[h * a.K + k] * v;

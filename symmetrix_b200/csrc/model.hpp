@@ -144,6 +144,21 @@ struct HostModel {
     bool poly_canonical = true;
     int num_canon0 = 0, num_canon1 = 0;
     std::vector<double> coef_M0_canon, coef_M1_canon;
+
+    // Optional middle interaction block (file key "num_interactions": 3; an extension of the reference's two-block
+    // format, whose exporter stops at two blocks, extract_mace_data.py:70-71). Same tensor-product tables as the last
+    // block, a contraction that keeps every (L, M) like M0, a per-L linear plus a per-element, per-L residual of H1.
+    int num_interactions = 2;
+    std::vector<double> coefm;             // radial splines, as coef1
+    std::vector<double> Am_w;              // as A1_w
+    std::array<long, kLmaxSH + 2> Am_w_off{};
+    std::vector<PolyProgram> progm;        // as prog0
+    std::vector<int> mono_offm;
+    int num_monom = 0, num_canonm = 0;
+    std::vector<double> coef_Mm, coef_Mm_canon;
+    std::vector<double> Hm_w;              // [L_max+1][K][K]
+    std::vector<double> Hm_res;            // [E][L_max+1][K][K]
+    std::vector<double> ro_m;              // [K]
 };
 
 namespace detail {
@@ -373,15 +388,24 @@ inline HostModel load_model_file(const std::string& filename) {
     for (int p = 0; p < P; ++p)
         for (int k = 0; k < K; ++k) fn_map[p * K + k] = m.path_file_to_canon[p] * K + k;
     load_splines("radial_spline_values_1", "radial_spline_derivs_1", m.F1, fn_map, m.coef1);
-    {   // fold the per-path coupling scale into the radial functions of that path
+    auto fold_path_scale = [&](std::vector<double>& coef) {   // per-path coupling scale into the radial functions of that path
         const size_t rows = static_cast<size_t>(m.num_pairs) * m.num_bins;
         for (size_t row = 0; row < rows; ++row)
             for (int c = 0; c < m.tp.P; ++c) {
                 const double sc = m.path_scale[c];
                 if (sc == 1.0) continue;
-                double* o = m.coef1.data() + (row * m.F1 + static_cast<size_t>(c) * K) * 4;
+                double* o = coef.data() + (row * m.F1 + static_cast<size_t>(c) * K) * 4;
                 for (int q = 0; q < 4 * K; ++q) o[q] *= sc;
             }
+    };
+    fold_path_scale(m.coef1);
+    if (const JsonValue* ni = file.find("num_interactions")) m.num_interactions = ni->as_int();
+    if (m.num_interactions != 2 && m.num_interactions != 3) throw UnsupportedError("num_interactions must be 2 or 3");
+    if (m.num_interactions == 3) {
+        if (m.has_zbl || m.A0_scaled || m.A1_scaled)
+            throw UnsupportedError("ZBL / density normalisation are not defined for models with three interaction blocks");
+        load_splines("radial_spline_values_m", "radial_spline_derivs_m", m.F1, fn_map, m.coefm);
+        fold_path_scale(m.coefm);
     }
 
     // ---- dense weights
@@ -391,26 +415,33 @@ inline HostModel load_model_file(const std::string& filename) {
     m.H0_w = file.at("H0_weights").flat();  expect(m.H0_w, size_t(E) * K, "H0_weights");
     m.A0_w = file.at("A0_weights").flat();  expect(m.A0_w, size_t(E) * (m.l_max + 1) * K * K, "A0_weights");
     m.H1_w = file.at("H1_weights").flat();  expect(m.H1_w, size_t(m.L_max + 1) * K * K, "H1_weights");
-    {
-        const JsonValue& a1 = file.at("A1_weights");
-        if (static_cast<int>(a1.size()) != m.l_max + 1) throw ModelError("model file: A1_weights needs one matrix per l");
+    auto load_A_weights = [&](const char* key, std::vector<double>& out, std::array<long, kLmaxSH + 2>& offs) {
+        const JsonValue& a1 = file.at(key);
+        if (static_cast<int>(a1.size()) != m.l_max + 1) throw ModelError(std::string("model file: ") + key + " needs one matrix per l");
         long off = 0;
         for (int l = 0; l <= m.l_max; ++l) {
             std::vector<double> w = a1.arr.empty() ? std::vector<double>() : a1.arr[l].flat();
             const int ne = m.tp.n_e[l];
-            expect(w, size_t(ne) * K * K, "A1_weights[l]");
-            m.A1_w_off[l] = off;
-            m.A1_w.resize(off + long(ne) * K * K);
+            expect(w, size_t(ne) * K * K, key);
+            offs[l] = off;
+            out.resize(off + long(ne) * K * K);
             // permute the e-blocks of rows from file order to canonical order
             for (int p = 0; p < P; ++p) {
                 if (pl[p] != l) continue;
                 const int ec = m.tp.e[m.path_file_to_canon[p]];
                 std::copy(w.begin() + long(file_e[p]) * K * K, w.begin() + long(file_e[p] + 1) * K * K,
-                          m.A1_w.begin() + off + long(ec) * K * K);
+                          out.begin() + off + long(ec) * K * K);
             }
             off += long(ne) * K * K;
         }
-        m.A1_w_off[m.l_max + 1] = off;
+        offs[m.l_max + 1] = off;
+    };
+    load_A_weights("A1_weights", m.A1_w, m.A1_w_off);
+    if (m.num_interactions == 3) {
+        load_A_weights("Am_weights", m.Am_w, m.Am_w_off);
+        m.Hm_w = file.at("Hm_weights").flat();            expect(m.Hm_w, size_t(m.L_max + 1) * K * K, "Hm_weights");
+        m.Hm_res = file.at("Hm_weights_for_H1").flat();   expect(m.Hm_res, size_t(E) * (m.L_max + 1) * K * K, "Hm_weights_for_H1");
+        m.ro_m = file.at("readout_m_weights").flat();     expect(m.ro_m, K, "readout_m_weights");
     }
     m.H2_w_H1 = file.at("H2_weights_for_H1").flat();  expect(m.H2_w_H1, size_t(E) * K * K, "H2_weights_for_H1");
     m.H2_w_M1 = file.at("H2_weights_for_M1").flat();  expect(m.H2_w_M1, size_t(K) * K, "H2_weights_for_M1");
@@ -420,19 +451,21 @@ inline HostModel load_model_file(const std::string& filename) {
     m.ro2_scale = file.at("readout_2_scale_factor").as_double();
 
     // ---- symmetric contractions
-    {
-        const JsonValue& monos = file.at("M0_monomials");
-        const JsonValue& weights = file.at("M0_weights");
-        m.mono_off0.assign(m.num_LM + 1, 0);
+    auto load_full_contraction = [&](const char* mono_key, const char* weight_key, std::vector<PolyProgram>& prog,
+                                     std::vector<int>& mono_off, int& num_mono, std::vector<double>& coef, int& num_canon,
+                                     std::vector<double>& coef_canon) {
+        const JsonValue& monos = file.at(mono_key);
+        const JsonValue& weights = file.at(weight_key);
+        mono_off.assign(m.num_LM + 1, 0);
         for (int lm = 0; lm < m.num_LM; ++lm) {
             auto lists = detail::int_lists(monos.at(std::to_string(lm)));
-            m.prog0.push_back(compile_polynomial(lists, m.num_lm));
-            m.mono_off0[lm + 1] = m.mono_off0[lm] + static_cast<int>(lists.size());
+            prog.push_back(compile_polynomial(lists, m.num_lm));
+            mono_off[lm + 1] = mono_off[lm] + static_cast<int>(lists.size());
         }
-        m.num_mono0 = m.mono_off0[m.num_LM];
-        m.coef_M0.assign(size_t(E) * m.num_mono0 * K, 0.0);
-        m.num_canon0 = kCanonPolyOffset[m.num_LM];
-        m.coef_M0_canon.assign(size_t(E) * m.num_canon0 * K, 0.0);
+        num_mono = mono_off[m.num_LM];
+        coef.assign(size_t(E) * num_mono * K, 0.0);
+        num_canon = kCanonPolyOffset[m.num_LM];
+        coef_canon.assign(size_t(E) * num_canon * K, 0.0);
         std::vector<std::vector<int>> slots0;
         for (int lm = 0; lm < m.num_LM; ++lm) {
             slots0.push_back(detail::canonical_slots(detail::int_lists(monos.at(std::to_string(lm))), lm));
@@ -442,19 +475,22 @@ inline HostModel load_model_file(const std::string& filename) {
             const JsonValue& wa = weights.at(std::to_string(a));
             for (int lm = 0; lm < m.num_LM; ++lm) {
                 const JsonValue& wl = wa.at(std::to_string(lm));
-                const int nm = m.mono_off0[lm + 1] - m.mono_off0[lm];
+                const int nm = mono_off[lm + 1] - mono_off[lm];
                 for (int k = 0; k < K; ++k) {
                     const JsonValue& wk = wl.at(std::to_string(k));
-                    if (static_cast<int>(wk.size()) != nm) throw ModelError("M0_weights row length differs from M0_monomials");
+                    if (static_cast<int>(wk.size()) != nm) throw ModelError(std::string(weight_key) + " row length differs from " + mono_key);
                     for (int mu = 0; mu < nm; ++mu) {
-                        m.coef_M0[(size_t(a) * m.num_mono0 + m.mono_off0[lm] + mu) * K + k] = wk.nums[mu];
+                        coef[(size_t(a) * num_mono + mono_off[lm] + mu) * K + k] = wk.nums[mu];
                         if (slots0[lm][mu] >= 0)
-                            m.coef_M0_canon[(size_t(a) * m.num_canon0 + kCanonPolyOffset[lm] + slots0[lm][mu]) * K + k] += wk.nums[mu];
+                            coef_canon[(size_t(a) * num_canon + kCanonPolyOffset[lm] + slots0[lm][mu]) * K + k] += wk.nums[mu];
                     }
                 }
             }
         }
-    }
+    };
+    load_full_contraction("M0_monomials", "M0_weights", m.prog0, m.mono_off0, m.num_mono0, m.coef_M0, m.num_canon0, m.coef_M0_canon);
+    if (m.num_interactions == 3)
+        load_full_contraction("Mm_monomials", "Mm_weights", m.progm, m.mono_offm, m.num_monom, m.coef_Mm, m.num_canonm, m.coef_Mm_canon);
     {
         auto lists = detail::int_lists(file.at("M1_monomials"));
         m.prog1 = compile_polynomial(lists, m.num_lm);

@@ -15,7 +15,9 @@ import numpy as np
 from . import _lib
 
 _ARRAYS = ["node_energies", "node_forces", "A0", "A0_adj", "M0", "M0_adj", "H1", "H1_adj", "Phi1", "Phi1_adj",
-           "A1", "A1_adj", "M1", "M1_adj", "H2", "H2_adj"]
+           "A1", "A1_adj", "M1", "M1_adj", "H2", "H2_adj",
+           # middle interaction block of models with three blocks (no counterpart in the reference)
+           "Phim", "Phim_adj", "Am", "Am_adj", "Mm", "Mm_adj", "Hm", "Hm_adj"]
 
 
 class SymmetrixError(RuntimeError):
@@ -66,6 +68,7 @@ class MACE:
         self.num_elements, self.num_channels, self.r_cut = info.num_elements, info.num_channels, info.r_cut
         self.l_max, self.num_lm, self.L_max, self.num_LM = info.l_max, info.num_lm, info.L_max, info.num_LM
         self.num_lme, self.num_lelm1lm2, self.has_zbl = info.num_lme, info.num_lelm1lm2, bool(info.has_zbl)
+        self.num_interactions = info.num_interactions
         buf = (ctypes.c_int * info.num_elements)()
         self._lib.smx_atomic_numbers(self._h, ctypes.cast(buf, ctypes.c_void_p), info.num_elements)
         self.atomic_numbers = list(buf)
@@ -143,6 +146,19 @@ class MACE:
     def reverse_M0(self, *a): self._stage("reverse_M0")
     def reverse_A0_scaled(self, *a): self._stage("reverse_A0_scaled")
     def reverse_A0(self, *a): self._stage("reverse_A0")
+
+    # Middle interaction block (models whose file says "num_interactions": 3; the reference stops at two blocks)
+    def compute_Rm(self, *a): self._stage("compute_Rm")
+    def compute_Phim(self, *a): self._stage("compute_Phim")
+    def compute_Am(self, *a): self._stage("compute_Am")
+    def compute_Mm(self, *a): self._stage("compute_Mm")
+    def compute_Hm(self, *a): self._stage("compute_Hm")
+    def reverse_Hm(self, *a): self._stage("reverse_Hm")
+    def reverse_Mm(self, *a): self._stage("reverse_Mm")
+    def reverse_Am(self, *a): self._stage("reverse_Am")
+
+    def reverse_Phim(self, *a, zero_dxyz=True, zero_H1_adj=True):
+        self._stage("reverse_Phim", zero_dxyz, zero_H1_adj)
 
     def reverse_H2(self, *a, zero_H1_adj=True):
         self._stage("reverse_H2", True, zero_H1_adj)

@@ -40,6 +40,7 @@ class ModelSpec:
     correlation: int = 3
     zbl: bool = False          # add a ZBL pair repulsion (MACE "pair_repulsion")
     density: bool = False      # density-normalised interaction blocks (A0_scaled / A1_scaled)
+    num_interactions: int = 2  # 3 adds a middle block (full-L output) between the reference's two; file keys "*m*"
     extra: dict = field(default_factory=dict)
 
 
@@ -304,6 +305,31 @@ def generate_model(spec: ModelSpec) -> dict:
 
     out["H1_weights"] = (rng.standard_normal((L_max + 1, k, k)) / math.sqrt(k)).ravel()
 
+    if spec.num_interactions == 3:
+        # Middle interaction block, an extension of the reference's two-block file format (its exporter stops at two,
+        # extract_mace_data.py:70-71). Same tensor-product tables as the last block; the contraction keeps every (L, M)
+        # like M0; the new features are a per-L linear of it plus a per-element, per-L residual of the previous
+        # features; a linear readout on its scalar part.
+        if spec.density or spec.zbl:
+            raise ValueError("density normalisation / ZBL are not defined for the three-block extension")
+        out["num_interactions"] = 3
+        _, vm, dm, _, _ = radial_mlp_tables(spec, rng, len(paths) * k, gain=1.0)
+        out["radial_spline_values_m"] = vm
+        out["radial_spline_derivs_m"] = dm
+        num_e_m = [sum(1 for p in paths if p[0] == l) for l in range(l_max + 1)]
+        out["Am_weights"] = [
+            (rng.standard_normal(num_e_m[l] * k * k) / (math.sqrt(num_e_m[l] * k) * math.sqrt(spec.avg_num_neighbors)))
+            for l in range(l_max + 1)
+        ]
+        mm_w, mm_m, mm_stats = contraction_weights(range(L_max + 1))
+        out["Mm_weights"] = mm_w
+        out["Mm_monomials"] = mm_m
+        out["Hm_weights"] = (rng.standard_normal((L_max + 1, k, k)) / math.sqrt(k)).ravel()
+        out["Hm_weights_for_H1"] = (rng.standard_normal((n_el, L_max + 1, k, k)) / math.sqrt(k)).ravel()
+        out["readout_m_weights"] = 0.25 * rng.standard_normal(k) / math.sqrt(k)
+    elif spec.num_interactions != 2:
+        raise ValueError("num_interactions must be 2 or 3")
+
     out["Phi1_l"] = [p[0] for p in paths]
     out["Phi1_l1"] = [p[1] for p in paths]
     out["Phi1_l2"] = [p[2] for p in paths]
@@ -365,6 +391,11 @@ def expand_contraction_weights(model: dict) -> dict:
         for a, per_lm in model["M0_weights"].items()
     }
     m["M1_weights"] = {a: {kk: row for kk, row in enumerate(np.asarray(arr))} for a, arr in model["M1_weights"].items()}
+    if "Mm_weights" in model:
+        m["Mm_weights"] = {
+            a: {lm: {kk: row for kk, row in enumerate(np.asarray(arr))} for lm, arr in per_lm.items()}
+            for a, per_lm in model["Mm_weights"].items()
+        }
     return m
 
 
@@ -392,6 +423,8 @@ def named_spec(name: str, **over) -> ModelSpec:
                          avg_num_neighbors=50.0, seed=13)
     elif name == "large256":   # configuration 4: 256x0e+256x1o+256x2e
         spec = ModelSpec([1, 6, 7, 8], 256, L_max=2, r_cut=5.0, num_bessel=8, avg_num_neighbors=48.0, seed=14)
+    elif name == "deep256":    # configuration 4 as asked: three interaction blocks (no reference implementation exists)
+        spec = ModelSpec([1, 6, 7, 8], 256, L_max=2, r_cut=5.0, num_bessel=8, avg_num_neighbors=48.0, seed=15, num_interactions=3)
     elif name == "tiny":       # committed golden fixture: a few channels, coarse spline grid
         spec = ModelSpec([1, 8], 8, L_max=1, r_cut=4.0, num_bessel=4, radial_mlp=(8, 8), num_spline_points=24,
                          avg_num_neighbors=30.0, seed=5)

@@ -400,3 +400,60 @@ def test_zbl_and_density_normalised_models(model_file, dtype, flags):
     for stage in ["reverse_H1", "reverse_M0", "reverse_A0_scaled", "reverse_A0"]:
         getattr(ev, stage)()
     check_against(dtype, ev.node_energies, ev.node_forces, e_ref, f_ref)
+
+
+# ------------------------------------------------------------------------------------------------
+# Three interaction blocks (256x0e+256x1o+256x2e family). The reference has no such model, so the checker is the
+# generalised numpy restatement (oracle/mace_numpy_deep.py; parity unpinned by the reference, validated on CPU by
+# finite differences, rotation invariance and reduction to the two-block oracle).
+# ------------------------------------------------------------------------------------------------
+DEEP_FWD = ["A0", "M0", "H1", "Phim", "Am", "Mm", "Hm", "Phi1", "A1", "M1", "H2"]
+DEEP_ADJ = ["H2_adj", "M1_adj", "A1_adj", "Phi1_adj", "Hm_adj", "Mm_adj", "Am_adj", "Phim_adj", "H1_adj", "M0_adj", "A0_adj"]
+
+
+@pytest.mark.parametrize("dtype", ["float64", "float32"])
+@pytest.mark.parametrize("channels", [8, 160])
+def test_three_block_model_matches_the_generalised_oracle(model_file, dtype, channels):
+    from oracle.mace_numpy_deep import DeepMaceOracle
+    path, model, spec = model_file("deep256", num_channels=channels, num_spline_points=32, radial_mlp=(8, 8))
+    s = st.molecular_liquid(5 if channels == 8 else 3, seed=9)
+    nl = st.neighbor_list(s, spec.r_cut)
+    inputs = st.evaluator_inputs(s, nl, model["atomic_numbers"])
+    o = DeepMaceOracle(model)
+    e_ref, f_ref = o.compute_node_energies_forces(inputs)
+    ev = MACE(path, dtype=dtype)
+    assert ev.num_interactions == 3
+    e, f = run(ev, inputs)
+    check_against(dtype, e, f, e_ref, f_ref)
+    rel = 1e-10 if dtype == "float64" else 5e-4
+    names = {"Phi1_adj": "dPhi1", "Phim_adj": "dPhim"}
+    for name in DEEP_FWD + DEEP_ADJ:
+        want = np.asarray(getattr(o, names.get(name, name))).reshape(-1)
+        got = getattr(ev, name)
+        assert got.size == want.size, name
+        assert rel_err(got, want) <= rel, (name, rel_err(got, want))
+
+
+def test_three_block_stage_calls_equal_the_whole_evaluation(model_file):
+    path, model, spec = model_file("deep256", num_channels=8, num_spline_points=32, radial_mlp=(8, 8))
+    s = st.molecular_liquid(4, seed=10)
+    nl = st.neighbor_list(s, spec.r_cut)
+    inputs = st.evaluator_inputs(s, nl, model["atomic_numbers"])
+    ev = MACE(path, dtype="float64")
+    e, f = run(ev, inputs)
+    ev2 = MACE(path, dtype="float64")
+    ev2.begin(int(inputs["num_nodes"]), *[inputs[k] for k in INPUT_KEYS[1:]])
+    for stage in ["compute_A0", "compute_M0", "compute_H1", "compute_Rm", "compute_Phim", "compute_Am", "compute_Mm", "compute_Hm",
+                  "compute_R1", "compute_Phi1", "compute_A1", "compute_M1", "compute_H2", "compute_readouts"]:
+        getattr(ev2, stage)()
+    ev2.reverse_H2(zero_H1_adj=False); ev2.reverse_M1(); ev2.reverse_A1(); ev2.reverse_Phi1(zero_dxyz=False, zero_H1_adj=False)
+    ev2.reverse_Hm(); ev2.reverse_Mm(); ev2.reverse_Am(); ev2.reverse_Phim(zero_dxyz=False, zero_H1_adj=False)
+    ev2.reverse_H1(); ev2.reverse_M0(); ev2.reverse_A0()
+    np.testing.assert_array_equal(ev2.node_energies, e)
+    np.testing.assert_array_equal(ev2.node_forces, f)
+    # a two-block model refuses the middle-block stages
+    tiny_ev = MACE(GOLDEN / "tiny_model.json")
+    case = np.load(GOLDEN / "tiny_case.npz")
+    run(tiny_ev, {k: case[k] for k in INPUT_KEYS})
+    with pytest.raises(SymmetrixError):
+        tiny_ev.compute_Phim()

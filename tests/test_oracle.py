@@ -156,3 +156,61 @@ def test_port_forces_with_zbl_and_density_are_energy_gradients(model_file):
                 inp = dict(inputs); inp["xyz"] = x2.reshape(-1); inp["r"] = np.linalg.norm(x2, axis=1)
                 vals.append(o.compute_node_energies_forces(inp)[0].sum())
             assert abs(-(vals[0] - vals[1]) / (2 * h) - f[e, c]) < 2e-6 * max(1.0, abs(f[e, c]))
+
+
+# ------------------------------------------------------------------------------------------------
+# Three interaction blocks: no reference implementation exists (parity unpinned by the reference); the generalised
+# restatement is checked by finite differences, rotation invariance and reduction to the two-block oracle.
+# ------------------------------------------------------------------------------------------------
+def _deep_case(model_file, channels=6):
+    import copy
+    from oracle.mace_numpy_deep import DeepMaceOracle
+    path, model, spec = model_file("deep256", num_channels=channels, num_spline_points=32, radial_mlp=(8, 8))
+    s = st.molecular_liquid(4, seed=3)
+    nl = st.neighbor_list(s, spec.r_cut)
+    inputs = st.evaluator_inputs(s, nl, model["atomic_numbers"])
+    return copy, DeepMaceOracle, model, spec, s, nl, inputs
+
+
+def test_three_block_oracle_forces_are_energy_gradients(model_file):
+    copy, DeepMaceOracle, model, spec, s, nl, inputs = _deep_case(model_file)
+    e, f = DeepMaceOracle(model).compute_node_energies_forces(inputs)
+    forces, _ = st.atom_forces_and_virial(inputs, nl, f)
+    h = 1e-5
+    for atom, comp in [(0, 0), (5, 2), (11, 1)]:
+        es = []
+        for sign in (+1, -1):
+            s2 = copy.deepcopy(s)
+            s2.positions[atom, comp] += sign * h
+            nl2 = st.neighbor_list(s2, spec.r_cut)
+            es.append(DeepMaceOracle(model).compute_node_energies_forces(st.evaluator_inputs(s2, nl2, model["atomic_numbers"]))[0].sum())
+        assert abs(-(es[0] - es[1]) / (2 * h) - forces[atom, comp]) < 1e-6 * max(1.0, np.abs(forces).max())
+
+
+def test_three_block_oracle_is_rotation_invariant(model_file):
+    copy, DeepMaceOracle, model, spec, s, nl, inputs = _deep_case(model_file)
+    e, f = DeepMaceOracle(model).compute_node_energies_forces(inputs)
+    rot = random_rotation(np.random.default_rng(1))
+    s2 = copy.deepcopy(s)
+    s2.positions = s.positions @ rot.T
+    s2.cell = s.cell @ rot.T
+    nl2 = st.neighbor_list(s2, spec.r_cut)
+    e2, _ = DeepMaceOracle(model).compute_node_energies_forces(st.evaluator_inputs(s2, nl2, model["atomic_numbers"]))
+    assert abs(e2.sum() - e.sum()) < 1e-11 * abs(e.sum())
+
+
+def test_three_block_oracle_reduces_to_the_two_block_oracle(model_file):
+    """With the middle block made the identity (no contraction term, residual = 1, no readout) the features that
+    reach the last block are H1 and the model is the two-block model, which is pinned against the reference."""
+    copy, DeepMaceOracle, model, spec, s, nl, inputs = _deep_case(model_file)
+    K, nL, n_el = spec.num_channels, spec.L_max + 1, len(model["atomic_numbers"])
+    ident = dict(model)
+    ident["Hm_weights"] = np.zeros(nL * K * K)
+    ident["Hm_weights_for_H1"] = np.tile(np.eye(K)[None, None], (n_el, nL, 1, 1)).ravel()
+    ident["readout_m_weights"] = np.zeros(K)
+    e3, f3 = DeepMaceOracle(ident).compute_node_energies_forces(inputs)
+    two = dict(ident)
+    two["num_interactions"] = 2
+    e2, f2 = MaceOracle(two).compute_node_energies_forces(inputs)
+    assert abs(e3.sum() - e2.sum()) < 1e-12 * abs(e2.sum())
+    np.testing.assert_allclose(f3, f2, atol=1e-12)
