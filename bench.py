@@ -41,6 +41,11 @@ WORKLOADS = {
     "water98304": ("organic128_HO", lambda st, z, seed: st.water_box_density(32, 1.0, seed=seed),
                    "configs[2]: 98,304-atom water box (32,768 H2O, 1.0 g/cm^3), organic-liquid model 128x0e+128x1o, r_cut 5 A, "
                    "10-element model exported for the species present (H, O)"),
+    "liquid500k": ("deep256", lambda st, z, seed: st.molecular_liquid(55556, 0.79, seed=seed),
+                   "configs[4]: 500,004-atom liquid (55,556 rigid 9-atom C2H5OH-like molecules, 0.79 g/cm^3), model 256x0e+256x1o+256x2e, "
+                   "three interaction blocks, r_cut 5 A; needs several GPUs (about 300 GB of per-atom arrays in float32)"),
+    "liquid62k": ("deep256", lambda st, z, seed: st.molecular_liquid(6945, 0.79, seed=seed),
+                  "configs[4] per-GPU share: 62,505-atom liquid (6,945 molecules) of the same construction and three-block model"),
     "water192": ("water64", lambda st, z, seed: st.water_box(4, 12.42, seed=seed),
                  "configs[0]: 64 H2O (192 atoms) in a 12.42 A cell, model 64x0e, r_cut 5 A"),
 }
@@ -160,11 +165,11 @@ def roofline_for(stage: str, ms: float, n_atoms: int, n_edges: int, K: int, L_ma
     fwd_flops = n_yh + 2 * nnz + 2 * Q + 6 * P
     rev_flops = nnz + 2 * nnz + 2 * nnz + 2 * T1 + 2 * T2 + 2 * T2 + 2 * P + 11 * P
     s = dtype_bytes
-    if stage == "reverse_Phi1":
+    if stage in ("reverse_Phi1", "reverse_Phim"):
         byts = n_edges * (40 + nLM * K * s + 24) + n_atoms * Q * K * s
         flops = n_edges * K * rev_flops
         kernel = "tp_reverse_kernel"
-    elif stage == "compute_Phi1":
+    elif stage in ("compute_Phi1", "compute_Phim"):
         byts = n_edges * (40 + nLM * K * s) + n_atoms * Q * K * s
         flops = n_edges * K * fwd_flops
         kernel = "tp_forward_kernel"
@@ -352,7 +357,7 @@ def run_decomposed(args, rank, world, local_rank, dist):
         s = WORKLOADS[args.workload][1](st, numbers, 1)
         scaling, label = "strong", f"{args.workload} in {world} slabs along x"
     ev = MACE(path, dtype=args.dtype, device=local_rank)
-    rk = SlabRank(make_slab_plan(s, spec.r_cut, rank, world, mode=args.dd_mode), ev, spec.r_cut, numbers)
+    rk = SlabRank(make_slab_plan(s, spec.r_cut, rank, world, mode=args.dd_mode, num_interactions=ev.num_interactions), ev, spec.r_cut, numbers)
     rk.build_edges()
     flush = torch.empty(256 * 1024 * 1024 // 4, dtype=torch.float32, device=f"cuda:{local_rank}")
 
@@ -588,7 +593,7 @@ def main():
     ap.add_argument("--no-extra", action="store_true")
     args = ap.parse_args()
     if args.dtype is None:   # configs[0] and [1] are quoted in float64 (the reference CPU precision), the larger ones in float32
-        args.dtype = "float32" if args.workload in ("fcc256k", "water98304") else "float64"
+        args.dtype = "float32" if args.workload in ("fcc256k", "water98304", "liquid500k", "liquid62k") else "float64"
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference(args)

@@ -139,7 +139,7 @@ long smx_launch_count(smx_handle h);
  * labels for external tools, e.g. mace_kokkos.cpp:866). smx_timer_start/stop bracket any sequence
  * of calls with CUDA events on the evaluator's stream and return the elapsed device time.
  * With profiling on, smx_compute additionally records one event per stage, and smx_stage_time
- * returns the name and device time of stage `index` (0..14, in execution order) of the last
+ * returns the name and device time of stage `index` (0..14, or 0..22 for a three-block model, in execution order) of the last
  * smx_compute. smx_measure_fma_peak runs a register-only FMA loop and returns the SIMT
  * fused-multiply-add rate in TFLOP/s, the roof of the FMA-bound edge kernels.
  * smx_measure_row_stream runs, over the evaluator's current edge set, a kernel that only reads the

@@ -47,15 +47,17 @@ class SlabPlan:
     recv_rows: dict = field(default_factory=dict)    # peer -> local ghost rows (ascending)
     mode: str = "message_passing"                    # or "recompute"
     n_inner: int = 0                                 # recompute mode: ghosts within r_cut of the slab (they come first)
+    n_within: list = field(default_factory=list)     # recompute mode: ghosts within 1, 2, ... r_cut (cumulative counts)
 
 
 def _ghost_list(frac: np.ndarray, owner: np.ndarray, rank: int, world: int, shell: float, inner: float = None):
     """Ghost images of `rank`: (global id, image shift) of atoms whose image lies in the shell around its slab.
 
     `frac` is the fractional coordinate along the slab axis, `shell` the ghost width in the same units. With `inner`
-    (a narrower width) the images inside that narrower shell come first and their count is returned as well."""
+    (the width of one sub-shell, `shell` being a multiple of it) the images are ordered by sub-shell, nearest first,
+    and the cumulative counts per sub-shell are returned as well."""
     lo, hi = rank / world, (rank + 1) / world
-    out_g, out_n, out_far = [], [], []
+    out_g, out_n, out_cls = [], [], []
     for n in (-1, 0, 1):
         x = frac + n
         sel = ((x >= lo - shell) & (x < lo)) | ((x >= hi) & (x < hi + shell))
@@ -66,19 +68,30 @@ def _ghost_list(frac: np.ndarray, owner: np.ndarray, rank: int, world: int, shel
         out_n.append(np.full(idx.size, n, dtype=np.int64))
         if inner is not None:
             xi = x[idx]
-            out_far.append(~(((xi >= lo - inner) & (xi < lo)) | ((xi >= hi) & (xi < hi + inner))))
+            # sub-shell c holds the images within (c + 1) * inner of the slab, decided with the same comparisons as `sel`
+            num = max(1, int(round(shell / inner)))
+            cls = np.full(idx.size, num - 1, dtype=np.int64)
+            for c in range(num - 2, -1, -1):
+                w = shell * (c + 1) / num if c + 1 < num else shell
+                cls[((xi >= lo - w) & (xi < lo)) | ((xi >= hi) & (xi < hi + w))] = c
+            out_cls.append(cls)
     g = np.concatenate(out_g)
     n = np.concatenate(out_n)
     if inner is None:
         order = np.lexsort((g, n, owner[g]))
         return g[order], n[order]
-    far = np.concatenate(out_far)
-    order = np.lexsort((g, n, owner[g], far))
-    return g[order], n[order], int(np.count_nonzero(~far))
+    cls = np.concatenate(out_cls)
+    order = np.lexsort((g, n, owner[g], cls))
+    num = max(1, int(round(shell / inner)))
+    within = [int(np.count_nonzero(cls <= c)) for c in range(num)]
+    return g[order], n[order], within
 
 
-def make_slab_plan(s: Structure, r_cut: float, rank: int, world: int, axis: int = 0, mode: str = "message_passing") -> SlabPlan:
-    """Plan of rank `rank` of `world` for structure `s` (positions inside the cell, orthogonal slab axis)."""
+def make_slab_plan(s: Structure, r_cut: float, rank: int, world: int, axis: int = 0, mode: str = "message_passing",
+                   num_interactions: int = 2) -> SlabPlan:
+    """Plan of rank `rank` of `world` for structure `s` (positions inside the cell, orthogonal slab axis).
+
+    `num_interactions` (2 or 3) only matters in recompute mode, whose ghost shell is one r_cut per interaction block."""
     if mode not in ("message_passing", "recompute"):
         raise ValueError(f"unknown decomposition mode {mode!r}")
     cell = np.asarray(s.cell, dtype=np.float64)
@@ -97,13 +110,14 @@ def make_slab_plan(s: Structure, r_cut: float, rank: int, world: int, axis: int 
     if world == 1:
         return SlabPlan(rank, world, axis, own.size, 0, own, np.zeros(0, np.int64), np.zeros(0, np.int64), np.zeros(0, np.int64),
                         pos[own].copy(), np.asarray(s.numbers)[own], cell.copy(), tuple(s.pbc))
-    width = r_cut if mode == "message_passing" else 2.0 * r_cut
+    width = r_cut if mode == "message_passing" else float(num_interactions) * r_cut
     if 2.0 * width > length + 1e-9 and mode == "recompute":
         raise ValueError(f"a {width:.2f} A ghost shell on both sides does not fit into a cell of {length:.2f} A")
     shell = width / length
-    n_inner = 0
+    n_inner, within = 0, []
     if mode == "recompute":
-        g, n, n_inner = _ghost_list(frac, owner, rank, world, shell, inner=r_cut / length)
+        g, n, within = _ghost_list(frac, owner, rank, world, shell, inner=r_cut / length)
+        n_inner = within[0]
     else:
         g, n = _ghost_list(frac, owner, rank, world, shell)
     gpos = pos[g].copy()
@@ -117,7 +131,7 @@ def make_slab_plan(s: Structure, r_cut: float, rank: int, world: int, axis: int 
     pbc = tuple(False if a == axis else bool(s.pbc[a]) for a in range(3))
     plan = SlabPlan(rank, world, axis, own.size, g.size, own, g, owner[g], n, positions,
                     np.concatenate([np.asarray(s.numbers)[own], np.asarray(s.numbers)[g]]), lcell, pbc)
-    plan.mode, plan.n_inner = mode, n_inner
+    plan.mode, plan.n_inner, plan.n_within = mode, n_inner, within
     plan.peers = sorted(set(int(q) for q in owner[g]))
     for q in plan.peers:
         plan.recv_rows[q] = own.size + np.nonzero(owner[g] == q)[0]
@@ -142,8 +156,13 @@ class SlabRank:
         self.ev = backend
         self.rows = plan.n_own + plan.n_ghost
         self.recompute = plan.mode == "recompute"
-        # receivers of layer 0: owned atoms, plus (recompute mode) the ghosts within r_cut of the slab
-        self.n_layer0 = plan.n_own + (plan.n_inner if self.recompute else 0)
+        self.blocks = int(getattr(backend, "num_interactions", 2))
+        if self.recompute and len(plan.n_within) != self.blocks:
+            raise ValueError("the plan's ghost shell does not match the model's number of interaction blocks")
+        # receivers of block b: owned atoms, plus (recompute mode) the ghosts within (blocks - 1 - b) r_cut of the slab
+        self.n_block = [plan.n_own + (plan.n_within[self.blocks - 2 - b] if self.recompute and b < self.blocks - 1 else 0)
+                        for b in range(self.blocks)]
+        self.n_layer0 = self.n_block[0]
         self.width = backend.num_LM * backend.num_channels
         zmap = {int(z): t for t, z in enumerate(atomic_numbers)}
         self.types = np.array([zmap[int(z)] for z in plan.numbers], dtype=np.int32)
@@ -186,20 +205,30 @@ class SlabRank:
         for stage in ("compute_A0", "compute_M0", "compute_H1"):
             self._run(stage)
         if self.recompute:
-            self.ev.set_active_nodes(self.plan.n_own)      # layer 1 on the owned atoms; H1 keeps its ghost rows
+            self.ev.set_active_nodes(self.n_block[1])      # next block on fewer receivers; H1 keeps its ghost rows
         else:
             self.ev.resize_rows("H1", self.rows)
+
+    def forward_middle(self):
+        """Middle block of a three-block model (features Hm from H1)."""
+        self._sync_torch()
+        for stage in ("compute_Phim", "compute_Am", "compute_Mm", "compute_Hm"):
+            self._run(stage)
+        if self.recompute:
+            self.ev.set_active_nodes(self.n_block[2])
+        else:
+            self.ev.resize_rows("Hm", self.rows)
 
     def _rows_view(self, name):
         return self.ev.device_view(name).view(-1, self.width)
 
-    def pack_forward(self, peer):
+    def pack_forward(self, peer, name="H1"):
         if not self.shared_stream:
             self.ev.sync()
-        return self._rows_view("H1").index_select(0, self.send_idx[peer]).contiguous()
+        return self._rows_view(name).index_select(0, self.send_idx[peer]).contiguous()
 
-    def unpack_forward(self, peer, buf):
-        self._rows_view("H1").index_copy_(0, self.recv_idx[peer], buf.to(self._rows_view("H1").dtype))
+    def unpack_forward(self, peer, buf, name="H1"):
+        self._rows_view(name).index_copy_(0, self.recv_idx[peer], buf.to(self._rows_view(name).dtype))
 
     def layer1_and_reverse(self):
         self._sync_torch()
@@ -210,14 +239,23 @@ class SlabRank:
         self._run("reverse_A1")
         self._run("reverse_Phi1", False, False)
 
-    def pack_reverse(self, peer):
+    def pack_reverse(self, peer, name="H1_adj"):
         if not self.shared_stream:
             self.ev.sync()
-        return self._rows_view("H1_adj").index_select(0, self.recv_idx[peer]).contiguous()
+        return self._rows_view(name).index_select(0, self.recv_idx[peer]).contiguous()
 
-    def unpack_reverse(self, peer, buf):
-        v = self._rows_view("H1_adj")
+    def unpack_reverse(self, peer, buf, name="H1_adj"):
+        v = self._rows_view(name)
         v.index_add_(0, self.send_idx[peer], buf.to(v.dtype))
+
+    def reverse_middle(self):
+        self._sync_torch()
+        if self.recompute:
+            self.ev.set_active_nodes(self.n_block[1])      # the partial Hm_adj of the ghosts goes through the middle block here
+        self._run("reverse_Hm")
+        self._run("reverse_Mm")
+        self._run("reverse_Am")
+        self._run("reverse_Phim", False, False)
 
     def reverse_layer0(self):
         self._sync_torch()
@@ -282,16 +320,33 @@ def evaluate_decomposed(ranks, dist=None):
     process emulation), or the single local rank when `dist` is an initialised ``torch.distributed``.
     Returns (total energy, virial[6], list of owned-force tensors per local rank).
     """
-    recompute = ranks[0].recompute
+    recompute, deep = ranks[0].recompute, ranks[0].blocks == 3
+
+    def forward_halo(name):
+        if not recompute:
+            _exchange(ranks, lambda r, q: r.recv_idx[q].numel(), lambda r, q: r.pack_forward(q, name),
+                      lambda r, q, b: r.unpack_forward(q, b, name), dist)
+
+    def reverse_halo(name):
+        if not recompute:
+            _exchange(ranks, lambda r, q: r.send_idx[q].numel(), lambda r, q: r.pack_reverse(q, name),
+                      lambda r, q, b: r.unpack_reverse(q, b, name), dist)
+
     for r in ranks:
         r.begin_step()
         r.forward_layer0()
-    if not recompute:
-        _exchange(ranks, lambda r, q: r.recv_idx[q].numel(), lambda r, q: r.pack_forward(q), lambda r, q, b: r.unpack_forward(q, b), dist)
+    forward_halo("H1")
+    if deep:
+        for r in ranks:
+            r.forward_middle()
+        forward_halo("Hm")
     for r in ranks:
         r.layer1_and_reverse()
-    if not recompute:
-        _exchange(ranks, lambda r, q: r.send_idx[q].numel(), lambda r, q: r.pack_reverse(q), lambda r, q, b: r.unpack_reverse(q, b), dist)
+    if deep:
+        reverse_halo("Hm_adj")
+        for r in ranks:
+            r.reverse_middle()
+    reverse_halo("H1_adj")
     for r in ranks:
         r.reverse_layer0()
     _exchange(ranks, lambda r, q: r.send_idx[q].numel(), lambda r, q: r.pack_forces(q), lambda r, q, b: r.unpack_forces(q, b), dist)

@@ -234,7 +234,7 @@ class MACE:
         out = {}
         buf = ctypes.create_string_buffer(64)
         ms = ctypes.c_double(0.0)
-        for idx in range(15):
+        for idx in range(23 if self.num_interactions == 3 else 15):
             if self._lib.smx_stage_time(self._h, idx, buf, 64, ctypes.byref(ms)) != _lib.SMX_OK:
                 break
             out[buf.value.decode()] = ms.value

@@ -4,13 +4,16 @@ without a GPU. Never used by the product."""
 import numpy as np
 import torch
 
-from oracle.mace_numpy import MaceOracle
+from oracle.mace_numpy import MaceOracle, load_model
+from oracle.mace_numpy_deep import DeepMaceOracle
 from symmetrix_b200 import structures as st
 
 
 class OracleBackend:
     def __init__(self, model):
-        self.o = MaceOracle(model)
+        model = load_model(model)
+        self.num_interactions = int(model.get("num_interactions", 2))
+        self.o = DeepMaceOracle(model) if self.num_interactions == 3 else MaceOracle(model)
         self.num_LM = self.o.nLM
         self.num_channels = self.o.K
         self.atomic_numbers = self.o.atomic_numbers
@@ -35,6 +38,8 @@ class OracleBackend:
                        "xyz": inp["xyz"][:3 * e], "r": inp["r"][:e]}
         self.o._edges(self.inputs)
         self.o.compute_Y(); self.o.compute_R0(); self.o.compute_R1()
+        if self.num_interactions == 3:
+            self.o.compute_Rm()
         return e
 
     def restrict_nodes(self, n_own):

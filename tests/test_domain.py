@@ -108,3 +108,37 @@ def test_decomposed_evaluation_over_gloo(world, mode, tmp_path):
         assert abs(float(d["energy"]) - e_ref) < 1e-11 * abs(e_ref)      # every rank holds the reduced total
         np.testing.assert_allclose(d["virial"], v_ref, atol=1e-10)
     np.testing.assert_allclose(forces, f_ref, atol=1e-11)
+
+
+# ------------------------------------------------------------------------------------------------ three blocks
+def _deep_structure(numbers):
+    return st.fcc_box((10, 2, 2), 3.6, numbers, seed=4, jitter=0.15)      # 36 A along the slab axis, r_cut 5 A
+
+
+@pytest.mark.parametrize("mode", ["message_passing", "recompute"])
+@pytest.mark.parametrize("world", [2, 3])
+def test_three_block_model_decomposes_in_both_modes(model_file, world, mode):
+    """Two feature exchanges each way (H1, Hm) in message-passing mode; a 3 r_cut shell with three receiver sets in
+    recompute mode. Checked against the single-domain evaluation of the same (numpy) evaluator."""
+    if mode == "recompute" and world == 3:
+        pytest.skip("a 15 A shell on both sides needs slabs the 36 A box cannot give three ranks")
+    path, model, spec = model_file("deep256", num_channels=4, num_spline_points=24, radial_mlp=(8, 8))
+    s = _deep_structure(model["atomic_numbers"])
+    b0 = OracleBackend(model)
+    nl = st.neighbor_list(s, spec.r_cut)
+    inputs = st.evaluator_inputs(s, nl, b0.atomic_numbers)
+    e, f = b0.o.compute_node_energies_forces(inputs)
+    f_ref, v_ref = st.atom_forces_and_virial(inputs, nl, f)
+    ranks = []
+    for r in range(world):
+        b = OracleBackend(model)
+        rk = SlabRank(make_slab_plan(s, spec.r_cut, r, world, mode=mode, num_interactions=3), b, spec.r_cut, b.atomic_numbers)
+        rk.build_edges()
+        ranks.append(rk)
+    energy, virial, owned = evaluate_decomposed(ranks)
+    forces = np.zeros_like(f_ref)
+    for rk, fo in zip(ranks, owned):
+        forces[rk.plan.own_global] = fo.numpy()
+    assert abs(energy - e.sum()) < 1e-11 * abs(e.sum())
+    np.testing.assert_allclose(forces, f_ref, atol=1e-11)
+    np.testing.assert_allclose(virial, v_ref, atol=1e-10)

@@ -69,3 +69,28 @@ def test_ranks_over_nccl_match_single_domain(model_file, dtype, mode, tmp_path):
     assert abs(float(d["energy"]) - float(d["e_ref"])) <= rel * abs(float(d["e_ref"]))
     assert np.abs(d["forces"] - d["f_ref"]).max() <= fabs
     assert np.abs(d["virial"] - d["v_ref"]).max() <= 100 * rel * max(1.0, np.abs(d["v_ref"]).max())
+
+
+@pytest.mark.parametrize("dtype,mode", [("float64", "message_passing"), ("float64", "recompute"), ("float32", "message_passing")])
+def test_three_block_model_emulated_ranks_match_single_domain(model_file, dtype, mode):
+    """Three interaction blocks: H1 and Hm rows travel forward, Hm_adj and H1_adj back (message passing), or a 3 r_cut
+    shell with three receiver sets (recompute)."""
+    world = 2
+    path, model, spec = model_file("deep256", num_channels=32, num_spline_points=32, radial_mlp=(8, 8))
+    s = st.fcc_box((10, 2, 2), 3.6, model["atomic_numbers"], seed=21, jitter=0.12)      # 36 A along x, r_cut 5 A
+    f_ref, v_ref, e_ref = _single(path, s)
+    ranks = []
+    for r in range(world):
+        ev = MACE(path, dtype=dtype)
+        rk = SlabRank(make_slab_plan(s, spec.r_cut, r, world, mode=mode, num_interactions=3), ev, spec.r_cut, ev.atomic_numbers)
+        rk.build_edges()
+        ranks.append(rk)
+    rel, fabs = (1e-10, 1e-9) if dtype == "float64" else (1e-4, 1e-3)
+    for _ in range(2):
+        energy, virial, owned = evaluate_decomposed(ranks)
+        forces = np.zeros_like(f_ref)
+        for rk, f in zip(ranks, owned):
+            forces[rk.plan.own_global] = f.cpu().numpy()
+        assert abs(energy - e_ref) <= rel * abs(e_ref)
+        assert np.abs(forces - f_ref).max() <= fabs
+        assert np.abs(virial - v_ref).max() <= 100 * rel * max(1.0, np.abs(v_ref).max())
