@@ -59,6 +59,7 @@ public:
 
     // Host mirrors of the public vectors the callers read or swap (mace.hpp:28,104)
     std::vector<double> node_energies, node_forces, H1, H1_adj;
+    std::vector<double> Hm, Hm_adj;   // features of the middle block of a three-block model (exchanged like H1 / H1_adj)
 
     // mace.hpp:29-36 / mace.cpp:17-64
     void compute_node_energies_forces(const int num_nodes, std::span<const int> node_types, std::span<const int> num_neigh,
@@ -105,6 +106,20 @@ public:
     void reverse_A1_scaled(const int, std::span<const int>, std::span<const int>, std::span<const int>, std::span<const double>,
                            std::span<const double>, bool zero_dxyz = true) { stage("reverse_A1_scaled", zero_dxyz, true); }
 
+    // Middle interaction block of a model whose file says "num_interactions": 3. The reference has no counterpart (its
+    // models have exactly two blocks, extract_mace_data.py:70-71); the stages take the place of a second
+    // compute_Phi1 ... compute_H2 group with every (L, M) kept, called between compute_H1 and compute_R1 / compute_Phi1,
+    // and their reverses between reverse_Phi1 and reverse_H1. Arrays: "Phim", "Am", "Mm", "Hm" and "*_adj".
+    void compute_Rm() { stage("compute_Rm"); }
+    void compute_Phim() { stage("compute_Phim"); }
+    void compute_Am() { stage("compute_Am"); }
+    void compute_Mm() { stage("compute_Mm"); }
+    void compute_Hm() { stage("compute_Hm"); }
+    void reverse_Hm() { stage("reverse_Hm"); }
+    void reverse_Mm() { stage("reverse_Mm"); }
+    void reverse_Am() { stage("reverse_Am"); }
+    void reverse_Phim(bool zero_dxyz = true, bool zero_H1_adj = true) { stage("reverse_Phim", zero_dxyz, zero_H1_adj); }
+
     // Device <-> host mirrors: pull("H1") after compute_H1, push("H1") after a forward halo exchange, etc.
     std::vector<double>& pull(const std::string& name) {
         std::vector<double>& v = mirror(name);
@@ -144,6 +159,8 @@ private:
         if (name == "node_forces") return node_forces;
         if (name == "H1") return H1;
         if (name == "H1_adj") return H1_adj;
+        if (name == "Hm") return Hm;
+        if (name == "Hm_adj") return Hm_adj;
         throw std::runtime_error("no host mirror for '" + name + "'");
     }
 };
