@@ -195,6 +195,16 @@ int smx_set_active_nodes(smx_handle h, int num_nodes, long* num_edges);
 int smx_resize_rows(smx_handle h, const char* name, int rows);
 int smx_device_ptr(smx_handle h, const char* name, void** ptr, long* count, int* elem_bytes);
 
+/* Input check. The reference trusts its callers (unchecked spline bin and gather indices, cubic_spline_set.cpp:31-32,
+ * 55-56; mace.cpp:470-480); on a GPU an out-of-range sender index is a memory fault, so callers that cannot vouch for
+ * their arrays call this after smx_begin / smx_build_neighbors and before the first stage. It counts, per kind, the
+ * entries of the current edge set that are out of range or inconsistent: counts[0] node type outside the model,
+ * [1] negative neighbour count, [2] neighbour counts not adding up to the number of edges, [3] sender index outside
+ * [0, feature_rows), [4] sender type outside the model, [5] r not finite, <= 0 or beyond r_cut, [6] r differing from
+ * |xyz| by more than 1e-6 relative. `counts` (7 entries) and `total` may be NULL. Returns SMX_ERR_INVALID_ARGUMENT if
+ * anything was found. Only the given arrays are read. */
+int smx_validate_inputs(smx_handle h, int feature_rows, long* counts, long* total);
+
 /* Energy + virial reduction for callers that cannot let the library allocate device memory: hosts
  * that give the whole GPU to their own memory pool at start-up, jobs with a fixed device-memory
  * budget, and step loops that cannot take the device-wide synchronisation of cudaMalloc / cudaFree.

@@ -20,7 +20,7 @@ EXPORTED_SYMBOLS = [
     "smx_create", "smx_destroy", "smx_last_error", "smx_info", "smx_atomic_numbers", "smx_atomic_energies",
     "smx_compute", "smx_begin", "smx_stage", "smx_get_array", "smx_set_array", "smx_reduce_forces",
     "smx_last_device_ms", "smx_launch_count", "smx_build_neighbors", "smx_get_edges", "smx_compute_current",
-    "smx_timer_start", "smx_timer_stop", "smx_set_profiling", "smx_stage_time", "smx_measure_fma_peak", "smx_measure_row_stream",
+    "smx_timer_start", "smx_timer_stop", "smx_set_profiling", "smx_stage_time", "smx_measure_fma_peak", "smx_measure_row_stream", "smx_validate_inputs",
     "smx_energy_virial_noalloc", "smx_sync", "smx_set_stream", "smx_restrict_nodes", "smx_set_active_nodes", "smx_resize_rows", "smx_device_ptr",
 ]
 
@@ -75,6 +75,7 @@ def load():
     lib.smx_stage_time.argtypes = [vp, ctypes.c_int, ctypes.c_char_p, ctypes.c_int, ctypes.POINTER(ctypes.c_double)]
     lib.smx_measure_fma_peak.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.POINTER(ctypes.c_double)]
     lib.smx_measure_row_stream.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_double)]
+    lib.smx_validate_inputs.argtypes = [vp, ctypes.c_int, lp, lp]
     lib.smx_sync.argtypes = [vp]
     lib.smx_set_stream.argtypes = [vp, vp, ctypes.c_int]
     lib.smx_restrict_nodes.argtypes = [vp, ctypes.c_int, lp]

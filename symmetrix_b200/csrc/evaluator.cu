@@ -72,6 +72,7 @@ public:
     virtual double timer_stop() = 0;
     virtual void sync() = 0;
     virtual void measure_row_stream(int layer, double* ms, double* bytes) = 0;
+    virtual long validate_inputs(int feature_rows, long* counts) = 0;
     virtual void set_stream(void* s, bool external) = 0;
     virtual long restrict_nodes(int num_nodes, bool keep_outputs) = 0;
     virtual void resize_rows(const std::string& name, int rows) = 0;
@@ -536,12 +537,21 @@ public:
         }
         return a;
     }
+    // Nodes of one element type per thread in the straight-line contraction kernels (see PolyVec): measured best
+#ifndef SMX_POLY_NB_FWD
+#define SMX_POLY_NB_FWD 2
+#endif
+#ifndef SMX_POLY_NB_REV
+#define SMX_POLY_NB_REV 2
+#endif
+    static constexpr int kPolyNodesFwd = SMX_POLY_NB_FWD, kPolyNodesRev = SMX_POLY_NB_REV;
     template <int NOUT>
     void launch_poly_fixed(int first, bool reverse) {
-        const long long total = static_cast<long long>(N) * model.K;
-        const int grid = static_cast<int>((total + 127) / 128);
-        if (reverse) poly_fixed_reverse_kernel<T, NOUT><<<grid, 128, 0, stream>>>(poly_args(first));
-        else poly_fixed_forward_kernel<T, NOUT><<<grid, 128, 0, stream>>>(poly_args(first));
+        const int nb = reverse ? kPolyNodesRev : kPolyNodesFwd;
+        const long long total = static_cast<long long>((N + nb - 1) / nb) * model.K;     // upper bound of (group, channel) pairs per type
+        dim3 grid(static_cast<unsigned>((total + 127) / 128), static_cast<unsigned>(model.num_elements));
+        if (reverse) poly_fixed_reverse_kernel<T, NOUT, kPolyNodesRev><<<grid, 128, 0, stream>>>(poly_args(first));
+        else poly_fixed_forward_kernel<T, NOUT, kPolyNodesFwd><<<grid, 128, 0, stream>>>(poly_args(first));
         check_launch(reverse ? "poly_fixed_reverse_kernel" : "poly_fixed_forward_kernel");
     }
     void run_poly(int first, bool reverse) {
@@ -971,6 +981,30 @@ public:
         }
         if (ms) *ms = best;
         if (bytes) *bytes = static_cast<double>(E) * 4.0 * P * K * sizeof(T);
+    }
+    // Counts the entries of the current edge set that are out of range or inconsistent (see validate_inputs_kernel);
+    // returns their total. `feature_rows` is the row count the sender indices may address (>= the receiver count).
+    long validate_inputs(int feature_rows, long* counts) override {
+        require_edges();
+        SMX_CUDA(cudaSetDevice(device));
+        if (feature_rows < N) throw ArgError("validate_inputs: feature_rows is smaller than the number of receivers");
+        DevBuf<unsigned long long> bad;
+        bad.resize(kNumInputChecks, stream);
+        bad.zero(stream);
+        const long long work = std::max<long long>(E, N);
+        const int grid = static_cast<int>(std::min<long long>(std::max<long long>((work + 255) / 256, 1), num_sms * 16LL));
+        validate_inputs_kernel<<<grid, 256, 0, stream>>>(N, E, model.num_elements, feature_rows, model.r_cut, node_types, num_neigh,
+                                                       first_neigh.p, neigh_indices, neigh_types, xyz, r, bad.p);
+        check_launch("validate_inputs_kernel");
+        unsigned long long host[kNumInputChecks] = {};
+        SMX_CUDA(cudaMemcpyAsync(host, bad.p, sizeof(host), cudaMemcpyDeviceToHost, stream));
+        SMX_CUDA(cudaStreamSynchronize(stream));
+        long total = 0;
+        for (int c = 0; c < kNumInputChecks; ++c) {
+            if (counts) counts[c] = static_cast<long>(host[c]);
+            total += static_cast<long>(host[c]);
+        }
+        return total;
     }
     void timer_start() override {
         SMX_CUDA(cudaSetDevice(device));
@@ -1428,6 +1462,14 @@ int smx_measure_fma_peak(int precision, int device, double* tflops) {
 
 int smx_measure_row_stream(smx_handle h, int layer, double* ms, double* bytes) {
     return guarded(h, [&](smx::EvaluatorBase& e) { e.measure_row_stream(layer, ms, bytes); });
+}
+
+int smx_validate_inputs(smx_handle h, int feature_rows, long* counts, long* total) {
+    return guarded(h, [&](smx::EvaluatorBase& e) {
+        const long n = e.validate_inputs(feature_rows, counts);
+        if (total) *total = n;
+        if (n != 0) throw smx::ArgError("the edge arrays hold " + std::to_string(n) + " out-of-range or inconsistent entries");
+    });
 }
 
 int smx_build_neighbors(smx_handle h, int num_atoms, const double* positions, const int* types, const double* cell,

@@ -651,6 +651,38 @@ __global__ void __launch_bounds__(kChannelBlock, tp_min_blocks<T>(LF, true)) tp_
     }
 }
 
+// Input check for callers that cannot vouch for their edge arrays: counts, per kind, the entries that would make the
+// evaluation read out of bounds or produce non-finite values. Reads only inside the given arrays.
+//   0 node type outside [0, num_elements)      1 negative neighbour count      2 counts do not add up to the edge total
+//   3 sender index outside [0, feature_rows)   4 sender type outside the model  5 r not finite, <= 0 or beyond r_cut
+//   6 r differs from |xyz| by more than 1e-6 relative
+constexpr int kNumInputChecks = 7;
+__global__ void validate_inputs_kernel(int N, long long E, int num_elements, int feature_rows, double r_cut,
+                                       const int* __restrict__ node_types, const int* __restrict__ num_neigh,
+                                       const long long* __restrict__ first_neigh, const int* __restrict__ neigh_indices,
+                                       const int* __restrict__ neigh_types, const double* __restrict__ xyz, const double* __restrict__ r,
+                                       unsigned long long* __restrict__ counts) {
+    const long long t0 = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    unsigned long long bad[kNumInputChecks] = {};
+    for (long long i = t0; i < N; i += stride) {
+        if (node_types[i] < 0 || node_types[i] >= num_elements) bad[0] += 1;
+        if (num_neigh[i] < 0) bad[1] += 1;
+    }
+    if (t0 == 0 && N > 0 && first_neigh[N - 1] + num_neigh[N - 1] != E) bad[2] += 1;
+    for (long long e = t0; e < E; e += stride) {
+        if (neigh_indices[e] < 0 || neigh_indices[e] >= feature_rows) bad[3] += 1;
+        if (neigh_types[e] < 0 || neigh_types[e] >= num_elements) bad[4] += 1;
+        const double rr = r[e];
+        if (!(rr > 0.0) || !(rr <= r_cut * (1.0 + 1e-12)) || !isfinite(rr)) bad[5] += 1;
+        const double x = xyz[3 * e], y = xyz[3 * e + 1], z = xyz[3 * e + 2];
+        const double d = sqrt(x * x + y * y + z * z);
+        if (!(fabs(d - rr) <= 1e-6 * fmax(d, rr))) bad[6] += 1;
+    }
+    for (int c = 0; c < kNumInputChecks; ++c)
+        if (bad[c]) atomicAdd(counts + c, bad[c]);
+}
+
 // Measurement probe: streams, for every edge of the current edge set, the spline row the edge kernels read
 // (same (pair, bin) addressing, same per-thread 16-byte loads) and does nothing else; its duration is the
 // floor the L2 -> SM path sets for one pass of an edge kernel over the edge set. No barriers and few
@@ -880,145 +912,244 @@ __global__ void poly_reverse_kernel(const PolyArgs<T> a) {
 // generated/poly_canon.hpp (l_max = 3, correlation 3): one thread per (node, channel), the 16 inputs and the
 // 16 gradient accumulators in registers, every coefficient one load at a compile-time offset. `coef` is then
 // ordered canonically, [element][canonical monomial][K]. NOUT = number of output components (1, 4 or 9).
-template <typename T, int NOUT>
-__global__ void __launch_bounds__(128) poly_fixed_forward_kernel(const PolyArgs<T> a) {
+// NB nodes of one element type share a thread: every coefficient load then feeds NB multiply-adds (the coefficient stream
+// from L2, one load per multiply-add for NB = 1, is what these kernels wait for). The generated code is written for a
+// type T with fma and *; here T is a short vector over the NB nodes. Grid: x over (node group, channel), y = element type.
+template <typename S, int NB>
+struct PolyVec {
+    S v[NB];
+    __device__ __forceinline__ PolyVec() {}
+    __device__ __forceinline__ PolyVec(S x) {
+#pragma unroll
+        for (int n = 0; n < NB; ++n) v[n] = x;
+    }
+};
+template <typename S, int NB>
+__device__ __forceinline__ PolyVec<S, NB> fma(const PolyVec<S, NB>& x, const PolyVec<S, NB>& y, const PolyVec<S, NB>& z) {
+    PolyVec<S, NB> r;
+#pragma unroll
+    for (int n = 0; n < NB; ++n) r.v[n] = ::fma(x.v[n], y.v[n], z.v[n]);
+    return r;
+}
+template <typename S, int NB>
+__device__ __forceinline__ PolyVec<S, NB> operator*(const PolyVec<S, NB>& x, const PolyVec<S, NB>& y) {
+    PolyVec<S, NB> r;
+#pragma unroll
+    for (int n = 0; n < NB; ++n) r.v[n] = x.v[n] * y.v[n];
+    return r;
+}
+
+template <typename S, int NOUT, int NB>
+__global__ void __launch_bounds__(128) poly_fixed_forward_kernel(const PolyArgs<S> a) {
+    using T = PolyVec<S, NB>;
+    const int type = blockIdx.y;
+    const int seg_begin = a.type_seg[type], count = a.type_seg[type + 1] - seg_begin;
     const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (idx >= static_cast<long long>(a.N) * a.K) return;
-    const int i = static_cast<int>(idx / a.K), k = static_cast<int>(idx - static_cast<long long>(i) * a.K);
+    const int groups = (count + NB - 1) / NB;
+    if (idx >= static_cast<long long>(groups) * a.K) return;
+    const int g = static_cast<int>(idx / a.K), k = static_cast<int>(idx - static_cast<long long>(g) * a.K);
+    int node[NB];
+    bool live[NB];
+#pragma unroll
+    for (int n = 0; n < NB; ++n) {
+        const int jn = g * NB + n;
+        live[n] = jn < count;
+        node[n] = a.perm[seg_begin + (live[n] ? jn : count - 1)];   // an empty slot repeats the last node; its results are dropped
+    }
+    const S* cf = a.coef + static_cast<size_t>(type) * a.num_mono * a.K + k;
     T A[kNumLm];
 #pragma unroll
-    for (int q = 0; q < kNumLm; ++q) A[q] = a.A[(static_cast<size_t>(i) * kNumLm + q) * a.K + k];
-    const T* cf = a.coef + static_cast<size_t>(a.node_types[i]) * a.num_mono * a.K + k;
+    for (int q = 0; q < kNumLm; ++q)
+#pragma unroll
+        for (int n = 0; n < NB; ++n) A[q].v[n] = a.A[(static_cast<size_t>(node[n]) * kNumLm + q) * a.K + k];
     {
-        constexpr int kOff = kCanonPolyOffset[0];
-        auto C = [&](int slot) { return __ldg(cf + static_cast<size_t>(kOff + slot) * a.K); };
+        {
+            constexpr int kOff = kCanonPolyOffset[0];
+            auto C = [&](int slot) { return T(__ldg(cf + static_cast<size_t>(kOff + slot) * a.K)); };
 #include "generated/poly_lm0_forward.inc"
-        a.M[(static_cast<size_t>(i) * NOUT + 0) * a.K + k] = total;
+#pragma unroll
+            for (int n = 0; n < NB; ++n)
+                if (live[n]) a.M[(static_cast<size_t>(node[n]) * NOUT + 0) * a.K + k] = total.v[n];
+        }
     }
     if constexpr (NOUT > 1) {
         {
             constexpr int kOff = kCanonPolyOffset[1];
-            auto C = [&](int slot) { return __ldg(cf + static_cast<size_t>(kOff + slot) * a.K); };
+            auto C = [&](int slot) { return T(__ldg(cf + static_cast<size_t>(kOff + slot) * a.K)); };
 #include "generated/poly_lm1_forward.inc"
-            a.M[(static_cast<size_t>(i) * NOUT + 1) * a.K + k] = total;
+#pragma unroll
+            for (int n = 0; n < NB; ++n)
+                if (live[n]) a.M[(static_cast<size_t>(node[n]) * NOUT + 1) * a.K + k] = total.v[n];
         }
         {
             constexpr int kOff = kCanonPolyOffset[2];
-            auto C = [&](int slot) { return __ldg(cf + static_cast<size_t>(kOff + slot) * a.K); };
+            auto C = [&](int slot) { return T(__ldg(cf + static_cast<size_t>(kOff + slot) * a.K)); };
 #include "generated/poly_lm2_forward.inc"
-            a.M[(static_cast<size_t>(i) * NOUT + 2) * a.K + k] = total;
+#pragma unroll
+            for (int n = 0; n < NB; ++n)
+                if (live[n]) a.M[(static_cast<size_t>(node[n]) * NOUT + 2) * a.K + k] = total.v[n];
         }
         {
             constexpr int kOff = kCanonPolyOffset[3];
-            auto C = [&](int slot) { return __ldg(cf + static_cast<size_t>(kOff + slot) * a.K); };
+            auto C = [&](int slot) { return T(__ldg(cf + static_cast<size_t>(kOff + slot) * a.K)); };
 #include "generated/poly_lm3_forward.inc"
-            a.M[(static_cast<size_t>(i) * NOUT + 3) * a.K + k] = total;
+#pragma unroll
+            for (int n = 0; n < NB; ++n)
+                if (live[n]) a.M[(static_cast<size_t>(node[n]) * NOUT + 3) * a.K + k] = total.v[n];
         }
     }
     if constexpr (NOUT > 4) {
         {
             constexpr int kOff = kCanonPolyOffset[4];
-            auto C = [&](int slot) { return __ldg(cf + static_cast<size_t>(kOff + slot) * a.K); };
+            auto C = [&](int slot) { return T(__ldg(cf + static_cast<size_t>(kOff + slot) * a.K)); };
 #include "generated/poly_lm4_forward.inc"
-            a.M[(static_cast<size_t>(i) * NOUT + 4) * a.K + k] = total;
+#pragma unroll
+            for (int n = 0; n < NB; ++n)
+                if (live[n]) a.M[(static_cast<size_t>(node[n]) * NOUT + 4) * a.K + k] = total.v[n];
         }
         {
             constexpr int kOff = kCanonPolyOffset[5];
-            auto C = [&](int slot) { return __ldg(cf + static_cast<size_t>(kOff + slot) * a.K); };
+            auto C = [&](int slot) { return T(__ldg(cf + static_cast<size_t>(kOff + slot) * a.K)); };
 #include "generated/poly_lm5_forward.inc"
-            a.M[(static_cast<size_t>(i) * NOUT + 5) * a.K + k] = total;
+#pragma unroll
+            for (int n = 0; n < NB; ++n)
+                if (live[n]) a.M[(static_cast<size_t>(node[n]) * NOUT + 5) * a.K + k] = total.v[n];
         }
         {
             constexpr int kOff = kCanonPolyOffset[6];
-            auto C = [&](int slot) { return __ldg(cf + static_cast<size_t>(kOff + slot) * a.K); };
+            auto C = [&](int slot) { return T(__ldg(cf + static_cast<size_t>(kOff + slot) * a.K)); };
 #include "generated/poly_lm6_forward.inc"
-            a.M[(static_cast<size_t>(i) * NOUT + 6) * a.K + k] = total;
+#pragma unroll
+            for (int n = 0; n < NB; ++n)
+                if (live[n]) a.M[(static_cast<size_t>(node[n]) * NOUT + 6) * a.K + k] = total.v[n];
         }
         {
             constexpr int kOff = kCanonPolyOffset[7];
-            auto C = [&](int slot) { return __ldg(cf + static_cast<size_t>(kOff + slot) * a.K); };
+            auto C = [&](int slot) { return T(__ldg(cf + static_cast<size_t>(kOff + slot) * a.K)); };
 #include "generated/poly_lm7_forward.inc"
-            a.M[(static_cast<size_t>(i) * NOUT + 7) * a.K + k] = total;
+#pragma unroll
+            for (int n = 0; n < NB; ++n)
+                if (live[n]) a.M[(static_cast<size_t>(node[n]) * NOUT + 7) * a.K + k] = total.v[n];
         }
         {
             constexpr int kOff = kCanonPolyOffset[8];
-            auto C = [&](int slot) { return __ldg(cf + static_cast<size_t>(kOff + slot) * a.K); };
+            auto C = [&](int slot) { return T(__ldg(cf + static_cast<size_t>(kOff + slot) * a.K)); };
 #include "generated/poly_lm8_forward.inc"
-            a.M[(static_cast<size_t>(i) * NOUT + 8) * a.K + k] = total;
+#pragma unroll
+            for (int n = 0; n < NB; ++n)
+                if (live[n]) a.M[(static_cast<size_t>(node[n]) * NOUT + 8) * a.K + k] = total.v[n];
         }
     }
 }
 
-template <typename T, int NOUT>
-__global__ void __launch_bounds__(128) poly_fixed_reverse_kernel(const PolyArgs<T> a) {
+template <typename S, int NOUT, int NB>
+__global__ void __launch_bounds__(128) poly_fixed_reverse_kernel(const PolyArgs<S> a) {
+    using T = PolyVec<S, NB>;
+    const int type = blockIdx.y;
+    const int seg_begin = a.type_seg[type], count = a.type_seg[type + 1] - seg_begin;
     const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (idx >= static_cast<long long>(a.N) * a.K) return;
-    const int i = static_cast<int>(idx / a.K), k = static_cast<int>(idx - static_cast<long long>(i) * a.K);
+    const int groups = (count + NB - 1) / NB;
+    if (idx >= static_cast<long long>(groups) * a.K) return;
+    const int g = static_cast<int>(idx / a.K), k = static_cast<int>(idx - static_cast<long long>(g) * a.K);
+    int node[NB];
+    bool live[NB];
+#pragma unroll
+    for (int n = 0; n < NB; ++n) {
+        const int jn = g * NB + n;
+        live[n] = jn < count;
+        node[n] = a.perm[seg_begin + (live[n] ? jn : count - 1)];   // an empty slot repeats the last node; its results are dropped
+    }
+    const S* cf = a.coef + static_cast<size_t>(type) * a.num_mono * a.K + k;
     T A[kNumLm], G[kNumLm];
 #pragma unroll
-    for (int q = 0; q < kNumLm; ++q) { A[q] = a.A[(static_cast<size_t>(i) * kNumLm + q) * a.K + k]; G[q] = T(0); }
-    const T* cf = a.coef + static_cast<size_t>(a.node_types[i]) * a.num_mono * a.K + k;
-    const T* seeds = a.M_adj + static_cast<size_t>(i) * NOUT * a.K + k;
+    for (int q = 0; q < kNumLm; ++q) {
+#pragma unroll
+        for (int n = 0; n < NB; ++n) A[q].v[n] = a.A[(static_cast<size_t>(node[n]) * kNumLm + q) * a.K + k];
+        G[q] = T(S(0));
+    }
     {
-        constexpr int kOff = kCanonPolyOffset[0];
-        auto C = [&](int slot) { return __ldg(cf + static_cast<size_t>(kOff + slot) * a.K); };
-        const T seed = seeds[0];
+        {
+            constexpr int kOff = kCanonPolyOffset[0];
+            auto C = [&](int slot) { return T(__ldg(cf + static_cast<size_t>(kOff + slot) * a.K)); };
+            T seed;
+#pragma unroll
+            for (int n = 0; n < NB; ++n) seed.v[n] = a.M_adj[(static_cast<size_t>(node[n]) * NOUT + 0) * a.K + k];
 #include "generated/poly_lm0_reverse.inc"
+        }
     }
     if constexpr (NOUT > 1) {
         {
             constexpr int kOff = kCanonPolyOffset[1];
-            auto C = [&](int slot) { return __ldg(cf + static_cast<size_t>(kOff + slot) * a.K); };
-            const T seed = seeds[static_cast<size_t>(1) * a.K];
+            auto C = [&](int slot) { return T(__ldg(cf + static_cast<size_t>(kOff + slot) * a.K)); };
+            T seed;
+#pragma unroll
+            for (int n = 0; n < NB; ++n) seed.v[n] = a.M_adj[(static_cast<size_t>(node[n]) * NOUT + 1) * a.K + k];
 #include "generated/poly_lm1_reverse.inc"
         }
         {
             constexpr int kOff = kCanonPolyOffset[2];
-            auto C = [&](int slot) { return __ldg(cf + static_cast<size_t>(kOff + slot) * a.K); };
-            const T seed = seeds[static_cast<size_t>(2) * a.K];
+            auto C = [&](int slot) { return T(__ldg(cf + static_cast<size_t>(kOff + slot) * a.K)); };
+            T seed;
+#pragma unroll
+            for (int n = 0; n < NB; ++n) seed.v[n] = a.M_adj[(static_cast<size_t>(node[n]) * NOUT + 2) * a.K + k];
 #include "generated/poly_lm2_reverse.inc"
         }
         {
             constexpr int kOff = kCanonPolyOffset[3];
-            auto C = [&](int slot) { return __ldg(cf + static_cast<size_t>(kOff + slot) * a.K); };
-            const T seed = seeds[static_cast<size_t>(3) * a.K];
+            auto C = [&](int slot) { return T(__ldg(cf + static_cast<size_t>(kOff + slot) * a.K)); };
+            T seed;
+#pragma unroll
+            for (int n = 0; n < NB; ++n) seed.v[n] = a.M_adj[(static_cast<size_t>(node[n]) * NOUT + 3) * a.K + k];
 #include "generated/poly_lm3_reverse.inc"
         }
     }
     if constexpr (NOUT > 4) {
         {
             constexpr int kOff = kCanonPolyOffset[4];
-            auto C = [&](int slot) { return __ldg(cf + static_cast<size_t>(kOff + slot) * a.K); };
-            const T seed = seeds[static_cast<size_t>(4) * a.K];
+            auto C = [&](int slot) { return T(__ldg(cf + static_cast<size_t>(kOff + slot) * a.K)); };
+            T seed;
+#pragma unroll
+            for (int n = 0; n < NB; ++n) seed.v[n] = a.M_adj[(static_cast<size_t>(node[n]) * NOUT + 4) * a.K + k];
 #include "generated/poly_lm4_reverse.inc"
         }
         {
             constexpr int kOff = kCanonPolyOffset[5];
-            auto C = [&](int slot) { return __ldg(cf + static_cast<size_t>(kOff + slot) * a.K); };
-            const T seed = seeds[static_cast<size_t>(5) * a.K];
+            auto C = [&](int slot) { return T(__ldg(cf + static_cast<size_t>(kOff + slot) * a.K)); };
+            T seed;
+#pragma unroll
+            for (int n = 0; n < NB; ++n) seed.v[n] = a.M_adj[(static_cast<size_t>(node[n]) * NOUT + 5) * a.K + k];
 #include "generated/poly_lm5_reverse.inc"
         }
         {
             constexpr int kOff = kCanonPolyOffset[6];
-            auto C = [&](int slot) { return __ldg(cf + static_cast<size_t>(kOff + slot) * a.K); };
-            const T seed = seeds[static_cast<size_t>(6) * a.K];
+            auto C = [&](int slot) { return T(__ldg(cf + static_cast<size_t>(kOff + slot) * a.K)); };
+            T seed;
+#pragma unroll
+            for (int n = 0; n < NB; ++n) seed.v[n] = a.M_adj[(static_cast<size_t>(node[n]) * NOUT + 6) * a.K + k];
 #include "generated/poly_lm6_reverse.inc"
         }
         {
             constexpr int kOff = kCanonPolyOffset[7];
-            auto C = [&](int slot) { return __ldg(cf + static_cast<size_t>(kOff + slot) * a.K); };
-            const T seed = seeds[static_cast<size_t>(7) * a.K];
+            auto C = [&](int slot) { return T(__ldg(cf + static_cast<size_t>(kOff + slot) * a.K)); };
+            T seed;
+#pragma unroll
+            for (int n = 0; n < NB; ++n) seed.v[n] = a.M_adj[(static_cast<size_t>(node[n]) * NOUT + 7) * a.K + k];
 #include "generated/poly_lm7_reverse.inc"
         }
         {
             constexpr int kOff = kCanonPolyOffset[8];
-            auto C = [&](int slot) { return __ldg(cf + static_cast<size_t>(kOff + slot) * a.K); };
-            const T seed = seeds[static_cast<size_t>(8) * a.K];
+            auto C = [&](int slot) { return T(__ldg(cf + static_cast<size_t>(kOff + slot) * a.K)); };
+            T seed;
+#pragma unroll
+            for (int n = 0; n < NB; ++n) seed.v[n] = a.M_adj[(static_cast<size_t>(node[n]) * NOUT + 8) * a.K + k];
 #include "generated/poly_lm8_reverse.inc"
         }
     }
 #pragma unroll
-    for (int q = 0; q < kNumLm; ++q) a.A_adj[(static_cast<size_t>(i) * kNumLm + q) * a.K + k] = G[q];
+    for (int q = 0; q < kNumLm; ++q)
+#pragma unroll
+        for (int n = 0; n < NB; ++n)
+            if (live[n]) a.A_adj[(static_cast<size_t>(node[n]) * kNumLm + q) * a.K + k] = G[q].v[n];
 }
 
 // =============================================================================================

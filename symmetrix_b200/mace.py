@@ -226,6 +226,17 @@ class MACE:
         self._check(self._lib.smx_measure_row_stream(self._h, int(layer), ctypes.byref(ms), ctypes.byref(nbytes)))
         return ms.value, nbytes.value
 
+    def validate_inputs(self, feature_rows=None):
+        """Counts per kind of the out-of-range or inconsistent entries of the current edge set (all zero for good inputs):
+        node type, negative neighbour count, counts not adding up, sender index, sender type, r out of range, r vs |xyz|."""
+        rows = self._num_nodes if feature_rows is None else int(feature_rows)
+        counts = (ctypes.c_long * 7)()
+        total = ctypes.c_long(0)
+        status = self._lib.smx_validate_inputs(self._h, rows, counts, ctypes.byref(total))
+        if status not in (_lib.SMX_OK, _lib.SMX_ERR_INVALID_ARGUMENT):
+            self._check(status)
+        return list(counts)
+
     def set_profiling(self, enabled: bool) -> None:
         self._check(self._lib.smx_set_profiling(self._h, int(bool(enabled))))
 

@@ -142,3 +142,37 @@ def test_three_block_model_decomposes_in_both_modes(model_file, world, mode):
     assert abs(energy - e.sum()) < 1e-11 * abs(e.sum())
     np.testing.assert_allclose(forces, f_ref, atol=1e-11)
     np.testing.assert_allclose(virial, v_ref, atol=1e-10)
+
+
+# ------------------------------------------------------------------------------------------------ a rank that leaves
+def _leaving_worker(rank, world, port, out_dir):
+    """Rank 1 leaves between two steps (no exchange in flight); rank 0 must learn of it as an error from its next halo
+    exchange within the process-group timeout, not hang."""
+    import datetime
+    import time
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    import torch.distributed as dist
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
+    s = _structure()
+    b = OracleBackend(GOLDEN / "tiny_model.json")
+    rk = SlabRank(make_slab_plan(s, R_CUT, rank, world), b, R_CUT, b.atomic_numbers)
+    rk.build_edges()
+    evaluate_decomposed([rk], dist=dist)          # one complete step with both ranks
+    if rank == 1:
+        os._exit(0)                               # gone before the next step starts
+    t0 = time.time()
+    outcome = "no error"
+    try:
+        evaluate_decomposed([rk], dist=dist)
+    except Exception as exc:                      # gloo reports the closed connection or the timeout
+        outcome = type(exc).__name__
+    (Path(out_dir) / "rank0.txt").write_text(f"{outcome} {time.time() - t0:.1f}")
+    os._exit(0)
+
+
+def test_a_rank_leaving_between_steps_ends_the_next_exchange_with_an_error(tmp_path):
+    import torch.multiprocessing as mp
+    port = 29500 + (os.getpid() % 2000) + 37
+    mp.spawn(_leaving_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    outcome, seconds = (tmp_path / "rank0.txt").read_text().split()
+    assert outcome != "no" and float(seconds) < 60.0, (outcome, seconds)

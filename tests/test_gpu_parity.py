@@ -457,3 +457,27 @@ def test_three_block_stage_calls_equal_the_whole_evaluation(model_file):
     run(tiny_ev, {k: case[k] for k in INPUT_KEYS})
     with pytest.raises(SymmetrixError):
         tiny_ev.compute_Phim()
+
+
+def test_input_validator_counts_bad_entries(tiny):
+    """smx_validate_inputs on good and on corrupted edge arrays. Nothing is evaluated on the corrupted set: the
+    validator only reads the arrays it was given."""
+    case, inputs = tiny
+    ev = MACE(GOLDEN / "tiny_model.json")
+    n = int(inputs["num_nodes"])
+    ev.begin(n, *[inputs[k] for k in INPUT_KEYS[1:]])
+    assert ev.validate_inputs() == [0] * 7
+    bad = {k: np.array(inputs[k]).copy() for k in INPUT_KEYS[1:]}
+    bad["node_types"][0] = 7                      # no such element
+    bad["neigh_indices"][3] = n                   # one past the last feature row
+    bad["neigh_types"][5] = -1
+    bad["r"][7] = -1.0                            # not a distance (also disagrees with |xyz|)
+    bad["r"][9] *= 1.01                           # disagrees with |xyz|
+    first_with_neighbours = int(np.nonzero(bad["num_neigh"] > 0)[0][0])
+    bad["num_neigh"][first_with_neighbours] -= 1  # counts no longer add up to the number of edges
+    ev.begin(n, *[bad[k] for k in INPUT_KEYS[1:]])
+    counts = ev.validate_inputs()
+    assert counts[0] == 1 and counts[1] == 0 and counts[2] == 1 and counts[3] == 1 and counts[4] == 1
+    assert counts[5] >= 1 and counts[6] == 2
+    # ghost rows widen the admissible sender range
+    assert ev.validate_inputs(feature_rows=n + 1)[3] == 0
