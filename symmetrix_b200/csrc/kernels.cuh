@@ -742,6 +742,7 @@ struct PolyArgs {
     const int* node_types;
     const int* perm;             // nodes sorted by element type
     const int* type_seg;         // [E + 1] segment of each type in perm
+    int num_types;               // E
     const int* prog;             // concatenated operation streams (see compile_polynomial)
     const int* prog_off;         // [num_out] first word of each stream
     const int* prog_cnt;         // [num_out] operations to execute (a multiple of the prefetch distance)
@@ -914,7 +915,7 @@ __global__ void poly_reverse_kernel(const PolyArgs<T> a) {
 // ordered canonically, [element][canonical monomial][K]. NOUT = number of output components (1, 4 or 9).
 // NB nodes of one element type share a thread: every coefficient load then feeds NB multiply-adds (the coefficient stream
 // from L2, one load per multiply-add for NB = 1, is what these kernels wait for). The generated code is written for a
-// type T with fma and *; here T is a short vector over the NB nodes. Grid: x over (node group, channel), y = element type.
+// type T with fma and *; here T is a short vector over the NB nodes. Grid: one thread per (node group, channel).
 template <typename S, int NB>
 struct PolyVec {
     S v[NB];
@@ -942,12 +943,19 @@ __device__ __forceinline__ PolyVec<S, NB> operator*(const PolyVec<S, NB>& x, con
 template <typename S, int NOUT, int NB>
 __global__ void __launch_bounds__(128) poly_fixed_forward_kernel(const PolyArgs<S> a) {
     using T = PolyVec<S, NB>;
-    const int type = blockIdx.y;
-    const int seg_begin = a.type_seg[type], count = a.type_seg[type + 1] - seg_begin;
+    // flat index -> (element type, group of NB nodes of that type, channel); groups of all types are numbered consecutively
     const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-    const int groups = (count + NB - 1) / NB;
-    if (idx >= static_cast<long long>(groups) * a.K) return;
-    const int g = static_cast<int>(idx / a.K), k = static_cast<int>(idx - static_cast<long long>(g) * a.K);
+    int g = static_cast<int>(idx / a.K);
+    const int k = static_cast<int>(idx - static_cast<long long>(g) * a.K);
+    int type = 0, seg_begin = 0, count = 0;
+    for (; type < a.num_types; ++type) {
+        seg_begin = a.type_seg[type];
+        count = a.type_seg[type + 1] - seg_begin;
+        const int groups = (count + NB - 1) / NB;
+        if (g < groups) break;
+        g -= groups;
+    }
+    if (type == a.num_types) return;
     int node[NB];
     bool live[NB];
 #pragma unroll
@@ -1045,12 +1053,19 @@ __global__ void __launch_bounds__(128) poly_fixed_forward_kernel(const PolyArgs<
 template <typename S, int NOUT, int NB>
 __global__ void __launch_bounds__(128) poly_fixed_reverse_kernel(const PolyArgs<S> a) {
     using T = PolyVec<S, NB>;
-    const int type = blockIdx.y;
-    const int seg_begin = a.type_seg[type], count = a.type_seg[type + 1] - seg_begin;
+    // flat index -> (element type, group of NB nodes of that type, channel); groups of all types are numbered consecutively
     const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-    const int groups = (count + NB - 1) / NB;
-    if (idx >= static_cast<long long>(groups) * a.K) return;
-    const int g = static_cast<int>(idx / a.K), k = static_cast<int>(idx - static_cast<long long>(g) * a.K);
+    int g = static_cast<int>(idx / a.K);
+    const int k = static_cast<int>(idx - static_cast<long long>(g) * a.K);
+    int type = 0, seg_begin = 0, count = 0;
+    for (; type < a.num_types; ++type) {
+        seg_begin = a.type_seg[type];
+        count = a.type_seg[type + 1] - seg_begin;
+        const int groups = (count + NB - 1) / NB;
+        if (g < groups) break;
+        g -= groups;
+    }
+    if (type == a.num_types) return;
     int node[NB];
     bool live[NB];
 #pragma unroll
