@@ -420,7 +420,6 @@ public:
         }
         return it->second->p;
     }
-    const double* weight_image(const GemmProblem<double>&) { return nullptr; }
     GemmProblem<T> problem(const T* A, T* C, const T* B, bool by_type, int type, int sub_count, long long a_ns, long long a_off,
                            long long a_ss, long long c_ns, long long c_off, long long c_ss, int Kd, int Nc, int ldb, bool transB,
                            bool acc) {

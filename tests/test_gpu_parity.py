@@ -96,6 +96,7 @@ def _oracle_for(path, model):
     ("large256", 32, lambda z: st.molecular_liquid(12, seed=6)),             # L_max = 2
     ("organic128", 48, lambda z: st.water_box(3, 9.4, seed=7)),              # channel count not a multiple of 32
     ("large256", 160, lambda z: st.molecular_liquid(8, seed=8)),             # more channels than one CTA pass
+    ("fcc128", 6, lambda z: st.fcc_box(2, 3.6, z, seed=9)),                  # channel count not a multiple of 4: scalar row loads in the GEMMs
 ])
 def test_downsized_benchmark_models(model_file, dtype, name, channels, builder):
     path, model, spec = model_file(name, num_channels=channels, num_spline_points=32)
