@@ -98,6 +98,11 @@ int smx_compute(smx_handle h, int num_nodes, const int* node_types, const int* n
  * reverse_A0_scaled, reverse_A1_scaled (no-ops for models without density normalisation, as in the
  * reference). `zero_dxyz` / `zero_H1_adj` carry the flags of reverse_Phi1 / reverse_H2 /
  * reverse_A1_scaled (mace.hpp:118,145,159).
+ * Models whose file says "num_interactions": 3 (an extension; the reference's exporter stops at two blocks,
+ * extract_mace_data.py:70-71) add compute_Rm (no-op), compute_Phim, compute_Am, compute_Mm, compute_Hm between
+ * compute_H1 and compute_R1, and reverse_Hm, reverse_Mm, reverse_Am, reverse_Phim between reverse_Phi1 and
+ * reverse_H1: the stages of a second interaction block whose contraction keeps every (L, M); the arrays Phim, Am,
+ * Mm, Hm and their adjoints are read and written like the others, and Hm / Hm_adj take ghost rows like H1 / H1_adj.
  * Radial functions and harmonics are recomputed inside the edge kernels, so compute_Y /
  * compute_R0 / compute_R1 only record the edge arrays they are given. A sequence of stage calls
  * must start with smx_begin, which replaces the zero-fill of node_energies / node_forces that
