@@ -139,6 +139,7 @@ public:
     DevBuf<int> kernel_status;    // non-zero if a bounded mbarrier wait ran out (1, 2: tcgen05 GEMM; 3, 4: staged tensor-product reverse)
     bool staged_reverse = false;  // spline rows of the tensor-product reverse through bulk copies into shared memory
                                   // (SMX_TP_STAGED=1; measured equal in float64 and 15 % slower in float32 on B200)
+    bool type_order = true;       // edge kernels walk the receivers in element-type order (SMX_TYPE_ORDER=0: natural order)
     bool waits_in_flight = false; // a kernel with bounded waits has been launched since the last status check
     bool use_tc5 = false;
     std::map<std::tuple<const void*, int, int, int, int>, std::unique_ptr<DevBuf<float>>> weight_images;
@@ -156,6 +157,7 @@ public:
         kernel_status.resize(1, stream);
         kernel_status.zero(stream);
         if (const char* t = std::getenv("SMX_TP_STAGED")) staged_reverse = std::string(t) != "0";
+        if (const char* t = std::getenv("SMX_TYPE_ORDER")) type_order = std::string(t) != "0";
         if constexpr (sizeof(T) == 4) {
             // float32 GEMMs run on tcgen05 unless SMX_GEMM=mma asks for the mma.sync kernel
             const char* g = std::getenv("SMX_GEMM");
@@ -441,7 +443,7 @@ public:
         Layer0Args<T> a{};
         a.N = N; a.K = model.K;
         a.node_types = node_types; a.first_neigh = first_neigh.p; a.neigh_indices = neigh_indices; a.neigh_types = neigh_types;
-        a.xyz = xyz; a.r = r; a.coef0 = coef0.p; a.sm = sm; a.H0_w = H0_w.p;
+        a.xyz = xyz; a.r = r; a.coef0 = coef0.p; a.sm = sm; a.H0_w = H0_w.p; a.order = type_order ? perm.p : nullptr;
         a.Phi0 = Phi0.p; a.Phi0_adj = Phi0_adj.p; a.node_forces = node_forces.p;
         return a;
     }
@@ -640,6 +642,7 @@ public:
         }
         a.Hmsg = Hmsg.p; a.node_forces = node_forces.p;
         a.status = kernel_status.p;
+        a.order = type_order ? perm.p : nullptr;
         return a;
     }
     template <int LF>
@@ -972,7 +975,8 @@ public:
         float best = 0.f;
         for (int rep = 0; rep < 4; ++rep) {
             SMX_CUDA(cudaEventRecord(evt0, stream));
-            row_stream_probe_kernel<T><<<grid, block, 0, stream>>>(N, K, P, node_types, first_neigh.p, neigh_types, r, table, sm, sink.p);
+            row_stream_probe_kernel<T><<<grid, block, 0, stream>>>(N, K, P, node_types, first_neigh.p, neigh_types, r, table, sm,
+                                                                    type_order ? perm.p : nullptr, sink.p);
             check_launch("row_stream_probe_kernel");
             SMX_CUDA(cudaEventRecord(evt1, stream));
             SMX_CUDA(cudaEventSynchronize(evt1));
