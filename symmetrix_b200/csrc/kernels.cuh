@@ -628,7 +628,9 @@ __global__ void __launch_bounds__(kChannelBlock, tp_min_blocks<T>(LF, true)) tp_
                         // float64: deterministic two-step scatter (per-edge message, then a fixed-order sum per sender)
                         T* mrow = a.Hmsg + static_cast<size_t>(e0 + e) * tp.nLM * a.K + k;
 #pragma unroll
-                        for (int lm2 = 0; lm2 < tp.nLM; ++lm2) mrow[static_cast<size_t>(lm2) * a.K] = msg[lm2];
+                        // streaming stores: the message buffer is written once and read once (sender_gather) and must not
+                        // push the spline tables out of L2
+                        for (int lm2 = 0; lm2 < tp.nLM; ++lm2) __stcs(mrow + static_cast<size_t>(lm2) * a.K, msg[lm2]);
                     } else {
                         // float32: one reduction per value directly into the sender's row (no message buffer)
                         T* arow = a.H_adj + static_cast<size_t>(s.j) * tp.nLM * a.K + k;
@@ -733,7 +735,7 @@ __global__ void sender_gather_kernel(int rows, int width, const long long* __res
         const long long b = in_ptr[j], e = in_ptr[j + 1];
         for (int c = threadIdx.x; c < width; c += blockDim.x) {
             T acc = 0;
-            for (long long n = b; n < e; ++n) acc += Hmsg[static_cast<size_t>(in_edge[n]) * width + c];
+            for (long long n = b; n < e; ++n) acc += __ldcs(Hmsg + static_cast<size_t>(in_edge[n]) * width + c);
             H_adj[static_cast<size_t>(j) * width + c] += acc;
         }
     }
