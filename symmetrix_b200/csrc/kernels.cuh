@@ -503,7 +503,7 @@ __global__ void __launch_bounds__(kChannelBlock, tp_min_blocks<T>(LF, false)) tp
         if (active) {
             T* out = a.Phi1 + static_cast<size_t>(i) * tp.Q * a.K + k;
 #pragma unroll
-            for (int q = 0; q < tp.Q; ++q) out[static_cast<size_t>(q) * a.K] = acc[q];
+            for (int q = 0; q < tp.Q; ++q) __stcs(out + static_cast<size_t>(q) * a.K, acc[q]);   // written once, read by the GEMM: stream past L2 residents
         }
     }
 }
@@ -556,7 +556,7 @@ __global__ void __launch_bounds__(kChannelBlock, tp_min_blocks<T>(LF, true)) tp_
         T d[tp.Q];
 #pragma unroll
         for (int q = 0; q < tp.Q; ++q)
-            d[q] = active ? a.dPhi1[(static_cast<size_t>(i) * tp.Q + q) * a.K + k] : T(0);
+            d[q] = active ? __ldcs(a.dPhi1 + (static_cast<size_t>(i) * tp.Q + q) * a.K + k) : T(0);
         for (long long e0 = e_begin; e0 < e_end; e0 += EB) {
             const int nb = static_cast<int>(e_end - e0 < EB ? e_end - e0 : EB);
             __syncthreads();
