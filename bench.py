@@ -185,7 +185,7 @@ def roofline_for(stage: str, ms: float, n_atoms: int, n_edges: int, K: int, L_ma
     achieved = byts / (ms * 1e-3) / 1e9
     # dram__bytes_read.sum + dram__bytes_write.sum per edge from the ncu capture summarised in
     # profiles/edge_kernels_fcc1372_fp64.md (a smaller box of the same construction; traffic grows with the edge count)
-    per_edge = {("tp_reverse_kernel", 8): 11560.0, ("tp_forward_kernel", 8): 5077.0,
+    per_edge = {("tp_reverse_kernel", 8): 6827.0, ("tp_forward_kernel", 8): 2812.0,
                 ("layer0_reverse_kernel", 8): 638.0, ("layer0_forward_kernel", 8): 405.0}.get((kernel, dtype_bytes))
     traffic = per_edge * n_edges if per_edge and K == 128 and L_max == 1 else None
     return {"bound": "hbm", "kernel": kernel, "stage": stage, "achieved": achieved, "peak": peak, "unit": "GB/s",
