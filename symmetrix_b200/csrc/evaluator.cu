@@ -513,9 +513,14 @@ public:
                 list.push_back(problem(A0_adj.p, Phi0_adj.p, A0_w.p + (static_cast<size_t>(a) * (kLmaxSH + 1) + l) * K * K, true, a,
                                        2 * l + 1, 16LL * K, 1LL * l * l * K, K, 16LL * K, 1LL * l * l * K, K, K, K, K, true, false));
         run_gemms(list, 7LL * N, K);
-        const int block = channel_block();
-        const int grid = persistent_grid(layer0_reverse_kernel<T>, block, 0, N);
-        layer0_reverse_kernel<T><<<grid, block, 0, stream>>>(layer0_args());
+#ifndef SMX_L0R_CPT
+#define SMX_L0R_CPT 2
+#endif
+        // SMX_L0R_CPT channels per thread; the CTA covers the same channels with fewer threads (at least one warp)
+        constexpr int kCpt = SMX_L0R_CPT;
+        const int block = std::max(32, ((channel_block() / kCpt + 31) / 32) * 32);
+        const int grid = persistent_grid(layer0_reverse_kernel<T, kCpt>, block, 0, N);
+        layer0_reverse_kernel<T, kCpt><<<grid, block, 0, stream>>>(layer0_args());
         check_launch("layer0_reverse_kernel");
     }
 

@@ -351,23 +351,30 @@ __global__ void __launch_bounds__(kChannelBlock) layer0_forward_kernel(const Lay
 //   nf[ij] -= sum_{lm,k} Phi0_adj[i,lm,k] H0[b,k] (xhat R0'[l,k] Y[lm] + R0[l,k] grad Y[lm])
 // (second half of MACE::reverse_A0, mace.cpp:238-269).
 // =============================================================================================
-template <typename T>
+// CPT channels per thread (k, k + blockDim.x, ...): the per-edge sums over channels (16 harmonic adjoints + 1 radial
+// adjoint, reduced across the warp with shuffles and across warps through shared memory) are what this kernel spends
+// most of its instructions on, and a thread that adds up CPT channels before the reduction needs 1 / CPT of them.
+template <typename T, int CPT>
 __global__ void __launch_bounds__(kChannelBlock) layer0_reverse_kernel(const Layer0Args<T> a) {
     __shared__ EdgeStage<T> st[kEdgeBatch];
     __shared__ T red[kMaxWarps][kEdgeBatch][17];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
     const int F = (kLmaxSH + 1) * a.K;
     for (int slot = blockIdx.x; slot < a.N; slot += gridDim.x)
-    for (int kc = 0; kc < a.K; kc += blockDim.x) {
+    for (int kc = 0; kc < a.K; kc += CPT * blockDim.x) {
         const int i = a.order ? a.order[slot] : slot;     // nodes in element-type order: see Layer0Args::order
-        const int k = kc + threadIdx.x;
-        const bool active = k < a.K;
+        int kk[CPT];
+        bool active[CPT];
+#pragma unroll
+        for (int c = 0; c < CPT; ++c) { kk[c] = kc + c * blockDim.x + threadIdx.x; active[c] = kk[c] < a.K; }
         const long long e_begin = a.first_neigh[i], e_end = a.first_neigh[i + 1];
         const int type_i = a.node_types[i];
-        T d[kNumLm];
+        T d[CPT][kNumLm];
 #pragma unroll
-        for (int lm = 0; lm < kNumLm; ++lm)
-            d[lm] = active ? a.Phi0_adj[(static_cast<size_t>(i) * kNumLm + lm) * a.K + k] : T(0);
+        for (int c = 0; c < CPT; ++c)
+#pragma unroll
+            for (int lm = 0; lm < kNumLm; ++lm)
+                d[c][lm] = active[c] ? a.Phi0_adj[(static_cast<size_t>(i) * kNumLm + lm) * a.K + kk[c]] : T(0);
         for (long long e0 = e_begin; e0 < e_end; e0 += kEdgeBatch) {
             const int nb = static_cast<int>(e_end - e0 < kEdgeBatch ? e_end - e0 : kEdgeBatch);
             __syncthreads();
@@ -376,23 +383,25 @@ __global__ void __launch_bounds__(kChannelBlock) layer0_reverse_kernel(const Lay
             __syncthreads();
             for (int e = 0; e < nb; ++e) {
                 const EdgeStage<T>& s = st[e];
-                T W[kNumLm], fr = 0;     // adjoints of the harmonics and of the edge length, this channel
+                T W[kNumLm], fr = 0;     // adjoints of the harmonics and of the edge length, summed over this thread's channels
 #pragma unroll
                 for (int lm = 0; lm < kNumLm; ++lm) W[lm] = T(0);
-                if (active) {
-                    const T h0 = a.H0_w[s.tj * a.K + k];
-                    const T x = s.x;
-                    const T* cb = a.coef0 + s.coef_base;
+                const T x = s.x;
+                const T* cb = a.coef0 + s.coef_base;
+#pragma unroll
+                for (int c = 0; c < CPT; ++c) {
+                    if (!active[c]) continue;
+                    const T h0 = a.H0_w[s.tj * a.K + kk[c]];
 #pragma unroll
                     for (int l = 0; l <= kLmaxSH; ++l) {
-                        const Vec4<T> c = load_coef<T>(cb + 4 * l * a.K, k, a.K);
-                        const T R = (c.x + x * (c.y + x * (c.z + x * c.w))) * h0;
-                        const T Rd = (c.y + x * (T(2) * c.z + T(3) * x * c.w)) * h0;
+                        const Vec4<T> cf = load_coef<T>(cb + 4 * l * a.K, kk[c], a.K);
+                        const T R = (cf.x + x * (cf.y + x * (cf.z + x * cf.w))) * h0;
+                        const T Rd = (cf.y + x * (T(2) * cf.z + T(3) * x * cf.w)) * h0;
                         T sv = 0;
 #pragma unroll
                         for (int lm = l * l; lm < (l + 1) * (l + 1); ++lm) {
-                            sv += d[lm] * s.Y[lm];
-                            W[lm] = R * d[lm];
+                            sv += d[c][lm] * s.Y[lm];
+                            W[lm] += R * d[c][lm];
                         }
                         fr += Rd * sv;
                     }
