@@ -45,7 +45,7 @@ inline size_t tc5_image_floats(int Kd, int Nc) {
 
 // One thread per (column block, k chunk, column n, 16-byte group): reads four weights, zero beyond the matrix,
 // and writes the hi and lo values where the tensor core expects column n of the K-major B tile.
-__global__ void gemm_tc5_prepare_b_kernel(const float* __restrict__ B, int Kd, int Nc, int ldb, int transB, float* __restrict__ image) {
+static __global__ void gemm_tc5_prepare_b_kernel(const float* __restrict__ B, int Kd, int Nc, int ldb, int transB, float* __restrict__ image) {
     const int k_chunks = (Kd + kTc5BK - 1) / kTc5BK, n_blocks = (Nc + kTc5BN - 1) / kTc5BN;
     const long long total = static_cast<long long>(n_blocks) * k_chunks * kTc5BN * (kTc5BK / 4);
     for (long long t = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; t < total; t += static_cast<long long>(gridDim.x) * blockDim.x) {
@@ -111,7 +111,7 @@ __device__ __forceinline__ void tc5_ld32(uint32_t taddr, uint32_t (&v)[32]) {
 
 // `status` receives a non-zero code if a bounded wait ran out (1: tensor core, 2: weight tile copy).
 // Every problem carries the operand image of its weight matrix in B_image.
-__global__ void __launch_bounds__(kTc5Threads) gemm_rows_tcgen05_kernel(const GemmProblem<float>* __restrict__ problems, int* __restrict__ status) {
+static __global__ void __launch_bounds__(kTc5Threads) gemm_rows_tcgen05_kernel(const GemmProblem<float>* __restrict__ problems, int* __restrict__ status) {
     const GemmProblem<float> pb = problems[blockIdx.z];
     int node_begin = 0, node_count = pb.num_nodes;
     if (pb.seg) { node_begin = pb.seg[pb.seg_index]; node_count = pb.seg[pb.seg_index + 1] - node_begin; }

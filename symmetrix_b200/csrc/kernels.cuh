@@ -677,7 +677,7 @@ __global__ void __launch_bounds__(kChannelBlock, tp_min_blocks<T>(LF, true)) tp_
 //   3 sender index outside [0, feature_rows)   4 sender type outside the model  5 r not finite, <= 0 or beyond r_cut
 //   6 r differs from |xyz| by more than 1e-6 relative
 constexpr int kNumInputChecks = 7;
-__global__ void validate_inputs_kernel(int N, long long E, int num_elements, int feature_rows, double r_cut,
+static __global__ void validate_inputs_kernel(int N, long long E, int num_elements, int feature_rows, double r_cut,
                                        const int* __restrict__ node_types, const int* __restrict__ num_neigh,
                                        const long long* __restrict__ first_neigh, const int* __restrict__ neigh_indices,
                                        const int* __restrict__ neigh_types, const double* __restrict__ xyz, const double* __restrict__ r,
@@ -1480,7 +1480,7 @@ struct ZblParams {
     const int* atomic_numbers;      // per model type
 };
 
-__global__ void zbl_kernel(int N, const int* __restrict__ node_types, const long long* __restrict__ first_neigh,
+static __global__ void zbl_kernel(int N, const int* __restrict__ node_types, const long long* __restrict__ first_neigh,
                            const int* __restrict__ neigh_types, const double* __restrict__ xyz, const double* __restrict__ r,
                            ZblParams z, double* __restrict__ node_energies, double* __restrict__ node_forces) {
     const double ce[4] = {-3.2, -0.9423, -0.4028, -0.2016};     // screening exponents, zbl.hpp:49-52
@@ -1608,12 +1608,12 @@ __global__ void density_scale_reverse_kernel(int N, int K, const int* __restrict
 // =============================================================================================
 // Small helpers
 // =============================================================================================
-__global__ void iota_kernel(int n, int* out) {
+static __global__ void iota_kernel(int n, int* out) {
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) out[i] = i;
 }
 
 // offsets[v] = first position in the sorted key array with key >= v, for v = 0..num_values
-__global__ void segment_offsets_kernel(long long n, const int* __restrict__ sorted_keys, int num_values, long long* __restrict__ offsets) {
+static __global__ void segment_offsets_kernel(long long n, const int* __restrict__ sorted_keys, int num_values, long long* __restrict__ offsets) {
     for (int v = blockIdx.x * blockDim.x + threadIdx.x; v <= num_values; v += gridDim.x * blockDim.x) {
         long long lo = 0, hi = n;
         while (lo < hi) {
@@ -1623,7 +1623,7 @@ __global__ void segment_offsets_kernel(long long n, const int* __restrict__ sort
         offsets[v] = lo;
     }
 }
-__global__ void segment_offsets_int_kernel(int n, const int* __restrict__ sorted_keys, int num_values, int* __restrict__ offsets) {
+static __global__ void segment_offsets_int_kernel(int n, const int* __restrict__ sorted_keys, int num_values, int* __restrict__ offsets) {
     for (int v = blockIdx.x * blockDim.x + threadIdx.x; v <= num_values; v += gridDim.x * blockDim.x) {
         int lo = 0, hi = n;
         while (lo < hi) {
@@ -1643,7 +1643,7 @@ __global__ void convert_kernel(long long n, const S* __restrict__ src, D* __rest
 // Per-atom forces from per-edge partial forces, without atomics:
 //   f[i] = - sum_{e in row i} nf[e] + sum_{e in in_edges(i)} nf[e]
 // (pair_symmetrix/pair_symmetrix_mace.cpp:334-347; symmetrix_calc.py:93-97)
-__global__ void atom_forces_kernel(int rows, int N, const long long* __restrict__ first_neigh, const long long* __restrict__ in_ptr,
+static __global__ void atom_forces_kernel(int rows, int N, const long long* __restrict__ first_neigh, const long long* __restrict__ in_ptr,
                                    const int* __restrict__ in_edge, const double* __restrict__ nf, double* __restrict__ f) {
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < rows; i += gridDim.x * blockDim.x) {
         double fx = 0, fy = 0, fz = 0;
@@ -1659,7 +1659,7 @@ __global__ void atom_forces_kernel(int rows, int N, const long long* __restrict_
 
 // Block-wise partial sums of {energy, virial xx yy zz xy xz yz}; partials[block][7].
 // Virial convention of pair_symmetrix_mace.cpp:349-368.
-__global__ void energy_virial_partial_kernel(int N, long long E, const double* __restrict__ node_energies, const double* __restrict__ xyz,
+static __global__ void energy_virial_partial_kernel(int N, long long E, const double* __restrict__ node_energies, const double* __restrict__ xyz,
                                              const double* __restrict__ nf, double* __restrict__ partials) {
     __shared__ double sh[7][256];
     double v[7] = {0, 0, 0, 0, 0, 0, 0};
@@ -1680,7 +1680,7 @@ __global__ void energy_virial_partial_kernel(int N, long long E, const double* _
     }
     if (threadIdx.x < 7) partials[blockIdx.x * 7 + threadIdx.x] = sh[threadIdx.x][0];
 }
-__global__ void energy_virial_final_kernel(int num_blocks, const double* __restrict__ partials, double* __restrict__ out7) {
+static __global__ void energy_virial_final_kernel(int num_blocks, const double* __restrict__ partials, double* __restrict__ out7) {
     if (threadIdx.x < 7) {
         double s = 0;
         for (int b = 0; b < num_blocks; ++b) s += partials[b * 7 + threadIdx.x];

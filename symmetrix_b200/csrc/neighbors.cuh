@@ -42,7 +42,7 @@ __device__ __forceinline__ int neigh_bin(const NeighGrid& g, const double* x, in
     return id;
 }
 
-__global__ void neigh_bin_kernel(int n, const double* __restrict__ pos, NeighGrid g, int* __restrict__ bin_of) {
+static __global__ void neigh_bin_kernel(int n, const double* __restrict__ pos, NeighGrid g, int* __restrict__ bin_of) {
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
         int b3[3];
         bin_of[i] = neigh_bin(g, pos + 3 * i, b3);
@@ -71,7 +71,7 @@ __device__ __forceinline__ unsigned long long neigh_key(int j, int n0, int n1, i
 // One thread per receiver atom. COUNT: number of edges of the row. Otherwise: write the keys of
 // the row, sort them (rows are short), then expand each key into the edge arrays.
 template <bool COUNT>
-__global__ void neigh_rows_kernel(int n, const double* __restrict__ pos, const int* __restrict__ types, NeighGrid g,
+static __global__ void neigh_rows_kernel(int n, const double* __restrict__ pos, const int* __restrict__ types, NeighGrid g,
                                   const int* __restrict__ bin_start, const int* __restrict__ sorted_atoms,
                                   int* __restrict__ num_neigh, const long long* __restrict__ first_neigh,
                                   unsigned long long* __restrict__ keys, int* __restrict__ neigh_indices,
@@ -140,10 +140,10 @@ __global__ void neigh_rows_kernel(int n, const double* __restrict__ pos, const i
     }
 }
 
-__global__ void neigh_iota_kernel(int n, int* out) {
+static __global__ void neigh_iota_kernel(int n, int* out) {
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) out[i] = i;
 }
-__global__ void neigh_offsets_kernel(int n, const int* __restrict__ sorted_keys, int num_values, int* __restrict__ offsets) {
+static __global__ void neigh_offsets_kernel(int n, const int* __restrict__ sorted_keys, int num_values, int* __restrict__ offsets) {
     for (int v = blockIdx.x * blockDim.x + threadIdx.x; v <= num_values; v += gridDim.x * blockDim.x) {
         int lo = 0, hi = n;
         while (lo < hi) {
