@@ -200,6 +200,38 @@ int smx_set_active_nodes(smx_handle h, int num_nodes, long* num_edges);
 int smx_resize_rows(smx_handle h, const char* name, int rows);
 int smx_device_ptr(smx_handle h, const char* name, void** ptr, long* count, int* elem_bytes);
 
+/* Halo rows as device kernels on the evaluator's stream -- the pack / unpack routines of the reference's pair style:
+ * pack_forward_comm / unpack_forward_comm / pack_reverse_comm / unpack_reverse_comm (pair_symmetrix_mace.cpp:194-238)
+ * and their device forms (pair_symmetrix_mace_kokkos.cpp:240-290, 351-367). `name` is "H1", "H1_adj", "Hm", "Hm_adj"
+ * (rows of num_LM * num_channels values in the evaluator's precision) or "atom_forces" (rows of 3 doubles, the array
+ * smx_atom_forces fills). `rows` (n row indices) and the buffers are device pointers; a buffer holds n rows in the
+ * array's own element type.
+ *   smx_halo_pack        buf[m, :] = array[rows[m], :]
+ *   smx_halo_unpack      array[rows[m], :] = buf[m, :]
+ *   smx_halo_unpack_add  array[rows[m], :] += buf[m, :], each row's contributions added in list order by one thread --
+ *                        the reference uses atomic adds here (pair_symmetrix_mace_kokkos.cpp:362-364); this one gives the
+ *                        same bits on every run, also when a row occurs more than once in the list.
+ * smx_atom_forces computes the per-atom forces of the current edge set (f[i] -= nf[ij], f[j] += nf[ij],
+ * pair_symmetrix_mace.cpp:334-347) into the device array "atom_forces" with at least `num_rows` rows, without copying
+ * them anywhere; smx_reduce_forces is this plus the copy to the caller. */
+int smx_halo_pack(smx_handle h, const char* name, const int* rows, int n, void* buf);
+int smx_halo_unpack(smx_handle h, const char* name, const int* rows, int n, const void* buf);
+int smx_halo_unpack_add(smx_handle h, const char* name, const int* rows, int n, const void* buf);
+int smx_atom_forces(smx_handle h, int num_rows);
+
+/* Receivers and edges the stages currently run on, and the receiver count the edge set was given or built with. The
+ * reference's stage methods take `num_nodes` and the neighbour arrays on every call (mace.hpp:44-145); here they are
+ * fixed by smx_begin / smx_restrict_nodes / smx_set_active_nodes, and a caller that mirrors the reference's argument
+ * lists checks its `num_nodes` against this. Any pointer may be NULL. */
+int smx_active_counts(smx_handle h, int* num_nodes, long* num_edges, int* built_nodes);
+
+/* Test switch for the bounded device-side waits (no counterpart in the reference, which has no such waits). With
+ * `polls` > 0 the first weight-tile wait of every CTA of the float32 tensor-core GEMM expects 16 bytes more than
+ * its copy delivers and gives up after `polls` polls: the kernel records the failure, releases its tensor memory and
+ * returns, and the next synchronising call reports SMX_ERR_CUDA. Nothing faults and the handle stays usable; 0 switches
+ * it off. */
+int smx_debug_expire_waits(smx_handle h, int polls);
+
 /* Input check. The reference trusts its callers (unchecked spline bin and gather indices, cubic_spline_set.cpp:31-32,
  * 55-56; mace.cpp:470-480); on a GPU an out-of-range sender index is a memory fault, so callers that cannot vouch for
  * their arrays call this after smx_begin / smx_build_neighbors and before the first stage. It counts, per kind, the
@@ -223,7 +255,9 @@ int smx_validate_inputs(smx_handle h, int feature_rows, long* counts, long* tota
  * 16,777,216 edges and as many nodes; larger inputs return SMX_ERR_INVALID_ARGUMENT with a message
  * in `errbuf` (capacity `errbuf_len`, may be NULL). All calls on one GPU share the scratch array,
  * which keeps the previous call's contents: calls whose kernels overlap on the device race. The first
- * call on each GPU looks up the array's device address; make it before any stream capture starts. */
+ * call on each GPU looks up the array's device address (and, with CUDA's lazy loading, may make the
+ * driver load the library's kernels, which is the driver's own allocation); make it before any
+ * stream capture starts. */
 int smx_energy_virial_noalloc(const double* node_energies, int num_nodes, const double* xyz,
                               const double* node_forces, long num_edges, double* out7, void* stream,
                               char* errbuf, int errbuf_len);

@@ -275,7 +275,10 @@ class MaceOracle:
                    + self.M1 @ self.H2_w_M1)
 
     def compute_readouts(self):                                     # mace.cpp:876-903, multilayer_perceptron.cpp:76-150
-        self.node_energies = self.atomic_energies[self.node_types].copy()
+        # adds into node_energies, which the caller zero-fills (mace.cpp:27-28, 880-890)
+        if getattr(self, "node_energies", None) is None or self.node_energies.shape[0] != self.N:
+            self.node_energies = np.zeros(self.N)
+        self.node_energies += self.atomic_energies[self.node_types]
         self.node_energies += self.H1[:self.N, 0] @ self.ro1
         self.H1_adj = np.zeros_like(self.H1)
         self.H1_adj[:self.N, 0] = self.ro1[None, :]
@@ -402,6 +405,7 @@ class MaceOracle:
     def compute_node_energies_forces(self, inp):                    # mace.cpp:17-64
         self._edges(inp)
         self.node_forces = np.zeros((self.r.size, 3))
+        self.node_energies = np.zeros(self.N)
         self.compute_Y(); self.compute_R0(); self.compute_A0(); self.compute_A0_scaled(); self.compute_M0(); self.compute_H1()
         self.compute_R1(); self.compute_Phi1(); self.compute_A1(); self.compute_A1_scaled(); self.compute_M1(); self.compute_H2()
         self.compute_readouts()

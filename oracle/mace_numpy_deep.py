@@ -147,6 +147,7 @@ class DeepMaceOracle(MaceOracle):
     def compute_node_energies_forces(self, inp):
         self._edges(inp)
         self.node_forces = np.zeros((self.r.size, 3))
+        self.node_energies = np.zeros(self.N)
         self.compute_Y(); self.compute_R0(); self.compute_A0(); self.compute_M0(); self.compute_H1()
         self.compute_Rm(); self.compute_Phim(); self.compute_Am(); self.compute_Mm(); self.compute_Hm()
         self.compute_R1(); self.compute_Phi1(); self.compute_A1(); self.compute_M1(); self.compute_H2()

@@ -22,6 +22,7 @@ EXPORTED_SYMBOLS = [
     "smx_last_device_ms", "smx_launch_count", "smx_build_neighbors", "smx_get_edges", "smx_compute_current",
     "smx_timer_start", "smx_timer_stop", "smx_set_profiling", "smx_stage_time", "smx_measure_fma_peak", "smx_measure_row_stream", "smx_validate_inputs",
     "smx_energy_virial_noalloc", "smx_sync", "smx_set_stream", "smx_restrict_nodes", "smx_set_active_nodes", "smx_resize_rows", "smx_device_ptr",
+    "smx_halo_pack", "smx_halo_unpack", "smx_halo_unpack_add", "smx_atom_forces", "smx_active_counts", "smx_debug_expire_waits",
 ]
 
 
@@ -82,6 +83,12 @@ def load():
     lib.smx_set_active_nodes.argtypes = [vp, ctypes.c_int, lp]
     lib.smx_resize_rows.argtypes = [vp, ctypes.c_char_p, ctypes.c_int]
     lib.smx_device_ptr.argtypes = [vp, ctypes.c_char_p, ctypes.POINTER(ctypes.c_void_p), lp, ctypes.POINTER(ctypes.c_int)]
+    lib.smx_halo_pack.argtypes = [vp, ctypes.c_char_p, ip, ctypes.c_int, vp]
+    lib.smx_halo_unpack.argtypes = [vp, ctypes.c_char_p, ip, ctypes.c_int, vp]
+    lib.smx_halo_unpack_add.argtypes = [vp, ctypes.c_char_p, ip, ctypes.c_int, vp]
+    lib.smx_atom_forces.argtypes = [vp, ctypes.c_int]
+    lib.smx_active_counts.argtypes = [vp, ctypes.POINTER(ctypes.c_int), lp, ctypes.POINTER(ctypes.c_int)]
+    lib.smx_debug_expire_waits.argtypes = [vp, ctypes.c_int]
     lib.smx_energy_virial_noalloc.argtypes = [dp, ctypes.c_int, dp, dp, ctypes.c_long, dp, vp, ctypes.c_char_p, ctypes.c_int]
     _lib = lib
     return lib

@@ -148,6 +148,35 @@ int smx_reduce_forces(smx_handle h, int num_rows, double* atom_forces, double* v
     return guarded(h, [&](smx::EvaluatorBase& e) { e.reduce_forces(num_rows, atom_forces, virial, energy, mem_space); });
 }
 
+int smx_atom_forces(smx_handle h, int num_rows) {
+    return guarded(h, [&](smx::EvaluatorBase& e) { e.atom_forces(num_rows); });
+}
+
+int smx_halo_pack(smx_handle h, const char* name, const int* rows, int n, void* dst) {
+    return guarded(h, [&](smx::EvaluatorBase& e) {
+        if (!name) throw smx::ArgError("smx_halo_pack: null name");
+        e.halo_pack(name, rows, n, dst);
+    });
+}
+int smx_halo_unpack(smx_handle h, const char* name, const int* rows, int n, const void* src) {
+    return guarded(h, [&](smx::EvaluatorBase& e) {
+        if (!name) throw smx::ArgError("smx_halo_unpack: null name");
+        e.halo_unpack(name, rows, n, src, false);
+    });
+}
+int smx_halo_unpack_add(smx_handle h, const char* name, const int* rows, int n, const void* src) {
+    return guarded(h, [&](smx::EvaluatorBase& e) {
+        if (!name) throw smx::ArgError("smx_halo_unpack_add: null name");
+        e.halo_unpack(name, rows, n, src, true);
+    });
+}
+int smx_active_counts(smx_handle h, int* num_nodes, long* num_edges, int* built_nodes) {
+    return guarded(h, [&](smx::EvaluatorBase& e) { e.active_counts(num_nodes, num_edges, built_nodes); });
+}
+int smx_debug_expire_waits(smx_handle h, int polls) {
+    return guarded(h, [&](smx::EvaluatorBase& e) { e.expire_waits(polls); });
+}
+
 int smx_last_device_ms(smx_handle h, double* ms) {
     return guarded(h, [&](smx::EvaluatorBase& e) { if (ms) *ms = e.last_ms; });
 }

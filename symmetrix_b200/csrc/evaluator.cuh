@@ -16,6 +16,7 @@
 #include <vector>
 
 #include <cub/cub.cuh>
+#include <nvtx3/nvToolsExt.h>
 
 #include "../../include/symmetrix_b200.h"
 #include "common.cuh"
@@ -57,6 +58,14 @@ static std::vector<T> spline_rows(const std::vector<double>& v, int K) {
     }
 }
 
+// NVTX range around a stage or a whole evaluation (visible in Nsight Systems timelines; costs nothing when no tool is attached).
+struct NvtxRange {
+    explicit NvtxRange(const char* name) { nvtxRangePushA(name); }
+    ~NvtxRange() { nvtxRangePop(); }
+    NvtxRange(const NvtxRange&) = delete;
+    NvtxRange& operator=(const NvtxRange&) = delete;
+};
+
 struct CastToLL {
     __host__ __device__ long long operator()(const int& v) const { return static_cast<long long>(v); }
 };
@@ -94,7 +103,10 @@ public:
     DevBuf<long long> first_neigh, in_ptr;
     DevBuf<int> perm, sorted_types, type_seg, iota, in_edge, sorted_senders;
     DevBuf<unsigned char> cub_tmp;
+    DevBuf<int> halo_iota, halo_rows, halo_pos;    // positions of an unpack-add list grouped by destination row
     int sender_rows = -1;
+    std::vector<long long> first_host;   // host copy of first_neigh for restrict_nodes (valid until the edge set changes)
+    bool first_host_valid = false;
 
     // per-call arrays
     DevBuf<T> Phi0, A0, A0_adj, Phi0_adj, M0, M0_adj, H1, H1_adj, Phi1, dPhi1, A1, A1_adj, M1, M1_adj, H2, H2_adj, Hmsg;
@@ -125,7 +137,7 @@ public:
         SMX_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
         SMX_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&host_ring), kProblemRing * sizeof(GemmProblem<T>), cudaHostAllocDefault));
         dev_ring.resize(kProblemRing, stream);
-        kernel_status.resize(1, stream);
+        kernel_status.resize(2, stream);      // [0] error code of a wait that ran out, [1] test switch (see gemm_rows_tcgen05_kernel)
         kernel_status.zero(stream);
         if (const char* t = std::getenv("SMX_TP_STAGED")) staged_reverse = std::string(t) != "0";
         if (const char* t = std::getenv("SMX_TYPE_ORDER")) type_order = std::string(t) != "0";
@@ -278,6 +290,7 @@ public:
         sender_rows = -1;
         have_edges = true;
         if (rescan) {
+            first_host_valid = false;
             // offsets of all receivers; a restricted set uses a prefix of this scan (entry n = edges of the first n)
             first_neigh.resize(static_cast<size_t>(N) + 1, stream);
             if (N > 0) {
@@ -845,6 +858,7 @@ public:
     void stage(const std::string& s, bool zero_dxyz, bool zero_H1_adj) override {
         require_edges();
         SMX_CUDA(cudaSetDevice(device));
+        NvtxRange range(s.c_str());
         if (s == "compute_Y" || s == "compute_R0" || s == "compute_R1") return;  // fused into the edge kernels
         if (s == "compute_A0") compute_A0();
         else if (s == "compute_ZBL") compute_ZBL();
@@ -903,9 +917,15 @@ public:
         require_edges();
         SMX_CUDA(cudaSetDevice(device));
         if (num_nodes < 0 || num_nodes > N_built) throw ArgError("restrict_nodes: num_nodes out of range");
-        long long e = 0;
-        SMX_CUDA(cudaMemcpyAsync(&e, first_neigh.p + num_nodes, sizeof(long long), cudaMemcpyDeviceToHost, stream));
-        SMX_CUDA(cudaStreamSynchronize(stream));
+        // The row offsets of an edge set are read back once (the only host synchronisation, at the first call after the
+        // edge set changed); every later switch of the receiver set is a host-side lookup.
+        if (!first_host_valid) {
+            first_host.resize(static_cast<size_t>(N_built) + 1);
+            SMX_CUDA(cudaMemcpyAsync(first_host.data(), first_neigh.p, first_host.size() * sizeof(long long), cudaMemcpyDeviceToHost, stream));
+            SMX_CUDA(cudaStreamSynchronize(stream));
+            first_host_valid = true;
+        }
+        const long long e = first_host[num_nodes];
         adopt_edges(num_nodes, static_cast<long>(e), keep_outputs, false);
         return static_cast<long>(e);
     }
@@ -923,10 +943,22 @@ public:
         if (name == "Hm") hm_rows = rows;
     }
     void* device_ptr(const std::string& name, long* count, int* elem_bytes) override {
+        if (name == "atom_forces") {
+            if (count) *count = static_cast<long>(atom_f.n);
+            if (elem_bytes) *elem_bytes = 8;
+            return atom_f.p;
+        }
         Field f = field(name);
         if (count) *count = static_cast<long>(f.t ? f.t->n : f.d->n);
         if (elem_bytes) *elem_bytes = f.t ? static_cast<int>(sizeof(T)) : 8;
         return f.t ? static_cast<void*>(f.t->p) : static_cast<void*>(f.d->p);
+    }
+    // Test switch: make the first weight-tile wait of every tcgen05 GEMM CTA run out after `polls` polls (0: normal operation).
+    void expire_waits(int polls) override {
+        SMX_CUDA(cudaSetDevice(device));
+        if (polls < 0) throw ArgError("expire_waits: negative poll count");
+        SMX_CUDA(cudaMemcpyAsync(kernel_status.p + 1, &polls, sizeof(int), cudaMemcpyHostToDevice, stream));
+        SMX_CUDA(cudaStreamSynchronize(stream));
     }
     // Synchronises the stream and reports a kernel whose bounded mbarrier wait ran out.
     void check_kernel_status() {
@@ -934,6 +966,11 @@ public:
         if (waits_in_flight) SMX_CUDA(cudaMemcpyAsync(&code, kernel_status.p, sizeof(int), cudaMemcpyDeviceToHost, stream));
         SMX_CUDA(cudaStreamSynchronize(stream));
         waits_in_flight = false;
+        if (code != 0) {
+            // re-arm the status word: later evaluations on this handle are judged on their own kernels
+            SMX_CUDA(cudaMemsetAsync(kernel_status.p, 0, sizeof(int), stream));
+            SMX_CUDA(cudaStreamSynchronize(stream));
+        }
         if (code != 0) throw CudaError("a bounded mbarrier wait ran out in a device kernel (code " + std::to_string(code) + "); results are invalid");
     }
     // Duration of one pass of row_stream_probe_kernel over the current edge set (best of three after a warm-up)
@@ -1020,7 +1057,16 @@ public:
             }
         }
         int mark = 0;
-        auto tick = [&]() { if (profiling) SMX_CUDA(cudaEventRecord(stage_events[mark++], stream)); };
+        NvtxRange whole("smx_compute");
+        struct StageRange { bool open = false; ~StageRange() { if (open) nvtxRangePop(); } } stage_range;
+        // one NVTX range per stage, closed when the next stage starts (or when an exception leaves this function)
+        auto tick = [&]() {
+            if (stage_range.open) nvtxRangePop();
+            stage_range.open = mark < kStages;
+            if (stage_range.open) nvtxRangePushA(names[mark]);
+            if (profiling) SMX_CUDA(cudaEventRecord(stage_events[mark], stream));
+            ++mark;
+        };
         SMX_CUDA(cudaEventRecord(ev0, stream));
         compute_ZBL();
         tick(); compute_A0(); compute_A_scaled(true); tick(); compute_M0(); tick(); compute_H1();
@@ -1130,21 +1176,81 @@ public:
         SMX_CUDA(cudaStreamSynchronize(stream));
     }
 
+    // Per-atom forces of the current edge set into the device array "atom_forces" (at least `rows` rows of 3), asynchronous.
+    void atom_forces(int rows) override {
+        require_edges();
+        SMX_CUDA(cudaSetDevice(device));
+        if (rows < N) throw ArgError("atom_forces: num_rows must be at least num_nodes");
+        ensure_sender_lists(std::max(rows, std::max(h1_rows, N)));
+        const int srows = sender_rows;
+        atom_f.resize(3 * static_cast<size_t>(srows), stream);
+        if (srows > 0) {
+            atom_forces_kernel<<<std::min((srows + 127) / 128, num_sms * 16), 128, 0, stream>>>(srows, N, first_neigh.p, in_ptr.p, in_edge.p,
+                                                                                              node_forces.p, atom_f.p);
+            check_launch("atom_forces_kernel");
+        }
+    }
+
+    // ------------------------------------------------------------------ halo rows (see rows_gather_kernel)
+    // Row width and storage of a named array that has halo rows: the feature arrays (num_LM * K values of T) and the
+    // per-atom forces (3 doubles).
+    template <typename F>
+    void with_halo_array(const std::string& name, F&& fn) {
+        if (name == "atom_forces") { fn(atom_f.p, atom_f.n, 3); return; }
+        if (name != "H1" && name != "H1_adj" && name != "Hm" && name != "Hm_adj")
+            throw ArgError("halo: only H1, Hm, their adjoints and atom_forces have halo rows");
+        Field f = field(name);
+        fn(f.t->p, f.t->n, model.num_LM * model.K);
+    }
+    static int copy_grid(long long total, int num_sms) { return static_cast<int>(std::min<long long>((total + 255) / 256, num_sms * 32LL)); }
+    void halo_pack(const std::string& name, const int* rows, int n, void* dst) override {
+        SMX_CUDA(cudaSetDevice(device));
+        if (n < 0 || (n > 0 && (!rows || !dst))) throw ArgError("halo_pack: bad arguments");
+        if (n == 0) return;
+        with_halo_array(name, [&](auto* p, size_t, int width) {
+            using U = std::remove_pointer_t<decltype(p)>;
+            const long long total = static_cast<long long>(n) * width;
+            rows_gather_kernel<U><<<copy_grid(total, num_sms), 256, 0, stream>>>(p, width, rows, total, static_cast<U*>(dst));
+        });
+        check_launch("rows_gather_kernel");
+    }
+    void halo_unpack(const std::string& name, const int* rows, int n, const void* src, bool add) override {
+        SMX_CUDA(cudaSetDevice(device));
+        if (n < 0 || (n > 0 && (!rows || !src))) throw ArgError("halo_unpack: bad arguments");
+        if (n == 0) return;
+        if (add) {
+            // group the list positions by destination row (stable), so each row is summed by one thread in list order
+            halo_iota.resize(n, stream); halo_rows.resize(n, stream); halo_pos.resize(n, stream);
+            iota_kernel<<<std::min(1024, (n + 255) / 256), 256, 0, stream>>>(n, halo_iota.p);
+            check_launch("iota");
+            size_t bytes = 0;
+            SMX_CUDA(cub::DeviceRadixSort::SortPairs(nullptr, bytes, rows, halo_rows.p, halo_iota.p, halo_pos.p, n, 0, 32, stream));
+            cub_tmp.resize(bytes, stream);
+            SMX_CUDA(cub::DeviceRadixSort::SortPairs(cub_tmp.p, bytes, rows, halo_rows.p, halo_iota.p, halo_pos.p, n, 0, 32, stream));
+            launches += 1;
+        }
+        with_halo_array(name, [&](auto* p, size_t, int width) {
+            using U = std::remove_pointer_t<decltype(p)>;
+            const long long total = static_cast<long long>(n) * width;
+            if (add) rows_scatter_add_kernel<U><<<copy_grid(total, num_sms), 256, 0, stream>>>(p, width, halo_rows.p, halo_pos.p, n, static_cast<const U*>(src));
+            else rows_scatter_kernel<U><<<copy_grid(total, num_sms), 256, 0, stream>>>(p, width, rows, total, static_cast<const U*>(src));
+        });
+        check_launch(add ? "rows_scatter_add_kernel" : "rows_scatter_kernel");
+    }
+    void active_counts(int* nodes, long* edges, int* built_nodes) const override {
+        if (nodes) *nodes = N;
+        if (edges) *edges = E;
+        if (built_nodes) *built_nodes = N_built;
+    }
+
     void reduce_forces(int rows, double* f, double* virial, double* energy, int mem_space) override {
         require_edges();
         SMX_CUDA(cudaSetDevice(device));
         if (rows < N) throw ArgError("reduce_forces: num_rows must be at least num_nodes");
         const cudaMemcpyKind kind = mem_space == SMX_DEVICE ? cudaMemcpyDeviceToDevice : cudaMemcpyDeviceToHost;
         if (f) {
-            ensure_sender_lists(std::max(rows, std::max(h1_rows, N)));
-            const int srows = sender_rows;
-            atom_f.resize(3 * static_cast<size_t>(srows), stream);
-            if (srows > 0) {
-                atom_forces_kernel<<<std::min((srows + 127) / 128, num_sms * 16), 128, 0, stream>>>(srows, N, first_neigh.p, in_ptr.p, in_edge.p,
-                                                                                                  node_forces.p, atom_f.p);
-                check_launch("atom_forces_kernel");
-                SMX_CUDA(cudaMemcpyAsync(f, atom_f.p, 3 * static_cast<size_t>(rows) * sizeof(double), kind, stream));
-            }
+            atom_forces(rows);
+            if (rows > 0) SMX_CUDA(cudaMemcpyAsync(f, atom_f.p, 3 * static_cast<size_t>(rows) * sizeof(double), kind, stream));
         }
         if (virial || energy) {
             const int blocks = std::max(1, std::min(num_sms * 4, static_cast<int>((std::max<long>(E, N) + 255) / 256)));

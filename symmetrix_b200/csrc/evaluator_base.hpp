@@ -38,6 +38,11 @@ public:
     virtual long get_array(const std::string& name, double* dst, long cap, int mem_space) = 0;
     virtual void set_array(const std::string& name, const double* src, long n, int mem_space) = 0;
     virtual void reduce_forces(int rows, double* f, double* virial, double* energy, int mem_space) = 0;
+    virtual void atom_forces(int rows) = 0;
+    virtual void halo_pack(const std::string& name, const int* rows, int n, void* dst) = 0;
+    virtual void halo_unpack(const std::string& name, const int* rows, int n, const void* src, bool add) = 0;
+    virtual void expire_waits(int polls) = 0;
+    virtual void active_counts(int* nodes, long* edges, int* built_nodes) const = 0;
     virtual long build_neighbors(int natoms, const double* pos, const int* types, const double* cell, const int* pbc,
                                  double r_cut, int mem_space) = 0;
     virtual void get_edges(int* num_neigh, int* neigh_indices, int* neigh_types, int* shifts, double* xyz, double* r, int mem_space) = 0;

@@ -109,7 +109,10 @@ __device__ __forceinline__ void tc5_ld32(uint32_t taddr, uint32_t (&v)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-// `status` receives a non-zero code if a bounded wait ran out (1: tensor core, 2: weight tile copy).
+// `status[0]` receives a non-zero code if a bounded wait ran out (1: tensor core, 2: weight tile copy).
+// `status[1]` is a test switch, zero in normal operation: when set, the first weight-tile wait of every CTA expects 16
+// bytes more than the copy delivers and polls only `status[1]` times, so the wait runs out quickly and the error path
+// (status word, TMEM release, host-side error) can be exercised without any fault.
 // Every problem carries the operand image of its weight matrix in B_image.
 static __global__ void __launch_bounds__(kTc5Threads) gemm_rows_tcgen05_kernel(const GemmProblem<float>* __restrict__ problems, int* __restrict__ status) {
     const GemmProblem<float> pb = problems[blockIdx.z];
@@ -160,6 +163,8 @@ static __global__ void __launch_bounds__(kTc5Threads) gemm_rows_tcgen05_kernel(c
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_d = tmem_base_slot;
     const uint32_t idesc = tc5_instr_desc();
+    const int expire_test = status[1];
+    const unsigned spin_limit = expire_test > 0 ? static_cast<unsigned>(expire_test) : kMbarSpinLimit;
 
     const int num_chunks = (pb.Kd + kTc5BK - 1) / kTc5BK;
     const float* image = pb.B_image + static_cast<size_t>(blockIdx.y) * num_chunks * 2 * kTc5TileFloats;
@@ -195,12 +200,12 @@ static __global__ void __launch_bounds__(kTc5Threads) gemm_rows_tcgen05_kernel(c
     for (int ch = 0; ch < num_chunks; ++ch) {
         // the MMAs of the previous chunk read the tiles: wait for them before overwriting
         if (ch > 0) {
-            if (!*reinterpret_cast<volatile int*>(&failed) && !mbar_wait(&mma_bar, mma_par)) failed = 1;
+            if (!*reinterpret_cast<volatile int*>(&failed) && !mbar_wait(&mma_bar, mma_par, spin_limit)) atomicMax(&failed, 1);
             mma_par ^= 1u;
         }
         __syncthreads();
         if (tid == 0 && !failed) {
-            mbar_expect_tx(&b_bar, 2 * kTc5TileBytes);
+            mbar_expect_tx(&b_bar, 2 * kTc5TileBytes + ((expire_test > 0 && ch == 0) ? 16 : 0));
             bulk_copy_g2s(sB, image + static_cast<size_t>(ch) * 2 * kTc5TileFloats, 2 * kTc5TileBytes, &b_bar);
         }
 #pragma unroll
@@ -221,8 +226,8 @@ static __global__ void __launch_bounds__(kTc5Threads) gemm_rows_tcgen05_kernel(c
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncthreads();
         if (tid == 0 && !failed) {
-            if (!mbar_wait(&b_bar, b_par)) {
-                failed = 2;
+            if (!mbar_wait(&b_bar, b_par, spin_limit)) {
+                atomicMax(&failed, 2);
             } else {
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t a_hi = smem_u32(sA_hi), a_lo = smem_u32(sA_lo), b_hi = smem_u32(sB), b_lo = smem_u32(sB + kTc5TileBytes);
@@ -240,7 +245,7 @@ static __global__ void __launch_bounds__(kTc5Threads) gemm_rows_tcgen05_kernel(c
         b_par ^= 1u;
     }
     __syncthreads();                                             // `failed` as thread 0 left it
-    if (!*reinterpret_cast<volatile int*>(&failed) && !mbar_wait(&mma_bar, mma_par)) failed = 1;
+    if (!*reinterpret_cast<volatile int*>(&failed) && !mbar_wait(&mma_bar, mma_par, spin_limit)) atomicMax(&failed, 1);
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     if (!failed) {
@@ -285,7 +290,7 @@ static __global__ void __launch_bounds__(kTc5Threads) gemm_rows_tcgen05_kernel(c
     } else if (tid == 0) {
         atomicMax(status, failed);
         // a weight-tile copy that may still be in flight gets one more bounded wait before the CTA exits
-        mbar_wait(&b_bar, b_par ^ 1u);
+        mbar_wait(&b_bar, b_par ^ 1u, spin_limit);
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();

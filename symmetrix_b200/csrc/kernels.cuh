@@ -82,9 +82,9 @@ __device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned
     asm volatile("{\n\t.reg .b64 t;\n\tmbarrier.arrive.expect_tx.shared::cta.b64 t, [%0], %1;\n\t}" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
 constexpr unsigned kMbarSpinLimit = 1u << 22;
-__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity, unsigned limit = kMbarSpinLimit) {
     const uint32_t addr = smem_u32(bar);
-    for (unsigned spin = 0; spin < kMbarSpinLimit; ++spin) {
+    for (unsigned spin = 0; spin < limit; ++spin) {
         uint32_t done;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
@@ -1654,6 +1654,48 @@ static __global__ void atom_forces_kernel(int rows, int N, const long long* __re
             fx += nf[3 * e]; fy += nf[3 * e + 1]; fz += nf[3 * e + 2];
         }
         f[3 * i] = fx; f[3 * i + 1] = fy; f[3 * i + 2] = fz;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Halo rows of a decomposed run (what the reference's pair style does in pack_forward_comm / unpack_forward_comm /
+// pack_reverse_comm / unpack_reverse_comm, pair_symmetrix/pair_symmetrix_mace.cpp:194-238, and as device kernels in
+// pair_symmetrix_mace_kokkos.cpp:240-290, 351-367). Rows of `width` values, one thread per value.
+//   gather:       buf[m, :]        = array[rows[m], :]
+//   scatter:      array[rows[m], :] = buf[m, :]
+//   scatter_add:  array[row, :]   += sum of buf[m, :] over the positions m with rows[m] == row, in ascending m
+// The reference adds with atomics (order of the additions undefined); here the positions are grouped by row with a
+// stable sort (`sorted_rows`, `sorted_pos`) and one thread adds a row's contributions in list order, so two runs give
+// the same bits even when a row occurs several times in the list (an atom that is a ghost of the same peer twice).
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void rows_gather_kernel(const T* __restrict__ array, int width, const int* __restrict__ rows, long long total, T* __restrict__ buf) {
+    for (long long t = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; t < total; t += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const long long m = t / width;
+        const int c = static_cast<int>(t - m * width);
+        buf[t] = array[static_cast<size_t>(rows[m]) * width + c];
+    }
+}
+template <typename T>
+__global__ void rows_scatter_kernel(T* __restrict__ array, int width, const int* __restrict__ rows, long long total, const T* __restrict__ buf) {
+    for (long long t = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; t < total; t += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const long long m = t / width;
+        const int c = static_cast<int>(t - m * width);
+        array[static_cast<size_t>(rows[m]) * width + c] = buf[t];
+    }
+}
+template <typename T>
+__global__ void rows_scatter_add_kernel(T* __restrict__ array, int width, const int* __restrict__ sorted_rows, const int* __restrict__ sorted_pos,
+                                        int n, const T* __restrict__ buf) {
+    const long long total = static_cast<long long>(n) * width;
+    for (long long t = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; t < total; t += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int s = static_cast<int>(t / width);
+        const int c = static_cast<int>(t - static_cast<long long>(s) * width);
+        const int row = sorted_rows[s];
+        if (s > 0 && sorted_rows[s - 1] == row) continue;        // not the first list position of this row
+        T acc = array[static_cast<size_t>(row) * width + c];
+        for (int q = s; q < n && sorted_rows[q] == row; ++q) acc += buf[static_cast<size_t>(sorted_pos[q]) * width + c];
+        array[static_cast<size_t>(row) * width + c] = acc;
     }
 }
 

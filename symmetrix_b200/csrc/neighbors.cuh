@@ -7,7 +7,10 @@
 //   keep iff (d0*d0 + d1*d1) + d2*d2 < r_cut*r_cut, excluding i == j with a zero shift
 // Rows are ordered by (sender index, shift code), so the list is a pure function of its inputs.
 // Candidates come from a uniform grid over fractional coordinates whose cells are at least
-// r_cut(1+1e-9) thick; positions are expected inside the cell (wrap them first).
+// r_cut(1+1e-9) thick. Positions need not lie inside the cell: along a periodic axis an atom is binned by its
+// wrapped fractional coordinate, and the whole cell vectors w_i it is away from the cell are folded into the
+// integer shift of its edges (n = n' + w_i - w_j for the image n' found between the wrapped positions), so xyz
+// is still formed from the positions as given. Along a non-periodic axis outliers go to the edge bins.
 #pragma once
 
 #include <cuda_runtime.h>
@@ -29,11 +32,16 @@ struct NeighGrid {
     double rc2;
 };
 
-__device__ __forceinline__ int neigh_bin(const NeighGrid& g, const double* x, int* b3) {
+// Bin of an atom and (w3) the whole cell vectors its position is away from the cell along the periodic axes.
+__device__ __forceinline__ int neigh_bin(const NeighGrid& g, const double* x, int* b3, int* w3) {
     int id = 0;
 #pragma unroll
     for (int a = 0; a < 3; ++a) {
-        const double s = x[0] * g.inv[0 * 3 + a] + x[1] * g.inv[1 * 3 + a] + x[2] * g.inv[2 * 3 + a];
+        double s = x[0] * g.inv[0 * 3 + a] + x[1] * g.inv[1 * 3 + a] + x[2] * g.inv[2 * 3 + a];
+        const double wf = g.pbc[a] ? floor(s) : 0.0;
+        // far outliers are clamped here and rejected by the shift-range check of neigh_rows_kernel
+        w3[a] = static_cast<int>(wf < -1e6 ? -1e6 : (wf > 1e6 ? 1e6 : wf));
+        s -= wf;
         int b = static_cast<int>(floor(s * g.nb[a]));
         b = b < 0 ? 0 : (b >= g.nb[a] ? g.nb[a] - 1 : b);
         b3[a] = b;
@@ -42,10 +50,11 @@ __device__ __forceinline__ int neigh_bin(const NeighGrid& g, const double* x, in
     return id;
 }
 
-static __global__ void neigh_bin_kernel(int n, const double* __restrict__ pos, NeighGrid g, int* __restrict__ bin_of) {
+static __global__ void neigh_bin_kernel(int n, const double* __restrict__ pos, NeighGrid g, int* __restrict__ bin_of,
+                                        int* __restrict__ wrap) {
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
         int b3[3];
-        bin_of[i] = neigh_bin(g, pos + 3 * i, b3);
+        bin_of[i] = neigh_bin(g, pos + 3 * i, b3, wrap + 3 * i);
     }
 }
 
@@ -63,8 +72,11 @@ __device__ __forceinline__ bool neigh_test(const NeighGrid& g, const double* xi,
     return *r2 < g.rc2;
 }
 
+// Sort key of an edge inside its row: sender first, then the shift in lexicographic order. Shifts are kept in
+// 10 bits per axis (|n| <= kNeighMaxShift).
+constexpr int kNeighMaxShift = 511;
 __device__ __forceinline__ unsigned long long neigh_key(int j, int n0, int n1, int n2) {
-    const unsigned long long code = (static_cast<unsigned long long>(n0 + 64) * 128 + (n1 + 64)) * 128 + (n2 + 64);
+    const unsigned long long code = (static_cast<unsigned long long>(n0 + 512) * 1024 + (n1 + 512)) * 1024 + (n2 + 512);
     return (static_cast<unsigned long long>(j) << 32) | code;
 }
 
@@ -72,15 +84,15 @@ __device__ __forceinline__ unsigned long long neigh_key(int j, int n0, int n1, i
 // the row, sort them (rows are short), then expand each key into the edge arrays.
 template <bool COUNT>
 static __global__ void neigh_rows_kernel(int n, const double* __restrict__ pos, const int* __restrict__ types, NeighGrid g,
-                                  const int* __restrict__ bin_start, const int* __restrict__ sorted_atoms,
-                                  int* __restrict__ num_neigh, const long long* __restrict__ first_neigh,
+                                  const int* __restrict__ bin_start, const int* __restrict__ sorted_atoms, const int* __restrict__ wrap,
+                                  int* __restrict__ shift_overflow, int* __restrict__ num_neigh, const long long* __restrict__ first_neigh,
                                   unsigned long long* __restrict__ keys, int* __restrict__ neigh_indices,
                                   int* __restrict__ neigh_types, int* __restrict__ shifts, double* __restrict__ xyz,
                                   double* __restrict__ r) {
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
         const double xi[3] = {pos[3 * i], pos[3 * i + 1], pos[3 * i + 2]};
-        int b3[3];
-        neigh_bin(g, xi, b3);
+        int b3[3], wi[3];
+        neigh_bin(g, xi, b3, wi);
         long long out = COUNT ? 0 : first_neigh[i];
         const long long row_begin = out;
         int count = 0;
@@ -103,9 +115,12 @@ static __global__ void neigh_rows_kernel(int n, const double* __restrict__ pos, 
                     for (int s = bin_start[bin]; s < bin_start[bin + 1]; ++s) {
                         const int j = sorted_atoms[s];
                         if (j == i && n0 == 0 && n1 == 0 && n2 == 0) continue;
+                        // shift between the positions as given: image between the wrapped positions + the two wraps
+                        const int m0 = n0 + wi[0] - wrap[3 * j], m1 = n1 + wi[1] - wrap[3 * j + 1], m2 = n2 + wi[2] - wrap[3 * j + 2];
                         double d[3], r2;
-                        if (neigh_test(g, xi, pos + 3 * j, n0, n1, n2, d, &r2)) {
-                            if (!COUNT) keys[out++] = neigh_key(j, n0, n1, n2);
+                        if (neigh_test(g, xi, pos + 3 * j, m0, m1, m2, d, &r2)) {
+                            if (COUNT && (abs(m0) > kNeighMaxShift || abs(m1) > kNeighMaxShift || abs(m2) > kNeighMaxShift)) *shift_overflow = 1;
+                            if (!COUNT) keys[out++] = neigh_key(j, m0, m1, m2);
                             ++count;
                         }
                     }
@@ -126,8 +141,8 @@ static __global__ void neigh_rows_kernel(int n, const double* __restrict__ pos, 
                 const unsigned long long key = keys[e];
                 const int j = static_cast<int>(key >> 32);
                 const unsigned int code = static_cast<unsigned int>(key & 0xffffffffu);
-                const int n2 = static_cast<int>(code % 128) - 64, n1 = static_cast<int>((code / 128) % 128) - 64,
-                          n0 = static_cast<int>(code / (128 * 128)) - 64;
+                const int n2 = static_cast<int>(code % 1024) - 512, n1 = static_cast<int>((code / 1024) % 1024) - 512,
+                          n0 = static_cast<int>(code / (1024 * 1024)) - 512;
                 double d[3], r2;
                 neigh_test(g, xi, pos + 3 * j, n0, n1, n2, d, &r2);
                 neigh_indices[e] = j;
@@ -161,7 +176,7 @@ struct NeighCast {
 class NeighborBuilder {
 public:
     DevBuf<double> d_pos;
-    DevBuf<int> bin_of, sorted_bins, sorted_atoms, iota, bin_start;
+    DevBuf<int> bin_of, sorted_bins, sorted_atoms, iota, bin_start, wrap, overflow;
     DevBuf<long long> first;
     DevBuf<unsigned long long> keys;
     DevBuf<unsigned char> tmp;
@@ -212,7 +227,10 @@ public:
         const int blocks = std::min(4096, (n + 127) / 128);
         bin_of.resize(n, stream); sorted_bins.resize(n, stream); sorted_atoms.resize(n, stream); iota.resize(n, stream);
         bin_start.resize(static_cast<size_t>(nbins) + 1, stream);
-        neigh_bin_kernel<<<blocks, 128, 0, stream>>>(n, dpos, g, bin_of.p);
+        wrap.resize(3 * static_cast<size_t>(n), stream);
+        overflow.resize(1, stream);
+        overflow.zero(stream);
+        neigh_bin_kernel<<<blocks, 128, 0, stream>>>(n, dpos, g, bin_of.p, wrap.p);
         neigh_iota_kernel<<<blocks, 128, 0, stream>>>(n, iota.p);
         launches += 2;
         int bits = 1;
@@ -223,7 +241,7 @@ public:
         SMX_CUDA(cub::DeviceRadixSort::SortPairs(tmp.p, bytes, bin_of.p, sorted_bins.p, iota.p, sorted_atoms.p, n, 0, bits, stream));
         neigh_offsets_kernel<<<std::min(1024, (nbins + 128) / 128), 128, 0, stream>>>(n, sorted_bins.p, nbins, bin_start.p);
         launches += 2;
-        neigh_rows_kernel<true><<<blocks, 128, 0, stream>>>(n, dpos, d_types, g, bin_start.p, sorted_atoms.p, num_neigh.p, nullptr, nullptr,
+        neigh_rows_kernel<true><<<blocks, 128, 0, stream>>>(n, dpos, d_types, g, bin_start.p, sorted_atoms.p, wrap.p, overflow.p, num_neigh.p, nullptr, nullptr,
                                                           nullptr, nullptr, nullptr, nullptr, nullptr);
         launches += 1;
         first.resize(static_cast<size_t>(n) + 1, stream);
@@ -233,17 +251,19 @@ public:
         SMX_CUDA(cub::DeviceScan::ExclusiveSum(tmp.p, bytes, it, first.p, n, stream));
         launches += 1;
         long long last_first = 0;
-        int last_count = 0;
+        int last_count = 0, shift_overflow = 0;
+        SMX_CUDA(cudaMemcpyAsync(&shift_overflow, overflow.p, sizeof(int), cudaMemcpyDeviceToHost, stream));
         SMX_CUDA(cudaMemcpyAsync(&last_first, first.p + (n - 1), sizeof(long long), cudaMemcpyDeviceToHost, stream));
         SMX_CUDA(cudaMemcpyAsync(&last_count, num_neigh.p + (n - 1), sizeof(int), cudaMemcpyDeviceToHost, stream));
         SMX_CUDA(cudaStreamSynchronize(stream));
+        if (shift_overflow) throw ArgError("build_neighbors: an atom lies more than 500 cell lengths outside the cell along a periodic axis");
         const long long total = last_first + last_count;
         num_edges = static_cast<long>(total);
         keys.resize(total, stream);
         neigh_indices.resize(total, stream); neigh_types.resize(total, stream); shifts.resize(3 * total, stream);
         xyz.resize(3 * total, stream); r.resize(total, stream);
         if (total > 0) {
-            neigh_rows_kernel<false><<<blocks, 128, 0, stream>>>(n, dpos, d_types, g, bin_start.p, sorted_atoms.p, nullptr, first.p, keys.p,
+            neigh_rows_kernel<false><<<blocks, 128, 0, stream>>>(n, dpos, d_types, g, bin_start.p, sorted_atoms.p, wrap.p, overflow.p, nullptr, first.p, keys.p,
                                                                neigh_indices.p, neigh_types.p, shifts.p, xyz.p, r.p);
             launches += 1;
         }

@@ -168,8 +168,9 @@ class SlabRank:
         self.types = np.array([zmap[int(z)] for z in plan.numbers], dtype=np.int32)
         self.r_cut = r_cut
         self.device = self._device()
-        self.send_idx = {q: torch.as_tensor(np.ascontiguousarray(r), dtype=torch.long, device=self.device) for q, r in plan.send_rows.items()}
-        self.recv_idx = {q: torch.as_tensor(np.ascontiguousarray(r), dtype=torch.long, device=self.device) for q, r in plan.recv_rows.items()}
+        self.send_idx = {q: torch.as_tensor(np.ascontiguousarray(r), dtype=torch.int32, device=self.device) for q, r in plan.send_rows.items()}
+        self.recv_idx = {q: torch.as_tensor(np.ascontiguousarray(r), dtype=torch.int32, device=self.device) for q, r in plan.recv_rows.items()}
+        self.has_zbl = bool(getattr(backend, "has_zbl", False))
         self.num_edges = 0
         # on a GPU the evaluator shares torch's current stream: pack / unpack kernels, NCCL and the evaluator's kernels are
         # then ordered by the stream and no host synchronisation is needed between phases
@@ -198,11 +199,21 @@ class SlabRank:
         self.num_edges = self.ev.restrict_nodes(self.n_layer0)
 
     def begin_step(self):
-        """Re-arm the current edge set (zero node energies / partial forces) for another evaluation."""
+        """Re-arm the current edge set (zero node energies / partial forces) for another evaluation, then the pair
+        repulsion on the owned atoms (pair_symmetrix_mace.cpp:449-452; owned atoms only in recompute mode, :667-670)."""
         self.ev.restrict_nodes(self.n_layer0)
+        if self.has_zbl:
+            if self.n_layer0 != self.plan.n_own:
+                self.ev.set_active_nodes(self.plan.n_own)
+                self._run("compute_ZBL")
+                self.ev.set_active_nodes(self.n_layer0)
+            else:
+                self._run("compute_ZBL")
 
+    # The density-normalisation stages (compute/reverse_A0_scaled, _A1_scaled) sit where the reference has them
+    # (pair_symmetrix_mace.cpp:458,476,486,494 and :674,682,691,697); they do nothing for models without them.
     def forward_layer0(self):
-        for stage in ("compute_A0", "compute_M0", "compute_H1"):
+        for stage in ("compute_A0", "compute_A0_scaled", "compute_M0", "compute_H1"):
             self._run(stage)
         if self.recompute:
             self.ev.set_active_nodes(self.n_block[1])      # next block on fewer receivers; H1 keeps its ghost rows
@@ -219,34 +230,29 @@ class SlabRank:
         else:
             self.ev.resize_rows("Hm", self.rows)
 
-    def _rows_view(self, name):
-        return self.ev.device_view(name).view(-1, self.width)
-
+    # Halo rows are packed and unpacked by the evaluator's own kernels on its stream (smx_halo_pack / _unpack /
+    # _unpack_add); what travels between the ranks are the packed buffers.
     def pack_forward(self, peer, name="H1"):
-        if not self.shared_stream:
-            self.ev.sync()
-        return self._rows_view(name).index_select(0, self.send_idx[peer]).contiguous()
+        return self.ev.halo_pack(name, self.send_idx[peer])
 
     def unpack_forward(self, peer, buf, name="H1"):
-        self._rows_view(name).index_copy_(0, self.recv_idx[peer], buf.to(self._rows_view(name).dtype))
+        self.ev.halo_unpack(name, self.recv_idx[peer], buf)
 
     def layer1_and_reverse(self):
         self._sync_torch()
-        for stage in ("compute_Phi1", "compute_A1", "compute_M1", "compute_H2", "compute_readouts"):
+        for stage in ("compute_Phi1", "compute_A1", "compute_A1_scaled", "compute_M1", "compute_H2", "compute_readouts"):
             self._run(stage)
         self._run("reverse_H2", True, False)
         self._run("reverse_M1")
+        self._run("reverse_A1_scaled", False, True)
         self._run("reverse_A1")
         self._run("reverse_Phi1", False, False)
 
     def pack_reverse(self, peer, name="H1_adj"):
-        if not self.shared_stream:
-            self.ev.sync()
-        return self._rows_view(name).index_select(0, self.recv_idx[peer]).contiguous()
+        return self.ev.halo_pack(name, self.recv_idx[peer])
 
     def unpack_reverse(self, peer, buf, name="H1_adj"):
-        v = self._rows_view(name)
-        v.index_add_(0, self.send_idx[peer], buf.to(v.dtype))
+        self.ev.halo_unpack(name, self.send_idx[peer], buf, add=True)     # fixed order of additions: reproducible bits
 
     def reverse_middle(self):
         self._sync_torch()
@@ -261,24 +267,21 @@ class SlabRank:
         self._sync_torch()
         if self.recompute:
             self.ev.set_active_nodes(self.n_layer0)        # the partial H1_adj of the ghosts goes through layer 0 here
-        for stage in ("reverse_H1", "reverse_M0", "reverse_A0"):
+        for stage in ("reverse_H1", "reverse_M0", "reverse_A0_scaled", "reverse_A0"):
             self._run(stage)
-        if self.shared_stream:
-            # results stay on the device: no host synchronisation before the force-row exchange
-            self.forces, self.virial, self.energy = self.ev.reduce_forces(num_rows=self.rows, device=True)
-        else:
-            forces, virial, energy = self.ev.reduce_forces(num_rows=self.rows)
-            self.forces = self.torch.as_tensor(forces, device=self.device)
-            self.virial, self.energy = virial, energy
+        # per-atom forces stay in the evaluator's "atom_forces" array; on a GPU energy and virial stay on the device too,
+        # so there is no host synchronisation before the force-row exchange
+        self.ev.atom_forces(self.rows)
+        _, self.virial, self.energy = self.ev.reduce_forces(num_rows=self.rows, want_forces=False, device=self.shared_stream)
 
     def pack_forces(self, peer):
-        return self.forces.index_select(0, self.recv_idx[peer]).contiguous()
+        return self.ev.halo_pack("atom_forces", self.recv_idx[peer])
 
     def unpack_forces(self, peer, buf):
-        self.forces.index_add_(0, self.send_idx[peer], buf)
+        self.ev.halo_unpack("atom_forces", self.send_idx[peer], buf, add=True)
 
     def owned_forces(self):
-        return self.forces[: self.plan.n_own]
+        return self.ev.device_view("atom_forces").view(-1, 3)[: self.plan.n_own].clone()
 
     def _sync_torch(self):
         if self.device != "cpu" and not self.shared_stream:
@@ -355,8 +358,11 @@ def evaluate_decomposed(ranks, dist=None):
         t = sum(torch.cat([r.energy, r.virial]) for r in ranks)      # seven float64 values on the device
         if dist is not None:
             dist.all_reduce(t)
+        owned = [r.owned_forces() for r in ranks]
         vals = t.cpu().numpy()                                      # the only host synchronisation of the step
-        return float(vals[0]), vals[1:], [r.owned_forces() for r in ranks]
+        for r in ranks:
+            r.ev.sync()                                             # reports a device-side wait that ran out during the step
+        return float(vals[0]), vals[1:], owned
     energy = sum(r.energy for r in ranks)
     virial = sum(np.asarray(r.virial) for r in ranks)
     if dist is not None:

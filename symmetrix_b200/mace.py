@@ -311,6 +311,43 @@ class MACE:
     def resize_rows(self, name: str, rows: int) -> None:
         self._check(self._lib.smx_resize_rows(self._h, name.encode(), int(rows)))
 
+    # Halo rows of a decomposed run, as kernels on the evaluator's stream (smx_halo_pack / _unpack / _unpack_add).
+    # `rows` is an int32 CUDA tensor of row indices; buffers are CUDA tensors of the array's own element type.
+    def _halo_dtype(self, name: str):
+        import torch
+        return torch.float64 if name == "atom_forces" or self.dtype == "float64" else torch.float32
+
+    def halo_pack(self, name: str, rows):
+        """``buf[m] = array[rows[m]]`` for the named array ("H1", "H1_adj", "Hm", "Hm_adj" or "atom_forces")."""
+        import torch
+        width = 3 if name == "atom_forces" else self.num_LM * self.num_channels
+        buf = torch.empty((rows.numel(), width), dtype=self._halo_dtype(name), device=rows.device)
+        self._check(self._lib.smx_halo_pack(self._h, name.encode(), ctypes.c_void_p(rows.data_ptr()), rows.numel(),
+                                            ctypes.c_void_p(buf.data_ptr())))
+        return buf
+
+    def halo_unpack(self, name: str, rows, buf, add: bool = False) -> None:
+        """``array[rows[m]] = buf[m]`` or, with ``add``, ``+=`` with each row's contributions added in list order
+        (bitwise reproducible, also when a row occurs several times)."""
+        if buf.dtype != self._halo_dtype(name) or not buf.is_contiguous():
+            buf = buf.to(self._halo_dtype(name)).contiguous()
+        fn = self._lib.smx_halo_unpack_add if add else self._lib.smx_halo_unpack
+        self._check(fn(self._h, name.encode(), ctypes.c_void_p(rows.data_ptr()), rows.numel(), ctypes.c_void_p(buf.data_ptr())))
+
+    def atom_forces(self, num_rows: int) -> None:
+        """Per-atom forces of the current edge set into the device array "atom_forces" (no copy, no synchronisation)."""
+        self._check(self._lib.smx_atom_forces(self._h, int(num_rows)))
+
+    def active_counts(self):
+        """(active receivers, their edges, receivers the edge set was built with)."""
+        n, e, b = ctypes.c_int(0), ctypes.c_long(0), ctypes.c_int(0)
+        self._check(self._lib.smx_active_counts(self._h, ctypes.byref(n), ctypes.byref(e), ctypes.byref(b)))
+        return n.value, e.value, b.value
+
+    def debug_expire_waits(self, polls: int) -> None:
+        """Test switch: make the first bounded wait of every float32 tensor-core GEMM CTA run out after `polls` polls."""
+        self._check(self._lib.smx_debug_expire_waits(self._h, int(polls)))
+
     def device_view(self, name: str):
         """Zero-copy torch view (1-D, float32 or float64) of a named device array; valid until that array is resized."""
         import torch

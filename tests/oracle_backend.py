@@ -70,14 +70,38 @@ class OracleBackend:
         setattr(self.o, name, np.ascontiguousarray(np.concatenate([arr, np.zeros((extra,) + arr.shape[1:])])))
 
     def device_view(self, name):
-        arr = getattr(self.o, name)
+        arr = self._atom_forces if name == "atom_forces" else getattr(self.o, name)
         assert arr.flags["C_CONTIGUOUS"]
         return torch.from_numpy(arr.reshape(-1))
 
     def sync(self):
         pass
 
-    def reduce_forces(self, num_rows):
+    @property
+    def has_zbl(self):
+        return bool(getattr(self.o, "has_zbl", False))
+
+    # halo rows: the numpy statement of smx_halo_pack / _unpack / _unpack_add
+    def _halo_array(self, name):
+        if name == "atom_forces":
+            return self._atom_forces
+        arr = getattr(self.o, name)
+        return arr.reshape(arr.shape[0], -1)
+
+    def halo_pack(self, name, rows):
+        return torch.from_numpy(self._halo_array(name)[rows.numpy()].copy())
+
+    def halo_unpack(self, name, rows, buf, add=False):
+        arr = self._halo_array(name)
+        if add:
+            np.add.at(arr, rows.numpy(), buf.numpy())      # sequential: contributions are added in list order
+        else:
+            arr[rows.numpy()] = buf.numpy()
+
+    def atom_forces(self, num_rows):
+        self._atom_forces = self.reduce_forces(num_rows)[0]
+
+    def reduce_forces(self, num_rows, want_forces=True, device=False):
         inp = self.inputs
         nf = self.o.node_forces
         recv = np.repeat(np.arange(inp["num_nodes"]), inp["num_neigh"])

@@ -81,6 +81,34 @@ def test_decomposed_evaluation_equals_single_domain(world, mode):
         np.testing.assert_allclose(virial, v_ref, atol=1e-10)
 
 
+@pytest.mark.parametrize("mode", ["message_passing", "recompute"])
+@pytest.mark.parametrize("world", [2, 3])
+def test_zbl_and_density_normalised_model_decomposes(model_file, world, mode):
+    """Pair repulsion and density-normalised blocks in a decomposed run: compute_ZBL on the owned atoms and the
+    *_scaled stages where the pair style has them (pair_symmetrix_mace.cpp:449-494, 667-697)."""
+    path, model, spec = model_file("tiny", zbl=True, density=True)
+    s = st.fcc_box((7, 2, 2), 3.2, model["atomic_numbers"], seed=5, jitter=0.25)      # some pairs inside the ZBL envelope
+    b0 = OracleBackend(model)
+    assert b0.has_zbl
+    nl = st.neighbor_list(s, spec.r_cut)
+    inputs = st.evaluator_inputs(s, nl, b0.atomic_numbers)
+    e, f = b0.o.compute_node_energies_forces(inputs)
+    f_ref, v_ref = st.atom_forces_and_virial(inputs, nl, f)
+    ranks = []
+    for r in range(world):
+        b = OracleBackend(model)
+        rk = SlabRank(make_slab_plan(s, spec.r_cut, r, world, mode=mode), b, spec.r_cut, b.atomic_numbers)
+        rk.build_edges()
+        ranks.append(rk)
+    energy, virial, owned = evaluate_decomposed(ranks)
+    forces = np.zeros_like(f_ref)
+    for rk, fo in zip(ranks, owned):
+        forces[rk.plan.own_global] = fo.numpy()
+    assert abs(energy - e.sum()) < 1e-11 * abs(e.sum())
+    np.testing.assert_allclose(forces, f_ref, atol=1e-10)
+    np.testing.assert_allclose(virial, v_ref, atol=1e-9)
+
+
 def _gloo_worker(rank, world, port, out_dir, mode="message_passing"):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
     import torch.distributed as dist

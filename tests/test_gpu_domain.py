@@ -48,6 +48,55 @@ def test_emulated_ranks_on_one_gpu_match_single_domain(model_file, dtype, world,
         assert np.abs(virial - v_ref).max() <= 100 * rel * max(1.0, np.abs(v_ref).max())
 
 
+@pytest.mark.parametrize("dtype,mode", [("float64", "message_passing"), ("float64", "recompute"), ("float32", "message_passing")])
+def test_zbl_and_density_normalised_model_decomposes_on_gpu(model_file, dtype, mode):
+    """compute_ZBL and the *_scaled stages in a decomposed run (pair_symmetrix_mace.cpp:449-494, 667-697)."""
+    world = 2
+    path, model, spec = model_file("fcc128", num_channels=32, num_spline_points=32, zbl=True, density=True)
+    s = st.fcc_box((4 * world, 3, 3), 3.2, model["atomic_numbers"], seed=9, jitter=0.25)
+    f_ref, v_ref, e_ref = _single(path, s)
+    ranks = []
+    for r in range(world):
+        ev = MACE(path, dtype=dtype)
+        assert ev.has_zbl
+        rk = SlabRank(make_slab_plan(s, spec.r_cut, r, world, mode=mode), ev, spec.r_cut, ev.atomic_numbers)
+        rk.build_edges()
+        ranks.append(rk)
+    rel, fabs = (1e-10, 1e-8) if dtype == "float64" else (1e-4, 1e-3)
+    energy, virial, owned = evaluate_decomposed(ranks)
+    forces = np.zeros_like(f_ref)
+    for rk, f in zip(ranks, owned):
+        forces[rk.plan.own_global] = f.cpu().numpy()
+    assert abs(energy - e_ref) <= rel * abs(e_ref)
+    assert np.abs(forces - f_ref).max() <= fabs * max(1.0, np.abs(f_ref).max())
+
+
+def test_decomposed_float64_evaluations_are_bitwise_reproducible(model_file):
+    """The fold-back of H1_adj and force rows on the owner adds in a fixed order (no atomics): two evaluations give the
+    same bits. Thin slabs make atoms ghosts of the same peer twice, so rows repeat inside one unpack list."""
+    world = 2
+    path, model, spec = model_file("fcc128", num_channels=32, num_spline_points=32)
+    s = st.fcc_box((4, 3, 3), 3.6, model["atomic_numbers"], seed=23, jitter=0.12)      # 7.2 A slabs, r_cut 6 A
+    ranks = []
+    for r in range(world):
+        ev = MACE(path, dtype="float64")
+        rk = SlabRank(make_slab_plan(s, spec.r_cut, r, world), ev, spec.r_cut, ev.atomic_numbers)
+        rk.build_edges()
+        ranks.append(rk)
+    assert any(np.unique(rows).size < rows.size for rk in ranks for rows in rk.plan.send_rows.values())
+    f_ref, v_ref, e_ref = _single(path, s)
+    results = []
+    for _ in range(3):
+        energy, virial, owned = evaluate_decomposed(ranks)
+        results.append((energy, np.asarray(virial).copy(), [f.cpu().numpy().copy() for f in owned]))
+    assert abs(results[0][0] - e_ref) <= 1e-10 * abs(e_ref)
+    for energy, virial, owned in results[1:]:
+        assert energy == results[0][0]
+        assert np.array_equal(virial, results[0][1])
+        for a, b in zip(owned, results[0][2]):
+            assert np.array_equal(a, b)
+
+
 def _gpu_count():
     import torch
     return torch.cuda.device_count()
