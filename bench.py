@@ -308,8 +308,10 @@ def run_ours(args):
             "clocks": clocks, "roofline": roof, "stage_ms": stage_ms,
             "wall_ms_per_step": wall_s * 1e3 / args.steps,
         }
+        sample = None
         if world == 1 and not args.no_cpu_baseline:
-            out["cpu_baseline"] = cpu_baseline(args.workload)
+            out["cpu_baseline"], sample = cpu_baseline(args.workload)
+        ev2 = None
         if world == 1 and not args.no_extra:
             other = "float32" if args.dtype == "float64" else "float64"
             ev2 = MACE(path, dtype=other, device=local_rank)
@@ -328,11 +330,70 @@ def run_ours(args):
             e32 = ev2.reduce_forces()[2] if args.dtype == "float64" else ev_saved.reduce_forces()[2]
             out["extra"] = {other: {"value": n_atoms * args.steps / (ms2 * 1e-3), "ms_per_step": ms2 / args.steps},
                             "fp32_vs_fp64_rel_energy_diff": abs(e32 - e64) / abs(e64)}
+        if sample is not None:
+            # the GPU path on the CPU baseline's own inputs, against the reference's results (outside every timed region)
+            evs = {("f64" if args.dtype == "float64" else "f32"): ev}
+            if ev2 is not None:
+                evs["f32" if args.dtype == "float64" else "f64"] = ev2
+            out["parity"] = parity_on_sample(evs, sample)
+            out["parity"]["against"] = out["cpu_baseline"]["kind"] + " CPU evaluator on the cpu_baseline sample"
+        if world == 1 and not args.no_extra and args.workload == "fcc4000":
+            del ev2
+            out.setdefault("extra", {})["config3"] = config3_single(local_rank, torch)
         emit(out)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
     return out
+
+
+def config3_single(local_rank, torch) -> dict:
+    """configs[3] at one GPU: its per-GPU share, a 256,000-atom slab (10x80x80 cells) of the configs[1] model in float32."""
+    from symmetrix_b200 import MACE
+    path, spec, s, nl, inputs = build_inputs("fcc256k", seed=1)
+    ev = MACE(path, dtype="float32", device=local_rank)
+    keys = ["node_types", "num_neigh", "neigh_indices", "neigh_types", "xyz", "r"]
+    dev = {k: torch.as_tensor(np.ascontiguousarray(inputs[k])).cuda(local_rank) for k in keys}
+    steps, ms = 3, 0.0
+    for it in range(1 + steps):
+        ev.timer_start()
+        ev.compute_node_energies_forces(s.num_atoms, *[dev[k] for k in keys])
+        ev.reduce_forces(want_forces=True)
+        t = ev.timer_stop()
+        if it > 0:
+            ms += t
+    return {"workload": "fcc256k", "dtype": "f32", "atoms": s.num_atoms, "edges": int(inputs["r"].size), "steps": steps,
+            "ms_per_step": ms / steps, "value": s.num_atoms * steps / (ms * 1e-3), "unit": UNIT,
+            "note": "inputs larger than L2; one warm-up step; efficiency at N GPUs = value(N) / (N x this value)"}
+
+
+def config3_decomposed(args, rank, world, local_rank, dist, torch) -> dict:
+    """configs[3] at N GPUs: N slabs of 256,000 atoms (10x80x80 cells each; at N = 8 the 2,048,000-atom box, 80x80x80
+    cells), configs[1] model in float32, ghost shell and halo exchange as in the main run."""
+    from symmetrix_b200 import MACE, structures as st
+    from symmetrix_b200.domain import SlabRank, evaluate_decomposed, make_slab_plan
+    path, numbers, spec = model_path("fcc128")
+    s = st.fcc_box((10 * world, 80, 80), 3.6, numbers, seed=1)
+    ev = MACE(path, dtype="float32", device=local_rank)
+    rk = SlabRank(make_slab_plan(s, spec.r_cut, rank, world, mode=args.dd_mode), ev, spec.r_cut, numbers)
+    rk.build_edges()
+    steps, total = 3, 0.0
+    for it in range(1 + steps):
+        dist.barrier(); torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        evaluate_decomposed([rk], dist=dist)
+        torch.cuda.synchronize()
+        e1.record(); e1.synchronize()
+        if it > 0:
+            total += e0.elapsed_time(e1)
+    t = torch.tensor([total], dtype=torch.float64, device=f"cuda:{local_rank}")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    return {"workload": f"fcc256k x {world} along x", "dtype": "f32", "atoms": s.num_atoms, "steps": steps, "ms_per_step": ms / steps,
+            "value": s.num_atoms * steps / (ms * 1e-3), "unit": UNIT, "ghost_rows_this_rank": rk.plan.n_ghost,
+            "note": "weak scaling of configs[3]; efficiency = value / (N x the single-GPU extra.config3.value); "
+                    "timed with CUDA events, barrier + synchronize on both sides, max over ranks"}
 
 
 def run_decomposed(args, rank, world, local_rank, dist):
@@ -411,14 +472,46 @@ def run_decomposed(args, rank, world, local_rank, dist):
                         8 if args.dtype == "float64" else 4)
     roof["scope"] = "rank 0's slab"
 
+    # Correctness of the decomposed run, outside the timed region: rank 0 evaluates the whole box as one domain and every
+    # rank compares its owned forces (and the reduced energy) with it.
+    dd_check = None
+    if s.num_atoms <= 300_000:
+        energy_dd, _, owned = evaluate_decomposed([rk], dist=dist)
+        ref_f = torch.zeros((s.num_atoms, 3), dtype=torch.float64, device=f"cuda:{local_rank}")
+        ref_e = torch.zeros(1, dtype=torch.float64, device=f"cuda:{local_rank}")
+        if rank == 0:
+            single = MACE(path, dtype=args.dtype, device=local_rank)
+            zmap = {int(z): t_ for t_, z in enumerate(single.atomic_numbers)}
+            single.build_neighbors(s.positions, np.array([zmap[int(z)] for z in s.numbers], dtype=np.int32), s.cell, s.pbc, r_cut=spec.r_cut)
+            single.compute_current()
+            f1, _, e1 = single.reduce_forces()
+            ref_f.copy_(torch.as_tensor(f1)); ref_e[0] = e1
+            del single
+        dist.broadcast(ref_f, 0); dist.broadcast(ref_e, 0)
+        own = torch.as_tensor(rk.plan.own_global, device=ref_f.device)
+        err = torch.stack([(owned[0] - ref_f[own]).abs().max(), ref_f.abs().max()])
+        dist.all_reduce(err, op=dist.ReduceOp.MAX)
+        e1 = float(ref_e.item())
+        dd_check = {"rel_dE": abs(energy_dd - e1) / abs(e1), "max_abs_dF": float(err[0].item()), "rel_dF": float((err[0] / err[1]).item()),
+                    "against": "the whole box evaluated as one domain on rank 0 (same precision), outside the timed region",
+                    "gate": "1e-10 relative" if args.dtype == "float64" else "1e-4 relative, 1e-3 eV/A"}
+    else:
+        dd_check = {"skipped": "the whole box does not fit one GPU's evaluation; checked on smaller boxes by tests/test_gpu_domain.py"}
+
     t = torch.tensor([ms, e2e_ms], dtype=torch.float64, device=f"cuda:{local_rank}")
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_max, e2e_max = (float(x) for x in t.cpu())
     counts = torch.tensor([rk.plan.n_own, rk.plan.n_ghost, rk.num_edges], dtype=torch.float64, device=f"cuda:{local_rank}")
     dist.all_reduce(counts)
+    width = ev.num_LM * ev.num_channels * (8 if args.dtype == "float64" else 4)
+    h2d_bytes = int((rk.plan.n_own + rk.plan.n_ghost) * 28 * world)
+    config3 = None
+    if args.workload == "fcc4000" and not args.no_extra:
+        del ev, rk                       # the evaluator's arrays make room for the larger workload
+        torch.cuda.empty_cache()
+        config3 = config3_decomposed(args, rank, world, local_rank, dist, torch)
     if rank == 0:
         n_total = s.num_atoms
-        width = ev.num_LM * ev.num_channels * (8 if args.dtype == "float64" else 4)
         out = {
             "metric": METRIC, "value": n_total * args.steps / (ms_max * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_max / args.steps, "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
@@ -433,12 +526,14 @@ def run_decomposed(args, rank, world, local_rank, dist):
                        "l2": "256 MB buffer written between timed steps (L2 flush)",
                        "timing": "CUDA events around each step with a barrier + synchronize on both sides, summed, max over ranks"},
             "e2e": {"value": n_total * e2e_steps / (e2e_max * 1e-3), "unit": UNIT,
-                    "h2d_bytes_per_step": int((rk.plan.n_own + rk.plan.n_ghost) * 28 * world),
+                    "h2d_bytes_per_step": h2d_bytes,
                     "d2h_bytes_per_step": int(n_total * 24 + 56 * world), "ms_per_step": e2e_max / e2e_steps,
                     "timing": "per step: local positions/types from host, neighbour list rebuilt on the device, evaluation, owned forces to host"},
             "gpu_launches": launches * world, "gpu_launches_per_step": launches // (args.steps + args.warmup),
-            "clocks": clocks, "roofline": roof, "stage_ms": stage_ms,
+            "clocks": clocks, "roofline": roof, "stage_ms": stage_ms, "dd_check": dd_check,
         }
+        if config3 is not None:
+            out["extra"] = {"config3": config3}
         emit(out)
     dist.barrier()
     dist.destroy_process_group()
@@ -479,33 +574,67 @@ def _cpu_sample_inputs(workload: str, seed: int):
     return path, s, st.evaluator_inputs(s, nl, numbers), sample
 
 
-def cpu_baseline(workload: str) -> dict:
+def _timed_variant():
+    """The timed build of the reference: with OpenBLAS (one thread) when that build is here and loads, else with the
+    plain-loop BLAS; (None, None) when the reference was never compiled."""
+    from oracle import ref as ref_driver
+    os.environ.setdefault("OPENBLAS_NUM_THREADS", "1")
+    if ref_driver.available("timed_openblas"):
+        try:
+            ref_driver._load("timed_openblas")
+            return "timed_openblas", "OpenBLAS 0.3.15 (one thread)"
+        except OSError:
+            pass
+    if ref_driver.available("timed"):
+        return "timed", "plain-loop BLAS"
+    return None, None
+
+
+def cpu_baseline(workload: str):
     """The reference CPU evaluator (serial, one core) on a bounded sample of the workload."""
     from oracle import ref as ref_driver
     path, s, inputs, sample = _cpu_sample_inputs(workload, seed=1)
-    if ref_driver.available("timed"):
-        r = ref_driver.ReferenceMACE(path, "timed")
+    variant, blas = _timed_variant()
+    if variant:
+        r = ref_driver.ReferenceMACE(path, variant)
         kind = "reference"
         fn = lambda: r.compute_node_energies_forces(inputs)   # noqa: E731
     else:
         from oracle.mace_numpy import MaceOracle
         o = MaceOracle(path)
-        kind = "port"
+        kind, blas = "port", "numpy"
         fn = lambda: o.compute_node_energies_forces(inputs)   # noqa: E731
-    fn()                                   # first call sizes the evaluator's internal arrays
+    e_ref, f_ref = fn()                    # first call sizes the evaluator's internal arrays
     reps, t0 = 0, time.perf_counter()
     while reps < 3 and (time.perf_counter() - t0) < 20.0:
         fn(); reps += 1
     dt = (time.perf_counter() - t0) / reps
-    return {"value": s.num_atoms / dt, "unit": UNIT, "cores": 1, "kind": kind,
-            "sample": f"{sample}; {reps} evaluations after one warm-up; -O3 -ffast-math -march=x86-64-v3, plain-loop BLAS",
-            "seconds_per_step": dt}
+    out = {"value": s.num_atoms / dt, "unit": UNIT, "cores": 1, "kind": kind,
+           "sample": f"{sample}; {reps} evaluations after one warm-up; -O3 -ffast-math -march=x86-64-v3, {blas}",
+           "seconds_per_step": dt,
+           "note": "a lower bound on the reference's CPU speed when the BLAS is the plain-loop one"}
+    return out, (path, inputs, e_ref, f_ref)
+
+
+def parity_on_sample(evaluators: dict, sample) -> dict:
+    """The GPU path on exactly the inputs the CPU baseline evaluated, against the reference's energies and forces."""
+    path, inputs, e_ref, f_ref = sample
+    out = {}
+    for name, ev in evaluators.items():
+        ev.compute_node_energies_forces(int(inputs["num_nodes"]), inputs["node_types"], inputs["num_neigh"], inputs["neigh_indices"],
+                                        inputs["neigh_types"], inputs["xyz"], inputs["r"])
+        e, f = ev.node_energies, ev.node_forces
+        out[name] = {"rel_dE": float(abs(e.sum() - e_ref.sum()) / abs(e_ref.sum())), "max_abs_dF": float(np.abs(f - f_ref).max()),
+                     "rel_dF": float(np.abs(f - f_ref).max() / np.abs(f_ref).max()), "atoms": int(inputs["num_nodes"]),
+                     "gate": "1e-10 relative" if name == "f64" else "1e-4 relative, 1e-3 eV/A"}
+    return out
 
 
 def _replica_main(idx, workload, steps, warmup, barrier, times):
     from oracle import ref as ref_driver
     path, s, inputs, _ = _cpu_sample_inputs(workload, seed=100 + idx)
-    r = ref_driver.ReferenceMACE(path, "timed") if ref_driver.available("timed") else None
+    variant, _ = _timed_variant()
+    r = ref_driver.ReferenceMACE(path, variant) if variant else None
     if r is None:
         from oracle.mace_numpy import MaceOracle
         o = MaceOracle(path)
@@ -558,7 +687,8 @@ def run_reference(args):
         return None
     t = max(times)
     value = replicas * s.num_atoms * steps / t
-    kind = "reference" if ref_driver.available("timed") else "port"
+    variant, blas = _timed_variant()
+    kind = "reference" if variant else "port"
     out = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": steps, "warmup": warmup,
         "ms_per_step": t * 1e3 / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f64",
@@ -567,7 +697,7 @@ def run_reference(args):
                    "parallelism": f"{replicas} independent serial replicas on the host cores (the reference CPU path has no threading)"},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": replicas, "kind": kind,
                          "sample": f"each replica evaluates a {sample} per step; requested steps/warmup {args.steps}/{args.warmup} "
-                                   f"bounded to {steps}/{warmup}"},
+                                   f"bounded to {steps}/{warmup}; BLAS: {blas}"},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }

@@ -16,6 +16,11 @@ copied; outputs go only to ``oracle/_ref/``:
   except that ``-march=native`` is replaced by ``-march=x86-64-v3`` because the binary is built
   on one machine and timed on another): the CPU baseline.
 
+* ``libref_timed_openblas.so``  the timed build linked against the OpenBLAS that ships inside the image's
+  ``opencv_python_headless`` wheel (plain ``cblas_*`` symbols) instead of the plain-loop BLAS, when that library is
+  found: the closer stand-in for how the reference is normally deployed. It resolves the library by absolute path, so
+  it loads only on machines with the same image.
+
 Usage: ``python oracle/build_ref.py [--reference DIR] [--force]``. Does nothing (returns
 False) when the reference checkout is absent.
 """
@@ -52,8 +57,21 @@ def _find_json_include() -> Path | None:
     return None
 
 
+def _find_openblas() -> Path | None:
+    """An OpenBLAS shared library that exports the plain cblas_* symbols (inside the opencv wheel of this image)."""
+    purelib = Path(sysconfig.get_paths()["purelib"])
+    hits = sorted((purelib / "opencv_python_headless.libs").glob("libopenblas*.so*"))
+    return hits[0] if hits else None
+
+
+def _default_reference() -> Path:
+    """The reference checkout: $SYMMETRIX_REFERENCE, else a `reference` folder beside the repository."""
+    env = os.environ.get("SYMMETRIX_REFERENCE")
+    return Path(env) if env else HERE.parent.parent / "reference"
+
+
 def build(reference: str | os.PathLike | None = None, force: bool = False, verbose: bool = True) -> bool:
-    ref = Path(reference or os.environ.get("SYMMETRIX_REFERENCE", "/root/reference"))
+    ref = Path(reference) if reference else _default_reference()
     src_dir = ref / "libsymmetrix" / "source"
     if not src_dir.is_dir():
         if verbose:
@@ -88,6 +106,14 @@ def build(reference: str | os.PathLike | None = None, force: bool = False, verbo
             print("[oracle/_ref] building", name)
         subprocess.run(cmd, check=True)
         blas_obj.unlink()
+    openblas = _find_openblas()
+    target = OUT / "libref_timed_openblas.so"
+    if openblas is not None and (force or not target.exists() or target.stat().st_mtime <= newest):
+        if verbose:
+            print("[oracle/_ref] building", target.name, "against", openblas.name)
+        cmd = ["g++", *common, *variants["libref_timed.so"], *sources, f"-L{openblas.parent}", f"-l:{openblas.name}",
+               f"-Wl,--disable-new-dtags,-rpath,{openblas.parent}", "-o", str(target)]   # DT_RPATH: also for the library's own dependencies
+        subprocess.run(cmd, check=True)
     return True
 
 

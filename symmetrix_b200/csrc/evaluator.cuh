@@ -122,6 +122,7 @@ public:
     DevBuf<int> kernel_status;    // non-zero if a bounded mbarrier wait ran out (1, 2: tcgen05 GEMM; 3, 4: staged tensor-product reverse)
     bool staged_reverse = false;  // spline rows of the tensor-product reverse through bulk copies into shared memory
                                   // (SMX_TP_STAGED=1; measured equal in float64 and 15 % slower in float32 on B200)
+    bool tmem_reverse = true;     // float64 tensor-product reverse with the receiver adjoint in tensor memory (SMX_TP_TMEM=0: in registers)
     bool type_order = true;       // edge kernels walk the receivers in element-type order (SMX_TYPE_ORDER=0: natural order)
     bool waits_in_flight = false; // a kernel with bounded waits has been launched since the last status check
     bool use_tc5 = false;
@@ -141,6 +142,7 @@ public:
         kernel_status.zero(stream);
         if (const char* t = std::getenv("SMX_TP_STAGED")) staged_reverse = std::string(t) != "0";
         if (const char* t = std::getenv("SMX_TYPE_ORDER")) type_order = std::string(t) != "0";
+        if (const char* t = std::getenv("SMX_TP_TMEM")) tmem_reverse = std::string(t) != "0";
         if constexpr (sizeof(T) == 4) {
             // float32 GEMMs run on tcgen05 unless SMX_GEMM=mma asks for the mma.sync kernel
             const char* g = std::getenv("SMX_GEMM");
@@ -637,6 +639,23 @@ public:
     template <int LF>
     void launch_tp(bool reverse, int which) {
         const int block = channel_block();
+        if constexpr (sizeof(T) == 8) {
+            if (reverse && tmem_reverse && !staged_reverse) {
+                // receiver adjoint in tensor memory: more resident CTAs (see tp_reverse_tmem_kernel). The CTAs of one SM
+                // must fit into its 512 TMEM columns, or the allocation of the last one would wait for another to exit.
+                constexpr int kMinBlocks = LF >= 2 ? 2 : 4;
+                constexpr int kCols = tp_tmem_cols(LF);
+                static_assert(kCols * kMinBlocks <= 512, "resident CTAs must fit into tensor memory");
+                auto kern = tp_reverse_tmem_kernel<LF, kMinBlocks>;
+                int per_sm = 1;
+                SMX_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, block, 0));
+                per_sm = std::max(1, std::min(per_sm, 512 / kCols));
+                const int grid = static_cast<int>(std::max<long long>(1, std::min<long long>(static_cast<long long>(num_sms) * per_sm, N)));
+                kern<<<grid, block, 0, stream>>>(tp_args(which));
+                check_launch("tp_reverse_tmem_kernel");
+                return;
+            }
+        }
         if (reverse) {
             // two slots of one spline-row chunk each; staged only if that costs no resident CTA
             const size_t slots = 2 * sizeof(T) * 4 * make_tp_table(LF).P * static_cast<size_t>(std::min(model.K, block));

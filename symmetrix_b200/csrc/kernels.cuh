@@ -671,6 +671,176 @@ __global__ void __launch_bounds__(kChannelBlock, tp_min_blocks<T>(LF, true)) tp_
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// float64 reverse of the tensor product with the receiver's adjoint in tensor memory.
+//
+// tp_reverse_kernel<double> keeps d[Q] (the adjoint of the receiver's tensor product, 2 registers per value: 80 registers
+// for Q = 40) in registers for the whole walk over the receiver's edges; with the 16 harmonic adjoints, the messages, the
+// radial values and the coupling temporaries that is 254 registers, i.e. two resident CTAs (8 warps) per SM, too few to
+// cover the latency of the coefficient loads that start every edge. Blackwell's tensor memory (TMEM, 512 columns x 128
+// lanes x 32 bits per SM, normally the accumulator of tcgen05.mma) is used here as a per-thread scratchpad instead: thread
+// t of the CTA owns TMEM lane t and keeps its d values there (tcgen05.st once per receiver), fetching the 2l+1 values of
+// one path at a time (tcgen05.ld) while it works on the previous path. TMEM has its own data path, so this costs neither
+// registers nor shared-memory / L1 bandwidth, which the coefficient stream needs. The register budget then allows three
+// resident CTAs per SM.
+//
+// Column layout (per lane): path p starts at tp_tmem_col(p), aligned to its padded width (2, 8, 16 or 16 columns for
+// l = 0, 1, 2, 3; a double takes two 32-bit columns). A CTA allocates the next power of two >= the total; the host
+// checks that the resident CTAs of one SM fit into the 512 columns.
+// ---------------------------------------------------------------------------------------------
+constexpr int tp_tmem_width(int l) { return l == 0 ? 2 : (l == 1 ? 8 : 16); }
+constexpr int tp_tmem_col(const TPTable& tp, int p) {
+    int col = 0;
+    for (int q = 0; q < p; ++q) {
+        const int w = tp_tmem_width(tp.l[q]);
+        col = (col + w - 1) / w * w + w;
+    }
+    const int w = tp_tmem_width(tp.l[p]);
+    return (col + w - 1) / w * w;
+}
+constexpr int tp_tmem_cols(int LF) {
+    const TPTable tp = make_tp_table(LF);
+    const int used = tp_tmem_col(tp, tp.P - 1) + tp_tmem_width(tp.l[tp.P - 1]);
+    int alloc = 32;
+    while (alloc < used) alloc *= 2;
+    return alloc;
+}
+
+// Starts the asynchronous fetch of W 32-bit columns of this thread's TMEM lane into `v` (W = 2, 8 or 16).
+template <int W>
+__device__ __forceinline__ void tmem_ld_issue(uint32_t taddr, uint32_t (&v)[16]) {
+    if constexpr (W == 2) {
+        asm volatile("tcgen05.ld.sync.aligned.32x32b.x2.b32 {%0, %1}, [%2];" : "=r"(v[0]), "=r"(v[1]) : "r"(taddr) : "memory");
+    } else if constexpr (W == 8) {
+        asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                     : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]) : "r"(taddr) : "memory");
+    } else {
+        asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                     : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
+                       "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]) : "r"(taddr) : "memory");
+    }
+}
+// Waits for the fetches this thread started; the registers are operands so that no use of them moves above the wait.
+__device__ __forceinline__ void tmem_ld_wait(uint32_t (&v)[16]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]), "+r"(v[8]), "+r"(v[9]),
+                   "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15]) :: "memory");
+}
+__device__ __forceinline__ void tmem_st2(uint32_t taddr, double x) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x2.b32 [%0], {%1, %2};" ::"r"(taddr), "r"(__double2loint(x)), "r"(__double2hiint(x)) : "memory");
+}
+
+template <int LF, int MINB>
+__global__ void __launch_bounds__(kChannelBlock, MINB) tp_reverse_tmem_kernel(const TPArgs<double> a) {
+    using T = double;
+    constexpr TPTable tp = make_tp_table(LF);
+    constexpr int EB = kEdgeBatch;
+    constexpr int kCols = tp_tmem_cols(LF);
+    __shared__ EdgeStage<T> st[EB];
+    __shared__ T red[kMaxWarps][EB][17];
+    __shared__ uint32_t tmem_slot;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    const int F = tp.P * a.K;
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(kCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    // this thread's lane: 32 * (warp % 4) + lane, in bits 16.. of the address (a warp reaches the 32 lanes of its quadrant)
+    const uint32_t tbase = tmem_slot + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+    uint32_t stage[16];
+#pragma unroll
+    for (int q = 0; q < 16; ++q) stage[q] = 0u;
+
+    for (int slot = blockIdx.x; slot < a.N; slot += gridDim.x)
+    for (int kc = 0; kc < a.K; kc += blockDim.x) {
+        const int i = a.order ? a.order[slot] : slot;     // nodes in element-type order: see Layer0Args::order
+        const bool active = kc + static_cast<int>(threadIdx.x) < a.K;
+        const int k = active ? kc + threadIdx.x : a.K - 1;     // idle lanes shadow the last channel with a zero adjoint: the
+                                                               // tensor-memory instructions need the whole warp
+        const long long e_begin = a.first_neigh[i], e_end = a.first_neigh[i + 1];
+        const int type_i = a.node_types[i];
+        // the receiver's adjoint into this thread's TMEM lane, path by path
+        static_for<tp.P>([&](auto pc) {
+            constexpr int p = decltype(pc)::value;
+            constexpr int col = tp_tmem_col(tp, p);
+#pragma unroll
+            for (int m = 0; m < 2 * tp.l[p] + 1; ++m) {
+                const T v = active ? __ldcs(a.dPhi1 + (static_cast<size_t>(i) * tp.Q + tp.lme(p, m)) * a.K + k) : T(0);
+                tmem_st2(tbase + col + 2 * m, v);
+            }
+        });
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        tmem_ld_issue<tp_tmem_width(tp.l[0])>(tbase + tp_tmem_col(tp, 0), stage);      // path 0 of the first edge
+        for (long long e0 = e_begin; e0 < e_end; e0 += EB) {
+            const int nb = static_cast<int>(e_end - e0 < EB ? e_end - e0 : EB);
+            __syncthreads();
+            if (threadIdx.x < nb)
+                stage_edge<T, true>(st[threadIdx.x], e0 + threadIdx.x, type_i, a.neigh_indices, a.neigh_types, a.xyz, a.r, a.sm, F);
+            __syncthreads();
+            for (int e = 0; e < nb; ++e) {
+                const EdgeStage<T>& s = st[e];
+                T W[kNumLm], fr = 0;
+#pragma unroll
+                for (int lm = 0; lm < kNumLm; ++lm) W[lm] = T(0);
+                T R[tp.P], Rd[tp.P];
+                const T x = s.x;
+                const T* hrow = a.H + static_cast<size_t>(s.j) * tp.nLM * a.K + k;
+                T h[tp.nLM], msg[tp.nLM], Y[kNumLm];
+#pragma unroll
+                for (int lm2 = 0; lm2 < tp.nLM; ++lm2) { h[lm2] = __ldg(hrow + static_cast<size_t>(lm2) * a.K); msg[lm2] = T(0); }
+                const T* cb = a.coef1 + s.coef_base;
+#pragma unroll
+                for (int p = 0; p < tp.P; ++p) {
+                    const Vec4<T> c = load_coef<T>(cb + 4 * p * a.K, k, a.K);
+                    R[p] = c.x + x * (c.y + x * (c.z + x * c.w));
+                    Rd[p] = c.y + x * (T(2) * c.z + T(3) * x * c.w);
+                }
+#pragma unroll
+                for (int lm = 0; lm < kNumLm; ++lm) Y[lm] = s.Y[lm];
+                // Path p's adjoint values arrive in `stage` (fetch started while path p - 1 was computed); they are moved
+                // into dp and the fetch of the next path (path 0 again after the last: the adjoint belongs to the receiver,
+                // not to the edge) starts before path p is computed.
+#define TP_PATH_D(p, n, dp)                                                                                   \
+                tmem_ld_wait(stage);                                                                          \
+                _Pragma("unroll") for (int m_ = 0; m_ < (n); ++m_) dp[m_] = __hiloint2double(static_cast<int>(stage[2 * m_ + 1]), static_cast<int>(stage[2 * m_])); \
+                tmem_ld_issue<tp_tmem_width(tp.l[((p) + 1) % tp.P])>(tbase + tp_tmem_col(tp, ((p) + 1) % tp.P), stage);
+                if constexpr (LF == 0) {
+#include "generated/tp_L0_reverse_bypath.inc"
+                } else if constexpr (LF == 1) {
+#include "generated/tp_L1_reverse_bypath.inc"
+                } else {
+#include "generated/tp_L2_reverse_bypath.inc"
+                }
+#undef TP_PATH_D
+                if (active) {
+                    // deterministic two-step scatter: per-edge message, then a fixed-order sum per sender (sender_gather_kernel)
+                    T* mrow = a.Hmsg + static_cast<size_t>(e0 + e) * tp.nLM * a.K + k;
+#pragma unroll
+                    for (int lm2 = 0; lm2 < tp.nLM; ++lm2) __stcs(mrow + static_cast<size_t>(lm2) * a.K, msg[lm2]);
+                }
+                int idx;
+                const T wsum = warp_reduce_scatter16(W, lane, idx);
+                fr = warp_sum(fr);
+                if ((lane & 1) == 0) red[warp][e][idx] = wsum;
+                if (lane == 0) red[warp][e][16] = fr;
+            }
+            __syncthreads();
+            if (threadIdx.x < nb) {
+                const int e = threadIdx.x;
+                finish_edge_force<T, EB>(red, nwarps, e, st[e].dY[0], st[e].dY[1], st[e].dY[2], st[e].ux, st[e].uy, st[e].uz,
+                                         a.node_forces + 3 * (e0 + e));
+            }
+        }
+        tmem_ld_wait(stage);      // the fetch started after the last path of the last edge: nothing may be in flight when d is rewritten
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_slot), "r"(kCols) : "memory");
+}
+
 // Input check for callers that cannot vouch for their edge arrays: counts, per kind, the entries that would make the
 // evaluation read out of bounds or produce non-finite values. Reads only inside the given arrays.
 //   0 node type outside [0, num_elements)      1 negative neighbour count      2 counts do not add up to the edge total

@@ -111,6 +111,7 @@ def test_downsized_benchmark_models(model_file, dtype, name, channels, builder):
 
 @pytest.mark.parametrize("dtype,env", [
     ("float32", {"SMX_GEMM": "mma"}),           # mma.sync 3xTF32 GEMM instead of the tcgen05 kernel
+    ("float64", {"SMX_TP_TMEM": "0"}),          # receiver adjoint of the tensor-product reverse in registers instead of tensor memory
     ("float64", {"SMX_TP_STAGED": "1"}),        # spline rows of the tensor-product reverse through TMA bulk copies
     ("float32", {"SMX_TP_STAGED": "1"}),
 ])
@@ -373,6 +374,48 @@ def test_models_with_unusual_monomials_use_the_table_driven_contraction(tiny, tm
     ev = MACE(path, dtype=dtype)
     e, f = run(ev, inputs)
     check_against(dtype, e, f, e_ref, f_ref)
+
+
+def test_positions_outside_the_cell_give_the_same_energy_and_forces(model_file):
+    """Atoms that have drifted out of the cell (the normal state in molecular dynamics): translating atoms by whole
+    lattice vectors changes neither the edge set nor any result. The reference's ASE neighbour list accepts such
+    positions (symmetrix_calc.py:77)."""
+    path, model, spec = model_file("fcc128", num_channels=32, num_spline_points=32)
+    s = st.fcc_box(3, 3.6, model["atomic_numbers"], seed=31, jitter=0.1)
+    calc = Symmetrix(path, dtype="float64")
+    base = calc.calculate(s.positions, s.cell, s.numbers, s.pbc)
+    e0, f0, s0 = base["energy"], base["forces"].copy(), base["stress"].copy()
+    edges0 = calc.evaluator.get_edges()
+    rng = np.random.default_rng(3)
+    moves = rng.integers(-3, 4, size=(s.num_atoms, 3))
+    moved = s.positions + moves @ s.cell
+    out = calc.calculate(moved, s.cell, s.numbers, s.pbc)
+    edges1 = calc.evaluator.get_edges()
+    assert np.array_equal(edges0["num_neigh"], edges1["num_neigh"])
+    # the same images, expressed between the positions as given: shift' = shift + move_i - move_j
+    recv = np.repeat(np.arange(s.num_atoms), edges0["num_neigh"])
+    key = lambda ed, sh: sorted(zip(recv.tolist(), ed["neigh_indices"].tolist(), map(tuple, sh.tolist())))   # noqa: E731
+    assert key(edges0, edges0["shifts"]) == key(edges1, edges1["shifts"] - moves[recv] + moves[edges1["neigh_indices"]])
+    assert abs(out["energy"] - e0) <= 1e-10 * abs(e0)
+    np.testing.assert_allclose(out["forces"], f0, atol=1e-9)
+    np.testing.assert_allclose(out["stress"], s0, atol=1e-10)
+
+
+def test_a_bounded_wait_that_runs_out_is_reported_and_the_handle_recovers(tiny):
+    """The float32 tensor-core GEMM waits on mbarriers with a poll limit. The test switch makes the first wait of every
+    CTA expect bytes that never come: the kernel must give up, release its tensor memory and return, the call must
+    report SMX_ERR_CUDA, and the next evaluation on the same handle must be right again. Nothing faults."""
+    case, inputs = tiny
+    ev = MACE(GOLDEN / "tiny_model.json", dtype="float32")
+    e0, f0 = run(ev, inputs)
+    ev.debug_expire_waits(2000)
+    with pytest.raises(SymmetrixError) as err:
+        run(ev, inputs)
+    assert err.value.status == _lib.SMX_ERR_CUDA and "wait" in str(err.value)
+    ev.debug_expire_waits(0)
+    e1, f1 = run(ev, inputs)
+    np.testing.assert_array_equal(e1, e0)
+    check_against("float32", e1, f1, case["node_energies"], case["node_forces"])
 
 
 @pytest.mark.parametrize("dtype", ["float64", "float32"])

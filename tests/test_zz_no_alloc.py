@@ -58,6 +58,30 @@ def test_noalloc_energy_virial_matches_reduce_forces_twice():
         np.testing.assert_allclose(got[1:], virial, rtol=1e-11, atol=1e-10)
 
 
+def _numpy_sums(e, xyz, nf):
+    x, f = xyz.reshape(-1, 3), nf.reshape(-1, 3)
+    return np.array([e.sum(), (x[:, 0] * f[:, 0]).sum(), (x[:, 1] * f[:, 1]).sum(), (x[:, 2] * f[:, 2]).sum(),
+                     0.5 * (x[:, 0] * f[:, 1] + x[:, 1] * f[:, 0]).sum(), 0.5 * (x[:, 0] * f[:, 2] + x[:, 2] * f[:, 0]).sum(),
+                     0.5 * (x[:, 1] * f[:, 2] + x[:, 2] * f[:, 1]).sum()])
+
+
+def test_noalloc_uses_several_scratch_rows_and_ignores_stale_ones():
+    """Inputs that span several 4096-item chunks (one scratch row each), first with more edges than nodes, then a smaller
+    call with more nodes than edges: the second call must not read the rows the first one left behind."""
+    import torch
+    from symmetrix_b200 import _lib
+
+    lib = _lib.load()
+    rng = np.random.default_rng(5)
+    out = torch.full((7,), float("nan"), dtype=torch.float64, device="cuda")
+    for n_nodes, n_edges in ((3000, 10000), (6000, 5000), (1, 4097)):
+        e = rng.normal(size=n_nodes); xyz = rng.normal(size=3 * n_edges); nf = rng.normal(size=3 * n_edges)
+        status, msg = _call(lib, torch.as_tensor(e).cuda(), n_nodes, torch.as_tensor(xyz).cuda(), torch.as_tensor(nf).cuda(), n_edges, out)
+        assert status == _lib.SMX_OK, msg
+        torch.cuda.synchronize()
+        np.testing.assert_allclose(out.cpu().numpy(), _numpy_sums(e, xyz, nf), rtol=1e-12, atol=1e-10)
+
+
 def test_noalloc_rejects_oversized_and_null_inputs():
     import torch
     from symmetrix_b200 import _lib
