@@ -10,7 +10,12 @@
 //     compute_node_energies_forces() (node_energies, node_forces) or on request (pull("H1"));
 //   * stage methods use the edge arrays handed to begin() (or to the last whole evaluation):
 //     call begin(...) where the reference code zero-fills node_energies / node_forces
-//     (pair_symmetrix_mace.cpp:437-440); the per-stage array arguments are accepted and ignored;
+//     (pair_symmetrix_mace.cpp:437-440), with the arrays of ALL receivers that any stage of the step will
+//     use (owned atoms first). The array arguments of the stage methods are accepted and not read again;
+//     their `num_nodes` argument is honoured: a stage called with another receiver count than the one in
+//     effect switches the active receivers first (smx_set_active_nodes), which is what the pair style's
+//     recompute branch relies on (layer 0 on nlocal + nghost receivers, layer 1 on nlocal,
+//     pair_symmetrix_mace.cpp:672-697); a count beyond what begin() was given throws;
 //   * errors surface as std::runtime_error carrying the library's message, like the reference's
 //     exceptions (e.g. a non-JSON model file, symmetrix_calc.py:54-68).
 #pragma once
@@ -54,7 +59,7 @@ public:
     // The pair style calls mace->zbl.compute_ZBL(...) by hand in its staged modes (pair_symmetrix_mace.cpp:441-444).
     struct ZBLStage {
         MACE* owner = nullptr;
-        template <typename... A> void compute_ZBL(A&&...) { owner->stage("compute_ZBL"); }
+        template <typename... A> void compute_ZBL(int num_nodes, A&&...) { owner->stage_on(num_nodes, "compute_ZBL"); }
     } zbl{this};
 
     // Host mirrors of the public vectors the callers read or swap (mace.hpp:28,104)
@@ -67,6 +72,7 @@ public:
                                       std::span<const double> xyz, std::span<const double> r) {
         check(smx_compute(h_, num_nodes, node_types.data(), num_neigh.data(), neigh_indices.data(), neigh_types.data(),
                           xyz.data(), r.data(), static_cast<long>(r.size()), SMX_HOST));
+        active_nodes_ = num_nodes;
         pull("node_energies");
         pull("node_forces");
     }
@@ -77,34 +83,36 @@ public:
                std::span<const double> r) {
         check(smx_begin(h_, num_nodes, node_types.data(), num_neigh.data(), neigh_indices.data(), neigh_types.data(), xyz.data(),
                         r.data(), static_cast<long>(r.size()), SMX_HOST));
+        active_nodes_ = num_nodes;
     }
 
-    // Stage methods (mace.hpp:40-164). Arguments are those of the reference and are ignored.
+    // Stage methods (mace.hpp:40-164) with the reference's argument lists: `num_nodes` selects the active receivers
+    // (see the header comment), the array arguments are those already given to begin() and are not read again.
     template <typename... A> void compute_Y(A&&...) { stage("compute_Y"); }
-    template <typename... A> void compute_R0(A&&...) { stage("compute_R0"); }
-    template <typename... A> void compute_R1(A&&...) { stage("compute_R1"); }
-    template <typename... A> void compute_A0(A&&...) { stage("compute_A0"); }
-    template <typename... A> void compute_A0_scaled(A&&...) { stage("compute_A0_scaled"); }
-    template <typename... A> void compute_M0(A&&...) { stage("compute_M0"); }
-    template <typename... A> void compute_H1(A&&...) { stage("compute_H1"); }
-    template <typename... A> void compute_A1(A&&...) { stage("compute_A1"); }
-    template <typename... A> void compute_A1_scaled(A&&...) { stage("compute_A1_scaled"); }
-    template <typename... A> void compute_M1(A&&...) { stage("compute_M1"); }
-    template <typename... A> void compute_H2(A&&...) { stage("compute_H2"); }
-    template <typename... A> void compute_readouts(A&&...) { stage("compute_readouts"); }
-    template <typename... A> void reverse_M1(A&&...) { stage("reverse_M1"); }
-    template <typename... A> void reverse_A1(A&&...) { stage("reverse_A1"); }
-    template <typename... A> void reverse_H1(A&&...) { stage("reverse_H1"); }
-    template <typename... A> void reverse_M0(A&&...) { stage("reverse_M0"); }
-    template <typename... A> void reverse_A0(A&&...) { stage("reverse_A0"); }
-    template <typename... A> void reverse_A0_scaled(A&&...) { stage("reverse_A0_scaled"); }
+    template <typename... A> void compute_R0(int num_nodes, A&&...) { stage_on(num_nodes, "compute_R0"); }
+    template <typename... A> void compute_R1(int num_nodes, A&&...) { stage_on(num_nodes, "compute_R1"); }
+    template <typename... A> void compute_A0(int num_nodes, A&&...) { stage_on(num_nodes, "compute_A0"); }
+    template <typename... A> void compute_A0_scaled(int num_nodes, A&&...) { stage_on(num_nodes, "compute_A0_scaled"); }
+    template <typename... A> void compute_M0(int num_nodes, A&&...) { stage_on(num_nodes, "compute_M0"); }
+    template <typename... A> void compute_H1(int num_nodes, A&&...) { stage_on(num_nodes, "compute_H1"); }
+    template <typename... A> void compute_A1(int num_nodes, A&&...) { stage_on(num_nodes, "compute_A1"); }
+    template <typename... A> void compute_A1_scaled(int num_nodes, A&&...) { stage_on(num_nodes, "compute_A1_scaled"); }
+    template <typename... A> void compute_M1(int num_nodes, A&&...) { stage_on(num_nodes, "compute_M1"); }
+    template <typename... A> void compute_H2(int num_nodes, A&&...) { stage_on(num_nodes, "compute_H2"); }
+    template <typename... A> void compute_readouts(int num_nodes, A&&...) { stage_on(num_nodes, "compute_readouts"); }
+    template <typename... A> void reverse_M1(int num_nodes, A&&...) { stage_on(num_nodes, "reverse_M1"); }
+    template <typename... A> void reverse_A1(int num_nodes, A&&...) { stage_on(num_nodes, "reverse_A1"); }
+    template <typename... A> void reverse_H1(int num_nodes, A&&...) { stage_on(num_nodes, "reverse_H1"); }
+    template <typename... A> void reverse_M0(int num_nodes, A&&...) { stage_on(num_nodes, "reverse_M0"); }
+    template <typename... A> void reverse_A0(int num_nodes, A&&...) { stage_on(num_nodes, "reverse_A0"); }
+    template <typename... A> void reverse_A0_scaled(int num_nodes, A&&...) { stage_on(num_nodes, "reverse_A0_scaled"); }
     // The sender index array decides which rows of H1 are gathered (mace.hpp:117); here it is the one given to begin().
-    void compute_Phi1(const int, std::span<const int>, std::span<const int>) { stage("compute_Phi1"); }
-    void reverse_Phi1(const int, std::span<const int>, std::span<const int>, std::span<const double>, std::span<const double>,
-                      bool zero_dxyz = true, bool zero_H1_adj = true) { stage("reverse_Phi1", zero_dxyz, zero_H1_adj); }
-    void reverse_H2(const int, std::span<const int>, bool zero_H1_adj = true) { stage("reverse_H2", true, zero_H1_adj); }
-    void reverse_A1_scaled(const int, std::span<const int>, std::span<const int>, std::span<const int>, std::span<const double>,
-                           std::span<const double>, bool zero_dxyz = true) { stage("reverse_A1_scaled", zero_dxyz, true); }
+    void compute_Phi1(const int num_nodes, std::span<const int>, std::span<const int>) { stage_on(num_nodes, "compute_Phi1"); }
+    void reverse_Phi1(const int num_nodes, std::span<const int>, std::span<const int>, std::span<const double>, std::span<const double>,
+                      bool zero_dxyz = true, bool zero_H1_adj = true) { stage_on(num_nodes, "reverse_Phi1", zero_dxyz, zero_H1_adj); }
+    void reverse_H2(const int num_nodes, std::span<const int>, bool zero_H1_adj = true) { stage_on(num_nodes, "reverse_H2", true, zero_H1_adj); }
+    void reverse_A1_scaled(const int num_nodes, std::span<const int>, std::span<const int>, std::span<const int>, std::span<const double>,
+                           std::span<const double>, bool zero_dxyz = true) { stage_on(num_nodes, "reverse_A1_scaled", zero_dxyz, true); }
 
     // Middle interaction block of a model whose file says "num_interactions": 3. The reference has no counterpart (its
     // models have exactly two blocks, extract_mace_data.py:70-71); the stages take the place of a second
@@ -141,8 +149,11 @@ public:
     // branch (pair_symmetrix_mace.cpp:551-748) runs layer 0 on nlocal + nghost receivers and layer 1 on nlocal. Here the
     // edge set is given once to begin() with all receivers (owned first); restrict_nodes starts an evaluation on the
     // first `num_nodes`, set_active_nodes changes the count in the middle of one and keeps the accumulated outputs.
-    long restrict_nodes(int num_nodes) { long e = 0; check(smx_restrict_nodes(h_, num_nodes, &e)); return e; }
-    long set_active_nodes(int num_nodes) { long e = 0; check(smx_set_active_nodes(h_, num_nodes, &e)); return e; }
+    long restrict_nodes(int num_nodes) { long e = 0; check(smx_restrict_nodes(h_, num_nodes, &e)); active_nodes_ = num_nodes; return e; }
+    long set_active_nodes(int num_nodes) { long e = 0; check(smx_set_active_nodes(h_, num_nodes, &e)); active_nodes_ = num_nodes; return e; }
+    // Grow "H1" / "H1_adj" to `rows` feature rows (ghost rows appended, zero-filled), as the pair style resizes its H1
+    // vector to nlocal + nghost rows before forward_comm (pair_symmetrix_mace.cpp:463-464).
+    void resize_rows(const std::string& name, int rows) { check(smx_resize_rows(h_, name.c_str(), rows)); }
     smx_handle handle() const { return h_; }
 
 private:
@@ -151,8 +162,15 @@ private:
     void check(int status) const {
         if (status != SMX_OK) throw std::runtime_error(smx_last_error(h_));
     }
+    int active_nodes_ = -1;       // receiver count in effect (-1: taken from the library at the first staged call)
     void stage(const char* name, bool zero_dxyz = true, bool zero_H1_adj = true) {
         check(smx_stage(h_, name, zero_dxyz ? 1 : 0, zero_H1_adj ? 1 : 0));
+    }
+    // A stage on `num_nodes` receivers: switches the active receivers when the count differs from the one in effect.
+    void stage_on(int num_nodes, const char* name, bool zero_dxyz = true, bool zero_H1_adj = true) {
+        if (active_nodes_ < 0) check(smx_active_counts(h_, &active_nodes_, nullptr, nullptr));
+        if (num_nodes != active_nodes_) set_active_nodes(num_nodes);
+        stage(name, zero_dxyz, zero_H1_adj);
     }
     std::vector<double>& mirror(const std::string& name) {
         if (name == "node_energies") return node_energies;

@@ -97,6 +97,55 @@ def test_decomposed_float64_evaluations_are_bitwise_reproducible(model_file):
             assert np.array_equal(a, b)
 
 
+def _write_vec(f, a, dt):
+    a = np.ascontiguousarray(a, dtype=dt).reshape(-1)
+    f.write(np.int64(a.size).tobytes()); f.write(a.tobytes())
+
+
+@pytest.mark.parametrize("mode", ["message_passing", "recompute"])
+@pytest.mark.parametrize("flags", [dict(), dict(zbl=True, density=True)])
+def test_cpp_pair_style_harness_replays_both_decomposed_modes(model_file, tmp_path, mode, flags):
+    """tests/pair_harness.cpp: the stage sequences of the reference pair style's two decomposed compute() modes
+    (pair_symmetrix_mace.cpp:436-495 and :551-748), with the reference's argument lists, against the C++ facade, for all
+    ranks of a 3-slab decomposition; forward_comm / reverse_comm are played on the host vectors. Energy and forces must
+    equal the single-domain evaluation."""
+    root = Path(__file__).resolve().parents[1]
+    pkg = root / "symmetrix_b200"
+    exe = tmp_path / "pair_harness"
+    subprocess.run(["g++", "-std=c++20", "-O1", f"-I{root / 'include'}", str(root / "tests" / "pair_harness.cpp"), "-o", str(exe),
+                    f"-L{pkg}", "-lsymmetrix_b200", f"-Wl,-rpath,{pkg}"], check=True)
+    world = 3
+    path, model, spec = model_file("fcc128", num_channels=32, num_spline_points=32, **flags)
+    a0 = 3.2 if flags else 3.6
+    s = st.fcc_box((4 * world, 3, 3), a0, model["atomic_numbers"], seed=13, jitter=0.2 if flags else 0.12)
+    f_ref, v_ref, e_ref = _single(path, s)
+    zmap = {int(z): t for t, z in enumerate(model["atomic_numbers"])}
+    plans = [make_slab_plan(s, spec.r_cut, r, world, mode=mode) for r in range(world)]
+    for plan in plans:
+        local = st.Structure(plan.positions, plan.cell, plan.numbers, plan.pbc)
+        nl = st.neighbor_list(local, spec.r_cut)
+        n_recv = plan.n_own + (plan.n_inner if mode == "recompute" else 0)
+        types = np.array([zmap[int(z)] for z in plan.numbers], dtype=np.int32)
+        num_neigh = np.bincount(nl["i"], minlength=local.num_atoms).astype(np.int32)[:n_recv]
+        e_cnt = int(num_neigh.sum())
+        with open(tmp_path / f"case{plan.rank}.bin", "wb") as f:
+            _write_vec(f, [plan.n_own, plan.n_own + plan.n_ghost, n_recv, len(plan.peers)], np.int32)
+            _write_vec(f, types[:n_recv], np.int32); _write_vec(f, num_neigh, np.int32)
+            _write_vec(f, nl["j"][:e_cnt], np.int32); _write_vec(f, types[nl["j"][:e_cnt]], np.int32)
+            _write_vec(f, nl["D"][:e_cnt], np.float64); _write_vec(f, nl["d"][:e_cnt], np.float64)
+            for q in plan.peers:
+                _write_vec(f, [q], np.int32); _write_vec(f, plan.send_rows[q], np.int32); _write_vec(f, plan.recv_rows[q], np.int32)
+    subprocess.run([str(exe), str(path), "0" if mode == "message_passing" else "1", str(world), str(tmp_path / "case"),
+                    str(tmp_path / "out")], check=True)
+    energy, forces = 0.0, np.zeros_like(f_ref)
+    for plan in plans:
+        out = np.fromfile(tmp_path / f"out{plan.rank}.bin", dtype=np.float64)
+        energy += out[0]
+        forces[plan.own_global] = out[1:].reshape(-1, 3)
+    assert abs(energy - e_ref) <= 1e-10 * abs(e_ref)
+    assert np.abs(forces - f_ref).max() <= 1e-8 * max(1.0, np.abs(f_ref).max())
+
+
 def _gpu_count():
     import torch
     return torch.cuda.device_count()
