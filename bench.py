@@ -337,6 +337,8 @@ def run_ours(args):
                 evs["f32" if args.dtype == "float64" else "f64"] = ev2
             out["parity"] = parity_on_sample(evs, sample)
             out["parity"]["against"] = out["cpu_baseline"]["kind"] + " CPU evaluator on the cpu_baseline sample"
+        if world == 1 and not args.no_extra:
+            out.setdefault("extra", {})["radial_mlp"] = radial_mode_comparison(path, n_atoms, dev, keys, flush, torch, local_rank)
         if world == 1 and not args.no_extra and args.workload == "fcc4000":
             del ev2
             out.setdefault("extra", {})["config3"] = config3_single(local_rank, torch)
@@ -344,6 +346,42 @@ def run_ours(args):
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    return out
+
+
+def radial_mode_comparison(path, n_atoms, dev, keys, flush, torch, local_rank) -> dict:
+    """float32 stage times of the tensor product with the radial functions from the spline tables and, where the model
+    file carries the un-splined network, from that network at run time (SMX_RADIAL=mlp: hidden layers per edge + last layer
+    as a tensor-core GEMM, then the same tensor-product kernels reading per-edge values)."""
+    from symmetrix_b200 import MACE
+    out = {}
+    for mode in ("spline", "mlp"):
+        os.environ["SMX_RADIAL"] = mode
+        try:
+            ev = MACE(path, dtype="float32", device=local_rank)
+        except Exception as exc:            # model without x_radial_* keys
+            out[mode] = {"unavailable": str(exc)}
+            continue
+        finally:
+            os.environ.pop("SMX_RADIAL", None)
+        ev.set_profiling(True)
+        acc: dict = {}
+        total = 0.0
+        for it in range(4):
+            flush.zero_(); torch.cuda.synchronize()
+            ev.timer_start()
+            ev.compute_node_energies_forces(n_atoms, *[dev[k] for k in keys])
+            t = ev.timer_stop()
+            if it > 0:
+                total += t
+                for name, ms in ev.stage_times().items():
+                    acc[name] = acc.get(name, 0.0) + ms / 3
+        energy = ev.reduce_forces(want_forces=False)[2]
+        out[mode] = {"compute_Phi1_ms": acc.get("compute_Phi1"), "reverse_Phi1_ms": acc.get("reverse_Phi1"), "step_ms": total / 3,
+                     "energy": energy}
+        del ev
+    if "energy" in out.get("spline", {}) and "energy" in out.get("mlp", {}):
+        out["rel_energy_diff"] = abs(out["mlp"]["energy"] - out["spline"]["energy"]) / abs(out["spline"]["energy"])
     return out
 
 

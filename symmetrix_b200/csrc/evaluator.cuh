@@ -122,6 +122,13 @@ public:
     DevBuf<int> kernel_status;    // non-zero if a bounded mbarrier wait ran out (1, 2: tcgen05 GEMM; 3, 4: staged tensor-product reverse)
     bool staged_reverse = false;  // spline rows of the tensor-product reverse through bulk copies into shared memory
                                   // (SMX_TP_STAGED=1; measured equal in float64 and 15 % slower in float32 on B200)
+    // Run-time radial mode (SMX_RADIAL=mlp, float32, two-block models whose file carries the x_radial_* keys): the radial
+    // functions of block 1 come from the un-splined network -- hidden layers per edge (radial_hidden_kernel), last layer
+    // as a tensor-core GEMM over all edges -- instead of the spline tables.
+    bool radial_mlp = false;
+    bool radial_hidden_valid = false;     // x3 / dx3 hold the hidden activations of the current active edge set
+    DevBuf<float> rn_w_first, rn_w_hidden, rn_w_last, rn_pair_scale, rn_x, rn_dx;
+    DevBuf<T> R_edge, Rd_edge;
     bool tmem_reverse = true;     // float64 tensor-product reverse with the receiver adjoint in tensor memory (SMX_TP_TMEM=0: in registers)
     bool type_order = true;       // edge kernels walk the receivers in element-type order (SMX_TYPE_ORDER=0: natural order)
     bool waits_in_flight = false; // a kernel with bounded waits has been launched since the last status check
@@ -143,6 +150,17 @@ public:
         if (const char* t = std::getenv("SMX_TP_STAGED")) staged_reverse = std::string(t) != "0";
         if (const char* t = std::getenv("SMX_TYPE_ORDER")) type_order = std::string(t) != "0";
         if (const char* t = std::getenv("SMX_TP_TMEM")) tmem_reverse = std::string(t) != "0";
+        if (const char* t = std::getenv("SMX_RADIAL")) {
+            const std::string mode(t);
+            if (mode == "mlp") {
+                if (sizeof(T) != 4) throw UnsupportedError("SMX_RADIAL=mlp is a float32 mode (the float64 path reproduces the reference's splines)");
+                if (!model.rmlp1.present) throw UnsupportedError("SMX_RADIAL=mlp needs the x_radial_* keys in the model file");
+                if (model.num_interactions != 2) throw UnsupportedError("SMX_RADIAL=mlp supports two-block models");
+                radial_mlp = true;
+            } else if (mode != "spline" && !mode.empty()) {
+                throw ArgError("SMX_RADIAL must be 'spline' or 'mlp'");
+            }
+        }
         if constexpr (sizeof(T) == 4) {
             // float32 GEMMs run on tcgen05 unless SMX_GEMM=mma asks for the mma.sync kernel
             const char* g = std::getenv("SMX_GEMM");
@@ -206,6 +224,12 @@ public:
             progm_off.upload(offs, stream);
             progm_cnt.upload(counts, stream);
             monom_off.upload(std::vector<int>(m.mono_offm.begin(), m.mono_offm.end() - 1), stream);
+        }
+        if (radial_mlp) {
+            rn_w_first.upload(cast_vec<float>(m.rmlp1.w_first), stream);
+            rn_w_hidden.upload(cast_vec<float>(m.rmlp1.w_hidden), stream);
+            rn_w_last.upload(cast_vec<float>(m.rmlp1.w_last), stream);
+            rn_pair_scale.upload(cast_vec<float>(m.rmlp1.pair_scale), stream);
         }
         E0.upload(m.atomic_energies, stream);
         if (m.has_zbl) { zbl_radii.upload(m.zbl_covalent_radii, stream); zbl_numbers.upload(m.atomic_numbers, stream); }
@@ -291,6 +315,7 @@ public:
         if (!keep) { h1_rows = N; hm_rows = N; }
         sender_rows = -1;
         have_edges = true;
+        radial_hidden_valid = false;
         if (rescan) {
             first_host_valid = false;
             // offsets of all receivers; a restricted set uses a prefix of this scan (entry n = edges of the first n)
@@ -632,6 +657,7 @@ public:
             a.coef1 = coef1.p; a.H = deep() ? Hm.p : H1.p; a.Phi1 = Phi1.p; a.dPhi1 = dPhi1.p; a.H_adj = deep() ? Hm_adj.p : H1_adj.p;
         }
         a.Hmsg = Hmsg.p; a.node_forces = node_forces.p;
+        if (radial_mlp && which == 1) { a.R_edge = R_edge.p; a.Rd_edge = Rd_edge.p; }
         a.status = kernel_status.p;
         a.order = type_order ? perm.p : nullptr;
         return a;
@@ -659,7 +685,7 @@ public:
         if (reverse) {
             // two slots of one spline-row chunk each; staged only if that costs no resident CTA
             const size_t slots = 2 * sizeof(T) * 4 * make_tp_table(LF).P * static_cast<size_t>(std::min(model.K, block));
-            bool staged = staged_reverse && slots <= static_cast<size_t>(max_dynamic_smem);
+            bool staged = staged_reverse && !radial_mlp && slots <= static_cast<size_t>(max_dynamic_smem);
             int plain_per_sm = 0, staged_per_sm = 0;
             if (staged) {
                 SMX_CUDA(cudaFuncSetAttribute(tp_reverse_kernel<T, LF, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(slots)));
@@ -691,6 +717,44 @@ public:
         }
     }
 
+    // Run-time radial mode: R_edge (and Rd_edge when `with_derivative`) of the active edges from the un-splined network.
+    void radial_from_network(bool with_derivative) {
+        if constexpr (sizeof(T) == 4) {
+            const auto& rm = model.rmlp1;
+            const int H = rm.hidden, F1 = model.tp.P * model.K;
+            if (!radial_hidden_valid) {
+                rn_x.resize(static_cast<size_t>(E) * H, stream);
+                rn_dx.resize(static_cast<size_t>(E) * H, stream);
+                RadialNetArgs a{};
+                a.N = N; a.num_bessel = rm.num_bessel; a.poly_p = rm.poly_p; a.hidden = H; a.num_hidden_layers = rm.num_hidden_layers;
+                a.num_elements = model.num_elements; a.r_cut = static_cast<float>(model.r_cut); a.silu_scale = static_cast<float>(rm.silu_scale);
+                a.node_types = node_types; a.first_neigh = first_neigh.p; a.neigh_types = neigh_types; a.r = r;
+                a.w_first = rn_w_first.p; a.w_hidden = rn_w_hidden.p; a.pair_scale = rn_pair_scale.p; a.x_out = rn_x.p; a.dx_out = rn_dx.p;
+                const size_t smem = sizeof(float) * (static_cast<size_t>(rm.num_bessel) * H + static_cast<size_t>(rm.num_hidden_layers - 1) * H * H +
+                                                     kRadialGroups * 4 * 64);
+                SMX_CUDA(cudaFuncSetAttribute(radial_hidden_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+                const int grid = std::max(1, std::min(N, num_sms * 4));
+                radial_hidden_kernel<<<grid, kRadialGroups * 64, smem, stream>>>(a);
+                check_launch("radial_hidden_kernel");
+                radial_hidden_valid = true;
+            }
+            if (E > 0x7fffffffL) throw UnsupportedError("more than 2^31 edges in one call");
+            R_edge.resize(static_cast<size_t>(E) * F1, stream);
+            std::vector<GemmProblem<T>> list;
+            auto last_layer = [&](const float* in, T* out) {
+                GemmProblem<T> p = problem(in, out, rn_w_last.p, false, 0, 1, H, 0, 0, F1, 0, 0, H, F1, F1, false, false);
+                p.num_nodes = static_cast<int>(E);
+                return p;
+            };
+            list.push_back(last_layer(rn_x.p, R_edge.p));
+            if (with_derivative) {
+                Rd_edge.resize(static_cast<size_t>(E) * F1, stream);
+                list.push_back(last_layer(rn_dx.p, Rd_edge.p));
+            }
+            run_gemms(list, E, F1);
+        }
+    }
+
     // Tensor product of block `which` (1: last, 2: middle). Sender features / their adjoints: see tp_args.
     void tp_forward_stage(int which, const char* what) {   // MACE::compute_Phi1, mace.cpp:453-502
         const int K = model.K;
@@ -699,6 +763,7 @@ public:
         DevBuf<T>& out = which == 2 ? Phim : Phi1;
         out.resize(static_cast<size_t>(N) * model.tp.Q * K, stream);
         if (N == 0) return;
+        if (radial_mlp && which == 1) radial_from_network(false);
         dispatch_tp(false, which);
     }
     void tp_reverse_stage(int which, bool zero_dxyz, bool zero_adj, const char* what) {   // MACE::reverse_Phi1, mace.cpp:504-605
@@ -714,6 +779,7 @@ public:
         if (zero_adj) adj.zero(stream);
         if (N == 0) return;
         if (sizeof(T) == 4) {      // float32: messages are accumulated in place by the kernel
+            if (radial_mlp && which == 1) radial_from_network(true);
             dispatch_tp(true, which);
             return;
         }

@@ -445,6 +445,10 @@ struct TPArgs {
     double* node_forces;    // reverse: accumulated into
     int* status;            // set non-zero by a bounded wait that ran out (staged reverse kernel)
     const int* order;       // optional processing order of the receivers (see Layer0Args::order)
+    // Run-time radial mode: the radial functions of every edge (and their derivatives, reverse pass) evaluated from the
+    // un-splined network by radial_hidden_kernel + a tensor-core GEMM, [num_edges][P * K]; null: cubic splines (coef1).
+    const T* R_edge;
+    const T* Rd_edge;
 };
 
 // Resident CTAs per SM the compiler is asked to allow for (register budget): measured best on B200 for the
@@ -492,10 +496,16 @@ __global__ void __launch_bounds__(kChannelBlock, tp_min_blocks<T>(LF, false)) tp
                     T h[tp.nLM], R[tp.P], Y[kNumLm];
 #pragma unroll
                     for (int lm2 = 0; lm2 < tp.nLM; ++lm2) h[lm2] = __ldg(hrow + static_cast<size_t>(lm2) * a.K);
+                    if (a.R_edge) {
+                        const T* re = a.R_edge + static_cast<size_t>(e0 + e) * F + k;
 #pragma unroll
-                    for (int p = 0; p < tp.P; ++p) {
-                        const Vec4<T> c = load_coef<T>(cb + 4 * p * a.K, k, a.K);
-                        R[p] = c.x + x * (c.y + x * (c.z + x * c.w));
+                        for (int p = 0; p < tp.P; ++p) R[p] = __ldcs(re + static_cast<size_t>(p) * a.K);
+                    } else {
+#pragma unroll
+                        for (int p = 0; p < tp.P; ++p) {
+                            const Vec4<T> c = load_coef<T>(cb + 4 * p * a.K, k, a.K);
+                            R[p] = c.x + x * (c.y + x * (c.z + x * c.w));
+                        }
                     }
 #pragma unroll
                     for (int lm = 0; lm < kNumLm; ++lm) Y[lm] = s.Y[lm];
@@ -616,12 +626,19 @@ __global__ void __launch_bounds__(kChannelBlock, tp_min_blocks<T>(LF, true)) tp_
 #pragma unroll
                     for (int lm2 = 0; lm2 < tp.nLM; ++lm2) { h[lm2] = __ldg(hrow + static_cast<size_t>(lm2) * a.K); msg[lm2] = T(0); }
                     if constexpr (!STAGED) {
-                        const T* cb = a.coef1 + s.coef_base;
+                        if (a.R_edge) {
+                            const T* re = a.R_edge + static_cast<size_t>(e0 + e) * F + k;
+                            const T* rde = a.Rd_edge + static_cast<size_t>(e0 + e) * F + k;
 #pragma unroll
-                        for (int p = 0; p < tp.P; ++p) {
-                            const Vec4<T> c = load_coef<T>(cb + 4 * p * a.K, k, a.K);
-                            R[p] = c.x + x * (c.y + x * (c.z + x * c.w));
-                            Rd[p] = c.y + x * (T(2) * c.z + T(3) * x * c.w);
+                            for (int p = 0; p < tp.P; ++p) { R[p] = __ldcs(re + static_cast<size_t>(p) * a.K); Rd[p] = __ldcs(rde + static_cast<size_t>(p) * a.K); }
+                        } else {
+                            const T* cb = a.coef1 + s.coef_base;
+#pragma unroll
+                            for (int p = 0; p < tp.P; ++p) {
+                                const Vec4<T> c = load_coef<T>(cb + 4 * p * a.K, k, a.K);
+                                R[p] = c.x + x * (c.y + x * (c.z + x * c.w));
+                                Rd[p] = c.y + x * (T(2) * c.z + T(3) * x * c.w);
+                            }
                         }
                     }
 #pragma unroll
@@ -839,6 +856,96 @@ __global__ void __launch_bounds__(kChannelBlock, MINB) tp_reverse_tmem_kernel(co
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_slot), "r"(kCols) : "memory");
+}
+
+// ---------------------------------------------------------------------------------------------
+// Run-time radial mode, first part: the hidden activations of the radial network and their derivatives with respect
+// to the edge length, per edge. The network is what the reference's exporter tabulates into its cubic splines
+// (symmetrix/source/symmetrix/extract_mace_data.py:144-172):
+//   f_n(r) = sqrt(2 / r_cut) sin(n pi r / r_cut) / r * cutoff_p(r / r_cut) * pair_scale[pair][n]
+//   x <- s silu(x W) per hidden layer (s = silu_scale),  dx/dr by the chain rule alongside.
+// The last layer (hidden -> P K values per edge) is a dense GEMM over all edges and runs on the tensor cores
+// (gemm_rows_tcgen05_kernel). One group of `hidden` threads per edge, four groups per CTA; the weights sit in shared
+// memory, thread j of a group owns neuron j.
+// ---------------------------------------------------------------------------------------------
+struct RadialNetArgs {
+    int N, num_bessel, poly_p, hidden, num_hidden_layers, num_elements;
+    float r_cut, silu_scale;
+    const int* node_types; const long long* first_neigh; const int* neigh_types; const double* r;
+    const float* w_first;      // [num_bessel][hidden]
+    const float* w_hidden;     // [num_hidden_layers - 1][hidden][hidden]
+    const float* pair_scale;   // [pairs][num_bessel]
+    float* x_out;              // [num_edges][hidden]
+    float* dx_out;             // [num_edges][hidden]
+};
+constexpr int kRadialGroups = 4;
+
+static __global__ void __launch_bounds__(kRadialGroups * 64) radial_hidden_kernel(const RadialNetArgs a) {
+    extern __shared__ float radial_smem[];
+    const int H = a.hidden;
+    float* w1 = radial_smem;                                        // [num_bessel][H]
+    float* wh = w1 + a.num_bessel * H;                              // [(layers - 1)][H][H]
+    float* act = wh + (a.num_hidden_layers - 1) * H * H;            // [groups][2 buffers][2 (x, dx)][64]
+    for (int t = threadIdx.x; t < a.num_bessel * H; t += blockDim.x) w1[t] = a.w_first[t];
+    for (int t = threadIdx.x; t < (a.num_hidden_layers - 1) * H * H; t += blockDim.x) wh[t] = a.w_hidden[t];
+    __syncthreads();
+    const int group = threadIdx.x / 64, j = threadIdx.x % 64;
+    float* mine = act + group * 4 * 64;
+    const double pi = 3.14159265358979323846;
+    for (int i = blockIdx.x; i < a.N; i += gridDim.x) {
+        const int type_i = a.node_types[i];
+        const long long e_begin = a.first_neigh[i], e_end = a.first_neigh[i + 1];
+        const long long rounds = (e_end - e_begin + kRadialGroups - 1) / kRadialGroups;
+        for (long long rd = 0; rd < rounds; ++rd) {
+            const long long e = e_begin + rd * kRadialGroups + group;
+            const bool live = e < e_end;
+            if (live && j < a.num_bessel) {
+                const double rr = a.r[e], rc = a.r_cut;
+                const int tj = a.neigh_types[e];
+                const int lo = type_i <= tj ? type_i : tj, hi = type_i <= tj ? tj : type_i;
+                const int pair = lo * (2 * a.num_elements - lo - 1) / 2 + hi;
+                const double kn = (j + 1) * pi / rc, amp = sqrt(2.0 / rc);
+                const double sn = sin(kn * rr), cs = cos(kn * rr);
+                const double b = amp * sn / rr, db = amp * (kn * cs / rr - sn / (rr * rr));
+                const double x = rr / rc, p = a.poly_p;
+                double c = 0.0, dc = 0.0;
+                if (x < 1.0) {
+                    c = 1.0 - (p + 1.0) * (p + 2.0) / 2.0 * pow(x, p) + p * (p + 2.0) * pow(x, p + 1.0) - p * (p + 1.0) / 2.0 * pow(x, p + 2.0);
+                    dc = (-(p + 1.0) * (p + 2.0) / 2.0 * p * pow(x, p - 1.0) + p * (p + 2.0) * (p + 1.0) * pow(x, p)
+                          - p * (p + 1.0) / 2.0 * (p + 2.0) * pow(x, p + 1.0)) / rc;
+                }
+                const double sc = a.pair_scale[pair * a.num_bessel + j];
+                mine[j] = static_cast<float>(b * c * sc);
+                mine[64 + j] = static_cast<float>((db * c + b * dc) * sc);
+            }
+            __syncthreads();
+            int cur = 0;
+            for (int layer = 0; layer < a.num_hidden_layers; ++layer) {
+                const float* xin = mine + cur * 128;
+                float* xout = mine + (cur ^ 1) * 128;
+                const int n_in = layer == 0 ? a.num_bessel : H;
+                const float* w = layer == 0 ? w1 : wh + (layer - 1) * H * H;
+                if (live && j < H) {
+                    float z = 0.f, dz = 0.f;
+                    for (int q = 0; q < n_in; ++q) {
+                        const float wv = w[q * H + j];
+                        z = fmaf(xin[q], wv, z);
+                        dz = fmaf(xin[64 + q], wv, dz);
+                    }
+                    const float sig = 1.f / (1.f + expf(-z));
+                    xout[j] = a.silu_scale * z * sig;
+                    xout[64 + j] = a.silu_scale * sig * (1.f + z * (1.f - sig)) * dz;
+                }
+                __syncthreads();
+                cur ^= 1;
+            }
+            if (live && j < H) {
+                a.x_out[static_cast<size_t>(e) * H + j] = mine[cur * 128 + j];
+                a.dx_out[static_cast<size_t>(e) * H + j] = mine[cur * 128 + 64 + j];
+            }
+            __syncthreads();
+        }
+    }
 }
 
 // Input check for callers that cannot vouch for their edge arrays: counts, per kind, the entries that would make the

@@ -130,6 +130,20 @@ struct HostModel {
     std::vector<int> path_file_to_canon;   // index by the file's path number
     std::vector<int> lme_file_to_canon;    // output slot permutation (identity for canonical files)
     std::vector<double> path_scale;        // per canonical path: file coupling / canonical coupling
+    // Un-splined radial network of interaction block 1 (optional extra keys "x_radial_*" of a model file; what the
+    // reference's exporter tabulates into the splines, extract_mace_data.py:144-172):
+    //   basis_n(r) = sqrt(2 / r_cut) sin(n pi r / r_cut) / r * cutoff_p(r / r_cut) * pair_scale[pair][n],  n = 1..num_bessel
+    //   x <- silu_scale * silu(x W_i) for the hidden layers,  R = x W_last
+    // `w_last` is in canonical path order with the per-path coupling scale folded in, like the spline tables.
+    struct RadialMlp {
+        bool present = false;
+        int num_bessel = 0, poly_p = 0, hidden = 0, num_hidden_layers = 0;
+        double silu_scale = 1.0;
+        std::vector<double> w_first;      // [num_bessel][hidden]
+        std::vector<double> w_hidden;     // [num_hidden_layers - 1][hidden][hidden]
+        std::vector<double> w_last;       // [hidden][P K]
+        std::vector<double> pair_scale;   // [pairs][num_bessel]
+    } rmlp1;
 
     // symmetric contractions: programs per LM (M0) and one for M1; coefficients [element][monomial][K]
     std::vector<PolyProgram> prog0;
@@ -399,6 +413,44 @@ inline HostModel load_model_file(const std::string& filename) {
             }
     };
     fold_path_scale(m.coef1);
+    if (const JsonValue* dims_v = file.find("x_radial_mlp_dims_1")) {
+        HostModel::RadialMlp& r = m.rmlp1;
+        const std::vector<int> dims = dims_v->flat_int();
+        const JsonValue& ws = file.at("x_radial_mlp_weights_1");
+        r.num_bessel = file.at("x_radial_num_bessel").as_int();
+        r.poly_p = file.at("x_radial_poly_p").as_int();
+        r.silu_scale = file.at("x_radial_silu_scale").as_double();
+        // supported shape: num_bessel -> hidden -> ... -> hidden -> P K with at least one hidden layer of equal widths
+        bool ok = dims.size() >= 3 && ws.size() + 1 == dims.size() && dims.front() == r.num_bessel && dims.back() == m.F1 &&
+                  r.num_bessel >= 1 && r.num_bessel <= 16;
+        for (size_t i = 2; ok && i + 1 < dims.size(); ++i) ok = dims[i] == dims[1];
+        if (ok && (dims[1] < 1 || dims[1] > 64)) ok = false;
+        if (ok) {
+            r.hidden = dims[1];
+            r.num_hidden_layers = static_cast<int>(dims.size()) - 2;
+            r.w_first = ws.arr[0].flat();
+            for (int i = 1; i < r.num_hidden_layers; ++i) {
+                const std::vector<double> w = ws.arr[i].flat();
+                if (w.size() != static_cast<size_t>(r.hidden) * r.hidden) ok = false;
+                r.w_hidden.insert(r.w_hidden.end(), w.begin(), w.end());
+            }
+            const std::vector<double> last = ws.arr[ws.size() - 1].flat();
+            r.pair_scale = file.at("x_radial_pair_scale_1").flat();
+            if (r.w_first.size() != static_cast<size_t>(r.num_bessel) * r.hidden || last.size() != static_cast<size_t>(r.hidden) * m.F1 ||
+                r.pair_scale.size() != static_cast<size_t>(m.num_pairs) * r.num_bessel) ok = false;
+            if (ok) {
+                r.w_last.assign(last.size(), 0.0);
+                for (int j = 0; j < r.hidden; ++j)
+                    for (int pf = 0; pf < P; ++pf) {
+                        const int c = m.path_file_to_canon[pf];
+                        for (int k = 0; k < K; ++k)
+                            r.w_last[static_cast<size_t>(j) * m.F1 + c * K + k] = m.path_scale[c] * last[static_cast<size_t>(j) * m.F1 + pf * K + k];
+                    }
+            }
+        }
+        if (!ok) throw ModelError("model file: x_radial_* keys are inconsistent (expected num_bessel -> equal hidden layers -> num_paths * num_channels)");
+        r.present = true;
+    }
     if (const JsonValue* ni = file.find("num_interactions")) m.num_interactions = ni->as_int();
     if (m.num_interactions != 2 && m.num_interactions != 3) throw UnsupportedError("num_interactions must be 2 or 3");
     if (m.num_interactions == 3) {

@@ -253,7 +253,17 @@ def generate_model(spec: ModelSpec) -> dict:
 
     paths, lme, t_idx, cg = tp_tables(l_max, L_max)
     h, v0, d0, mlp0, _ = radial_mlp_tables(spec, rng, (l_max + 1) * k, gain=1.0)
-    h1, v1, d1, mlp1, _ = radial_mlp_tables(spec, rng, len(paths) * k, gain=1.0)
+    h1, v1, d1, mlp1, pair_scale1 = radial_mlp_tables(spec, rng, len(paths) * k, gain=1.0)
+    # The un-splined radial network of interaction block 1 (what the reference's exporter feeds to its cubic splines,
+    # extract_mace_data.py:144-172): Bessel functions times the polynomial cutoff, a per-pair rescaling of the basis, and
+    # the MLP. Keys with the "x_" prefix are extras that the reference loader ignores; the evaluator's run-time radial
+    # mode (SMX_RADIAL=mlp) evaluates R(r) from them instead of reading the spline tables.
+    out["x_radial_num_bessel"] = int(spec.num_bessel)
+    out["x_radial_poly_p"] = int(spec.poly_p)
+    out["x_radial_silu_scale"] = SILU_CST
+    out["x_radial_mlp_dims_1"] = [int(w.shape[0]) for w in mlp1] + [int(mlp1[-1].shape[1])]
+    out["x_radial_mlp_weights_1"] = [np.ascontiguousarray(w).ravel() for w in mlp1]          # each [in][out], row-major
+    out["x_radial_pair_scale_1"] = [pair_scale1[(a, b)] for a in range(n_el) for b in range(a, n_el)]
     out["radial_spline_h"] = h
     out["radial_spline_values_0"] = v0
     out["radial_spline_derivs_0"] = d0

@@ -376,6 +376,74 @@ def test_models_with_unusual_monomials_use_the_table_driven_contraction(tiny, tm
     check_against(dtype, e, f, e_ref, f_ref)
 
 
+def _permute_paths(model: dict, rng) -> dict:
+    """The same model with the tensor-product paths listed in another order inside each group of equal output degree l
+    (an exporter probes the paths numerically and need not produce the evaluator's own order,
+    symmetrix/source/symmetrix/extract_mace_data.py:323-381). Everything indexed by path moves along: Phi1_l1 / Phi1_l2,
+    the rows of radial_spline_*_1, the row blocks of A1_weights and both index arrays of the Clebsch-Gordan COO."""
+    out = dict(model)
+    K = int(model["num_channels"])
+    pl, pl1, pl2 = list(model["Phi1_l"]), list(model["Phi1_l1"]), list(model["Phi1_l2"])
+    P = len(pl)
+    new_of_old = np.zeros(P, dtype=int)          # new position of old path p
+    order = []                                   # old path at each new position
+    for l in sorted(set(pl)):
+        group = [p for p in range(P) if pl[p] == l]
+        order += list(rng.permutation(group))
+    for new, old in enumerate(order):
+        new_of_old[old] = new
+    assert any(new_of_old[p] != p for p in range(P))
+    out["Phi1_l"] = [pl[o] for o in order]; out["Phi1_l1"] = [pl1[o] for o in order]; out["Phi1_l2"] = [pl2[o] for o in order]
+    for key in ("radial_spline_values_1", "radial_spline_derivs_1"):
+        out[key] = [np.concatenate([np.asarray(pair)[o * K:(o + 1) * K] for o in order]) for pair in model[key]]
+    n_e = {l: pl.count(l) for l in set(pl)}
+    e_old = [sum(1 for q in range(p) if pl[q] == pl[p]) for p in range(P)]
+    e_new = [sum(1 for q in range(new_of_old[p]) if out["Phi1_l"][q] == pl[p]) for p in range(P)]
+    a1 = []
+    for l, w in enumerate(model["A1_weights"]):
+        w = np.asarray(w).reshape(-1, K, K) if n_e.get(l) else np.asarray(w)
+        if n_e.get(l):
+            blocks = [None] * n_e[l]
+            for p in range(P):
+                if pl[p] == l:
+                    blocks[e_new[p]] = w[e_old[p]]
+            w = np.concatenate([b.ravel() for b in blocks])
+        a1.append(w)
+    out["A1_weights"] = a1
+    t_off_old = np.concatenate([[0], np.cumsum([(2 * pl1[p] + 1) * (2 * pl2[p] + 1) for p in range(P)])])
+    t_off_new = np.concatenate([[0], np.cumsum([(2 * out["Phi1_l1"][q] + 1) * (2 * out["Phi1_l2"][q] + 1) for q in range(P)])])
+    lme_off = np.concatenate([[0], np.cumsum([(2 * l + 1) * n_e.get(l, 0) for l in range(4)])])
+    lme_new, t_new = [], []
+    for lme, t in zip(model["Phi1_lme"], model["Phi1_lelm1lm2"]):
+        p = int(np.searchsorted(t_off_old, t, side="right") - 1)
+        l = pl[p]
+        rel = lme - lme_off[l]
+        assert rel % n_e[l] == e_old[p]
+        lme_new.append(int(lme_off[l] + (rel // n_e[l]) * n_e[l] + e_new[p]))
+        t_new.append(int(t_off_new[new_of_old[p]] + (t - t_off_old[p])))
+    out["Phi1_lme"], out["Phi1_lelm1lm2"] = lme_new, t_new
+    return out
+
+
+@pytest.mark.parametrize("dtype", ["float64", "float32"])
+def test_model_file_with_paths_in_another_order(model_file, tmp_path, dtype):
+    """Path lists in any order inside an l-group are accepted and mean the same model: the permuted file gives, on the
+    GPU, what the reference gives for the permuted file, and what the GPU gives for the original."""
+    from symmetrix_b200.modelgen.generate import write_json
+    path, model, spec = model_file("fcc128", num_channels=32, num_spline_points=32)
+    permuted = _permute_paths(model, np.random.default_rng(8))
+    ppath = tmp_path / "permuted.json"
+    write_json(permuted, ppath)
+    s = st.fcc_box(3, 3.6, model["atomic_numbers"], seed=4)
+    nl = st.neighbor_list(s, spec.r_cut)
+    inputs = st.evaluator_inputs(s, nl, model["atomic_numbers"])
+    e_ref, f_ref = _oracle_for(ppath, permuted)(inputs)
+    e, f = run(MACE(ppath, dtype=dtype), inputs)
+    check_against(dtype, e, f, e_ref, f_ref)
+    e0, f0 = run(MACE(path, dtype=dtype), inputs)
+    check_against(dtype, e, f, e0, f0)
+
+
 def test_positions_outside_the_cell_give_the_same_energy_and_forces(model_file):
     """Atoms that have drifted out of the cell (the normal state in molecular dynamics): translating atoms by whole
     lattice vectors changes neither the edge set nor any result. The reference's ASE neighbour list accepts such
