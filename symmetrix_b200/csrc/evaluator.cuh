@@ -129,6 +129,10 @@ public:
     bool radial_hidden_valid = false;     // x3 / dx3 hold the hidden activations of the current active edge set
     DevBuf<float> rn_w_first, rn_w_hidden, rn_w_last, rn_pair_scale, rn_x, rn_dx;
     DevBuf<T> R_edge, Rd_edge;
+    DevBuf<unsigned char> rn_tiles;       // float16 weight tiles of the last layer, one per path (radial_prepare_tiles_kernel)
+    bool radial_fused = true;             // SMX_RADIAL_FUSED=0: last layer as a separate GEMM into per-edge arrays also in the forward pass
+    bool radial_in_kernel = false;        // set around the launch of the fused forward kernel
+    int tmem_min_blocks = 4;      // SMX_TP_TMEM_BLOCKS: 2, 3 or 4 resident CTAs per SM for that kernel
     bool tmem_reverse = true;     // float64 tensor-product reverse with the receiver adjoint in tensor memory (SMX_TP_TMEM=0: in registers)
     bool type_order = true;       // edge kernels walk the receivers in element-type order (SMX_TYPE_ORDER=0: natural order)
     bool waits_in_flight = false; // a kernel with bounded waits has been launched since the last status check
@@ -150,6 +154,7 @@ public:
         if (const char* t = std::getenv("SMX_TP_STAGED")) staged_reverse = std::string(t) != "0";
         if (const char* t = std::getenv("SMX_TYPE_ORDER")) type_order = std::string(t) != "0";
         if (const char* t = std::getenv("SMX_TP_TMEM")) tmem_reverse = std::string(t) != "0";
+        if (const char* t = std::getenv("SMX_TP_TMEM_BLOCKS")) tmem_min_blocks = std::max(2, std::min(4, std::atoi(t)));
         if (const char* t = std::getenv("SMX_RADIAL")) {
             const std::string mode(t);
             if (mode == "mlp") {
@@ -157,6 +162,7 @@ public:
                 if (!model.rmlp1.present) throw UnsupportedError("SMX_RADIAL=mlp needs the x_radial_* keys in the model file");
                 if (model.num_interactions != 2) throw UnsupportedError("SMX_RADIAL=mlp supports two-block models");
                 radial_mlp = true;
+                if (const char* f = std::getenv("SMX_RADIAL_FUSED")) radial_fused = std::string(f) != "0";
             } else if (mode != "spline" && !mode.empty()) {
                 throw ArgError("SMX_RADIAL must be 'spline' or 'mlp'");
             }
@@ -230,6 +236,11 @@ public:
             rn_w_hidden.upload(cast_vec<float>(m.rmlp1.w_hidden), stream);
             rn_w_last.upload(cast_vec<float>(m.rmlp1.w_last), stream);
             rn_pair_scale.upload(cast_vec<float>(m.rmlp1.pair_scale), stream);
+            if (m.K <= 128 && m.L_max <= 1 && m.rmlp1.hidden <= kRnHidden) {
+                rn_tiles.resize(static_cast<size_t>(m.tp.P) * kRnTileBytes, stream);
+                radial_prepare_tiles_kernel<<<64, 256, 0, stream>>>(rn_w_last.p, m.rmlp1.hidden, m.K, m.tp.P, rn_tiles.p);
+                check_launch("radial_prepare_tiles_kernel");
+            }
         }
         E0.upload(m.atomic_energies, stream);
         if (m.has_zbl) { zbl_radii.upload(m.zbl_covalent_radii, stream); zbl_numbers.upload(m.atomic_numbers, stream); }
@@ -657,7 +668,7 @@ public:
             a.coef1 = coef1.p; a.H = deep() ? Hm.p : H1.p; a.Phi1 = Phi1.p; a.dPhi1 = dPhi1.p; a.H_adj = deep() ? Hm_adj.p : H1_adj.p;
         }
         a.Hmsg = Hmsg.p; a.node_forces = node_forces.p;
-        if (radial_mlp && which == 1) { a.R_edge = R_edge.p; a.Rd_edge = Rd_edge.p; }
+        if (radial_mlp && which == 1 && !radial_in_kernel) { a.R_edge = R_edge.p; a.Rd_edge = Rd_edge.p; }
         a.status = kernel_status.p;
         a.order = type_order ? perm.p : nullptr;
         return a;
@@ -669,15 +680,18 @@ public:
             if (reverse && tmem_reverse && !staged_reverse) {
                 // receiver adjoint in tensor memory: more resident CTAs (see tp_reverse_tmem_kernel). The CTAs of one SM
                 // must fit into its 512 TMEM columns, or the allocation of the last one would wait for another to exit.
-                constexpr int kMinBlocks = LF >= 2 ? 2 : 4;
                 constexpr int kCols = tp_tmem_cols(LF);
-                static_assert(kCols * kMinBlocks <= 512, "resident CTAs must fit into tensor memory");
-                auto kern = tp_reverse_tmem_kernel<LF, kMinBlocks>;
-                int per_sm = 1;
-                SMX_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, block, 0));
-                per_sm = std::max(1, std::min(per_sm, 512 / kCols));
-                const int grid = static_cast<int>(std::max<long long>(1, std::min<long long>(static_cast<long long>(num_sms) * per_sm, N)));
-                kern<<<grid, block, 0, stream>>>(tp_args(which));
+                auto launch = [&](auto kern, int min_blocks) {
+                    int per_sm = 1;
+                    SMX_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, block, 0));
+                    per_sm = std::max(1, std::min(std::min(per_sm, min_blocks), 512 / kCols));
+                    const int grid = static_cast<int>(std::max<long long>(1, std::min<long long>(static_cast<long long>(num_sms) * per_sm, N)));
+                    kern<<<grid, block, 0, stream>>>(tp_args(which));
+                };
+                // resident CTAs per SM the kernel is compiled for (register budget 255 / 168 / 128)
+                if (LF >= 2 || tmem_min_blocks <= 2) launch(tp_reverse_tmem_kernel<LF, 2>, 2);
+                else if (tmem_min_blocks == 3) launch(tp_reverse_tmem_kernel<LF, 3>, 3);
+                else launch(tp_reverse_tmem_kernel<LF, 4>, 4);
                 check_launch("tp_reverse_tmem_kernel");
                 return;
             }
@@ -703,6 +717,18 @@ public:
             }
             check_launch("tp_reverse_kernel");
         } else {
+            if constexpr (sizeof(T) == 4 && LF <= 1) {      // for L_max = 2 the 17 weight tiles exceed shared memory
+                if (radial_in_kernel) {
+                    // radial functions from the un-splined network on the tensor cores inside the kernel: one CTA per SM
+                    constexpr int smem = RnSmem<LF>::kTotal;
+                    SMX_CUDA(cudaFuncSetAttribute(tp_forward_rnet_kernel<LF>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+                    const int grid = std::max(1, std::min(num_sms, N));
+                    waits_in_flight = true;
+                    tp_forward_rnet_kernel<LF><<<grid, kRnThreads, smem, stream>>>(tp_args(which), rn_tiles.p, rn_x.p, model.rmlp1.hidden);
+                    check_launch("tp_forward_rnet_kernel");
+                    return;
+                }
+            }
             const int grid = persistent_grid(tp_forward_kernel<T, LF>, block, 0, N);
             tp_forward_kernel<T, LF><<<grid, block, 0, stream>>>(tp_args(which));
             check_launch("tp_forward_kernel");
@@ -718,10 +744,10 @@ public:
     }
 
     // Run-time radial mode: R_edge (and Rd_edge when `with_derivative`) of the active edges from the un-splined network.
-    void radial_from_network(bool with_derivative) {
+    void radial_hidden() {
         if constexpr (sizeof(T) == 4) {
             const auto& rm = model.rmlp1;
-            const int H = rm.hidden, F1 = model.tp.P * model.K;
+            const int H = rm.hidden;
             if (!radial_hidden_valid) {
                 rn_x.resize(static_cast<size_t>(E) * H, stream);
                 rn_dx.resize(static_cast<size_t>(E) * H, stream);
@@ -738,6 +764,13 @@ public:
                 check_launch("radial_hidden_kernel");
                 radial_hidden_valid = true;
             }
+        }
+    }
+    void radial_from_network(bool with_derivative) {
+        if constexpr (sizeof(T) == 4) {
+            const auto& rm = model.rmlp1;
+            const int H = rm.hidden, F1 = model.tp.P * model.K;
+            radial_hidden();
             if (E > 0x7fffffffL) throw UnsupportedError("more than 2^31 edges in one call");
             R_edge.resize(static_cast<size_t>(E) * F1, stream);
             std::vector<GemmProblem<T>> list;
@@ -763,8 +796,13 @@ public:
         DevBuf<T>& out = which == 2 ? Phim : Phi1;
         out.resize(static_cast<size_t>(N) * model.tp.Q * K, stream);
         if (N == 0) return;
-        if (radial_mlp && which == 1) radial_from_network(false);
+        radial_in_kernel = false;
+        if (radial_mlp && which == 1) {
+            if (radial_fused && K <= 128 && model.L_max <= 1 && model.rmlp1.hidden <= kRnHidden) { radial_hidden(); radial_in_kernel = true; }
+            else radial_from_network(false);
+        }
         dispatch_tp(false, which);
+        radial_in_kernel = false;
     }
     void tp_reverse_stage(int which, bool zero_dxyz, bool zero_adj, const char* what) {   // MACE::reverse_Phi1, mace.cpp:504-605
         const int K = model.K, nLM = model.num_LM;

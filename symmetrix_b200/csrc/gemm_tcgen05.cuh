@@ -19,6 +19,8 @@
 
 #include <cuda_runtime.h>
 
+#include <cuda_fp16.h>
+
 #include <cstdint>
 
 #include "kernels.cuh"
@@ -295,6 +297,279 @@ static __global__ void __launch_bounds__(kTc5Threads) gemm_rows_tcgen05_kernel(c
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(kTc5BN) : "memory");
+}
+
+// =============================================================================================
+// Tensor product (forward) of block 1 with the radial functions evaluated on the tensor cores inside the kernel.
+//
+// The edge kernels that read spline tables stream 4 coefficients per (edge, path, channel) from L2 -- 20 KB per edge in
+// float32 for 10 paths x 128 channels -- and run at the speed of that stream. The radial functions are the outputs of
+// a small network, R[e, (p, k)] = sum_j x[e, j] W[j, (p, k)] with x the hidden activations of the edge
+// (radial_hidden_kernel, 64 values per edge), so per batch of 16 edges the P x 128 x 16 values are one small GEMM per path:
+//     D_p[k, e] = sum_j A_p[k, j] B[e, j],   A_p = W[:, (p, :)]^T  (128 x 64, float16, resident in shared memory for the
+//                                            whole kernel: P x 16 KB), B = x of the batch (16 x 64, float16)
+// issued as tcgen05.mma (kind::f16, M = 128, N = 16, K = 16, float32 accumulation) by one thread, with the result in
+// tensor memory: lane = channel, column = (path, edge). The thread that owns channel k reads its radial values with
+// tcgen05.ld, so nothing but the 128 bytes of x per edge is streamed. float16 operands (11-bit significands) keep the
+// radial values to about 1e-4 relative, inside the float32 gates.
+//
+// One CTA of 512 threads per SM (the operand tiles take 160 KB of shared memory): warp w works on the channels of TMEM
+// quadrant w % 4 and, as member of group w / 4, on 4 of the 16 edges of a batch; the groups' partial sums over edges are
+// added through shared memory when a receiver is finished. Batches are double-buffered (operand B, per-edge data and the
+// 160 accumulator columns), so the tensor core works on batch b + 1 while the CUDA cores consume batch b; a CTA walks
+// the batches of all its receivers as one sequence. Every mbarrier wait is bounded (status codes 5, 6).
+// =============================================================================================
+constexpr int kRnEdges = 16, kRnGroups = 4, kRnThreads = 512, kRnHidden = 64;
+constexpr int kRnTileBytes = 128 * kRnHidden * 2;          // one path's weight tile, float16
+constexpr int kRnBTileBytes = kRnEdges * kRnHidden * 2;
+
+// byte offset of element (row, j) in a K-major tile of 64 float16 per row with the 128-byte swizzle
+__host__ __device__ __forceinline__ int rn_swizzled(int row, int j) {
+    return (row >> 3) * 1024 + (row & 7) * 128 + ((((j >> 3) ^ (row & 7)) & 7) << 4) + (j & 7) * 2;
+}
+
+// Weight tiles of the last layer: image[c][swizzled (k, j)] = half(w_last[j][c * K + k]), zero beyond K or the hidden width.
+static __global__ void radial_prepare_tiles_kernel(const float* __restrict__ w_last, int hidden, int K, int P, unsigned char* __restrict__ image) {
+    const int total = P * 128 * kRnHidden;
+    for (int t = blockIdx.x * blockDim.x + threadIdx.x; t < total; t += gridDim.x * blockDim.x) {
+        const int j = t % kRnHidden, k = (t / kRnHidden) % 128, c = t / (kRnHidden * 128);
+        const float v = (k < K && j < hidden) ? w_last[static_cast<size_t>(j) * P * K + c * K + k] : 0.f;
+        *reinterpret_cast<__half*>(image + static_cast<size_t>(c) * kRnTileBytes + rn_swizzled(k, j)) = __float2half_rn(v);
+    }
+}
+
+__device__ __forceinline__ uint32_t rn_instr_desc() {   // D = F32, A = B = F16, both K-major, M = 128, N = 16
+    return (1u << 4) | (0u << 7) | (0u << 10) | ((kRnEdges >> 3) << 17) | ((128 >> 4) << 24);
+}
+__device__ __forceinline__ void rn_mma(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "}\n" ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld4(uint32_t taddr, float (&v)[4]) {
+    uint32_t r0, r1, r2, r3;
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" : "+r"(r0), "+r"(r1), "+r"(r2), "+r"(r3)::"memory");
+    v[0] = __uint_as_float(r0); v[1] = __uint_as_float(r1); v[2] = __uint_as_float(r2); v[3] = __uint_as_float(r3);
+}
+
+struct RnEdge {             // per-edge, channel-independent data of the forward pass
+    float Y[kNumLm];
+    int j;                  // sender row
+};
+
+template <int LF>
+struct RnSmem {
+    static constexpr TPTable tp = make_tp_table(LF);
+    static constexpr int kTiles = tp.P * kRnTileBytes;
+    static constexpr int kB = 2 * kRnBTileBytes;                             // both B tiles start on 1024-byte boundaries
+    static constexpr int kEdge = 2 * kRnEdges * static_cast<int>(sizeof(RnEdge));
+    static constexpr int kXchg = 2 * tp.Q * 128 * 4;                         // two groups' partial sums
+    static constexpr int kTotal = 1024 + kTiles + kB + kEdge + kXchg;
+    static constexpr int kDCols = tp.P * kRnEdges;                           // accumulator columns per buffer
+};
+constexpr int rn_tmem_cols(int dcols) { int a = 32; while (a < 2 * dcols) a *= 2; return a; }
+
+template <int LF>
+__global__ void __launch_bounds__(kRnThreads, 1) tp_forward_rnet_kernel(const TPArgs<float> a, const unsigned char* __restrict__ tiles_image,
+                                                                        const float* __restrict__ x_hidden, int hidden) {
+    using S = RnSmem<LF>;
+    constexpr TPTable tp = make_tp_table(LF);
+    constexpr int kDCols = S::kDCols, kCols = rn_tmem_cols(kDCols);
+    static_assert(kCols <= 512, "accumulator columns of two batches must fit into tensor memory");
+    extern __shared__ unsigned char rn_smem_raw[];
+    unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(rn_smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    unsigned char* sA = base;
+    unsigned char* sB = sA + S::kTiles;
+    RnEdge* st = reinterpret_cast<RnEdge*>(sB + S::kB);
+    float* xchg = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(st) + S::kEdge);
+    __shared__ __align__(8) unsigned long long a_bar, mma_bar[2];
+    __shared__ uint32_t tmem_slot;
+    __shared__ int failed;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int group = warp >> 2, k = (warp & 3) * 32 + lane;      // channel = TMEM lane
+    const bool active = k < a.K;
+    if (tid == 0) {
+        failed = 0;
+        mbar_init(&a_bar, 1); mbar_init(&mma_bar[0], 1); mbar_init(&mma_bar[1], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(kCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_d = tmem_slot;
+    const uint32_t my_taddr = tmem_d + (static_cast<uint32_t>((warp & 3) * 32) << 16) + 4 * group;
+    if (tid == 0) {      // the weight tiles of all paths, once per CTA
+        mbar_expect_tx(&a_bar, S::kTiles);
+        for (int p = 0; p < tp.P; ++p) bulk_copy_g2s(sA + p * kRnTileBytes, tiles_image + static_cast<size_t>(p) * kRnTileBytes, kRnTileBytes, &a_bar);
+    }
+    bool tiles_ready = false;
+    const uint32_t idesc = rn_instr_desc();
+    unsigned mma_par[2] = {0u, 0u};
+
+    // ---- the CTA's batches as one sequence: (receiver slot, first edge of the batch)
+    struct Cursor { int slot; int i; long long e0, e_end; };
+    auto load_receiver = [&](Cursor& c) {          // positions `c` on the first batch of receiver slot c.slot (or past the end)
+        if (c.slot < a.N) {
+            c.i = a.order ? a.order[c.slot] : c.slot;
+            c.e0 = a.first_neigh[c.i];
+            c.e_end = a.first_neigh[c.i + 1];
+        }
+    };
+    auto advance = [&](Cursor& c) {                // next batch; receivers without edges are batches with zero edges
+        c.e0 += kRnEdges;
+        if (c.e0 >= c.e_end) { c.slot += gridDim.x; load_receiver(c); }
+    };
+    // stage batch `c` into buffer `buf`: per-edge harmonics and sender row, and the B tile (hidden activations as float16)
+    auto stage_batch = [&](const Cursor& c, int buf) {
+        const int nb = static_cast<int>(c.e_end - c.e0 < kRnEdges ? c.e_end - c.e0 : kRnEdges);
+        if (tid < kRnEdges) {
+            RnEdge& s = st[buf * kRnEdges + tid];
+            if (tid < nb) {
+                const long long e = c.e0 + tid;
+                const double rr = a.r[e], inv = 1.0 / rr;
+                float dummy[3][kNumLm];
+                real_sh3<float, false>(float(a.xyz[3 * e] * inv), float(a.xyz[3 * e + 1] * inv), float(a.xyz[3 * e + 2] * inv), float(inv), s.Y, dummy);
+                s.j = a.neigh_indices[e];
+            } else {
+                s.j = 0;
+            }
+        }
+        {   // 16 edges x 64 activations: two per thread
+            const int e = tid >> 5, j0 = (tid & 31) * 2;
+            float2 v = make_float2(0.f, 0.f);
+            if (e < nb) {
+                const float* row = x_hidden + static_cast<size_t>(c.e0 + e) * hidden;
+                if (j0 < hidden) v.x = row[j0];
+                if (j0 + 1 < hidden) v.y = row[j0 + 1];
+            }
+            *reinterpret_cast<__half2*>(sB + buf * kRnBTileBytes + rn_swizzled(e, j0)) = __floats2half2_rn(v.x, v.y);
+        }
+    };
+    auto issue_mma = [&](int buf) {                // one thread: P x 4 MMAs into the accumulator columns of `buf`
+        const uint32_t b_addr = smem_u32(sB + buf * kRnBTileBytes);
+#pragma unroll 1
+        for (int p = 0; p < tp.P; ++p) {
+            const uint32_t a_addr = smem_u32(sA + p * kRnTileBytes);
+#pragma unroll
+            for (int ks = 0; ks < kRnHidden / 16; ++ks)
+                rn_mma(tmem_d + buf * kDCols + p * kRnEdges, tc5_smem_desc(a_addr + ks * 32), tc5_smem_desc(b_addr + ks * 32), idesc, ks > 0 ? 1u : 0u);
+        }
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&mma_bar[buf])) : "memory");
+    };
+
+    Cursor cur{static_cast<int>(blockIdx.x), 0, 0, 0};
+    load_receiver(cur);
+    float acc[tp.Q];
+#pragma unroll
+    for (int q = 0; q < tp.Q; ++q) acc[q] = 0.f;
+    int buf = 0;
+    if (cur.slot < a.N) {
+        stage_batch(cur, 0);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();
+        if (tid == 0) {
+            if (!mbar_wait(&a_bar, 0)) { atomicMax(&failed, 5); }
+            else { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); issue_mma(0); }
+        }
+        tiles_ready = true;
+    }
+    while (cur.slot < a.N) {
+        Cursor nxt = cur;
+        advance(nxt);
+        const bool have_next = nxt.slot < a.N;
+        if (have_next) stage_batch(nxt, buf ^ 1);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();
+        if (have_next && tid == 0 && !failed) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            issue_mma(buf ^ 1);
+        }
+        // ---- consume batch `cur` from buffer `buf`
+        if (!*reinterpret_cast<volatile int*>(&failed) && !mbar_wait(&mma_bar[buf], mma_par[buf])) atomicMax(&failed, 6);
+        mma_par[buf] ^= 1u;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const int nb = static_cast<int>(cur.e_end - cur.e0 < kRnEdges ? cur.e_end - cur.e0 : kRnEdges);
+        if (!*reinterpret_cast<volatile int*>(&failed)) {
+            float Rq[tp.P][4];
+#pragma unroll
+            for (int p = 0; p < tp.P; ++p) tmem_ld4(my_taddr + buf * kDCols + p * kRnEdges, Rq[p]);
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                const int e = 4 * group + t;
+                if (e < nb && active) {
+                    const RnEdge& s = st[buf * kRnEdges + e];
+                    const float* hrow = a.H + static_cast<size_t>(s.j) * tp.nLM * a.K + k;
+                    float h[tp.nLM], R[tp.P], Y[kNumLm];
+#pragma unroll
+                    for (int lm2 = 0; lm2 < tp.nLM; ++lm2) h[lm2] = __ldg(hrow + static_cast<size_t>(lm2) * a.K);
+#pragma unroll
+                    for (int p = 0; p < tp.P; ++p) R[p] = Rq[p][t];
+#pragma unroll
+                    for (int lm = 0; lm < kNumLm; ++lm) Y[lm] = s.Y[lm];
+                    using T = float;
+                    using ::fma;      // the generated code calls fma on plain floats (namespace smx has its own fma for node vectors)
+                    if constexpr (LF == 0) {
+#include "generated/tp_L0_forward.inc"
+                    } else if constexpr (LF == 1) {
+#include "generated/tp_L1_forward.inc"
+                    } else {
+#include "generated/tp_L2_forward.inc"
+                    }
+                }
+            }
+        }
+        const bool receiver_done = !have_next || nxt.slot != cur.slot;
+        if (receiver_done) {
+            // add the four groups' partial sums: groups 2, 3 -> shared memory -> groups 0, 1; then group 1 -> group 0 -> HBM
+            __syncthreads();
+            if (group >= 2) {
+#pragma unroll
+                for (int q = 0; q < tp.Q; ++q) xchg[((group - 2) * tp.Q + q) * 128 + k] = acc[q];
+            }
+            __syncthreads();
+            if (group < 2) {
+#pragma unroll
+                for (int q = 0; q < tp.Q; ++q) acc[q] += xchg[(group * tp.Q + q) * 128 + k];
+            }
+            __syncthreads();
+            if (group == 1) {
+#pragma unroll
+                for (int q = 0; q < tp.Q; ++q) xchg[q * 128 + k] = acc[q];
+            }
+            __syncthreads();
+            if (group == 0 && active) {
+                float* out = a.Phi1 + static_cast<size_t>(cur.i) * tp.Q * a.K + k;
+#pragma unroll
+                for (int q = 0; q < tp.Q; ++q) __stcs(out + static_cast<size_t>(q) * a.K, acc[q] + xchg[q * 128 + k]);
+            }
+#pragma unroll
+            for (int q = 0; q < tp.Q; ++q) acc[q] = 0.f;
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();      // everyone is done with buffer `buf` (accumulator columns, B tile, edge data) before it is staged again
+        cur = nxt;
+        buf ^= 1;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        if (!tiles_ready) mbar_wait(&a_bar, 0);      // a CTA without work still waits for its weight-tile copies before it exits
+        if (failed) atomicMax(a.status, failed);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(kCols) : "memory");
 }
 
 }  // namespace smx
