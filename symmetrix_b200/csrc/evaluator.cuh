@@ -681,10 +681,12 @@ public:
                 // receiver adjoint in tensor memory: more resident CTAs (see tp_reverse_tmem_kernel). The CTAs of one SM
                 // must fit into its 512 TMEM columns, or the allocation of the last one would wait for another to exit.
                 constexpr int kCols = tp_tmem_cols(LF);
+                // Grid: the resident CTAs per SM the kernel is compiled for (its register budget and 36 KB of shared memory
+                // allow them; the occupancy query reports one CTA per SM for kernels that allocate tensor memory, although
+                // several such CTAs do share an SM, so it is not used here). CTAs beyond what fits simply start later: the
+                // receivers are split statically over the grid.
                 auto launch = [&](auto kern, int min_blocks) {
-                    int per_sm = 1;
-                    SMX_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, block, 0));
-                    per_sm = std::max(1, std::min(std::min(per_sm, min_blocks), 512 / kCols));
+                    const int per_sm = std::max(1, std::min(min_blocks, 512 / kCols));
                     const int grid = static_cast<int>(std::max<long long>(1, std::min<long long>(static_cast<long long>(num_sms) * per_sm, N)));
                     kern<<<grid, block, 0, stream>>>(tp_args(which));
                 };
