@@ -350,12 +350,13 @@ def run_ours(args):
 
 
 def radial_mode_comparison(path, n_atoms, dev, keys, flush, torch, local_rank) -> dict:
-    """float32 stage times of the tensor product with the radial functions from the spline tables and, where the model
-    file carries the un-splined network, from that network at run time (SMX_RADIAL=mlp: hidden layers per edge + last layer
-    as a tensor-core GEMM, then the same tensor-product kernels reading per-edge values)."""
+    """float32 stage times of the tensor product with the radial functions (a) from the spline tables, (b) from the
+    un-splined network at run time (SMX_RADIAL=mlp: Bessel x cutoff and hidden layers per edge, last layer on the tensor
+    cores inside the tensor-product kernels) and (c) from the low-rank form of the tables (SMX_RADIAL=lowrank: tabulated
+    last hidden layer, last layer on the tensor cores inside the kernels), for model files that carry the extra keys."""
     from symmetrix_b200 import MACE
     out = {}
-    for mode in ("spline", "mlp"):
+    for mode in ("spline", "mlp", "lowrank"):
         os.environ["SMX_RADIAL"] = mode
         try:
             ev = MACE(path, dtype="float32", device=local_rank)
@@ -380,8 +381,9 @@ def radial_mode_comparison(path, n_atoms, dev, keys, flush, torch, local_rank) -
         out[mode] = {"compute_Phi1_ms": acc.get("compute_Phi1"), "reverse_Phi1_ms": acc.get("reverse_Phi1"), "step_ms": total / 3,
                      "energy": energy}
         del ev
-    if "energy" in out.get("spline", {}) and "energy" in out.get("mlp", {}):
-        out["rel_energy_diff"] = abs(out["mlp"]["energy"] - out["spline"]["energy"]) / abs(out["spline"]["energy"])
+    for mode in ("mlp", "lowrank"):
+        if "energy" in out.get("spline", {}) and "energy" in out.get(mode, {}):
+            out[mode]["rel_energy_diff_vs_spline"] = abs(out[mode]["energy"] - out["spline"]["energy"]) / abs(out["spline"]["energy"])
     return out
 
 
@@ -413,6 +415,8 @@ def config3_decomposed(args, rank, world, local_rank, dist, torch) -> dict:
     path, numbers, spec = model_path("fcc128")
     s = st.fcc_box((10 * world, 80, 80), 3.6, numbers, seed=1)
     ev = MACE(path, dtype="float32", device=local_rank)
+    if args.dd_transport == "library":
+        ev.comm_init(dist)
     rk = SlabRank(make_slab_plan(s, spec.r_cut, rank, world, mode=args.dd_mode), ev, spec.r_cut, numbers)
     rk.build_edges()
     steps, total = 3, 0.0
@@ -456,6 +460,8 @@ def run_decomposed(args, rank, world, local_rank, dist):
         s = WORKLOADS[args.workload][1](st, numbers, 1)
         scaling, label = "strong", f"{args.workload} in {world} slabs along x"
     ev = MACE(path, dtype=args.dtype, device=local_rank)
+    if args.dd_transport == "library":
+        ev.comm_init(dist)            # halo rows by ncclSend / ncclRecv issued inside the library, on the evaluator's stream
     rk = SlabRank(make_slab_plan(s, spec.r_cut, rank, world, mode=args.dd_mode, num_interactions=ev.num_interactions), ev, spec.r_cut, numbers)
     rk.build_edges()
     flush = torch.empty(256 * 1024 * 1024 // 4, dtype=torch.float32, device=f"cuda:{local_rank}")
@@ -560,6 +566,7 @@ def run_decomposed(args, rank, world, local_rank, dist):
                        "parallelism": (f"{world} slabs along x, ghost shell r_cut, halo exchange of H1 / H1_adj / force rows by NCCL send/recv"
                                        if args.dd_mode == "message_passing" else
                                        f"{world} slabs along x, ghost shell 2 r_cut, layer 0 recomputed on ghosts, force rows by NCCL send/recv"),
+                       "transport": args.dd_transport,
                        "halo_bytes_per_rank_per_exchange": int(counts[1].item() / world * width),
                        "l2": "256 MB buffer written between timed steps (L2 flush)",
                        "timing": "CUDA events around each step with a barrier + synchronize on both sides, summed, max over ranks"},
@@ -757,6 +764,8 @@ def main():
     ap.add_argument("--dtype", default=None, choices=["float64", "float32"])
     ap.add_argument("--dd-mode", default="message_passing", choices=["message_passing", "recompute"],
                     help="N > 1: exchange H1 / H1_adj rows (ghost shell r_cut) or recompute layer 0 on a 2 r_cut shell")
+    ap.add_argument("--dd-transport", default="torch", choices=["torch", "library"],
+                    help="N > 1: halo buffers through torch.distributed, or NCCL send / recv issued inside the library")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extra", action="store_true")
     args = ap.parse_args()

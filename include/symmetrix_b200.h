@@ -219,6 +219,24 @@ int smx_halo_unpack(smx_handle h, const char* name, const int* rows, int n, cons
 int smx_halo_unpack_add(smx_handle h, const char* name, const int* rows, int n, const void* buf);
 int smx_atom_forces(smx_handle h, int num_rows);
 
+/* Halo exchange between the ranks of a decomposed run, inside the library: what LAMMPS' Comm does for the reference's
+ * message-passing mode (comm->forward_comm(this) / comm->reverse_comm(this), pair_symmetrix_mace.cpp:470,489, with the pack /
+ * unpack routines above) as grouped ncclSend / ncclRecv on the evaluator's stream. NCCL is loaded at run time
+ * (dlopen "libnccl.so.2"), so a process that never calls these needs none. One rank obtains a 128-byte id with
+ * smx_comm_unique_id and distributes it by any means (MPI_Bcast, a file, torch.distributed); every rank then calls
+ * smx_comm_init(h, id, 128, num_ranks, rank) once (collective). smx_halo_exchange does one exchange with `num_peers`
+ * neighbours: for peer q it packs the rows send_rows[q][0..send_counts[q]) of array `name`, sends them to rank peers[q],
+ * receives recv_counts[q] rows from it and unpacks them into rows recv_rows[q][...] -- overwriting them (`add` == 0: forward
+ * exchange of "H1" / "Hm") or adding in a fixed order (`add` != 0: reverse exchange of "H1_adj" / "Hm_adj" / "atom_forces").
+ * The row lists are device pointers (the outer arrays of pointers and the counts are host arrays); nothing synchronises
+ * with the host. smx_allreduce_sum sums `n` doubles (device pointer, in place) over all ranks: energy and virial. */
+int smx_comm_unique_id(void* id, int id_bytes);
+int smx_comm_init(smx_handle h, const void* id, int id_bytes, int num_ranks, int rank);
+int smx_comm_destroy(smx_handle h);
+int smx_halo_exchange(smx_handle h, const char* name, int add, int num_peers, const int* peers, const int* const* send_rows,
+                      const int* send_counts, const int* const* recv_rows, const int* recv_counts);
+int smx_allreduce_sum(smx_handle h, double* values, int n);
+
 /* Receivers and edges the stages currently run on, and the receiver count the edge set was given or built with. The
  * reference's stage methods take `num_nodes` and the neighbour arrays on every call (mace.hpp:44-145); here they are
  * fixed by smx_begin / smx_restrict_nodes / smx_set_active_nodes, and a caller that mirrors the reference's argument

@@ -10,6 +10,7 @@
 #include "../../include/symmetrix_b200.h"
 #include "common.cuh"
 #include "evaluator_base.hpp"
+#include "nccl_transport.hpp"
 
 // =================================================================================================
 // extern "C" entry points
@@ -169,6 +170,33 @@ int smx_halo_unpack_add(smx_handle h, const char* name, const int* rows, int n, 
         if (!name) throw smx::ArgError("smx_halo_unpack_add: null name");
         e.halo_unpack(name, rows, n, src, true);
     });
+}
+int smx_comm_unique_id(void* id, int id_bytes) {
+    try {
+        if (!id || id_bytes != static_cast<int>(sizeof(smx::NcclApi::UniqueId))) throw smx::ArgError("smx_comm_unique_id: the id buffer must hold 128 bytes");
+        const smx::NcclApi& nccl = smx::NcclApi::get();
+        smx::NcclApi::UniqueId uid;
+        nccl.check(nccl.GetUniqueId(&uid), "ncclGetUniqueId");
+        std::memcpy(id, &uid, sizeof(uid));
+        return SMX_OK;
+    } catch (const smx::ArgError& e) { g_create_error = e.what(); return SMX_ERR_INVALID_ARGUMENT;
+    } catch (const std::exception& e) { g_create_error = e.what(); return SMX_ERR_CUDA; }
+}
+int smx_comm_init(smx_handle h, const void* id, int id_bytes, int num_ranks, int rank) {
+    return guarded(h, [&](smx::EvaluatorBase& e) { e.comm_init(id, id_bytes, num_ranks, rank); });
+}
+int smx_comm_destroy(smx_handle h) {
+    return guarded(h, [&](smx::EvaluatorBase& e) { e.comm_destroy(); });
+}
+int smx_halo_exchange(smx_handle h, const char* name, int add, int num_peers, const int* peers, const int* const* send_rows,
+                      const int* send_counts, const int* const* recv_rows, const int* recv_counts) {
+    return guarded(h, [&](smx::EvaluatorBase& e) {
+        if (!name) throw smx::ArgError("smx_halo_exchange: null name");
+        e.halo_exchange(name, add != 0, num_peers, peers, send_rows, send_counts, recv_rows, recv_counts);
+    });
+}
+int smx_allreduce_sum(smx_handle h, double* values, int n) {
+    return guarded(h, [&](smx::EvaluatorBase& e) { e.allreduce_sum(values, n); });
 }
 int smx_active_counts(smx_handle h, int* num_nodes, long* num_edges, int* built_nodes) {
     return guarded(h, [&](smx::EvaluatorBase& e) { e.active_counts(num_nodes, num_edges, built_nodes); });

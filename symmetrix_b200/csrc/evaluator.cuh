@@ -27,6 +27,7 @@
 #include "model.hpp"
 #include "evaluator_base.hpp"
 #include "neighbors.cuh"
+#include "nccl_transport.hpp"
 
 namespace smx {
 
@@ -126,13 +127,16 @@ public:
     // functions of block 1 come from the un-splined network -- hidden layers per edge (radial_hidden_kernel), last layer
     // as a tensor-core GEMM over all edges -- instead of the spline tables.
     bool radial_mlp = false;
+    bool radial_lowrank = false;          // SMX_RADIAL=lowrank: hidden activations from the tabulated last hidden layer (inside the
+                                          // fused kernels) instead of radial_hidden_kernel; the last layer on the tensor cores as above
+    DevBuf<float> rn_basis;
     bool radial_hidden_valid = false;     // x3 / dx3 hold the hidden activations of the current active edge set
     DevBuf<float> rn_w_first, rn_w_hidden, rn_w_last, rn_pair_scale, rn_x, rn_dx;
     DevBuf<T> R_edge, Rd_edge;
     DevBuf<unsigned char> rn_tiles;       // float16 weight tiles of the last layer, one per path (radial_prepare_tiles_kernel)
     bool radial_fused = true;             // SMX_RADIAL_FUSED=0: last layer as a separate GEMM into per-edge arrays also in the forward pass
     bool radial_in_kernel = false;        // set around the launch of the fused forward kernel
-    int tmem_min_blocks = 4;      // SMX_TP_TMEM_BLOCKS: 2, 3 or 4 resident CTAs per SM for that kernel
+    int tmem_min_blocks = 3;      // SMX_TP_TMEM_BLOCKS: 2, 3 or 4 resident CTAs per SM for that kernel (3 measured best on B200)
     bool tmem_reverse = true;     // float64 tensor-product reverse with the receiver adjoint in tensor memory (SMX_TP_TMEM=0: in registers)
     bool type_order = true;       // edge kernels walk the receivers in element-type order (SMX_TYPE_ORDER=0: natural order)
     bool waits_in_flight = false; // a kernel with bounded waits has been launched since the last status check
@@ -157,14 +161,21 @@ public:
         if (const char* t = std::getenv("SMX_TP_TMEM_BLOCKS")) tmem_min_blocks = std::max(2, std::min(4, std::atoi(t)));
         if (const char* t = std::getenv("SMX_RADIAL")) {
             const std::string mode(t);
-            if (mode == "mlp") {
-                if (sizeof(T) != 4) throw UnsupportedError("SMX_RADIAL=mlp is a float32 mode (the float64 path reproduces the reference's splines)");
-                if (!model.rmlp1.present) throw UnsupportedError("SMX_RADIAL=mlp needs the x_radial_* keys in the model file");
-                if (model.num_interactions != 2) throw UnsupportedError("SMX_RADIAL=mlp supports two-block models");
+            if (mode == "mlp" || mode == "lowrank") {
+                if (sizeof(T) != 4) throw UnsupportedError("SMX_RADIAL=" + mode + " is a float32 mode (the float64 path reproduces the reference's splines)");
+                if (!model.rmlp1.present) throw UnsupportedError("SMX_RADIAL=" + mode + " needs the x_radial_* keys in the model file");
+                if (model.num_interactions != 2) throw UnsupportedError("SMX_RADIAL=" + mode + " supports two-block models");
                 radial_mlp = true;
                 if (const char* f = std::getenv("SMX_RADIAL_FUSED")) radial_fused = std::string(f) != "0";
+                if (mode == "lowrank") {
+                    if (model.rmlp1.basis_coef.empty()) throw UnsupportedError("SMX_RADIAL=lowrank needs the x_radial_basis_* keys in the model file");
+                    if (model.K > 128 || model.L_max > 1 || model.rmlp1.hidden > kRnHidden)
+                        throw UnsupportedError("SMX_RADIAL=lowrank supports up to 128 channels, L_max <= 1 and a hidden width up to 64");
+                    radial_lowrank = true;
+                    radial_fused = true;
+                }
             } else if (mode != "spline" && !mode.empty()) {
-                throw ArgError("SMX_RADIAL must be 'spline' or 'mlp'");
+                throw ArgError("SMX_RADIAL must be 'spline', 'mlp' or 'lowrank'");
             }
         }
         if constexpr (sizeof(T) == 4) {
@@ -191,6 +202,7 @@ public:
         if (evt0) cudaEventDestroy(evt0);
         if (evt1) cudaEventDestroy(evt1);
         for (auto e : stage_events) cudaEventDestroy(e);
+        if (comm) NcclApi::get().CommDestroy(comm);
         if (host_ring) cudaFreeHost(host_ring);
         if (!own_stream && own_stream_handle) cudaStreamDestroy(own_stream_handle);
         if (stream && own_stream) cudaStreamDestroy(stream);
@@ -236,6 +248,7 @@ public:
             rn_w_hidden.upload(cast_vec<float>(m.rmlp1.w_hidden), stream);
             rn_w_last.upload(cast_vec<float>(m.rmlp1.w_last), stream);
             rn_pair_scale.upload(cast_vec<float>(m.rmlp1.pair_scale), stream);
+            if (radial_lowrank) rn_basis.upload(cast_vec<float>(m.rmlp1.basis_coef), stream);
             if (m.K <= 128 && m.L_max <= 1 && m.rmlp1.hidden <= kRnHidden) {
                 rn_tiles.resize(static_cast<size_t>(m.tp.P) * kRnTileBytes, stream);
                 radial_prepare_tiles_kernel<<<64, 256, 0, stream>>>(rn_w_last.p, m.rmlp1.hidden, m.K, m.tp.P, rn_tiles.p);
@@ -698,6 +711,18 @@ public:
                 return;
             }
         }
+        if constexpr (sizeof(T) == 4 && LF <= 1) {
+            if (reverse && radial_in_kernel) {
+                // radial functions and derivatives from the un-splined network on the tensor cores inside the kernel
+                constexpr int smem = RnRevSmem<LF>::kTotal;
+                SMX_CUDA(cudaFuncSetAttribute(tp_reverse_rnet_kernel<LF>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+                const int grid = std::max(1, std::min(num_sms, N));
+                waits_in_flight = true;
+                tp_reverse_rnet_kernel<LF><<<grid, kRnThreads, smem, stream>>>(tp_args(which), rn_tiles.p, radial_source());
+                check_launch("tp_reverse_rnet_kernel");
+                return;
+            }
+        }
         if (reverse) {
             // two slots of one spline-row chunk each; staged only if that costs no resident CTA
             const size_t slots = 2 * sizeof(T) * 4 * make_tp_table(LF).P * static_cast<size_t>(std::min(model.K, block));
@@ -726,7 +751,7 @@ public:
                     SMX_CUDA(cudaFuncSetAttribute(tp_forward_rnet_kernel<LF>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
                     const int grid = std::max(1, std::min(num_sms, N));
                     waits_in_flight = true;
-                    tp_forward_rnet_kernel<LF><<<grid, kRnThreads, smem, stream>>>(tp_args(which), rn_tiles.p, rn_x.p, model.rmlp1.hidden);
+                    tp_forward_rnet_kernel<LF><<<grid, kRnThreads, smem, stream>>>(tp_args(which), rn_tiles.p, radial_source());
                     check_launch("tp_forward_rnet_kernel");
                     return;
                 }
@@ -746,7 +771,13 @@ public:
     }
 
     // Run-time radial mode: R_edge (and Rd_edge when `with_derivative`) of the active edges from the un-splined network.
+    RnHidden radial_source() const {
+        RnHidden hd{};
+        hd.x = rn_x.p; hd.dx = rn_dx.p; hd.basis = radial_lowrank ? rn_basis.p : nullptr; hd.sm = sm; hd.hidden = model.rmlp1.hidden;
+        return hd;
+    }
     void radial_hidden() {
+        if (radial_lowrank) return;        // evaluated inside the fused kernels from the tabulated hidden layer
         if constexpr (sizeof(T) == 4) {
             const auto& rm = model.rmlp1;
             const int H = rm.hidden;
@@ -819,8 +850,13 @@ public:
         if (zero_adj) adj.zero(stream);
         if (N == 0) return;
         if (sizeof(T) == 4) {      // float32: messages are accumulated in place by the kernel
-            if (radial_mlp && which == 1) radial_from_network(true);
+            radial_in_kernel = false;
+            if (radial_mlp && which == 1) {
+                if (radial_fused && K <= 128 && model.L_max <= 1 && model.rmlp1.hidden <= kRnHidden) { radial_hidden(); radial_in_kernel = true; }
+                else radial_from_network(true);
+            }
             dispatch_tp(true, which);
+            radial_in_kernel = false;
             return;
         }
         Hmsg.resize(static_cast<size_t>(E) * nLM * K, stream);
@@ -1362,6 +1398,74 @@ public:
         });
         check_launch(add ? "rows_scatter_add_kernel" : "rows_scatter_kernel");
     }
+    // ------------------------------------------------------------------ halo exchange over NCCL (see nccl_transport.hpp)
+    NcclApi::Comm comm = nullptr;
+    int comm_rank = -1, comm_size = 0;
+    std::vector<std::unique_ptr<DevBuf<unsigned char>>> xbuf_send, xbuf_recv;
+    DevBuf<double> reduce_buf;
+    void comm_init(const void* id, int id_bytes, int nranks, int rank) override {
+        SMX_CUDA(cudaSetDevice(device));
+        if (id_bytes != static_cast<int>(sizeof(NcclApi::UniqueId)) || !id || nranks < 1 || rank < 0 || rank >= nranks)
+            throw ArgError("comm_init: bad arguments (the id is the 128 bytes of smx_comm_unique_id)");
+        const NcclApi& nccl = NcclApi::get();
+        comm_destroy();
+        NcclApi::UniqueId uid;
+        std::memcpy(&uid, id, sizeof(uid));
+        nccl.check(nccl.CommInitRank(&comm, nranks, uid, rank), "ncclCommInitRank");
+        comm_rank = rank; comm_size = nranks;
+    }
+    void comm_destroy() override {
+        if (comm) { NcclApi::get().CommDestroy(comm); comm = nullptr; comm_rank = -1; comm_size = 0; }
+    }
+    // One exchange with `num_peers` slab neighbours on the evaluator's stream: pack the rows send_rows[q] of `name`, grouped
+    // ncclSend / ncclRecv, unpack into the rows recv_rows[q] (copy, or fixed-order add). No host synchronisation.
+    void halo_exchange(const std::string& name, bool add, int num_peers, const int* peers, const int* const* send_rows,
+                       const int* send_counts, const int* const* recv_rows, const int* recv_counts) override {
+        SMX_CUDA(cudaSetDevice(device));
+        if (!comm) throw ArgError("halo_exchange: call smx_comm_init first");
+        if (num_peers < 0 || (num_peers > 0 && (!peers || !send_rows || !send_counts || !recv_rows || !recv_counts)))
+            throw ArgError("halo_exchange: bad arguments");
+        const NcclApi& nccl = NcclApi::get();
+        size_t row_bytes = 0;
+        int dtype = NcclApi::kFloat64, width = 0;
+        with_halo_array(name, [&](auto* p, size_t, int w) {
+            using U = std::remove_pointer_t<decltype(p)>;
+            row_bytes = static_cast<size_t>(w) * sizeof(U);
+            width = w;
+            dtype = sizeof(U) == 4 ? NcclApi::kFloat32 : NcclApi::kFloat64;
+        });
+        while (static_cast<int>(xbuf_send.size()) < num_peers) {
+            xbuf_send.push_back(std::make_unique<DevBuf<unsigned char>>());
+            xbuf_recv.push_back(std::make_unique<DevBuf<unsigned char>>());
+        }
+        for (int q = 0; q < num_peers; ++q) {
+            if (peers[q] < 0 || peers[q] >= comm_size || peers[q] == comm_rank || send_counts[q] < 0 || recv_counts[q] < 0)
+                throw ArgError("halo_exchange: bad peer or count");
+            xbuf_send[q]->resize(static_cast<size_t>(send_counts[q]) * row_bytes, stream);
+            xbuf_recv[q]->resize(static_cast<size_t>(recv_counts[q]) * row_bytes, stream);
+            halo_pack(name, send_rows[q], send_counts[q], xbuf_send[q]->p);
+        }
+        nccl.check(nccl.GroupStart(), "ncclGroupStart");
+        for (int q = 0; q < num_peers; ++q) {
+            if (send_counts[q] > 0)
+                nccl.check(nccl.Send(xbuf_send[q]->p, static_cast<size_t>(send_counts[q]) * width, dtype, peers[q], comm, stream), "ncclSend");
+            if (recv_counts[q] > 0)
+                nccl.check(nccl.Recv(xbuf_recv[q]->p, static_cast<size_t>(recv_counts[q]) * width, dtype, peers[q], comm, stream), "ncclRecv");
+        }
+        nccl.check(nccl.GroupEnd(), "ncclGroupEnd");
+        launches += 1;
+        for (int q = 0; q < num_peers; ++q) halo_unpack(name, recv_rows[q], recv_counts[q], xbuf_recv[q]->p, add);
+    }
+    // Sum of `n` doubles (device pointer, in place) over all ranks of the communicator, on the evaluator's stream.
+    void allreduce_sum(double* values, int n) override {
+        SMX_CUDA(cudaSetDevice(device));
+        if (!comm) throw ArgError("allreduce_sum: call smx_comm_init first");
+        if (n < 0 || (n > 0 && !values)) throw ArgError("allreduce_sum: bad arguments");
+        const NcclApi& nccl = NcclApi::get();
+        nccl.check(nccl.AllReduce(values, values, static_cast<size_t>(n), NcclApi::kFloat64, NcclApi::kSum, comm, stream), "ncclAllReduce");
+        launches += 1;
+    }
+
     void active_counts(int* nodes, long* edges, int* built_nodes) const override {
         if (nodes) *nodes = N;
         if (edges) *edges = E;

@@ -42,6 +42,11 @@ public:
     virtual void halo_pack(const std::string& name, const int* rows, int n, void* dst) = 0;
     virtual void halo_unpack(const std::string& name, const int* rows, int n, const void* src, bool add) = 0;
     virtual void expire_waits(int polls) = 0;
+    virtual void comm_init(const void* id, int id_bytes, int nranks, int rank) = 0;
+    virtual void comm_destroy() = 0;
+    virtual void halo_exchange(const std::string& name, bool add, int num_peers, const int* peers, const int* const* send_rows,
+                               const int* send_counts, const int* const* recv_rows, const int* recv_counts) = 0;
+    virtual void allreduce_sum(double* values, int n) = 0;
     virtual void active_counts(int* nodes, long* edges, int* built_nodes) const = 0;
     virtual long build_neighbors(int natoms, const double* pos, const int* types, const double* cell, const int* pbc,
                                  double r_cut, int mem_space) = 0;

@@ -357,6 +357,49 @@ __device__ __forceinline__ void tmem_ld4(uint32_t taddr, float (&v)[4]) {
     v[0] = __uint_as_float(r0); v[1] = __uint_as_float(r1); v[2] = __uint_as_float(r2); v[3] = __uint_as_float(r3);
 }
 
+// Source of the hidden activations that fill operand B: arrays written by radial_hidden_kernel (x, dx: [num_edges][hidden]),
+// or -- when `basis` is set -- the tabulated last hidden layer, cubic coefficients [pair][bin][hidden][4] on the grid of the
+// radial splines, evaluated here per (edge, hidden unit) with the bin rule of the spline path (stage_edge).
+struct RnHidden {
+    const float* x; const float* dx;
+    const float* basis;
+    SplineMeta sm;
+    int hidden;
+};
+__device__ __forceinline__ void rn_hidden_pair(const RnHidden& hd, const TPArgs<float>& a, int type_i, long long edge, int j0, bool want_dx,
+                                               float2& v, float2& dv) {
+    v = make_float2(0.f, 0.f); dv = make_float2(0.f, 0.f);
+    if (hd.basis) {
+        const double rr = a.r[edge];
+        int bin = static_cast<int>(rr / hd.sm.h);
+        bin = bin < 0 ? 0 : (bin > hd.sm.num_bins - 1 ? hd.sm.num_bins - 1 : bin);
+        const float x = static_cast<float>(rr - hd.sm.h * bin);
+        const int tj = a.neigh_types[edge];
+        const int lo = type_i <= tj ? type_i : tj, hi = type_i <= tj ? tj : type_i;
+        const int pair = lo * (2 * hd.sm.num_elements - lo - 1) / 2 + hi;
+        const float4* row = reinterpret_cast<const float4*>(hd.basis) + (static_cast<size_t>(pair) * hd.sm.num_bins + bin) * hd.hidden;
+        if (j0 < hd.hidden) {
+            const float4 c = __ldg(row + j0);
+            v.x = c.x + x * (c.y + x * (c.z + x * c.w));
+            dv.x = c.y + x * (2.f * c.z + 3.f * x * c.w);
+        }
+        if (j0 + 1 < hd.hidden) {
+            const float4 c = __ldg(row + j0 + 1);
+            v.y = c.x + x * (c.y + x * (c.z + x * c.w));
+            dv.y = c.y + x * (2.f * c.z + 3.f * x * c.w);
+        }
+    } else {
+        const float* r0 = hd.x + static_cast<size_t>(edge) * hd.hidden;
+        if (j0 < hd.hidden) v.x = r0[j0];
+        if (j0 + 1 < hd.hidden) v.y = r0[j0 + 1];
+        if (want_dx) {
+            const float* r1 = hd.dx + static_cast<size_t>(edge) * hd.hidden;
+            if (j0 < hd.hidden) dv.x = r1[j0];
+            if (j0 + 1 < hd.hidden) dv.y = r1[j0 + 1];
+        }
+    }
+}
+
 struct RnEdge {             // per-edge, channel-independent data of the forward pass
     float Y[kNumLm];
     int j;                  // sender row
@@ -376,7 +419,7 @@ constexpr int rn_tmem_cols(int dcols) { int a = 32; while (a < 2 * dcols) a *= 2
 
 template <int LF>
 __global__ void __launch_bounds__(kRnThreads, 1) tp_forward_rnet_kernel(const TPArgs<float> a, const unsigned char* __restrict__ tiles_image,
-                                                                        const float* __restrict__ x_hidden, int hidden) {
+                                                                        const RnHidden hd) {
     using S = RnSmem<LF>;
     constexpr TPTable tp = make_tp_table(LF);
     constexpr int kDCols = S::kDCols, kCols = rn_tmem_cols(kDCols);
@@ -417,10 +460,11 @@ __global__ void __launch_bounds__(kRnThreads, 1) tp_forward_rnet_kernel(const TP
     unsigned mma_par[2] = {0u, 0u};
 
     // ---- the CTA's batches as one sequence: (receiver slot, first edge of the batch)
-    struct Cursor { int slot; int i; long long e0, e_end; };
+    struct Cursor { int slot; int i; int type_i; long long e0, e_end; };
     auto load_receiver = [&](Cursor& c) {          // positions `c` on the first batch of receiver slot c.slot (or past the end)
         if (c.slot < a.N) {
             c.i = a.order ? a.order[c.slot] : c.slot;
+            c.type_i = a.node_types[c.i];
             c.e0 = a.first_neigh[c.i];
             c.e_end = a.first_neigh[c.i + 1];
         }
@@ -432,10 +476,11 @@ __global__ void __launch_bounds__(kRnThreads, 1) tp_forward_rnet_kernel(const TP
     // stage batch `c` into buffer `buf`: per-edge harmonics and sender row, and the B tile (hidden activations as float16)
     auto stage_batch = [&](const Cursor& c, int buf) {
         const int nb = static_cast<int>(c.e_end - c.e0 < kRnEdges ? c.e_end - c.e0 : kRnEdges);
-        if (tid < kRnEdges) {
-            RnEdge& s = st[buf * kRnEdges + tid];
-            if (tid < nb) {
-                const long long e = c.e0 + tid;
+        // the harmonics of the batch's edges: the first 16 lanes of the last warp (the first warp issues the tensor-core work)
+        if (warp == kRnThreads / 32 - 1 && lane < kRnEdges) {
+            RnEdge& s = st[buf * kRnEdges + lane];
+            if (lane < nb) {
+                const long long e = c.e0 + lane;
                 const double rr = a.r[e], inv = 1.0 / rr;
                 float dummy[3][kNumLm];
                 real_sh3<float, false>(float(a.xyz[3 * e] * inv), float(a.xyz[3 * e + 1] * inv), float(a.xyz[3 * e + 2] * inv), float(inv), s.Y, dummy);
@@ -446,12 +491,8 @@ __global__ void __launch_bounds__(kRnThreads, 1) tp_forward_rnet_kernel(const TP
         }
         {   // 16 edges x 64 activations: two per thread
             const int e = tid >> 5, j0 = (tid & 31) * 2;
-            float2 v = make_float2(0.f, 0.f);
-            if (e < nb) {
-                const float* row = x_hidden + static_cast<size_t>(c.e0 + e) * hidden;
-                if (j0 < hidden) v.x = row[j0];
-                if (j0 + 1 < hidden) v.y = row[j0 + 1];
-            }
+            float2 v = make_float2(0.f, 0.f), dv;
+            if (e < nb) rn_hidden_pair(hd, a, c.type_i, c.e0 + e, j0, false, v, dv);
             *reinterpret_cast<__half2*>(sB + buf * kRnBTileBytes + rn_swizzled(e, j0)) = __floats2half2_rn(v.x, v.y);
         }
     };
@@ -467,7 +508,7 @@ __global__ void __launch_bounds__(kRnThreads, 1) tp_forward_rnet_kernel(const TP
         asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&mma_bar[buf])) : "memory");
     };
 
-    Cursor cur{static_cast<int>(blockIdx.x), 0, 0, 0};
+    Cursor cur{static_cast<int>(blockIdx.x), 0, 0, 0, 0};
     load_receiver(cur);
     float acc[tp.Q];
 #pragma unroll
@@ -565,6 +606,236 @@ __global__ void __launch_bounds__(kRnThreads, 1) tp_forward_rnet_kernel(const TP
     __syncthreads();
     if (tid == 0) {
         if (!tiles_ready) mbar_wait(&a_bar, 0);      // a CTA without work still waits for its weight-tile copies before it exits
+        if (failed) atomicMax(a.status, failed);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(kCols) : "memory");
+}
+
+// =============================================================================================
+// Reverse of the tensor product with the radial functions AND their derivatives from the network on the tensor cores.
+// Same organisation as tp_forward_rnet_kernel; a batch is 8 edges, and operand B holds for each edge both its hidden
+// activations x and their derivatives dx/dr, ordered so that the 16 accumulator columns of a path are, per group g of
+// warps, {R(e_2g), R(e_2g+1), R'(e_2g), R'(e_2g+1)}: one 4-column tcgen05.ld per path gives a thread the radial values
+// and derivatives of its group's two edges. The adjoint messages go to the senders with red.global.add (float32 path),
+// the adjoints of the harmonics and of the edge length are summed over channels as in tp_reverse_kernel.
+// =============================================================================================
+constexpr int kRnRevEdges = 8;
+
+struct RnEdgeRev {
+    float Y[kNumLm];
+    float dY[3][kNumLm];
+    float ux, uy, uz;
+    int j;
+};
+
+template <int LF>
+struct RnRevSmem {
+    static constexpr TPTable tp = make_tp_table(LF);
+    static constexpr int kTiles = tp.P * kRnTileBytes;
+    static constexpr int kB = 2 * kRnBTileBytes;
+    static constexpr int kEdge = 2 * kRnRevEdges * static_cast<int>(sizeof(RnEdgeRev));
+    static constexpr int kRed = kRnRevEdges * 4 * 17 * 4;                    // [edge][quadrant][17] partial sums over channels
+    static constexpr int kTotal = 1024 + kTiles + kB + kEdge + kRed;
+    static constexpr int kDCols = tp.P * kRnEdges;
+};
+
+template <int LF>
+__global__ void __launch_bounds__(kRnThreads, 1) tp_reverse_rnet_kernel(const TPArgs<float> a, const unsigned char* __restrict__ tiles_image,
+                                                                        const RnHidden hd) {
+    using S = RnRevSmem<LF>;
+    using T = float;
+    constexpr TPTable tp = make_tp_table(LF);
+    constexpr int kDCols = S::kDCols, kCols = rn_tmem_cols(kDCols);
+    extern __shared__ unsigned char rn_smem_raw[];
+    unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(rn_smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    unsigned char* sA = base;
+    unsigned char* sB = sA + S::kTiles;
+    RnEdgeRev* st = reinterpret_cast<RnEdgeRev*>(sB + S::kB);
+    float (*red)[4][17] = reinterpret_cast<float (*)[4][17]>(reinterpret_cast<unsigned char*>(st) + S::kEdge);
+    __shared__ __align__(8) unsigned long long a_bar, mma_bar[2];
+    __shared__ uint32_t tmem_slot;
+    __shared__ int failed;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int group = warp >> 2, quad = warp & 3, k = quad * 32 + lane;
+    const bool active = k < a.K;
+    if (tid == 0) {
+        failed = 0;
+        mbar_init(&a_bar, 1); mbar_init(&mma_bar[0], 1); mbar_init(&mma_bar[1], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(kCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_d = tmem_slot;
+    const uint32_t my_taddr = tmem_d + (static_cast<uint32_t>(quad * 32) << 16) + 4 * group;
+    if (tid == 0) {
+        mbar_expect_tx(&a_bar, S::kTiles);
+        for (int p = 0; p < tp.P; ++p) bulk_copy_g2s(sA + p * kRnTileBytes, tiles_image + static_cast<size_t>(p) * kRnTileBytes, kRnTileBytes, &a_bar);
+    }
+    bool tiles_ready = false;
+    const uint32_t idesc = rn_instr_desc();
+    unsigned mma_par[2] = {0u, 0u};
+
+    struct Cursor { int slot; int i; int type_i; long long e0, e_end; };
+    auto load_receiver = [&](Cursor& c) {
+        if (c.slot < a.N) {
+            c.i = a.order ? a.order[c.slot] : c.slot;
+            c.type_i = a.node_types[c.i];
+            c.e0 = a.first_neigh[c.i];
+            c.e_end = a.first_neigh[c.i + 1];
+        }
+    };
+    auto advance = [&](Cursor& c) {
+        c.e0 += kRnRevEdges;
+        if (c.e0 >= c.e_end) { c.slot += gridDim.x; load_receiver(c); }
+    };
+    auto stage_batch = [&](const Cursor& c, int buf) {
+        const int nb = static_cast<int>(c.e_end - c.e0 < kRnRevEdges ? c.e_end - c.e0 : kRnRevEdges);
+        if (warp == kRnThreads / 32 - 1 && lane < kRnRevEdges) {
+            RnEdgeRev& s = st[buf * kRnRevEdges + lane];
+            if (lane < nb) {
+                const long long e = c.e0 + lane;
+                const double rr = a.r[e], inv = 1.0 / rr;
+                const double ax = a.xyz[3 * e] * inv, ay = a.xyz[3 * e + 1] * inv, az = a.xyz[3 * e + 2] * inv;
+                s.ux = float(ax); s.uy = float(ay); s.uz = float(az);
+                real_sh3<float, true>(float(ax), float(ay), float(az), float(inv), s.Y, s.dY);
+                s.j = a.neigh_indices[e];
+            } else {
+                s.j = 0;
+            }
+        }
+        {   // operand B: row 4 g + {0, 1} = x of the group's edges 2 g, 2 g + 1; row 4 g + {2, 3} = dx of the same edges
+            const int row = tid >> 5, j0 = (tid & 31) * 2;
+            const int e = 2 * (row >> 2) + (row & 1);
+            float2 v = make_float2(0.f, 0.f), dv = make_float2(0.f, 0.f);
+            if (e < nb) rn_hidden_pair(hd, a, c.type_i, c.e0 + e, j0, true, v, dv);
+            if (row & 2) v = dv;
+            *reinterpret_cast<__half2*>(sB + buf * kRnBTileBytes + rn_swizzled(row, j0)) = __floats2half2_rn(v.x, v.y);
+        }
+    };
+    auto issue_mma = [&](int buf) {
+        const uint32_t b_addr = smem_u32(sB + buf * kRnBTileBytes);
+#pragma unroll 1
+        for (int p = 0; p < tp.P; ++p) {
+            const uint32_t a_addr = smem_u32(sA + p * kRnTileBytes);
+#pragma unroll
+            for (int ks = 0; ks < kRnHidden / 16; ++ks)
+                rn_mma(tmem_d + buf * kDCols + p * kRnEdges, tc5_smem_desc(a_addr + ks * 32), tc5_smem_desc(b_addr + ks * 32), idesc, ks > 0 ? 1u : 0u);
+        }
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&mma_bar[buf])) : "memory");
+    };
+
+    Cursor cur{static_cast<int>(blockIdx.x), 0, 0, 0, 0};
+    load_receiver(cur);
+    float d[tp.Q];
+    int d_slot = -1;            // receiver whose adjoint is in d
+    int buf = 0;
+    if (cur.slot < a.N) {
+        stage_batch(cur, 0);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();
+        if (tid == 0) {
+            if (!mbar_wait(&a_bar, 0)) { atomicMax(&failed, 5); }
+            else { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); issue_mma(0); }
+        }
+        tiles_ready = true;
+    }
+    while (cur.slot < a.N) {
+        Cursor nxt = cur;
+        advance(nxt);
+        const bool have_next = nxt.slot < a.N;
+        if (have_next) stage_batch(nxt, buf ^ 1);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();
+        if (have_next && tid == 0 && !failed) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            issue_mma(buf ^ 1);
+        }
+        if (d_slot != cur.slot) {     // first batch of a receiver: its adjoint (overlaps the tensor-core work)
+#pragma unroll
+            for (int q = 0; q < tp.Q; ++q)
+                d[q] = active ? __ldg(a.dPhi1 + (static_cast<size_t>(cur.i) * tp.Q + q) * a.K + k) : 0.f;
+            d_slot = cur.slot;
+        }
+        if (!*reinterpret_cast<volatile int*>(&failed) && !mbar_wait(&mma_bar[buf], mma_par[buf])) atomicMax(&failed, 6);
+        mma_par[buf] ^= 1u;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const int nb = static_cast<int>(cur.e_end - cur.e0 < kRnRevEdges ? cur.e_end - cur.e0 : kRnRevEdges);
+        if (!*reinterpret_cast<volatile int*>(&failed)) {
+            float Rq[tp.P][4];
+#pragma unroll
+            for (int p = 0; p < tp.P; ++p) tmem_ld4(my_taddr + buf * kDCols + p * kRnEdges, Rq[p]);
+#pragma unroll
+            for (int t = 0; t < 2; ++t) {
+                const int e = 2 * group + t;
+                if (e < nb) {       // uniform over the warp
+                    const RnEdgeRev& s = st[buf * kRnRevEdges + e];
+                    float W[kNumLm], fr = 0.f;
+#pragma unroll
+                    for (int lm = 0; lm < kNumLm; ++lm) W[lm] = 0.f;
+                    if (active) {
+                        const float* hrow = a.H + static_cast<size_t>(s.j) * tp.nLM * a.K + k;
+                        float h[tp.nLM], msg[tp.nLM], R[tp.P], Rd[tp.P], Y[kNumLm];
+#pragma unroll
+                        for (int lm2 = 0; lm2 < tp.nLM; ++lm2) { h[lm2] = __ldg(hrow + static_cast<size_t>(lm2) * a.K); msg[lm2] = 0.f; }
+#pragma unroll
+                        for (int p = 0; p < tp.P; ++p) { R[p] = Rq[p][t]; Rd[p] = Rq[p][2 + t]; }
+#pragma unroll
+                        for (int lm = 0; lm < kNumLm; ++lm) Y[lm] = s.Y[lm];
+                        using ::fma;
+                        if constexpr (LF == 0) {
+#include "generated/tp_L0_reverse.inc"
+                        } else if constexpr (LF == 1) {
+#include "generated/tp_L1_reverse.inc"
+                        } else {
+#include "generated/tp_L2_reverse.inc"
+                        }
+                        float* arow = a.H_adj + static_cast<size_t>(s.j) * tp.nLM * a.K + k;
+#pragma unroll
+                        for (int lm2 = 0; lm2 < tp.nLM; ++lm2) atomicAdd(arow + static_cast<size_t>(lm2) * a.K, msg[lm2]);
+                    }
+                    int idx;
+                    const float wsum = warp_reduce_scatter16(W, lane, idx);
+                    fr = warp_sum(fr);
+                    if ((lane & 1) == 0) red[e][quad][idx] = wsum;
+                    if (lane == 0) red[e][quad][16] = fr;
+                }
+            }
+        }
+        __syncthreads();
+        if (tid < nb && !*reinterpret_cast<volatile int*>(&failed)) {
+            // partial force of edge `tid`: nf -= xhat * dE/dr + sum_lm dE/dY_lm grad Y_lm
+            const RnEdgeRev& s = st[buf * kRnRevEdges + tid];
+            double tr = 0, fx = 0, fy = 0, fz = 0;
+            for (int w = 0; w < 4; ++w) tr += red[tid][w][16];
+#pragma unroll
+            for (int lm = 0; lm < kNumLm; ++lm) {
+                double wv = 0;
+                for (int w = 0; w < 4; ++w) wv += red[tid][w][lm];
+                fx += wv * double(s.dY[0][lm]); fy += wv * double(s.dY[1][lm]); fz += wv * double(s.dY[2][lm]);
+            }
+            double* nf = a.node_forces + 3 * (cur.e0 + tid);
+            nf[0] -= double(s.ux) * tr + fx;
+            nf[1] -= double(s.uy) * tr + fy;
+            nf[2] -= double(s.uz) * tr + fz;
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();
+        cur = nxt;
+        buf ^= 1;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        if (!tiles_ready) mbar_wait(&a_bar, 0);
         if (failed) atomicMax(a.status, failed);
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");

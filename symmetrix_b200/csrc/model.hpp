@@ -143,6 +143,10 @@ struct HostModel {
         std::vector<double> w_hidden;     // [num_hidden_layers - 1][hidden][hidden]
         std::vector<double> w_last;       // [hidden][P K]
         std::vector<double> pair_scale;   // [pairs][num_bessel]
+        // Low-rank form of the radial tables (optional keys x_radial_basis_*_1): the last hidden layer tabulated on the
+        // spline grid, as cubic coefficients [pair][bin][hidden][4]. Spline construction and the last layer are both
+        // linear, so (these) x w_last reproduces the radial spline tables to rounding.
+        std::vector<double> basis_coef;
     } rmlp1;
 
     // symmetric contractions: programs per LM (M0) and one for M1; coefficients [element][monomial][K]
@@ -450,6 +454,16 @@ inline HostModel load_model_file(const std::string& filename) {
         }
         if (!ok) throw ModelError("model file: x_radial_* keys are inconsistent (expected num_bessel -> equal hidden layers -> num_paths * num_channels)");
         r.present = true;
+        if (const JsonValue* bv = file.find("x_radial_basis_values_1")) {
+            const JsonValue& bd = file.at("x_radial_basis_derivs_1");
+            if (static_cast<int>(bv->size()) != m.num_pairs || static_cast<int>(bd.size()) != m.num_pairs)
+                throw ModelError("model file: x_radial_basis_*_1 must have one table per unordered element pair");
+            const int G = m.num_bins + 1;
+            r.basis_coef.assign(static_cast<size_t>(m.num_pairs) * m.num_bins * r.hidden * 4, 0.0);
+            for (int pr = 0; pr < m.num_pairs; ++pr)
+                detail::spline_coefficients(bv->arr[pr], bd.arr[pr], m.spline_h, r.hidden, G, {},
+                                            r.basis_coef.data() + static_cast<size_t>(pr) * m.num_bins * r.hidden * 4);
+        }
     }
     if (const JsonValue* ni = file.find("num_interactions")) m.num_interactions = ni->as_int();
     if (m.num_interactions != 2 && m.num_interactions != 3) throw UnsupportedError("num_interactions must be 2 or 3");

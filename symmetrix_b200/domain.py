@@ -288,9 +288,11 @@ class SlabRank:
             self.torch.cuda.synchronize()
 
 
-def _exchange(ranks, transport_fn, pack, unpack, dist=None):
+def _exchange(ranks, transport_fn, pack, unpack, dist=None, native=None):
     """One halo exchange. With `dist` (torch.distributed) there is exactly one local rank and messages go
-    point to point; without it `ranks` holds every rank and messages are handed over in memory."""
+    point to point; without it `ranks` holds every rank and messages are handed over in memory. `native` =
+    (array name, add, forward?) lets an evaluator that holds its own NCCL communicator (``MACE.comm_init``) do the whole
+    exchange inside the library; otherwise the packed buffers travel through ``torch.distributed``."""
     if dist is None:
         box = {}
         for r in ranks:
@@ -302,6 +304,11 @@ def _exchange(ranks, transport_fn, pack, unpack, dist=None):
         return
     import torch
     r = ranks[0]
+    if native is not None and getattr(r.ev, "comm_ready", False):
+        # the library's own transport: pack kernels, grouped ncclSend / ncclRecv and unpack kernels on the evaluator's stream
+        name, add, forward = native
+        r.ev.halo_exchange(name, add, r.plan.peers, r.send_idx if forward else r.recv_idx, r.recv_idx if forward else r.send_idx)
+        return
     ops, recvs = [], {}
     sends = {q: pack(r, q) for q in r.plan.peers}
     for q in r.plan.peers:
@@ -328,12 +335,12 @@ def evaluate_decomposed(ranks, dist=None):
     def forward_halo(name):
         if not recompute:
             _exchange(ranks, lambda r, q: r.recv_idx[q].numel(), lambda r, q: r.pack_forward(q, name),
-                      lambda r, q, b: r.unpack_forward(q, b, name), dist)
+                      lambda r, q, b: r.unpack_forward(q, b, name), dist, native=(name, False, True))
 
     def reverse_halo(name):
         if not recompute:
             _exchange(ranks, lambda r, q: r.send_idx[q].numel(), lambda r, q: r.pack_reverse(q, name),
-                      lambda r, q, b: r.unpack_reverse(q, b, name), dist)
+                      lambda r, q, b: r.unpack_reverse(q, b, name), dist, native=(name, True, False))
 
     for r in ranks:
         r.begin_step()
@@ -352,12 +359,16 @@ def evaluate_decomposed(ranks, dist=None):
     reverse_halo("H1_adj")
     for r in ranks:
         r.reverse_layer0()
-    _exchange(ranks, lambda r, q: r.send_idx[q].numel(), lambda r, q: r.pack_forces(q), lambda r, q, b: r.unpack_forces(q, b), dist)
+    _exchange(ranks, lambda r, q: r.send_idx[q].numel(), lambda r, q: r.pack_forces(q), lambda r, q, b: r.unpack_forces(q, b), dist,
+              native=("atom_forces", True, False))
     if ranks[0].shared_stream:
         import torch
         t = sum(torch.cat([r.energy, r.virial]) for r in ranks)      # seven float64 values on the device
         if dist is not None:
-            dist.all_reduce(t)
+            if getattr(ranks[0].ev, "comm_ready", False):
+                ranks[0].ev.allreduce_sum(t)
+            else:
+                dist.all_reduce(t)
         owned = [r.owned_forces() for r in ranks]
         vals = t.cpu().numpy()                                      # the only host synchronisation of the step
         for r in ranks:

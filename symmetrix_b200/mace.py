@@ -77,6 +77,7 @@ class MACE:
         self.atomic_energies = list(ebuf)
         self._num_nodes = 0
         self._num_edges = 0
+        self.comm_ready = False
 
     # ------------------------------------------------------------------ plumbing
     def close(self):
@@ -347,6 +348,37 @@ class MACE:
     def debug_expire_waits(self, polls: int) -> None:
         """Test switch: make the first bounded wait of every float32 tensor-core GEMM CTA run out after `polls` polls."""
         self._check(self._lib.smx_debug_expire_waits(self._h, int(polls)))
+
+    # NCCL transport inside the library (smx_comm_init / smx_halo_exchange / smx_allreduce_sum)
+    def comm_init(self, dist) -> None:
+        """Create the library's own NCCL communicator over the ranks of an initialised ``torch.distributed`` group; the
+        128-byte id made by rank 0 travels through ``dist.broadcast_object_list``. Collective."""
+        rank, world = dist.get_rank(), dist.get_world_size()
+        box = [None]
+        if rank == 0:
+            buf = ctypes.create_string_buffer(128)
+            status = self._lib.smx_comm_unique_id(buf, 128)
+            if status != _lib.SMX_OK:
+                raise SymmetrixError(status, self._lib.smx_last_error(None).decode())
+            box[0] = buf.raw
+        dist.broadcast_object_list(box, src=0)
+        self._check(self._lib.smx_comm_init(self._h, box[0], 128, world, rank))
+        self.comm_ready = True
+
+    def halo_exchange(self, name: str, add: bool, peers, send_rows, recv_rows) -> None:
+        """One exchange with the ranks `peers`: rows ``send_rows[q]`` of the named array go to peer q, the rows received
+        from it are written (or, with `add`, added in a fixed order) to ``recv_rows[q]``. Index lists are int32 CUDA tensors."""
+        n = len(peers)
+        c_peers = (ctypes.c_int * n)(*[int(q) for q in peers])
+        c_send = (ctypes.c_void_p * n)(*[send_rows[q].data_ptr() for q in peers])
+        c_recv = (ctypes.c_void_p * n)(*[recv_rows[q].data_ptr() for q in peers])
+        c_ns = (ctypes.c_int * n)(*[send_rows[q].numel() for q in peers])
+        c_nr = (ctypes.c_int * n)(*[recv_rows[q].numel() for q in peers])
+        self._check(self._lib.smx_halo_exchange(self._h, name.encode(), int(bool(add)), n, c_peers, c_send, c_ns, c_recv, c_nr))
+
+    def allreduce_sum(self, values) -> None:
+        """In-place sum of a float64 CUDA tensor over the ranks of the library's communicator."""
+        self._check(self._lib.smx_allreduce_sum(self._h, ctypes.c_void_p(values.data_ptr()), values.numel()))
 
     def device_view(self, name: str):
         """Zero-copy torch view (1-D, float32 or float64) of a named device array; valid until that array is resized."""

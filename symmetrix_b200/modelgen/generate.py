@@ -207,6 +207,7 @@ def radial_mlp_tables(spec: ModelSpec, rng: np.random.Generator, num_out: int, g
     n_el = len(spec.atomic_numbers)
     pair_scale = {}
     values, derivs = [], []
+    hidden_values, hidden_derivs = [], []
     basis = bessel_cutoff_basis(r, spec.r_cut, spec.num_bessel, spec.poly_p)
     for a in range(n_el):
         for b in range(a, n_el):
@@ -220,6 +221,13 @@ def radial_mlp_tables(spec: ModelSpec, rng: np.random.Generator, num_out: int, g
             spl = CubicSpline(r, y, axis=0, bc_type=("not-a-knot", "clamped"))
             values.append(np.ascontiguousarray(spl(r).T))            # [num_out, G]
             derivs.append(np.ascontiguousarray(spl.derivative()(r).T))
+            # The same tabulation of the last hidden layer. Spline construction is linear in the nodal data and the last
+            # layer is linear, so the tables above are, to rounding, these times weights[-1]: the radial tables have the
+            # rank of the hidden width, whatever the number of output functions.
+            hspl = CubicSpline(r, x, axis=0, bc_type=("not-a-knot", "clamped"))
+            hidden_values.append(np.ascontiguousarray(hspl(r).T))    # [hidden, G]
+            hidden_derivs.append(np.ascontiguousarray(hspl.derivative()(r).T))
+    radial_mlp_tables.last_hidden = (np.stack(hidden_values), np.stack(hidden_derivs))
     return float(h), np.stack(values), np.stack(derivs), weights, pair_scale
 
 
@@ -264,6 +272,9 @@ def generate_model(spec: ModelSpec) -> dict:
     out["x_radial_mlp_dims_1"] = [int(w.shape[0]) for w in mlp1] + [int(mlp1[-1].shape[1])]
     out["x_radial_mlp_weights_1"] = [np.ascontiguousarray(w).ravel() for w in mlp1]          # each [in][out], row-major
     out["x_radial_pair_scale_1"] = [pair_scale1[(a, b)] for a in range(n_el) for b in range(a, n_el)]
+    # Low-rank form of the block-1 radial tables: the last hidden layer tabulated exactly like the radial functions
+    # ([pair][hidden][G] nodal values and derivatives); radial_spline_*_1 = these x x_radial_mlp_weights_1[-1] to rounding.
+    out["x_radial_basis_values_1"], out["x_radial_basis_derivs_1"] = radial_mlp_tables.last_hidden
     out["radial_spline_h"] = h
     out["radial_spline_values_0"] = v0
     out["radial_spline_derivs_0"] = d0

@@ -18,10 +18,13 @@ from symmetrix_b200.domain import SlabRank, evaluate_decomposed, make_slab_plan 
 def main():
     model, dtype, out = sys.argv[1], sys.argv[2], sys.argv[3]
     mode = sys.argv[4] if len(sys.argv) > 4 else "message_passing"
+    transport = sys.argv[5] if len(sys.argv) > 5 else "torch"      # "library": NCCL send / recv issued inside libsymmetrix_b200
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     ev = MACE(model, dtype=dtype, device=local)
+    if transport == "library":
+        ev.comm_init(dist)
     s = st.fcc_box((4 * world, 3, 3), 3.6, ev.atomic_numbers, seed=17, jitter=0.12)
     rk = SlabRank(make_slab_plan(s, ev.r_cut, rank, world, mode=mode), ev, ev.r_cut, ev.atomic_numbers)
     rk.build_edges()

@@ -99,12 +99,14 @@ def test_lmax2_model_at_benchmark_width(model_file, dtype):
     ("water64", lambda z: st.water_box(4, 12.42, seed=0)),                   # configs[0] as stated: 192 atoms, 64x0e
     ("fcc128", lambda z: st.fcc_box(4, 3.6, z, seed=2)),                     # configs[1] model on a 256-atom box
 ])
-def test_runtime_radial_network_mode_meets_the_float32_gates(monkeypatch, workload, builder):
+@pytest.mark.parametrize("mode", ["mlp", "lowrank"])
+def test_runtime_radial_network_mode_meets_the_float32_gates(monkeypatch, workload, builder, mode):
     """SMX_RADIAL=mlp: the radial functions of block 1 evaluated at run time from the un-splined network (Bessel functions
     x polynomial cutoff, hidden layers per edge, last layer as a tensor-core GEMM) instead of the spline tables that the
     reference's exporter makes of the same network (extract_mace_data.py:144-172). The two differ by the interpolation
     error of the 256-point splines and float32 rounding; gate: 1e-4 relative energy, 1e-3 eV/A, against the float64 spline
-    path (which is pinned to the reference)."""
+    path (which is pinned to the reference). SMX_RADIAL=lowrank uses the tabulated last hidden layer instead of the network's
+    first layers: spline construction and the last layer are linear, so that form equals the spline tables to rounding."""
     path, numbers, spec = bench.model_path(workload)
     s = builder(numbers)
     nl = st.neighbor_list(s, spec.r_cut)
@@ -117,12 +119,12 @@ def test_runtime_radial_network_mode_meets_the_float32_gates(monkeypatch, worklo
         return ev.node_energies, ev.node_forces
 
     e64, f64 = evaluate("float64")
-    monkeypatch.setenv("SMX_RADIAL", "mlp")
+    monkeypatch.setenv("SMX_RADIAL", mode)
     e_mlp, f_mlp = evaluate("float32")
     monkeypatch.delenv("SMX_RADIAL")
     assert abs(e_mlp.sum() - e64.sum()) <= 1e-4 * abs(e64.sum())
     assert np.abs(f_mlp - f64).max() <= 1e-3
     # and the mode is refused where it does not apply
-    monkeypatch.setenv("SMX_RADIAL", "mlp")
+    monkeypatch.setenv("SMX_RADIAL", mode)
     with pytest.raises(Exception):
         MACE(path, dtype="float64")

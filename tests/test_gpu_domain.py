@@ -151,8 +151,10 @@ def _gpu_count():
     return torch.cuda.device_count()
 
 
-@pytest.mark.parametrize("dtype,mode", [("float64", "message_passing"), ("float32", "message_passing"), ("float64", "recompute")])
-def test_ranks_over_nccl_match_single_domain(model_file, dtype, mode, tmp_path):
+@pytest.mark.parametrize("dtype,mode,transport", [("float64", "message_passing", "torch"), ("float32", "message_passing", "torch"),
+                                                  ("float64", "recompute", "torch"), ("float64", "message_passing", "library"),
+                                                  ("float32", "message_passing", "library"), ("float64", "recompute", "library")])
+def test_ranks_over_nccl_match_single_domain(model_file, dtype, mode, transport, tmp_path):
     world = min(_gpu_count(), 4)
     if world < 2:
         pytest.skip("needs at least two GPUs")
@@ -160,7 +162,7 @@ def test_ranks_over_nccl_match_single_domain(model_file, dtype, mode, tmp_path):
     out = tmp_path / "dd.npz"
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
-           "--master-port", str(29400 + os.getpid() % 500), str(ROOT / "tests" / "dd_nccl_worker.py"), str(path), dtype, str(out), mode]
+           "--master-port", str(29400 + os.getpid() % 500), str(ROOT / "tests" / "dd_nccl_worker.py"), str(path), dtype, str(out), mode, transport]
     subprocess.run(cmd, check=True, env=env, timeout=600)
     d = np.load(out)
     rel, fabs = (1e-10, 1e-9) if dtype == "float64" else (1e-4, 1e-3)
