@@ -400,6 +400,18 @@ __device__ __forceinline__ void rn_hidden_pair(const RnHidden& hd, const TPArgs<
     }
 }
 
+// Starts the fetch of 4 accumulator columns; rn_ld_wait completes all fetches of the thread (the registers are operands of
+// the wait so that no use of them is scheduled before it).
+__device__ __forceinline__ void rn_ld4_issue(uint32_t taddr, uint32_t (&v)[4]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]) : "r"(taddr) : "memory");
+}
+template <int P>
+__device__ __forceinline__ void rn_ld_wait(uint32_t (&v)[P][4]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int p = 0; p < P; ++p) asm volatile("" : "+r"(v[p][0]), "+r"(v[p][1]), "+r"(v[p][2]), "+r"(v[p][3]) :: "memory");
+}
+
 struct RnEdge {             // per-edge, channel-independent data of the forward pass
     float Y[kNumLm];
     int j;                  // sender row
@@ -543,20 +555,29 @@ __global__ void __launch_bounds__(kRnThreads, 1) tp_forward_rnet_kernel(const TP
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const int nb = static_cast<int>(cur.e_end - cur.e0 < kRnEdges ? cur.e_end - cur.e0 : kRnEdges);
         if (!*reinterpret_cast<volatile int*>(&failed)) {
-            float Rq[tp.P][4];
+            uint32_t Rq[tp.P][4];
 #pragma unroll
-            for (int p = 0; p < tp.P; ++p) tmem_ld4(my_taddr + buf * kDCols + p * kRnEdges, Rq[p]);
+            for (int p = 0; p < tp.P; ++p) rn_ld4_issue(my_taddr + buf * kDCols + p * kRnEdges, Rq[p]);
+            // sender features of the group's four edges: all loads in flight before the first use
+            float hq[4][tp.nLM];
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                const int e = 4 * group + t;
+                const float* hrow = a.H + static_cast<size_t>(st[buf * kRnEdges + (e < nb ? e : 0)].j) * tp.nLM * a.K + k;
+#pragma unroll
+                for (int lm2 = 0; lm2 < tp.nLM; ++lm2) hq[t][lm2] = (e < nb && active) ? __ldg(hrow + static_cast<size_t>(lm2) * a.K) : 0.f;
+            }
+            rn_ld_wait<tp.P>(Rq);
 #pragma unroll
             for (int t = 0; t < 4; ++t) {
                 const int e = 4 * group + t;
                 if (e < nb && active) {
                     const RnEdge& s = st[buf * kRnEdges + e];
-                    const float* hrow = a.H + static_cast<size_t>(s.j) * tp.nLM * a.K + k;
                     float h[tp.nLM], R[tp.P], Y[kNumLm];
 #pragma unroll
-                    for (int lm2 = 0; lm2 < tp.nLM; ++lm2) h[lm2] = __ldg(hrow + static_cast<size_t>(lm2) * a.K);
+                    for (int lm2 = 0; lm2 < tp.nLM; ++lm2) h[lm2] = hq[t][lm2];
 #pragma unroll
-                    for (int p = 0; p < tp.P; ++p) R[p] = Rq[p][t];
+                    for (int p = 0; p < tp.P; ++p) R[p] = __uint_as_float(Rq[p][t]);
 #pragma unroll
                     for (int lm = 0; lm < kNumLm; ++lm) Y[lm] = s.Y[lm];
                     using T = float;
@@ -771,9 +792,18 @@ __global__ void __launch_bounds__(kRnThreads, 1) tp_reverse_rnet_kernel(const TP
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const int nb = static_cast<int>(cur.e_end - cur.e0 < kRnRevEdges ? cur.e_end - cur.e0 : kRnRevEdges);
         if (!*reinterpret_cast<volatile int*>(&failed)) {
-            float Rq[tp.P][4];
+            uint32_t Rq[tp.P][4];
 #pragma unroll
-            for (int p = 0; p < tp.P; ++p) tmem_ld4(my_taddr + buf * kDCols + p * kRnEdges, Rq[p]);
+            for (int p = 0; p < tp.P; ++p) rn_ld4_issue(my_taddr + buf * kDCols + p * kRnEdges, Rq[p]);
+            float hq[2][tp.nLM];
+#pragma unroll
+            for (int t = 0; t < 2; ++t) {
+                const int e = 2 * group + t;
+                const float* hrow = a.H + static_cast<size_t>(st[buf * kRnRevEdges + (e < nb ? e : 0)].j) * tp.nLM * a.K + k;
+#pragma unroll
+                for (int lm2 = 0; lm2 < tp.nLM; ++lm2) hq[t][lm2] = (e < nb && active) ? __ldg(hrow + static_cast<size_t>(lm2) * a.K) : 0.f;
+            }
+            rn_ld_wait<tp.P>(Rq);
 #pragma unroll
             for (int t = 0; t < 2; ++t) {
                 const int e = 2 * group + t;
@@ -783,12 +813,11 @@ __global__ void __launch_bounds__(kRnThreads, 1) tp_reverse_rnet_kernel(const TP
 #pragma unroll
                     for (int lm = 0; lm < kNumLm; ++lm) W[lm] = 0.f;
                     if (active) {
-                        const float* hrow = a.H + static_cast<size_t>(s.j) * tp.nLM * a.K + k;
                         float h[tp.nLM], msg[tp.nLM], R[tp.P], Rd[tp.P], Y[kNumLm];
 #pragma unroll
-                        for (int lm2 = 0; lm2 < tp.nLM; ++lm2) { h[lm2] = __ldg(hrow + static_cast<size_t>(lm2) * a.K); msg[lm2] = 0.f; }
+                        for (int lm2 = 0; lm2 < tp.nLM; ++lm2) { h[lm2] = hq[t][lm2]; msg[lm2] = 0.f; }
 #pragma unroll
-                        for (int p = 0; p < tp.P; ++p) { R[p] = Rq[p][t]; Rd[p] = Rq[p][2 + t]; }
+                        for (int p = 0; p < tp.P; ++p) { R[p] = __uint_as_float(Rq[p][t]); Rd[p] = __uint_as_float(Rq[p][2 + t]); }
 #pragma unroll
                         for (int lm = 0; lm < kNumLm; ++lm) Y[lm] = s.Y[lm];
                         using ::fma;

@@ -905,14 +905,17 @@ static __global__ void __launch_bounds__(kRadialGroups * 64) radial_hidden_kerne
                 const int lo = type_i <= tj ? type_i : tj, hi = type_i <= tj ? tj : type_i;
                 const int pair = lo * (2 * a.num_elements - lo - 1) / 2 + hi;
                 const double kn = (j + 1) * pi / rc, amp = sqrt(2.0 / rc);
-                const double sn = sin(kn * rr), cs = cos(kn * rr);
+                double sn, cs;
+                sincos(kn * rr, &sn, &cs);
                 const double b = amp * sn / rr, db = amp * (kn * cs / rr - sn / (rr * rr));
                 const double x = rr / rc, p = a.poly_p;
                 double c = 0.0, dc = 0.0;
                 if (x < 1.0) {
-                    c = 1.0 - (p + 1.0) * (p + 2.0) / 2.0 * pow(x, p) + p * (p + 2.0) * pow(x, p + 1.0) - p * (p + 1.0) / 2.0 * pow(x, p + 2.0);
-                    dc = (-(p + 1.0) * (p + 2.0) / 2.0 * p * pow(x, p - 1.0) + p * (p + 2.0) * (p + 1.0) * pow(x, p)
-                          - p * (p + 1.0) / 2.0 * (p + 2.0) * pow(x, p + 1.0)) / rc;
+                    double xp1 = 1.0;                              // x^(p - 1) by repeated multiplication (p is a small integer)
+                    for (int q = 1; q < a.poly_p; ++q) xp1 *= x;
+                    const double xp = xp1 * x, xq = xp * x, xr = xq * x;
+                    c = 1.0 - (p + 1.0) * (p + 2.0) / 2.0 * xp + p * (p + 2.0) * xq - p * (p + 1.0) / 2.0 * xr;
+                    dc = (-(p + 1.0) * (p + 2.0) / 2.0 * p * xp1 + p * (p + 2.0) * (p + 1.0) * xp - p * (p + 1.0) / 2.0 * (p + 2.0) * xq) / rc;
                 }
                 const double sc = a.pair_scale[pair * a.num_bessel + j];
                 mine[j] = static_cast<float>(b * c * sc);
