@@ -168,7 +168,7 @@ def roofline_for(stage: str, ms: float, n_atoms: int, n_edges: int, K: int, L_ma
     if stage in ("reverse_Phi1", "reverse_Phim"):
         byts = n_edges * (40 + nLM * K * s + 24) + n_atoms * Q * K * s
         flops = n_edges * K * rev_flops
-        kernel = "tp_reverse_kernel"
+        kernel = "tp_reverse_tmem_kernel" if dtype_bytes == 8 else "tp_reverse_kernel"
     elif stage in ("compute_Phi1", "compute_Phim"):
         byts = n_edges * (40 + nLM * K * s) + n_atoms * Q * K * s
         flops = n_edges * K * fwd_flops
@@ -183,9 +183,10 @@ def roofline_for(stage: str, ms: float, n_atoms: int, n_edges: int, K: int, L_ma
         kernel = "layer0_forward_kernel"
     peak, how = measured_peaks()
     achieved = byts / (ms * 1e-3) / 1e9
-    # dram__bytes_read.sum + dram__bytes_write.sum per edge from the ncu capture summarised in
-    # profiles/edge_kernels_fcc1372_fp64.md (a smaller box of the same construction; traffic grows with the edge count)
-    per_edge = {("tp_reverse_kernel", 8): 6827.0, ("tp_forward_kernel", 8): 2812.0,
+    # dram__bytes_read.sum + dram__bytes_write.sum per edge from the ncu captures summarised in
+    # profiles/tp_reverse_tmem_fcc1372_fp64.md and profiles/edge_kernels_fcc1372_fp64.md (a smaller box of the same
+    # construction; traffic grows with the edge count)
+    per_edge = {("tp_reverse_tmem_kernel", 8): 8530.0, ("tp_forward_kernel", 8): 2812.0,
                 ("layer0_reverse_kernel", 8): 638.0, ("layer0_forward_kernel", 8): 405.0}.get((kernel, dtype_bytes))
     traffic = per_edge * n_edges if per_edge and K == 128 and L_max == 1 else None
     return {"bound": "hbm", "kernel": kernel, "stage": stage, "achieved": achieved, "peak": peak, "unit": "GB/s",
