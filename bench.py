@@ -403,8 +403,22 @@ def config3_single(local_rank, torch) -> dict:
         t = ev.timer_stop()
         if it > 0:
             ms += t
+    # per-stage device times of one more evaluation, and the channel-mixing GEMM of the tensor-product output (compute_A1,
+    # tcgen05 kernel) against the HBM roofline: it reads Phi1 [N, Q, K] and writes A1 [N, 16, K] once each
+    ev.set_profiling(True)
+    ev.compute_node_energies_forces(s.num_atoms, *[dev[k] for k in keys])
+    stage_ms = ev.stage_times()
+    ev.set_profiling(False)
+    peak, how = measured_peaks()
+    K, Q = ev.num_channels, ev.num_lme
+    a1_bytes = s.num_atoms * (Q + 16) * K * 4
+    a1_flops = 2.0 * s.num_atoms * Q * K * K
+    a1 = {"kernel": "gemm_rows_tcgen05_kernel", "stage": "compute_A1", "launch_ms": stage_ms.get("compute_A1"),
+          "algorithmic_bytes": a1_bytes, "achieved_gbs": a1_bytes / (stage_ms["compute_A1"] * 1e-3) / 1e9,
+          "hbm_frac": a1_bytes / (stage_ms["compute_A1"] * 1e-3) / 1e9 / peak, "peak_source": f"of {how}",
+          "achieved_tflops_3xtf32_counted_once": a1_flops / (stage_ms["compute_A1"] * 1e-3) / 1e12}
     return {"workload": "fcc256k", "dtype": "f32", "atoms": s.num_atoms, "edges": int(inputs["r"].size), "steps": steps,
-            "ms_per_step": ms / steps, "value": s.num_atoms * steps / (ms * 1e-3), "unit": UNIT,
+            "ms_per_step": ms / steps, "value": s.num_atoms * steps / (ms * 1e-3), "unit": UNIT, "stage_ms": stage_ms, "gemm_A1": a1,
             "note": "inputs larger than L2; one warm-up step; efficiency at N GPUs = value(N) / (N x this value)"}
 
 
