@@ -43,7 +43,8 @@ def _inputs() -> list[Path]:
 
 
 def _compile(nvcc: str, src: Path, obj: Path, verbose: bool) -> str:
-    cmd = [nvcc, *NVCC_FLAGS, "-c", str(src), "-o", str(obj)]
+    # SMX_NVCC_FLAGS: extra compiler flags (e.g. -D switches of the kernels' tuning macros) for measurement builds
+    cmd = [nvcc, *NVCC_FLAGS, *os.environ.get("SMX_NVCC_FLAGS", "").split(), "-c", str(src), "-o", str(obj)]
     if verbose:
         cmd += ["-Xptxas", "-v"]
         print(" ".join(cmd), flush=True)

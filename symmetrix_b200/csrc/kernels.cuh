@@ -661,6 +661,9 @@ __global__ void __launch_bounds__(kChannelBlock, tp_min_blocks<T>(LF, true)) tp_
                         // float32: one reduction per value directly into the sender's row (no message buffer)
                         T* arow = a.H_adj + static_cast<size_t>(s.j) * tp.nLM * a.K + k;
 #pragma unroll
+#ifdef SMX_TIMING_ONLY_NO_SCATTER      // measurement builds only: what the reductions into the senders' rows cost (results are wrong)
+                        if (msg[0] == T(1.2345e30))
+#endif
                         for (int lm2 = 0; lm2 < tp.nLM; ++lm2) atomicAdd(arow + static_cast<size_t>(lm2) * a.K, msg[lm2]);
                     }
                 }

@@ -5,7 +5,7 @@
 //   p = x_j + ((n0*a0 + n1*a1) + n2*a2)        image position, float64, no fused multiply-add
 //   d = p - x_i
 //   keep iff (d0*d0 + d1*d1) + d2*d2 < r_cut*r_cut, excluding i == j with a zero shift
-// Rows are ordered by (sender index, shift code), so the list is a pure function of its inputs.
+// Rows are ordered by (sender index, shift code), so the list is a pure function of its inputs. One warp builds one row.
 // Candidates come from a uniform grid over fractional coordinates whose cells are at least
 // r_cut(1+1e-9) thick. Positions need not lie inside the cell: along a periodic axis an atom is binned by its
 // wrapped fractional coordinate, and the whole cell vectors w_i it is away from the cell are folded into the
@@ -80,22 +80,29 @@ __device__ __forceinline__ unsigned long long neigh_key(int j, int n0, int n1, i
     return (static_cast<unsigned long long>(j) << 32) | code;
 }
 
-// One thread per receiver atom. COUNT: number of edges of the row. Otherwise: write the keys of
-// the row, sort them (rows are short), then expand each key into the edge arrays.
+// One warp per receiver atom; the lanes share the candidates of the 27 (or more) bins around the atom's bin.
+// COUNT: number of edges of the row. Otherwise: the keys of the row are collected in shared memory in traversal order,
+// ranked (keys are unique, so the rank of a key is the number of smaller keys: the row comes out ordered by
+// (sender, shift) whatever the traversal order was), and each key is expanded into the edge arrays with the same
+// arithmetic that tested it. Rows longer than kNeighRowCap keys are ranked in global memory by the same rule.
+constexpr int kNeighWarps = 4;           // warps per CTA
+constexpr int kNeighRowCap = 512;        // keys of one row held in shared memory
+
 template <bool COUNT>
-static __global__ void neigh_rows_kernel(int n, const double* __restrict__ pos, const int* __restrict__ types, NeighGrid g,
-                                  const int* __restrict__ bin_start, const int* __restrict__ sorted_atoms, const int* __restrict__ wrap,
-                                  int* __restrict__ shift_overflow, int* __restrict__ num_neigh, const long long* __restrict__ first_neigh,
-                                  unsigned long long* __restrict__ keys, int* __restrict__ neigh_indices,
-                                  int* __restrict__ neigh_types, int* __restrict__ shifts, double* __restrict__ xyz,
-                                  double* __restrict__ r) {
-    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+static __global__ void __launch_bounds__(kNeighWarps * 32) neigh_rows_kernel(
+    int n, const double* __restrict__ pos, const int* __restrict__ types, NeighGrid g, const int* __restrict__ bin_start,
+    const int* __restrict__ sorted_atoms, const int* __restrict__ wrap, int* __restrict__ shift_overflow, int* __restrict__ num_neigh,
+    const long long* __restrict__ first_neigh, unsigned long long* __restrict__ keys, int* __restrict__ neigh_indices,
+    int* __restrict__ neigh_types, int* __restrict__ shifts, double* __restrict__ xyz, double* __restrict__ r) {
+    __shared__ unsigned long long row_keys[COUNT ? 1 : kNeighWarps][COUNT ? 1 : kNeighRowCap];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int warps_total = gridDim.x * kNeighWarps;
+    for (int i = blockIdx.x * kNeighWarps + warp; i < n; i += warps_total) {
         const double xi[3] = {pos[3 * i], pos[3 * i + 1], pos[3 * i + 2]};
         int b3[3], wi[3];
         neigh_bin(g, xi, b3, wi);
-        long long out = COUNT ? 0 : first_neigh[i];
-        const long long row_begin = out;
-        int count = 0;
+        const long long row_begin = COUNT ? 0 : first_neigh[i];
+        int count = 0;                     // edges found so far (the same value in every lane)
         for (int o0 = -g.reach[0]; o0 <= g.reach[0]; ++o0) {
             const int v0 = b3[0] + o0;
             const int n0 = static_cast<int>(floor(double(v0) / g.nb[0]));
@@ -112,46 +119,59 @@ static __global__ void neigh_rows_kernel(int n, const double* __restrict__ pos, 
                     if (n2 != 0 && !g.pbc[2]) continue;
                     const int c2 = v2 - n2 * g.nb[2];
                     const int bin = (c0 * g.nb[1] + c1) * g.nb[2] + c2;
-                    for (int s = bin_start[bin]; s < bin_start[bin + 1]; ++s) {
-                        const int j = sorted_atoms[s];
-                        if (j == i && n0 == 0 && n1 == 0 && n2 == 0) continue;
-                        // shift between the positions as given: image between the wrapped positions + the two wraps
-                        const int m0 = n0 + wi[0] - wrap[3 * j], m1 = n1 + wi[1] - wrap[3 * j + 1], m2 = n2 + wi[2] - wrap[3 * j + 2];
-                        double d[3], r2;
-                        if (neigh_test(g, xi, pos + 3 * j, m0, m1, m2, d, &r2)) {
-                            if (COUNT && (abs(m0) > kNeighMaxShift || abs(m1) > kNeighMaxShift || abs(m2) > kNeighMaxShift)) *shift_overflow = 1;
-                            if (!COUNT) keys[out++] = neigh_key(j, m0, m1, m2);
-                            ++count;
+                    const int s_end = bin_start[bin + 1];
+                    for (int s0 = bin_start[bin]; s0 < s_end; s0 += 32) {
+                        const int s = s0 + lane;
+                        bool hit = false;
+                        unsigned long long key = 0;
+                        if (s < s_end) {
+                            const int j = sorted_atoms[s];
+                            if (!(j == i && n0 == 0 && n1 == 0 && n2 == 0)) {
+                                // shift between the positions as given: image between the wrapped positions + the two wraps
+                                const int m0 = n0 + wi[0] - wrap[3 * j], m1 = n1 + wi[1] - wrap[3 * j + 1], m2 = n2 + wi[2] - wrap[3 * j + 2];
+                                double d[3], r2;
+                                if (neigh_test(g, xi, pos + 3 * j, m0, m1, m2, d, &r2)) {
+                                    hit = true;
+                                    if (COUNT && (abs(m0) > kNeighMaxShift || abs(m1) > kNeighMaxShift || abs(m2) > kNeighMaxShift)) *shift_overflow = 1;
+                                    key = neigh_key(j, m0, m1, m2);
+                                }
+                            }
                         }
+                        const unsigned mask = __ballot_sync(0xffffffffu, hit);
+                        if (!COUNT && hit) {
+                            const int slot = count + __popc(mask & ((1u << lane) - 1u));
+                            if (slot < kNeighRowCap) row_keys[warp][slot] = key;
+                            keys[row_begin + slot] = key;         // long rows are ranked from here
+                        }
+                        count += __popc(mask);
                     }
                 }
             }
         }
         if (COUNT) {
-            num_neigh[i] = count;
-        } else {
-            // insertion sort of the row's keys
-            for (long long a = row_begin + 1; a < out; ++a) {
-                const unsigned long long key = keys[a];
-                long long b = a - 1;
-                while (b >= row_begin && keys[b] > key) { keys[b + 1] = keys[b]; --b; }
-                keys[b + 1] = key;
-            }
-            for (long long e = row_begin; e < out; ++e) {
-                const unsigned long long key = keys[e];
-                const int j = static_cast<int>(key >> 32);
-                const unsigned int code = static_cast<unsigned int>(key & 0xffffffffu);
-                const int n2 = static_cast<int>(code % 1024) - 512, n1 = static_cast<int>((code / 1024) % 1024) - 512,
-                          n0 = static_cast<int>(code / (1024 * 1024)) - 512;
-                double d[3], r2;
-                neigh_test(g, xi, pos + 3 * j, n0, n1, n2, d, &r2);
-                neigh_indices[e] = j;
-                neigh_types[e] = types[j];
-                shifts[3 * e] = n0; shifts[3 * e + 1] = n1; shifts[3 * e + 2] = n2;
-                xyz[3 * e] = d[0]; xyz[3 * e + 1] = d[1]; xyz[3 * e + 2] = d[2];
-                r[e] = __dsqrt_rn(r2);
-            }
+            if (lane == 0) num_neigh[i] = count;
+            continue;
         }
+        __syncwarp();
+        const bool in_smem = count <= kNeighRowCap;
+        for (int a = lane; a < count; a += 32) {
+            const unsigned long long key = in_smem ? row_keys[warp][a] : keys[row_begin + a];
+            int rank = 0;
+            for (int b = 0; b < count; ++b) rank += (in_smem ? row_keys[warp][b] : keys[row_begin + b]) < key ? 1 : 0;
+            const long long e = row_begin + rank;
+            const int j = static_cast<int>(key >> 32);
+            const unsigned int code = static_cast<unsigned int>(key & 0xffffffffu);
+            const int n2 = static_cast<int>(code % 1024) - 512, n1 = static_cast<int>((code / 1024) % 1024) - 512,
+                      n0 = static_cast<int>(code / (1024 * 1024)) - 512;
+            double d[3], r2;
+            neigh_test(g, xi, pos + 3 * j, n0, n1, n2, d, &r2);
+            neigh_indices[e] = j;
+            neigh_types[e] = types[j];
+            shifts[3 * e] = n0; shifts[3 * e + 1] = n1; shifts[3 * e + 2] = n2;
+            xyz[3 * e] = d[0]; xyz[3 * e + 1] = d[1]; xyz[3 * e + 2] = d[2];
+            r[e] = __dsqrt_rn(r2);
+        }
+        __syncwarp();
     }
 }
 
@@ -241,7 +261,8 @@ public:
         SMX_CUDA(cub::DeviceRadixSort::SortPairs(tmp.p, bytes, bin_of.p, sorted_bins.p, iota.p, sorted_atoms.p, n, 0, bits, stream));
         neigh_offsets_kernel<<<std::min(1024, (nbins + 128) / 128), 128, 0, stream>>>(n, sorted_bins.p, nbins, bin_start.p);
         launches += 2;
-        neigh_rows_kernel<true><<<blocks, 128, 0, stream>>>(n, dpos, d_types, g, bin_start.p, sorted_atoms.p, wrap.p, overflow.p, num_neigh.p, nullptr, nullptr,
+        const int row_blocks = std::min(16384, (n + kNeighWarps - 1) / kNeighWarps);      // one warp per atom
+        neigh_rows_kernel<true><<<row_blocks, kNeighWarps * 32, 0, stream>>>(n, dpos, d_types, g, bin_start.p, sorted_atoms.p, wrap.p, overflow.p, num_neigh.p, nullptr, nullptr,
                                                           nullptr, nullptr, nullptr, nullptr, nullptr);
         launches += 1;
         first.resize(static_cast<size_t>(n) + 1, stream);
@@ -263,7 +284,7 @@ public:
         neigh_indices.resize(total, stream); neigh_types.resize(total, stream); shifts.resize(3 * total, stream);
         xyz.resize(3 * total, stream); r.resize(total, stream);
         if (total > 0) {
-            neigh_rows_kernel<false><<<blocks, 128, 0, stream>>>(n, dpos, d_types, g, bin_start.p, sorted_atoms.p, wrap.p, overflow.p, nullptr, first.p, keys.p,
+            neigh_rows_kernel<false><<<row_blocks, kNeighWarps * 32, 0, stream>>>(n, dpos, d_types, g, bin_start.p, sorted_atoms.p, wrap.p, overflow.p, nullptr, first.p, keys.p,
                                                                neigh_indices.p, neigh_types.p, shifts.p, xyz.p, r.p);
             launches += 1;
         }
