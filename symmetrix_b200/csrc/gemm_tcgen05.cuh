@@ -809,13 +809,16 @@ __global__ void __launch_bounds__(kRnThreads, 1) tp_reverse_rnet_kernel(const TP
                 const int e = 2 * group + t;
                 if (e < nb) {       // uniform over the warp
                     const RnEdgeRev& s = st[buf * kRnRevEdges + e];
-                    float W[kNumLm], fr = 0.f;
+                    float W[kNumLm], fr;
+                    if (!active) {
 #pragma unroll
-                    for (int lm = 0; lm < kNumLm; ++lm) W[lm] = 0.f;
+                        for (int lm = 0; lm < kNumLm; ++lm) W[lm] = 0.f;
+                        fr = 0.f;
+                    }
                     if (active) {
                         float h[tp.nLM], msg[tp.nLM], R[tp.P], Rd[tp.P], Y[kNumLm];
 #pragma unroll
-                        for (int lm2 = 0; lm2 < tp.nLM; ++lm2) { h[lm2] = hq[t][lm2]; msg[lm2] = 0.f; }
+                        for (int lm2 = 0; lm2 < tp.nLM; ++lm2) h[lm2] = hq[t][lm2];
 #pragma unroll
                         for (int p = 0; p < tp.P; ++p) { R[p] = __uint_as_float(Rq[p][t]); Rd[p] = __uint_as_float(Rq[p][2 + t]); }
 #pragma unroll

@@ -590,9 +590,7 @@ __global__ void __launch_bounds__(kChannelBlock, tp_min_blocks<T>(LF, true)) tp_
             }
             for (int e = 0; e < nb; ++e) {
                 const EdgeStage<T>& s = st[e];
-                T W[kNumLm], fr = 0;
-#pragma unroll
-                for (int lm = 0; lm < kNumLm; ++lm) W[lm] = T(0);
+                T W[kNumLm], fr;      // assigned by the generated code (first contribution of each entry), zero for idle lanes
                 const int sl = e & 1;
                 T R[tp.P], Rd[tp.P];
                 if constexpr (STAGED) {
@@ -624,7 +622,7 @@ __global__ void __launch_bounds__(kChannelBlock, tp_min_blocks<T>(LF, true)) tp_
                     const T* hrow = a.H + static_cast<size_t>(s.j) * tp.nLM * a.K + k;
                     T h[tp.nLM], msg[tp.nLM], Y[kNumLm];
 #pragma unroll
-                    for (int lm2 = 0; lm2 < tp.nLM; ++lm2) { h[lm2] = __ldg(hrow + static_cast<size_t>(lm2) * a.K); msg[lm2] = T(0); }
+                    for (int lm2 = 0; lm2 < tp.nLM; ++lm2) h[lm2] = __ldg(hrow + static_cast<size_t>(lm2) * a.K);
                     if constexpr (!STAGED) {
                         if (a.R_edge) {
                             const T* re = a.R_edge + static_cast<size_t>(e0 + e) * F + k;
@@ -666,6 +664,10 @@ __global__ void __launch_bounds__(kChannelBlock, tp_min_blocks<T>(LF, true)) tp_
 #endif
                         for (int lm2 = 0; lm2 < tp.nLM; ++lm2) atomicAdd(arow + static_cast<size_t>(lm2) * a.K, msg[lm2]);
                     }
+                } else {
+#pragma unroll
+                    for (int lm = 0; lm < kNumLm; ++lm) W[lm] = T(0);
+                    fr = T(0);
                 }
                 int idx;
                 const T wsum = warp_reduce_scatter16(W, lane, idx);
@@ -770,9 +772,11 @@ __global__ void __launch_bounds__(kChannelBlock, MINB) tp_reverse_tmem_kernel(co
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     // this thread's lane: 32 * (warp % 4) + lane, in bits 16.. of the address (a warp reaches the 32 lanes of its quadrant)
     const uint32_t tbase = tmem_slot + (static_cast<uint32_t>((warp & 3) * 32) << 16);
-    uint32_t stage[16];
+    // two sets of staging registers, used by the paths of even and odd index: the set a path has just consumed is dead
+    // until the path after the next one refills it, so its registers can become the path's double-precision values in place
+    uint32_t stage0[16], stage1[16];
 #pragma unroll
-    for (int q = 0; q < 16; ++q) stage[q] = 0u;
+    for (int q = 0; q < 16; ++q) { stage0[q] = 0u; stage1[q] = 0u; }
 
     for (int slot = blockIdx.x; slot < a.N; slot += gridDim.x)
     for (int kc = 0; kc < a.K; kc += blockDim.x) {
@@ -793,7 +797,7 @@ __global__ void __launch_bounds__(kChannelBlock, MINB) tp_reverse_tmem_kernel(co
             }
         });
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-        tmem_ld_issue<tp_tmem_width(tp.l[0])>(tbase + tp_tmem_col(tp, 0), stage);      // path 0 of the first edge
+        tmem_ld_issue<tp_tmem_width(tp.l[0])>(tbase + tp_tmem_col(tp, 0), stage0);     // path 0 of the first edge
         for (long long e0 = e_begin; e0 < e_end; e0 += EB) {
             const int nb = static_cast<int>(e_end - e0 < EB ? e_end - e0 : EB);
             __syncthreads();
@@ -802,15 +806,13 @@ __global__ void __launch_bounds__(kChannelBlock, MINB) tp_reverse_tmem_kernel(co
             __syncthreads();
             for (int e = 0; e < nb; ++e) {
                 const EdgeStage<T>& s = st[e];
-                T W[kNumLm], fr = 0;
-#pragma unroll
-                for (int lm = 0; lm < kNumLm; ++lm) W[lm] = T(0);
+                T W[kNumLm], fr;      // assigned by the generated code (first contribution of each entry)
                 T R[tp.P], Rd[tp.P];
                 const T x = s.x;
                 const T* hrow = a.H + static_cast<size_t>(s.j) * tp.nLM * a.K + k;
                 T h[tp.nLM], msg[tp.nLM], Y[kNumLm];
 #pragma unroll
-                for (int lm2 = 0; lm2 < tp.nLM; ++lm2) { h[lm2] = __ldg(hrow + static_cast<size_t>(lm2) * a.K); msg[lm2] = T(0); }
+                for (int lm2 = 0; lm2 < tp.nLM; ++lm2) h[lm2] = __ldg(hrow + static_cast<size_t>(lm2) * a.K);
                 const T* cb = a.coef1 + s.coef_base;
 #pragma unroll
                 for (int p = 0; p < tp.P; ++p) {
@@ -824,9 +826,13 @@ __global__ void __launch_bounds__(kChannelBlock, MINB) tp_reverse_tmem_kernel(co
                 // into dp and the fetch of the next path (path 0 again after the last: the adjoint belongs to the receiver,
                 // not to the edge) starts before path p is computed.
 #define TP_PATH_D(p, n, dp)                                                                                   \
-                tmem_ld_wait(stage);                                                                          \
-                _Pragma("unroll") for (int m_ = 0; m_ < (n); ++m_) dp[m_] = __hiloint2double(static_cast<int>(stage[2 * m_ + 1]), static_cast<int>(stage[2 * m_])); \
-                tmem_ld_issue<tp_tmem_width(tp.l[((p) + 1) % tp.P])>(tbase + tp_tmem_col(tp, ((p) + 1) % tp.P), stage);
+                {                                                                                             \
+                    uint32_t (&cur_)[16] = ((p) & 1) ? stage1 : stage0;                                       \
+                    uint32_t (&nxt_)[16] = ((((p) + 1) % tp.P) & 1) ? stage1 : stage0;                        \
+                    tmem_ld_wait(cur_);                                                                       \
+                    _Pragma("unroll") for (int m_ = 0; m_ < (n); ++m_) dp[m_] = __hiloint2double(static_cast<int>(cur_[2 * m_ + 1]), static_cast<int>(cur_[2 * m_])); \
+                    tmem_ld_issue<tp_tmem_width(tp.l[((p) + 1) % tp.P])>(tbase + tp_tmem_col(tp, ((p) + 1) % tp.P), nxt_); \
+                }
                 if constexpr (LF == 0) {
 #include "generated/tp_L0_reverse_bypath.inc"
                 } else if constexpr (LF == 1) {
@@ -854,7 +860,7 @@ __global__ void __launch_bounds__(kChannelBlock, MINB) tp_reverse_tmem_kernel(co
                                          a.node_forces + 3 * (e0 + e));
             }
         }
-        tmem_ld_wait(stage);      // the fetch started after the last path of the last edge: nothing may be in flight when d is rewritten
+        tmem_ld_wait(stage0);     // the fetch started after the last path of the last edge: nothing may be in flight when d is rewritten
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -1026,8 +1032,17 @@ __global__ void sender_gather_kernel(int rows, int width, const long long* __res
     for (int j = blockIdx.x; j < rows; j += gridDim.x) {
         const long long b = in_ptr[j], e = in_ptr[j + 1];
         for (int c = threadIdx.x; c < width; c += blockDim.x) {
+            // eight rows in flight per thread; the additions stay in list order
             T acc = 0;
-            for (long long n = b; n < e; ++n) acc += __ldcs(Hmsg + static_cast<size_t>(in_edge[n]) * width + c);
+            long long n = b;
+            for (; n + 8 <= e; n += 8) {
+                T v[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) v[u] = __ldcs(Hmsg + static_cast<size_t>(in_edge[n + u]) * width + c);
+#pragma unroll
+                for (int u = 0; u < 8; ++u) acc += v[u];
+            }
+            for (; n < e; ++n) acc += __ldcs(Hmsg + static_cast<size_t>(in_edge[n]) * width + c);
             H_adj[static_cast<size_t>(j) * width + c] += acc;
         }
     }

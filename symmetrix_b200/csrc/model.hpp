@@ -44,6 +44,8 @@ struct PolyProgram {
     std::vector<int> words;
     int num_monomials = 0;
     int num_leaves = 0, num_pairs = 0;
+    std::vector<int> alias;      // alias[mu]: the monomial whose coefficient row the program reads for monomial mu (mu itself
+                                 // unless the list repeats a monomial: then the first occurrence, whose row must hold the sum)
 };
 
 inline int poly_word(int kind, int q, int mu) { return kind | (q << 3) | ((mu + 1) << 8); }
@@ -52,21 +54,25 @@ inline PolyProgram compile_polynomial(const std::vector<std::vector<int>>& monom
     struct Pair { int mu = -1; std::vector<std::pair<int, int>> leaves; };
     struct Head { int mu = -1; std::map<int, Pair> pairs; };
     std::map<int, Head> heads;
+    std::vector<int> alias(monomials.size());
     for (size_t mu = 0; mu < monomials.size(); ++mu) {
+        alias[mu] = static_cast<int>(mu);
         std::vector<int> m = monomials[mu];
         std::sort(m.begin(), m.end());
         if (m.empty() || m.size() > 3) throw UnsupportedError("symmetric contraction: monomial degree must be 1..3");
         for (int q : m)
             if (q < 0 || q >= num_vars) throw ModelError("symmetric contraction: variable index out of range");
         Head& h = heads[m[0]];
-        if (m.size() == 1) { if (h.mu < 0) h.mu = static_cast<int>(mu); continue; }
+        if (m.size() == 1) { if (h.mu < 0) h.mu = static_cast<int>(mu); else alias[mu] = h.mu; continue; }
         Pair& p = h.pairs[m[1]];
-        if (m.size() == 2) { if (p.mu < 0) p.mu = static_cast<int>(mu); continue; }
+        if (m.size() == 2) { if (p.mu < 0) p.mu = static_cast<int>(mu); else alias[mu] = p.mu; continue; }
         bool dup = false;
-        for (auto& lf : p.leaves) dup = dup || (lf.first == m[2]);
+        for (auto& lf : p.leaves)
+            if (lf.first == m[2]) { dup = true; alias[mu] = lf.second; }
         if (!dup) p.leaves.emplace_back(m[2], static_cast<int>(mu));
     }
     PolyProgram prog;
+    prog.alias = alias;
     prog.num_monomials = static_cast<int>(monomials.size());
     for (auto& [q1, h] : heads) {
         prog.words.push_back(poly_word(kPolyHeadBegin, q1, h.mu));
@@ -546,7 +552,8 @@ inline HostModel load_model_file(const std::string& filename) {
                     const JsonValue& wk = wl.at(std::to_string(k));
                     if (static_cast<int>(wk.size()) != nm) throw ModelError(std::string(weight_key) + " row length differs from " + mono_key);
                     for (int mu = 0; mu < nm; ++mu) {
-                        coef[(size_t(a) * num_mono + mono_off[lm] + mu) * K + k] = wk.nums[mu];
+                        // a monomial listed twice contributes the sum of its coefficients (as the reference's product DAG does)
+                        coef[(size_t(a) * num_mono + mono_off[lm] + prog[prog.size() - m.num_LM + lm].alias[mu]) * K + k] += wk.nums[mu];
                         if (slots0[lm][mu] >= 0)
                             coef_canon[(size_t(a) * num_canon + kCanonPolyOffset[lm] + slots0[lm][mu]) * K + k] += wk.nums[mu];
                     }
@@ -573,7 +580,7 @@ inline HostModel load_model_file(const std::string& filename) {
                 const JsonValue& wk = wa.at(std::to_string(k));
                 if (static_cast<int>(wk.size()) != m.num_mono1) throw ModelError("M1_weights row length differs from M1_monomials");
                 for (int mu = 0; mu < m.num_mono1; ++mu) {
-                    m.coef_M1[(size_t(a) * m.num_mono1 + mu) * K + k] = wk.nums[mu];
+                    m.coef_M1[(size_t(a) * m.num_mono1 + m.prog1.alias[mu]) * K + k] += wk.nums[mu];
                     if (slots1[mu] >= 0) m.coef_M1_canon[(size_t(a) * m.num_canon1 + slots1[mu]) * K + k] += wk.nums[mu];
                 }
             }

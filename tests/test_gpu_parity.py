@@ -355,15 +355,16 @@ def test_cpp_facade_replays_pair_style_compute(tiny, tmp_path):
 @pytest.mark.parametrize("dtype", ["float64", "float32"])
 def test_models_with_unusual_monomials_use_the_table_driven_contraction(tiny, tmp_path, dtype):
     """A model file whose monomial lists are not the symmetry-complete ones (here: extra, symmetry-breaking monomials in
-    both contractions) cannot use the generated straight-line contraction code and runs the interpreter instead."""
+    both contractions, one of them listed twice with its variables in another order: its two coefficients add up, as in the
+    reference's product DAG) cannot use the generated straight-line contraction code and runs the interpreter instead."""
     import json
     _, inputs = tiny
     model = json.loads((GOLDEN / "tiny_model.json").read_text())
     rng = np.random.default_rng(5)
-    model["M1_monomials"] = model["M1_monomials"] + [[1], [2, 7], [0, 3, 11]]
+    model["M1_monomials"] = model["M1_monomials"] + [[1], [2, 7], [0, 3, 11], [7, 2], [11, 0, 3]]
     for a in model["M1_weights"]:
         for k in model["M1_weights"][a]:
-            model["M1_weights"][a][k] = model["M1_weights"][a][k] + (0.3 * rng.standard_normal(3)).tolist()
+            model["M1_weights"][a][k] = model["M1_weights"][a][k] + (0.3 * rng.standard_normal(5)).tolist()
     model["M0_monomials"]["2"] = model["M0_monomials"]["2"] + [[5, 5]]
     for a in model["M0_weights"]:
         for k in model["M0_weights"][a]["2"]:
