@@ -219,6 +219,16 @@ int smx_halo_unpack(smx_handle h, const char* name, const int* rows, int n, cons
 int smx_halo_unpack_add(smx_handle h, const char* name, const int* rows, int n, const void* buf);
 int smx_atom_forces(smx_handle h, int num_rows);
 
+/* Model loading with a binary side-car. MACE::load_from_json (mace.cpp:905-1030) parses the JSON text on every start;
+ * smx_create does that once per model file and then reads `<file>.smxcache`, the parsed and re-laid-out tables, written
+ * next to the file (a 314 MB file: 3.3 s of parsing against a fraction of a second). The side-car is valid only for the
+ * exact source file (size, modification time) and the exact build of this library, is rewritten when either changes,
+ * and is never required: without write permission, or with SMX_MODEL_CACHE=0 in the environment, the text is parsed.
+ * smx_model_digest loads a model file (through the side-car when `use_cache` is non-zero) and returns a 64-bit FNV-1a
+ * digest of everything the loader produced, so that a caller -- or a test -- can check that both routes give the same
+ * model; `from_cache` (may be NULL) tells which route was taken. It needs no GPU. */
+int smx_model_digest(const char* json_path, int use_cache, unsigned long long* digest, int* from_cache);
+
 /* Halo exchange between the ranks of a decomposed run, inside the library: what LAMMPS' Comm does for the reference's
  * message-passing mode (comm->forward_comm(this) / comm->reverse_comm(this), pair_symmetrix_mace.cpp:470,489, with the pack /
  * unpack routines above) as grouped ncclSend / ncclRecv on the evaluator's stream. NCCL is loaded at run time

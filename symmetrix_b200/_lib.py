@@ -23,7 +23,7 @@ EXPORTED_SYMBOLS = [
     "smx_timer_start", "smx_timer_stop", "smx_set_profiling", "smx_stage_time", "smx_measure_fma_peak", "smx_measure_row_stream", "smx_validate_inputs",
     "smx_energy_virial_noalloc", "smx_sync", "smx_set_stream", "smx_restrict_nodes", "smx_set_active_nodes", "smx_resize_rows", "smx_device_ptr",
     "smx_halo_pack", "smx_halo_unpack", "smx_halo_unpack_add", "smx_atom_forces", "smx_active_counts", "smx_debug_expire_waits",
-    "smx_comm_unique_id", "smx_comm_init", "smx_comm_destroy", "smx_halo_exchange", "smx_allreduce_sum",
+    "smx_comm_unique_id", "smx_comm_init", "smx_comm_destroy", "smx_halo_exchange", "smx_allreduce_sum", "smx_model_digest",
 ]
 
 
@@ -95,6 +95,7 @@ def load():
     lib.smx_comm_destroy.argtypes = [vp]
     lib.smx_halo_exchange.argtypes = [vp, ctypes.c_char_p, ctypes.c_int, ctypes.c_int, ip, vp, ip, vp, ip]
     lib.smx_allreduce_sum.argtypes = [vp, dp, ctypes.c_int]
+    lib.smx_model_digest.argtypes = [ctypes.c_char_p, ctypes.c_int, ctypes.POINTER(ctypes.c_ulonglong), ctypes.POINTER(ctypes.c_int)]
     lib.smx_energy_virial_noalloc.argtypes = [dp, ctypes.c_int, dp, dp, ctypes.c_long, dp, vp, ctypes.c_char_p, ctypes.c_int]
     _lib = lib
     return lib

@@ -10,6 +10,7 @@
 #include "../../include/symmetrix_b200.h"
 #include "common.cuh"
 #include "evaluator_base.hpp"
+#include "model_cache.hpp"
 #include "nccl_transport.hpp"
 
 // =================================================================================================
@@ -53,7 +54,7 @@ int smx_create(const char* json_path, int precision, int device, smx_handle* out
         if (!json_path) throw smx::ArgError("smx_create: null path");
         if (precision != SMX_FP32 && precision != SMX_FP64) throw smx::ArgError("smx_create: precision must be 32 or 64");
         // the model is read and validated first, so a bad file is reported as such on any machine
-        smx::HostModel m = smx::load_model_file(json_path);
+        smx::HostModel m = smx::load_model_cached(json_path);
         int count = 0;
         if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0) {
             cudaGetLastError();
@@ -171,6 +172,19 @@ int smx_halo_unpack_add(smx_handle h, const char* name, const int* rows, int n, 
         e.halo_unpack(name, rows, n, src, true);
     });
 }
+int smx_model_digest(const char* json_path, int use_cache, unsigned long long* digest, int* from_cache) {
+    try {
+        if (!json_path || !digest) throw smx::ArgError("smx_model_digest: null argument");
+        bool hit = false;
+        smx::HostModel m = use_cache ? smx::load_model_cached(json_path, &hit) : smx::load_model_file(json_path);
+        *digest = smx::model_digest(m);
+        if (from_cache) *from_cache = hit ? 1 : 0;
+        return SMX_OK;
+    } catch (const smx::ArgError& e) { g_create_error = e.what(); return SMX_ERR_INVALID_ARGUMENT;
+    } catch (const smx::UnsupportedError& e) { g_create_error = e.what(); return SMX_ERR_UNSUPPORTED;
+    } catch (const std::exception& e) { g_create_error = e.what(); return SMX_ERR_MODEL; }
+}
+
 int smx_comm_unique_id(void* id, int id_bytes) {
     try {
         if (!id || id_bytes != static_cast<int>(sizeof(smx::NcclApi::UniqueId))) throw smx::ArgError("smx_comm_unique_id: the id buffer must hold 128 bytes");

@@ -308,6 +308,53 @@ def test_calculator_matches_oracle_energy_forces_stress(model_file):
     np.testing.assert_allclose(res["stress"], voigt, atol=1e-10)
 
 
+def test_ase_calculator_class_with_a_stand_in_for_ase(model_file, monkeypatch):
+    """``symmetrix_b200.ase_calculator.Symmetrix`` has the constructor and results of the reference's ASE calculator
+    (symmetrix_calc.py:23-102). ASE is not installed here, so the test supplies the two names the module imports from it
+    (a ``Calculator`` base class that stores the atoms, and ``all_changes``) and an ``Atoms`` stand-in with the getters
+    used; the physics is checked against the array-based calculator."""
+    import importlib
+    import sys
+    import types
+
+    class Calculator:
+        def __init__(self, **kwargs):
+            self.results, self.atoms = {}, None
+
+        def calculate(self, atoms=None, properties=None, system_changes=None):
+            self.atoms = atoms
+
+    mods = {name: types.ModuleType(name) for name in ("ase", "ase.calculators", "ase.calculators.calculator")}
+    mods["ase.calculators.calculator"].Calculator = Calculator
+    mods["ase.calculators.calculator"].all_changes = ["positions", "numbers", "cell", "pbc"]
+    for name, mod in mods.items():
+        monkeypatch.setitem(sys.modules, name, mod)
+    sys.modules.pop("symmetrix_b200.ase_calculator", None)
+    ase_calc = importlib.import_module("symmetrix_b200.ase_calculator")
+
+    class Atoms:
+        def __init__(self, s):
+            self.s = s
+        def get_positions(self): return self.s.positions
+        def get_cell(self): return self.s.cell
+        def get_atomic_numbers(self): return self.s.numbers
+        def get_pbc(self): return self.s.pbc
+
+    path, model, spec = model_file("fcc128", num_channels=32, num_spline_points=32)
+    s = st.fcc_box(3, 3.6, model["atomic_numbers"], seed=12, jitter=0.1)
+    with pytest.raises(ValueError):
+        ase_calc.Symmetrix(path, dtype="float16")
+    calc = ase_calc.Symmetrix(path, dtype="float64", use_kokkos=True)
+    assert calc.cutoff == spec.r_cut and set(calc.implemented_properties) == {"energy", "free_energy", "energies", "forces", "stress"}
+    calc.calculate(Atoms(s), ["energy", "forces", "stress"])
+    want = Symmetrix(path).calculate(s.positions, s.cell, s.numbers, s.pbc)
+    assert calc.results["energy"] == want["energy"] == calc.results["free_energy"]
+    np.testing.assert_array_equal(calc.results["forces"], want["forces"])
+    np.testing.assert_array_equal(calc.results["stress"], want["stress"])
+    assert calc.results["energies"].shape == (s.num_atoms,)
+    sys.modules.pop("symmetrix_b200.ase_calculator", None)
+
+
 def test_error_reporting(tiny):
     _, inputs = tiny
     ev = MACE(GOLDEN / "tiny_model.json", dtype="float64")

@@ -232,3 +232,41 @@ def test_cpp_facade_compiles_and_reports_missing_device(tmp_path):
     if not _has_gpu():
         r = subprocess.run([str(exe), str(GOLDEN / "tiny_model.json"), "/dev/null", str(tmp_path / "o.bin")], capture_output=True, text=True)
         assert r.returncode == 1 and "no CPU path" in r.stderr
+
+
+def test_model_side_car_gives_the_same_model_and_follows_the_source_file(tmp_path, monkeypatch):
+    """`<file>.smxcache`: written at the first load, read at the next, identical content (digest over everything the loader
+    produces), invalidated when the source file changes, switched off by SMX_MODEL_CACHE=0. Runs without a GPU."""
+    import ctypes
+    import json
+    import os
+    import shutil
+    from symmetrix_b200 import _lib
+    lib = _lib.load()
+    path = tmp_path / "model.json"
+    shutil.copy(GOLDEN / "tiny_model.json", path)
+
+    def digest(use_cache):
+        d, hit = ctypes.c_ulonglong(0), ctypes.c_int(-1)
+        assert lib.smx_model_digest(str(path).encode(), int(use_cache), ctypes.byref(d), ctypes.byref(hit)) == _lib.SMX_OK
+        return d.value, hit.value
+
+    plain, _ = digest(False)
+    first, hit1 = digest(True)
+    second, hit2 = digest(True)
+    assert (hit1, hit2) == (0, 1) and plain == first == second
+    assert (tmp_path / "model.json.smxcache").is_file()
+    # a changed source file is parsed again (and gives another digest)
+    model = json.loads(path.read_text())
+    model["atomic_energies"][0] += 1.0
+    path.write_text(json.dumps(model))
+    os.utime(path, ns=(path.stat().st_atime_ns, path.stat().st_mtime_ns + 5_000_000_000))
+    changed, hit3 = digest(True)
+    assert hit3 == 0 and changed != plain
+    assert digest(True) == (changed, 1)
+    # a damaged side-car is ignored
+    side = tmp_path / "model.json.smxcache"
+    side.write_bytes(side.read_bytes()[: side.stat().st_size // 2])
+    assert digest(True) == (changed, 0)
+    monkeypatch.setenv("SMX_MODEL_CACHE", "0")
+    assert digest(True) == (changed, 0)
