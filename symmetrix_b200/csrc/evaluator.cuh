@@ -141,6 +141,7 @@ public:
     bool type_order = true;       // edge kernels walk the receivers in element-type order (SMX_TYPE_ORDER=0: natural order)
     bool waits_in_flight = false; // a kernel with bounded waits has been launched since the last status check
     bool use_tc5 = false;
+    bool gemm_async = true;       // float64 GEMMs with cp.async tile loads (SMX_GEMM=mma: the register-staged kernel)
     std::map<std::tuple<const void*, int, int, int, int>, std::unique_ptr<DevBuf<float>>> weight_images;
     cudaStream_t own_stream_handle = nullptr;
     NeighborBuilder nb;
@@ -178,6 +179,7 @@ public:
                 throw ArgError("SMX_RADIAL must be 'spline', 'mlp' or 'lowrank'");
             }
         }
+        if (const char* g = std::getenv("SMX_GEMM")) gemm_async = std::string(g) != "mma";
         if constexpr (sizeof(T) == 4) {
             // float32 GEMMs run on tcgen05 unless SMX_GEMM=mma asks for the mma.sync kernel
             const char* g = std::getenv("SMX_GEMM");
@@ -437,6 +439,19 @@ public:
             }
         }
         SMX_CUDA(cudaMemcpyAsync(dev_ring.p + ring_pos, host_ring + ring_pos, list.size() * sizeof(GemmProblem<T>), cudaMemcpyHostToDevice, stream));
+        if constexpr (sizeof(T) == 8) {
+            // asynchronous-copy kernel when every problem's rows, columns and leading dimension are 16-byte aligned
+            bool aligned = gemm_async;
+            for (const auto& q : list)
+                aligned = aligned && ((q.a_node_stride | q.a_off | q.a_sub_stride | q.ldb) & 1) == 0 &&
+                          (reinterpret_cast<uintptr_t>(q.A) & 15) == 0 && (reinterpret_cast<uintptr_t>(q.B) & 15) == 0;
+            if (aligned) {
+                gemm_rows_f64_async_kernel<<<grid, kGemmThreads, 0, stream>>>(dev_ring.p + ring_pos);
+                check_launch("gemm_rows_f64_async_kernel");
+                ring_pos += list.size();
+                return;
+            }
+        }
         gemm_rows_kernel<T><<<grid, kGemmThreads, 0, stream>>>(dev_ring.p + ring_pos);
         check_launch("gemm_rows_kernel");
         ring_pos += list.size();

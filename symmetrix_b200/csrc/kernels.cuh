@@ -1702,6 +1702,132 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_rows_kernel(const GemmProbl
     });
 }
 
+// float64 variant with asynchronous tile loads: the 64 x 16 tile of gathered A rows and the 16 x 64 tile of B go from
+// global to shared memory with 16-byte cp.async copies (no staging registers), two stages deep, so the copies of tile
+// t + 1 run while the DMMA instructions work on tile t and there is one barrier pair per tile instead of a
+// load - store - barrier sequence. Needs 16-byte aligned rows (even strides and offsets, even leading dimension); the
+// launch code falls back to gemm_rows_kernel otherwise. Out-of-range rows, columns and k values are zero-filled by the
+// copy's source-size operand.
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, int src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(smem)), "l"(gmem), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+static __global__ void __launch_bounds__(kGemmThreads) gemm_rows_f64_async_kernel(const GemmProblem<double>* __restrict__ problems) {
+    const GemmProblem<double> pb = problems[blockIdx.z];
+    int node_begin = 0, node_count = pb.num_nodes;
+    if (pb.seg) { node_begin = pb.seg[pb.seg_index]; node_count = pb.seg[pb.seg_index + 1] - node_begin; }
+    const long long M = static_cast<long long>(node_count) * pb.sub_count;
+    const long long row0 = static_cast<long long>(blockIdx.x) * kGemmBM;
+    const int col0 = blockIdx.y * kGemmBN;
+    if (row0 >= M || col0 >= pb.Nc) return;
+
+    constexpr int SA = GemmSmem<double>::SA, SB = GemmSmem<double>::SB;      // 20 and 68 doubles: rows start on 16-byte boundaries
+    constexpr int kBTile = kGemmBK * SB > kGemmBN * SA ? kGemmBK * SB : kGemmBN * SA;
+    __shared__ __align__(16) double As[2][kGemmBM * SA];
+    __shared__ __align__(16) double Bs[2][kBTile];          // [k][n] rows of SB, or for transposed B [n][k] rows of SA
+    __shared__ long long a_base[kGemmBM];
+    __shared__ long long c_base[kGemmBM];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int wm = warp >> 1, wn = warp & 1;
+    if (tid < kGemmBM) {
+        const long long r = row0 + tid;
+        if (r < M) {
+            const long long n = r / pb.sub_count;
+            const int sub = static_cast<int>(r - n * pb.sub_count);
+            const long long node = pb.perm ? pb.perm[node_begin + n] : (node_begin + n);
+            a_base[tid] = node * pb.a_node_stride + pb.a_off + sub * pb.a_sub_stride;
+            c_base[tid] = node * pb.c_node_stride + pb.c_off + sub * pb.c_sub_stride;
+        } else {
+            a_base[tid] = -1;
+            c_base[tid] = -1;
+        }
+    }
+    __syncthreads();
+
+    auto issue = [&](int stage, int k0) {
+        // A: 64 rows x 8 chunks of two doubles; B: 16 x 32 chunks (or 64 x 8 for transposed B): 4 + 4 chunks per thread
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+            const int lin = tid + it * kGemmThreads;
+            const int rr = lin >> 3, kk = (lin & 7) * 2;
+            const long long ab = a_base[rr];
+            const int left = pb.Kd - (k0 + kk);
+            const int bytes = ab >= 0 ? (left >= 2 ? 16 : (left == 1 ? 8 : 0)) : 0;
+            cp_async16(&As[stage][rr * SA + kk], pb.A + (bytes ? ab + k0 + kk : 0), bytes);
+        }
+        if (!pb.transB) {
+#pragma unroll
+            for (int it = 0; it < 4; ++it) {
+                const int lin = tid + it * kGemmThreads;
+                const int kb = lin >> 5, cc = (lin & 31) * 2;
+                const int left = pb.Nc - (col0 + cc);
+                const int bytes = (k0 + kb < pb.Kd) ? (left >= 2 ? 16 : (left == 1 ? 8 : 0)) : 0;
+                cp_async16(&Bs[stage][kb * SB + cc], pb.B + (bytes ? static_cast<size_t>(k0 + kb) * pb.ldb + col0 + cc : 0), bytes);
+            }
+        } else {
+#pragma unroll
+            for (int it = 0; it < 4; ++it) {
+                const int lin = tid + it * kGemmThreads;
+                const int cc = lin >> 3, kb = (lin & 7) * 2;
+                const int left = pb.Kd - (k0 + kb);
+                const int bytes = (col0 + cc < pb.Nc) ? (left >= 2 ? 16 : (left == 1 ? 8 : 0)) : 0;
+                cp_async16(&Bs[stage][cc * SA + kb], pb.B + (bytes ? static_cast<size_t>(col0 + cc) * pb.ldb + k0 + kb : 0), bytes);
+            }
+        }
+        cp_async_commit();
+    };
+
+    double c[4][4][2];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) c[i][j][0] = c[i][j][1] = 0.0;
+    const int num_tiles = (pb.Kd + kGemmBK - 1) / kGemmBK;
+    issue(0, 0);
+    for (int t = 0; t < num_tiles; ++t) {
+        const int stage = t & 1;
+        if (t + 1 < num_tiles) { issue(stage ^ 1, (t + 1) * kGemmBK); cp_async_wait<1>(); }
+        else cp_async_wait<0>();
+        __syncthreads();
+        const double* Asm = As[stage];
+        const double* Bsm = Bs[stage];
+#pragma unroll
+        for (int kk = 0; kk < kGemmBK; kk += 4) {
+            double a[4], b[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a[i] = Asm[(wm * 32 + i * 8 + (lane >> 2)) * SA + kk + (lane & 3)];
+            if (!pb.transB) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) b[j] = Bsm[(kk + (lane & 3)) * SB + wn * 32 + j * 8 + (lane >> 2)];
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) b[j] = Bsm[(wn * 32 + j * 8 + (lane >> 2)) * SA + kk + (lane & 3)];
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) dmma_m8n8k4(c[i][j][0], c[i][j][1], a[i], b[j]);
+        }
+        __syncthreads();      // this stage is refilled by the copies issued in the next iteration
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int r = wm * 32 + i * 8 + (lane >> 2), cidx = wn * 32 + j * 8 + 2 * (lane & 3) + e;
+                const long long cb = c_base[r];
+                const int col = col0 + cidx;
+                if (cb >= 0 && col < pb.Nc) {
+                    double* dst = pb.C + cb + col;
+                    *dst = pb.accumulate ? (*dst + c[i][j][e]) : c[i][j][e];
+                }
+            }
+}
+
 // =============================================================================================
 // Readouts (MACE::compute_readouts, mace.cpp:876-903 with MultilayerPerceptron::evaluate_gradient,
 // multilayer_perceptron.cpp:76-150, hidden width 16): one warp per node.

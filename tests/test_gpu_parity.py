@@ -111,6 +111,7 @@ def test_downsized_benchmark_models(model_file, dtype, name, channels, builder):
 
 @pytest.mark.parametrize("dtype,env", [
     ("float32", {"SMX_GEMM": "mma"}),           # mma.sync 3xTF32 GEMM instead of the tcgen05 kernel
+    ("float64", {"SMX_GEMM": "mma"}),           # register-staged DMMA GEMM instead of the cp.async one
     ("float64", {"SMX_TP_TMEM": "0"}),          # receiver adjoint of the tensor-product reverse in registers instead of tensor memory
     ("float64", {"SMX_TP_STAGED": "1"}),        # spline rows of the tensor-product reverse through TMA bulk copies
     ("float32", {"SMX_TP_STAGED": "1"}),
