@@ -122,6 +122,18 @@ def molecular_liquid(n_mol: int, density_g_cm3: float = 0.79, seed: int = 0, min
     return s
 
 
+def replicate(s: Structure, reps: tuple[int, int, int]) -> Structure:
+    """``reps`` periodic copies of the cell along its three lattice vectors; copy (a, b, c) holds atoms
+    ``((a * reps[1] + b) * reps[2] + c) * N ... + N`` in the order of ``s``. Every atom of the result has the environment of
+    its original, so energies and forces of a periodic evaluation repeat copy by copy."""
+    ra, rb, rc = (int(x) for x in reps)
+    shifts = np.stack(np.meshgrid(np.arange(ra), np.arange(rb), np.arange(rc), indexing="ij"), axis=-1).reshape(-1, 3)
+    offsets = shifts.astype(np.float64) @ s.cell
+    pos = (offsets[:, None, :] + s.positions[None, :, :]).reshape(-1, 3)
+    cell = s.cell * np.array([ra, rb, rc], dtype=np.float64)[:, None]
+    return Structure(pos, cell, np.tile(s.numbers, shifts.shape[0]), s.pbc)
+
+
 # --------------------------------------------------------------------------- neighbour list
 
 def _image_range(cell: np.ndarray, pbc, r_cut: float) -> list[int]:

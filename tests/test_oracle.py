@@ -123,6 +123,25 @@ def test_energy_is_rotation_invariant(tiny):
     np.testing.assert_allclose(f1.reshape(-1, 3), f0.reshape(-1, 3) @ rot.T, atol=1e-11)
 
 
+def test_periodic_copies_repeat_the_cell_answer():
+    """The property the full-size GPU tests rest on, here with the CPU restatement: a structure made of periodic copies
+    of a cell has the cell's per-atom energies and forces, copy by copy (`structures.replicate`)."""
+    o = MaceOracle(GOLDEN / "tiny_model.json")
+    numbers = json.loads((GOLDEN / "tiny_model.json").read_text())["atomic_numbers"]
+    cell = st.water_box(2, 7.0, seed=3)
+
+    def run(s):
+        nl = st.neighbor_list(s, o.r_cut)
+        inputs = st.evaluator_inputs(s, nl, numbers)
+        e, nf = o.compute_node_energies_forces(inputs)
+        return e, st.atom_forces_and_virial(inputs, nl, nf)[0]
+
+    e0, f0 = run(cell)
+    e1, f1 = run(st.replicate(cell, (2, 1, 3)))
+    np.testing.assert_allclose(e1.reshape(6, -1), np.broadcast_to(e0, (6, e0.size)), rtol=1e-11, atol=1e-12)
+    np.testing.assert_allclose(f1.reshape(6, -1, 3), np.broadcast_to(f0, (6,) + f0.shape), atol=1e-10)
+
+
 @pytest.mark.skipif(not ref_driver.available(), reason="oracle/_ref not built (needs the reference checkout)")
 def test_port_matches_compiled_reference_with_zbl_and_density_normalisation(model_file):
     path, model, spec = model_file("tiny", zbl=True, density=True)
