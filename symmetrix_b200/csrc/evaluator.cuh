@@ -103,6 +103,8 @@ public:
     const double *xyz = nullptr, *r = nullptr;
     DevBuf<long long> first_neigh, in_ptr;
     DevBuf<int> perm, sorted_types, type_seg, iota, in_edge, sorted_senders;
+    DevBuf<int> work_sched, work_counts, work_item_ptr, work_n_items;    // work distribution of the edge kernels (see work_first)
+    DevBuf<int4> work_items;
     DevBuf<unsigned char> cub_tmp;
     DevBuf<int> halo_iota, halo_rows, halo_pos;    // positions of an unpack-add list grouped by destination row
     int sender_rows = -1;
@@ -375,6 +377,26 @@ public:
         }
         segment_offsets_int_kernel<<<1, 128, 0, stream>>>(N, sorted_types.p, model.num_elements, type_seg.p);
         check_launch("type segments");
+        // work items of the reverse edge kernels: (receiver, batch of its edges) in the order the receivers are walked
+        work_sched.resize(2, stream);
+        work_sched.zero(stream);
+        work_n_items.resize(1, stream);
+        work_n_items.zero(stream);
+        work_counts.resize(static_cast<size_t>(N) + 1, stream);
+        work_item_ptr.resize(static_cast<size_t>(N) + 1, stream);
+        work_items.resize(static_cast<size_t>(N) + static_cast<size_t>(E) / kEdgeBatch + 1, stream);
+        if (N > 0) {
+            const int* order = type_order ? perm.p : nullptr;
+            work_items_count_kernel<<<(N + 255) / 256, 256, 0, stream>>>(N, order, first_neigh.p, work_counts.p);
+            check_launch("work_items_count_kernel");
+            size_t bytes = 0;
+            SMX_CUDA(cub::DeviceScan::ExclusiveSum(nullptr, bytes, work_counts.p, work_item_ptr.p, N, stream));
+            cub_tmp.resize(bytes, stream);
+            SMX_CUDA(cub::DeviceScan::ExclusiveSum(cub_tmp.p, bytes, work_counts.p, work_item_ptr.p, N, stream));
+            launches += 1;
+            work_items_fill_kernel<<<(N + 255) / 256, 256, 0, stream>>>(N, order, first_neigh.p, work_item_ptr.p, work_items.p, work_n_items.p);
+            check_launch("work_items_fill_kernel");
+        }
         // outputs the caller zero-fills in the reference (mace.cpp:27-30)
         if (keep) {
             // the arrays only ever grow and were zero-filled at their largest extent when the step began
@@ -495,6 +517,7 @@ public:
         a.node_types = node_types; a.first_neigh = first_neigh.p; a.neigh_indices = neigh_indices; a.neigh_types = neigh_types;
         a.xyz = xyz; a.r = r; a.coef0 = coef0.p; a.sm = sm; a.H0_w = H0_w.p; a.order = type_order ? perm.p : nullptr;
         a.Phi0 = Phi0.p; a.Phi0_adj = Phi0_adj.p; a.node_forces = node_forces.p;
+        a.sched = work_sched.p; a.items = work_items.p; a.n_items = work_n_items.p;
         return a;
     }
 
@@ -699,6 +722,7 @@ public:
         if (radial_mlp && which == 1 && !radial_in_kernel) { a.R_edge = R_edge.p; a.Rd_edge = Rd_edge.p; }
         a.status = kernel_status.p;
         a.order = type_order ? perm.p : nullptr;
+        a.sched = work_sched.p; a.items = work_items.p; a.n_items = work_n_items.p;
         return a;
     }
     template <int LF>
@@ -711,8 +735,8 @@ public:
                 constexpr int kCols = tp_tmem_cols(LF);
                 // Grid: the resident CTAs per SM the kernel is compiled for (its register budget and 36 KB of shared memory
                 // allow them; the occupancy query reports one CTA per SM for kernels that allocate tensor memory, although
-                // several such CTAs do share an SM, so it is not used here). CTAs beyond what fits simply start later: the
-                // receivers are split statically over the grid.
+                // several such CTAs do share an SM, so it is not used here). CTAs beyond what fits simply start later and
+                // find fewer work items left.
                 auto launch = [&](auto kern, int min_blocks) {
                     const int per_sm = std::max(1, std::min(min_blocks, 512 / kCols));
                     const int grid = static_cast<int>(std::max<long long>(1, std::min<long long>(static_cast<long long>(num_sms) * per_sm, N)));
