@@ -217,6 +217,13 @@ int smx_device_ptr(smx_handle h, const char* name, void** ptr, long* count, int*
 int smx_halo_pack(smx_handle h, const char* name, const int* rows, int n, void* buf);
 int smx_halo_unpack(smx_handle h, const char* name, const int* rows, int n, const void* buf);
 int smx_halo_unpack_add(smx_handle h, const char* name, const int* rows, int n, const void* buf);
+/* smx_halo_unpack_add (and smx_halo_exchange with add) first groups the list positions by destination row: a sort per
+ * call. LAMMPS rebuilds its send lists only when it re-neighbours (Comm::borders), and between those steps the pair
+ * style's unpack_reverse_comm sees the same list every time (pair_symmetrix_mace_kokkos.cpp:351-367). With enable != 0 the
+ * grouping of a list is kept and reused whenever a list with the same device address and length is passed again; the
+ * caller promises not to change such a list in place. enable = 0 drops all kept groupings and stops keeping them (call it
+ * when the lists are rebuilt, then enable again). Off by default. */
+int smx_halo_cache_lists(smx_handle h, int enable);
 int smx_atom_forces(smx_handle h, int num_rows);
 
 /* Model loading with a binary side-car. MACE::load_from_json (mace.cpp:905-1030) parses the JSON text on every start;

@@ -22,7 +22,7 @@ EXPORTED_SYMBOLS = [
     "smx_last_device_ms", "smx_launch_count", "smx_build_neighbors", "smx_get_edges", "smx_compute_current",
     "smx_timer_start", "smx_timer_stop", "smx_set_profiling", "smx_stage_time", "smx_measure_fma_peak", "smx_measure_row_stream", "smx_validate_inputs",
     "smx_energy_virial_noalloc", "smx_sync", "smx_set_stream", "smx_restrict_nodes", "smx_set_active_nodes", "smx_resize_rows", "smx_device_ptr",
-    "smx_halo_pack", "smx_halo_unpack", "smx_halo_unpack_add", "smx_atom_forces", "smx_active_counts", "smx_debug_expire_waits",
+    "smx_halo_pack", "smx_halo_unpack", "smx_halo_unpack_add", "smx_halo_cache_lists", "smx_atom_forces", "smx_active_counts", "smx_debug_expire_waits",
     "smx_comm_unique_id", "smx_comm_init", "smx_comm_destroy", "smx_halo_exchange", "smx_allreduce_sum", "smx_model_digest",
 ]
 
@@ -90,6 +90,7 @@ def load():
     lib.smx_atom_forces.argtypes = [vp, ctypes.c_int]
     lib.smx_active_counts.argtypes = [vp, ctypes.POINTER(ctypes.c_int), lp, ctypes.POINTER(ctypes.c_int)]
     lib.smx_debug_expire_waits.argtypes = [vp, ctypes.c_int]
+    lib.smx_halo_cache_lists.argtypes = [vp, ctypes.c_int]
     lib.smx_comm_unique_id.argtypes = [vp, ctypes.c_int]
     lib.smx_comm_init.argtypes = [vp, vp, ctypes.c_int, ctypes.c_int, ctypes.c_int]
     lib.smx_comm_destroy.argtypes = [vp]

@@ -215,6 +215,9 @@ int smx_allreduce_sum(smx_handle h, double* values, int n) {
 int smx_active_counts(smx_handle h, int* num_nodes, long* num_edges, int* built_nodes) {
     return guarded(h, [&](smx::EvaluatorBase& e) { e.active_counts(num_nodes, num_edges, built_nodes); });
 }
+int smx_halo_cache_lists(smx_handle h, int enable) {
+    return guarded(h, [&](smx::EvaluatorBase& e) { e.halo_cache_lists(enable); });
+}
 int smx_debug_expire_waits(smx_handle h, int polls) {
     return guarded(h, [&](smx::EvaluatorBase& e) { e.expire_waits(polls); });
 }

@@ -107,6 +107,10 @@ public:
     DevBuf<int4> work_items;
     DevBuf<unsigned char> cub_tmp;
     DevBuf<int> halo_iota, halo_rows, halo_pos;    // positions of an unpack-add list grouped by destination row
+    // smx_halo_cache_lists: groupings kept per (address, length) of an index list, for callers whose lists stay put
+    struct HaloGrouping { std::unique_ptr<DevBuf<int>> rows, pos; };
+    std::map<std::pair<const int*, int>, HaloGrouping> halo_groupings;
+    bool halo_cache = false;
     int sender_rows = -1;
     std::vector<long long> first_host;   // host copy of first_neigh for restrict_nodes (valid until the edge set changes)
     bool first_host_valid = false;
@@ -1418,24 +1422,48 @@ public:
         SMX_CUDA(cudaSetDevice(device));
         if (n < 0 || (n > 0 && (!rows || !src))) throw ArgError("halo_unpack: bad arguments");
         if (n == 0) return;
+        const int* grouped_rows = nullptr;
+        const int* grouped_pos = nullptr;
         if (add) {
             // group the list positions by destination row (stable), so each row is summed by one thread in list order
-            halo_iota.resize(n, stream); halo_rows.resize(n, stream); halo_pos.resize(n, stream);
-            iota_kernel<<<std::min(1024, (n + 255) / 256), 256, 0, stream>>>(n, halo_iota.p);
-            check_launch("iota");
-            size_t bytes = 0;
-            SMX_CUDA(cub::DeviceRadixSort::SortPairs(nullptr, bytes, rows, halo_rows.p, halo_iota.p, halo_pos.p, n, 0, 32, stream));
-            cub_tmp.resize(bytes, stream);
-            SMX_CUDA(cub::DeviceRadixSort::SortPairs(cub_tmp.p, bytes, rows, halo_rows.p, halo_iota.p, halo_pos.p, n, 0, 32, stream));
-            launches += 1;
+            DevBuf<int>* out_rows = &halo_rows;
+            DevBuf<int>* out_pos = &halo_pos;
+            bool have = false;
+            if (halo_cache) {
+                auto [it, fresh] = halo_groupings.try_emplace({rows, n});
+                if (fresh) { it->second.rows = std::make_unique<DevBuf<int>>(); it->second.pos = std::make_unique<DevBuf<int>>(); }
+                out_rows = it->second.rows.get(); out_pos = it->second.pos.get();
+                have = !fresh;
+            }
+            if (!have) {
+                halo_iota.resize(n, stream); out_rows->resize(n, stream); out_pos->resize(n, stream);
+                iota_kernel<<<std::min(1024, (n + 255) / 256), 256, 0, stream>>>(n, halo_iota.p);
+                check_launch("iota");
+                size_t bytes = 0;
+                SMX_CUDA(cub::DeviceRadixSort::SortPairs(nullptr, bytes, rows, out_rows->p, halo_iota.p, out_pos->p, n, 0, 32, stream));
+                cub_tmp.resize(bytes, stream);
+                SMX_CUDA(cub::DeviceRadixSort::SortPairs(cub_tmp.p, bytes, rows, out_rows->p, halo_iota.p, out_pos->p, n, 0, 32, stream));
+                launches += 1;
+            }
+            grouped_rows = out_rows->p; grouped_pos = out_pos->p;
         }
         with_halo_array(name, [&](auto* p, size_t, int width) {
             using U = std::remove_pointer_t<decltype(p)>;
             const long long total = static_cast<long long>(n) * width;
-            if (add) rows_scatter_add_kernel<U><<<copy_grid(total, num_sms), 256, 0, stream>>>(p, width, halo_rows.p, halo_pos.p, n, static_cast<const U*>(src));
+            if (add) rows_scatter_add_kernel<U><<<copy_grid(total, num_sms), 256, 0, stream>>>(p, width, grouped_rows, grouped_pos, n, static_cast<const U*>(src));
             else rows_scatter_kernel<U><<<copy_grid(total, num_sms), 256, 0, stream>>>(p, width, rows, total, static_cast<const U*>(src));
         });
         check_launch(add ? "rows_scatter_add_kernel" : "rows_scatter_kernel");
+    }
+    // Keep (enable != 0) or drop and stop keeping (0) the groupings of unpack-add index lists. A kept grouping is reused whenever
+    // a list of the same address and length comes again, so it is for callers whose lists do not change in place.
+    void halo_cache_lists(int enable) override {
+        SMX_CUDA(cudaSetDevice(device));
+        if (!enable) {
+            SMX_CUDA(cudaStreamSynchronize(stream));      // a kernel may still read a grouping about to be freed
+            halo_groupings.clear();
+        }
+        halo_cache = enable != 0;
     }
     // ------------------------------------------------------------------ halo exchange over NCCL (see nccl_transport.hpp)
     NcclApi::Comm comm = nullptr;

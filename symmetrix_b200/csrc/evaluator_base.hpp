@@ -42,6 +42,7 @@ public:
     virtual void halo_pack(const std::string& name, const int* rows, int n, void* dst) = 0;
     virtual void halo_unpack(const std::string& name, const int* rows, int n, const void* src, bool add) = 0;
     virtual void expire_waits(int polls) = 0;
+    virtual void halo_cache_lists(int enable) = 0;
     virtual void comm_init(const void* id, int id_bytes, int nranks, int rank) = 0;
     virtual void comm_destroy() = 0;
     virtual void halo_exchange(const std::string& name, bool add, int num_peers, const int* peers, const int* const* send_rows,

@@ -177,6 +177,9 @@ class SlabRank:
         self.shared_stream = self.device != "cpu" and hasattr(self.ev, "use_torch_stream")
         if self.shared_stream:
             self.ev.use_torch_stream(True)
+        if hasattr(self.ev, "halo_cache_lists"):
+            self.ev.halo_cache_lists(False)     # groupings kept for an earlier plan's lists (their addresses may come again)
+            self.ev.halo_cache_lists(True)      # send_idx / recv_idx live as long as this object and are never rewritten
         self.stage_ms = None          # set to {} to collect per-stage device times (adds a stream sync per stage)
 
     def _run(self, stage, *flags):

@@ -345,6 +345,11 @@ class MACE:
         self._check(self._lib.smx_active_counts(self._h, ctypes.byref(n), ctypes.byref(e), ctypes.byref(b)))
         return n.value, e.value, b.value
 
+    def halo_cache_lists(self, enable: bool) -> None:
+        """Keep (True) or drop (False) the per-list groupings of ``halo_unpack(add=True)`` / ``halo_exchange(add=True)``;
+        only for index lists that are not changed in place."""
+        self._check(self._lib.smx_halo_cache_lists(self._h, 1 if enable else 0))
+
     def debug_expire_waits(self, polls: int) -> None:
         """Test switch: make the first bounded wait of every float32 tensor-core GEMM CTA run out after `polls` polls."""
         self._check(self._lib.smx_debug_expire_waits(self._h, int(polls)))

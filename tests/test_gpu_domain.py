@@ -97,6 +97,55 @@ def test_decomposed_float64_evaluations_are_bitwise_reproducible(model_file):
             assert np.array_equal(a, b)
 
 
+def test_kept_groupings_of_unpack_add_lists(model_file):
+    """smx_halo_cache_lists: the grouping of an unpack-add index list is reused while the list stays at its address, gives
+    the same bits as a fresh grouping, and is dropped on request (here: before the list is rewritten in place)."""
+    import torch
+    path, model, spec = model_file("fcc128", num_channels=32, num_spline_points=32)
+    s = st.fcc_box(3, 3.6, model["atomic_numbers"], seed=4)
+    ev = MACE(path, dtype="float64")
+    nl = st.neighbor_list(s, ev.r_cut)
+    inp = st.evaluator_inputs(s, nl, ev.atomic_numbers)
+    ev.compute_node_energies_forces(inp["num_nodes"], inp["node_types"], inp["num_neigh"], inp["neigh_indices"], inp["neigh_types"],
+                                    inp["xyz"], inp["r"])
+    ev.atom_forces(s.num_atoms)
+    ev.use_torch_stream(True)          # the tensor operations below and the evaluator's kernels in one stream order
+    rng = np.random.default_rng(0)
+    dev = f"cuda:{ev.info.device}"
+    rows = torch.as_tensor(rng.integers(0, s.num_atoms, size=500).astype(np.int32), device=dev)      # rows repeat
+    buf = torch.as_tensor(rng.normal(size=(500, 3)), device=dev)
+
+    def apply(n_times):
+        base = ev.device_view("atom_forces").view(-1, 3)[: s.num_atoms]
+        start = base.clone()
+        for _ in range(n_times):
+            ev.halo_unpack("atom_forces", rows, buf, add=True)
+        out = base.clone()
+        base.copy_(start)
+        return start.cpu().numpy(), out.cpu().numpy()
+
+    launches0 = ev.launch_count
+    start, plain = apply(2)
+    per_call = (ev.launch_count - launches0) // 2
+    ev.halo_cache_lists(True)
+    launches0 = ev.launch_count
+    _, kept = apply(2)
+    assert np.array_equal(kept, plain)
+    assert ev.launch_count - launches0 < 2 * per_call            # the second call skipped the sort
+    expect = start.copy()
+    for _ in range(2):
+        np.add.at(expect, rows.cpu().numpy(), buf.cpu().numpy())
+    np.testing.assert_allclose(kept, expect, rtol=0, atol=1e-12)
+    # rewrite the list in place: drop the kept grouping first
+    ev.halo_cache_lists(False)
+    rows.copy_(torch.as_tensor(rng.integers(0, s.num_atoms, size=500).astype(np.int32), device=dev))
+    ev.halo_cache_lists(True)
+    start, again = apply(1)
+    expect = start.copy()
+    np.add.at(expect, rows.cpu().numpy(), buf.cpu().numpy())
+    np.testing.assert_allclose(again, expect, rtol=0, atol=1e-12)
+
+
 def _write_vec(f, a, dt):
     a = np.ascontiguousarray(a, dtype=dt).reshape(-1)
     f.write(np.int64(a.size).tobytes()); f.write(a.tobytes())
