@@ -189,8 +189,8 @@ def roofline_for(stage: str, ms: float, n_atoms: int, n_edges: int, K: int, L_ma
     # dram__bytes_read.sum + dram__bytes_write.sum per edge from the ncu captures summarised in
     # profiles/tp_reverse_tmem_fcc1372_fp64.md and profiles/edge_kernels_fcc1372_fp64.md (a smaller box of the same
     # construction; traffic grows with the edge count)
-    per_edge = {("tp_reverse_tmem_kernel", 8): 8530.0, ("tp_forward_kernel", 8): 2812.0,
-                ("layer0_reverse_kernel", 8): 638.0, ("layer0_forward_kernel", 8): 405.0}.get((kernel, dtype_bytes))
+    per_edge = {("tp_reverse_tmem_kernel", 8): 6527.0, ("tp_forward_kernel", 8): 2985.0,
+                ("layer0_reverse_kernel", 8): 654.0, ("layer0_forward_kernel", 8): 405.0}.get((kernel, dtype_bytes))
     traffic = per_edge * n_edges if per_edge and K == 128 and L_max == 1 else None
     return {"bound": "hbm", "kernel": kernel, "stage": stage, "achieved": achieved, "peak": peak, "unit": "GB/s",
             "frac": achieved / peak, "peak_source": f"of {how}", "traffic": traffic, "launch_ms": ms,

@@ -1389,7 +1389,7 @@ public:
         const int srows = sender_rows;
         atom_f.resize(3 * static_cast<size_t>(srows), stream);
         if (srows > 0) {
-            atom_forces_kernel<<<std::min((srows + 127) / 128, num_sms * 16), 128, 0, stream>>>(srows, N, first_neigh.p, in_ptr.p, in_edge.p,
+            atom_forces_kernel<<<std::min((srows + 3) / 4, num_sms * 16), 128, 0, stream>>>(srows, N, first_neigh.p, in_ptr.p, in_edge.p,
                                                                                               node_forces.p, atom_f.p);
             check_launch("atom_forces_kernel");
         }
@@ -1554,7 +1554,7 @@ public:
             out7.resize(7, stream);
             energy_virial_partial_kernel<<<blocks, 256, 0, stream>>>(N, E, node_energies.p, xyz, node_forces.p, partials.p);
             check_launch("energy_virial_partial_kernel");
-            energy_virial_final_kernel<<<1, 32, 0, stream>>>(blocks, partials.p, out7.p);
+            energy_virial_final_kernel<<<1, 7 * 32, 0, stream>>>(blocks, partials.p, out7.p);
             check_launch("energy_virial_final_kernel");
             if (energy) SMX_CUDA(cudaMemcpyAsync(energy, out7.p, sizeof(double), kind, stream));
             if (virial) SMX_CUDA(cudaMemcpyAsync(virial, out7.p + 1, 6 * sizeof(double), kind, stream));

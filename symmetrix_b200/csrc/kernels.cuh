@@ -2158,17 +2158,26 @@ __global__ void convert_kernel(long long n, const S* __restrict__ src, D* __rest
 // Per-atom forces from per-edge partial forces, without atomics:
 //   f[i] = - sum_{e in row i} nf[e] + sum_{e in in_edges(i)} nf[e]
 // (pair_symmetrix/pair_symmetrix_mace.cpp:334-347; symmetrix_calc.py:93-97)
+// One warp per atom: lane l takes the edges l, l + 32, ... of the atom's own row and of its incoming list in order, and the
+// lanes are combined by a fixed shuffle tree (same bits on every run).
 static __global__ void atom_forces_kernel(int rows, int N, const long long* __restrict__ first_neigh, const long long* __restrict__ in_ptr,
                                    const int* __restrict__ in_edge, const double* __restrict__ nf, double* __restrict__ f) {
-    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < rows; i += gridDim.x * blockDim.x) {
+    const int lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    for (int i = blockIdx.x * warps + (threadIdx.x >> 5); i < rows; i += gridDim.x * warps) {
         double fx = 0, fy = 0, fz = 0;
         if (i < N)
-            for (long long e = first_neigh[i]; e < first_neigh[i + 1]; ++e) { fx -= nf[3 * e]; fy -= nf[3 * e + 1]; fz -= nf[3 * e + 2]; }
-        for (long long n = in_ptr[i]; n < in_ptr[i + 1]; ++n) {
+            for (long long e = first_neigh[i] + lane; e < first_neigh[i + 1]; e += 32) { fx -= nf[3 * e]; fy -= nf[3 * e + 1]; fz -= nf[3 * e + 2]; }
+        for (long long n = in_ptr[i] + lane; n < in_ptr[i + 1]; n += 32) {
             const long long e = in_edge[n];
             fx += nf[3 * e]; fy += nf[3 * e + 1]; fz += nf[3 * e + 2];
         }
-        f[3 * i] = fx; f[3 * i + 1] = fy; f[3 * i + 2] = fz;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            fx += __shfl_down_sync(0xffffffffu, fx, off);
+            fy += __shfl_down_sync(0xffffffffu, fy, off);
+            fz += __shfl_down_sync(0xffffffffu, fz, off);
+        }
+        if (lane == 0) { f[3 * i] = fx; f[3 * i + 1] = fy; f[3 * i + 2] = fz; }
     }
 }
 
@@ -2237,12 +2246,16 @@ static __global__ void energy_virial_partial_kernel(int N, long long E, const do
     }
     if (threadIdx.x < 7) partials[blockIdx.x * 7 + threadIdx.x] = sh[threadIdx.x][0];
 }
+// One warp per component (launch with 7 warps): lane l adds the rows l, l + 32, ... in order, then the lanes are combined
+// by a fixed shuffle tree, so the sum has the same bits on every run.
 static __global__ void energy_virial_final_kernel(int num_blocks, const double* __restrict__ partials, double* __restrict__ out7) {
-    if (threadIdx.x < 7) {
-        double s = 0;
-        for (int b = 0; b < num_blocks; ++b) s += partials[b * 7 + threadIdx.x];
-        out7[threadIdx.x] = s;
-    }
+    const int comp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (comp >= 7) return;
+    double s = 0;
+    for (int b = lane; b < num_blocks; b += 32) s += partials[b * 7 + comp];
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) s += __shfl_down_sync(0xffffffffu, s, off);
+    if (lane == 0) out7[comp] = s;
 }
 
 }  // namespace smx

@@ -67,12 +67,15 @@ __global__ void __launch_bounds__(kThreads) chunk_partials_kernel(int num_nodes,
     if (threadIdx.x < 7) partials[blockIdx.x * 7 + threadIdx.x] = sh[threadIdx.x][0];
 }
 
+// One warp per component (7 warps): lane l adds the rows l, l + 32, ... in order, then a fixed shuffle tree combines the lanes.
 __global__ void sum_rows_kernel(int num_rows, const double* __restrict__ partials, double* __restrict__ out7) {
-    if (threadIdx.x < 7) {
-        double s = 0;
-        for (int b = 0; b < num_rows; ++b) s += partials[b * 7 + threadIdx.x];
-        out7[threadIdx.x] = s;
-    }
+    const int comp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (comp >= 7) return;
+    double s = 0;
+    for (int b = lane; b < num_rows; b += 32) s += partials[b * 7 + comp];
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) s += __shfl_down_sync(0xffffffffu, s, off);
+    if (lane == 0) out7[comp] = s;
 }
 
 std::mutex g_setup_mutex;
@@ -114,7 +117,7 @@ extern "C" int smx_energy_virial_noalloc(const double* node_energies, int num_no
     const int blocks = static_cast<int>((items + kChunk - 1) / kChunk);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (blocks > 0) chunk_partials_kernel<<<blocks, kThreads, 0, s>>>(num_nodes, num_edges, node_energies, xyz, node_forces, scratch);
-    sum_rows_kernel<<<1, 32, 0, s>>>(blocks, scratch, out7);
+    sum_rows_kernel<<<1, 7 * 32, 0, s>>>(blocks, scratch, out7);
     err = cudaGetLastError();
     if (err != cudaSuccess) return fail(SMX_ERR_CUDA, errbuf, errbuf_len, "kernel launch: ", cudaGetErrorString(err));
     return SMX_OK;
