@@ -20,13 +20,18 @@ class Symmetrix:
         self.evaluator = MACE(str(model_file), dtype=dtype, device=device)
         self.cutoff = self.evaluator.r_cut
         self.results: dict = {}
+        # atomic number -> node type of the model (-1: the model has no such element)
+        self._type_of = np.full(128, -1, dtype=np.int32)
+        for t, z in enumerate(self.evaluator.atomic_numbers):
+            self._type_of[int(z)] = t
 
     def calculate(self, positions, cell, numbers, pbc=(True, True, True)) -> dict:
-        mace_numbers = self.evaluator.atomic_numbers
-        try:
-            types = np.array([mace_numbers.index(int(z)) for z in numbers], dtype=np.int32)
-        except ValueError as exc:
-            raise ValueError("structure contains an element the model has no type for") from exc
+        z = np.asarray(numbers, dtype=np.int64)
+        if z.size and (z.min() < 0 or z.max() >= self._type_of.size):
+            raise ValueError("structure contains an element the model has no type for")
+        types = self._type_of[z]
+        if (types < 0).any():
+            raise ValueError("structure contains an element the model has no type for")
         cell = np.asarray(cell, dtype=np.float64).reshape(3, 3)
         self.evaluator.build_neighbors(positions, types, cell, pbc)
         self.evaluator.compute_current()
