@@ -23,7 +23,10 @@
 
 namespace smx {
 
-constexpr int kEdgeBatch = 32;      // edges staged in shared memory per pass (one staging latency and two barriers per batch)
+#ifndef SMX_EDGE_BATCH
+#define SMX_EDGE_BATCH 32
+#endif
+constexpr int kEdgeBatch = SMX_EDGE_BATCH;   // edges staged in shared memory per pass (one staging latency and two barriers per batch)
 constexpr int kChannelBlock = 128;  // threads per CTA of the edge kernels; more channels are done in chunks
 constexpr int kMaxWarps = kChannelBlock / 32;
 
