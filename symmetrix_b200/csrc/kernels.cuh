@@ -27,6 +27,11 @@ namespace smx {
 #define SMX_EDGE_BATCH 32
 #endif
 constexpr int kEdgeBatch = SMX_EDGE_BATCH;   // edges staged in shared memory per pass (one staging latency and two barriers per batch)
+// thread t of a CTA stages edge t of a batch and a CTA may be a single warp, so a batch holds at most 32 edges (the 40-edge
+// measurement was a build for 128-channel models only, with this check lifted)
+#ifndef SMX_EDGE_BATCH_UNCHECKED
+static_assert(kEdgeBatch >= 1 && kEdgeBatch <= 32, "SMX_EDGE_BATCH must be between 1 and 32");
+#endif
 constexpr int kChannelBlock = 128;  // threads per CTA of the edge kernels; more channels are done in chunks
 constexpr int kMaxWarps = kChannelBlock / 32;
 
