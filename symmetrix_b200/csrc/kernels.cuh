@@ -428,9 +428,9 @@ __global__ void __launch_bounds__(kChannelBlock) layer0_reverse_kernel(const Lay
     __shared__ int s_next[2];
     int par = 0;
     const int n_items = *a.n_items;
-    for (int item = work_first(a.sched, s_next); item < n_items; item = work_next(s_next, par)) {
-    work_prefetch(a.sched, s_next, par);
+    for (int item = work_first(a.sched, s_next); item < n_items; item = work_next(s_next, par))
     for (int kc = 0; kc < a.K; kc += CPT * blockDim.x) {
+        if (kc == 0) work_prefetch(a.sched, s_next, par);     // ask for the next item while this one is computed
         const int4 it = a.items[item];                    // one batch of one receiver's edges, receivers in element-type order
         const int i = it.x;
         int kk[CPT];
@@ -489,7 +489,6 @@ __global__ void __launch_bounds__(kChannelBlock) layer0_reverse_kernel(const Lay
                                                  a.node_forces + 3 * (e0 + e));
             }
         }
-    }
     }
     work_leave(a.sched);
 }
@@ -643,9 +642,9 @@ __global__ void __launch_bounds__(kChannelBlock, tp_min_blocks<T>(LF, true)) tp_
     int par = 0;
     const int n_work = STAGED ? a.N : *a.n_items;
     for (int w = STAGED ? static_cast<int>(blockIdx.x) : work_first(a.sched, s_next); w < n_work;
-         w = STAGED ? w + static_cast<int>(gridDim.x) : work_next(s_next, par)) {
-    if constexpr (!STAGED) work_prefetch(a.sched, s_next, par);
+         w = STAGED ? w + static_cast<int>(gridDim.x) : work_next(s_next, par))
     for (int kc = 0; kc < a.K; kc += blockDim.x) {
+        if constexpr (!STAGED) { if (kc == 0) work_prefetch(a.sched, s_next, par); }     // ask for the next item while this one is computed
         int i;
         long long e_begin, e_end;
         if constexpr (STAGED) {
@@ -773,7 +772,6 @@ __global__ void __launch_bounds__(kChannelBlock, tp_min_blocks<T>(LF, true)) tp_
             }
         }
     }
-    }
     if constexpr (!STAGED) work_leave(a.sched);
     if constexpr (STAGED) {
         // after a failed wait: give copies that may still be in flight one more bounded wait before the CTA exits
@@ -873,9 +871,9 @@ __global__ void __launch_bounds__(kChannelBlock, MINB) tp_reverse_tmem_kernel(co
     __shared__ int s_next[2];
     int par = 0;
     const int n_items = *a.n_items;
-    for (int item = work_first(a.sched, s_next); item < n_items; item = work_next(s_next, par)) {
-    work_prefetch(a.sched, s_next, par);
+    for (int item = work_first(a.sched, s_next); item < n_items; item = work_next(s_next, par))
     for (int kc = 0; kc < a.K; kc += blockDim.x) {
+        if (kc == 0) work_prefetch(a.sched, s_next, par);     // ask for the next item while this one is computed
         const int4 it = a.items[item];                    // one batch of one receiver's edges, receivers in element-type order
         const int i = it.x;
         const bool active = kc + static_cast<int>(threadIdx.x) < a.K;
@@ -958,7 +956,6 @@ __global__ void __launch_bounds__(kChannelBlock, MINB) tp_reverse_tmem_kernel(co
             }
         }
         tmem_ld_wait(stage0);     // the fetch started after the last path of the last edge: nothing may be in flight when d is rewritten
-    }
     }
     work_leave(a.sched);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
