@@ -150,6 +150,8 @@ public:
     bool gemm_async = true;       // float64 GEMMs with cp.async tile loads (SMX_GEMM=mma: the register-staged kernel)
     std::map<std::tuple<const void*, int, int, int, int>, std::unique_ptr<DevBuf<float>>> weight_images;
     cudaStream_t own_stream_handle = nullptr;
+    cudaStream_t copy_stream = nullptr;       // host -> device copies of the geometry (see begin)
+    cudaEvent_t copy_ready = nullptr, copy_done = nullptr;
     NeighborBuilder nb;
 
     explicit Evaluator(HostModel&& m, int dev) {
@@ -211,6 +213,7 @@ public:
         if (evt1) cudaEventDestroy(evt1);
         for (auto e : stage_events) cudaEventDestroy(e);
         if (comm) NcclApi::get().CommDestroy(comm);
+        if (copy_stream) { cudaStreamSynchronize(copy_stream); cudaStreamDestroy(copy_stream); cudaEventDestroy(copy_ready); cudaEventDestroy(copy_done); }
         if (host_ring) cudaFreeHost(host_ring);
         if (!own_stream && own_stream_handle) cudaStreamDestroy(own_stream_handle);
         if (stream && own_stream) cudaStreamDestroy(stream);
@@ -332,6 +335,29 @@ public:
         num_neigh = stage_input(nn, n_nodes, in_num_neigh, mem_space);
         neigh_indices = stage_input(ni, n_edges, in_neigh_indices, mem_space);
         neigh_types = stage_input(et, n_edges, in_neigh_types, mem_space);
+        if (mem_space == SMX_HOST && n_edges > 0) {
+            // The geometry (4/5 of the bytes) travels on a second stream while the index arrays of the edge set (CSR offsets,
+            // type order, work items: they need only the integer arrays) are built on the evaluator's stream.
+            if (!copy_stream) {
+                SMX_CUDA(cudaStreamCreateWithFlags(&copy_stream, cudaStreamNonBlocking));
+                SMX_CUDA(cudaEventCreateWithFlags(&copy_ready, cudaEventDisableTiming));
+                SMX_CUDA(cudaEventCreateWithFlags(&copy_done, cudaEventDisableTiming));
+            }
+            in_xyz.resize(3 * static_cast<size_t>(n_edges), stream);
+            in_r.resize(n_edges, stream);
+            SMX_CUDA(cudaEventRecord(copy_ready, stream));              // kernels of the previous evaluation may still read the buffers
+            SMX_CUDA(cudaStreamWaitEvent(copy_stream, copy_ready, 0));
+            SMX_CUDA(cudaMemcpyAsync(in_xyz.p, x, 3 * static_cast<size_t>(n_edges) * sizeof(double), cudaMemcpyHostToDevice, copy_stream));
+            SMX_CUDA(cudaMemcpyAsync(in_r.p, rr, static_cast<size_t>(n_edges) * sizeof(double), cudaMemcpyHostToDevice, copy_stream));
+            SMX_CUDA(cudaEventRecord(copy_done, copy_stream));
+            xyz = in_xyz.p;
+            r = in_r.p;
+            N_built = n_nodes;
+            adopt_edges(n_nodes, n_edges);
+            ensure_sender_lists(N);                                     // the sender-sorted edge list as well (needs neigh_indices only)
+            SMX_CUDA(cudaStreamWaitEvent(stream, copy_done, 0));
+            return;
+        }
         xyz = stage_input(x, 3 * static_cast<size_t>(n_edges), in_xyz, mem_space);
         r = stage_input(rr, n_edges, in_r, mem_space);
         N_built = n_nodes;
