@@ -758,7 +758,7 @@ public:
     template <int LF>
     void launch_tp(bool reverse, int which) {
         const int block = channel_block();
-        if constexpr (sizeof(T) == 8) {
+        if constexpr (sizeof(T) == 8 && LF <= 2) {     // L_max = 3 would need all 512 TMEM columns for one CTA: register kernel
             if (reverse && tmem_reverse && !staged_reverse) {
                 // receiver adjoint in tensor memory: more resident CTAs (see tp_reverse_tmem_kernel). The CTAs of one SM
                 // must fit into its 512 TMEM columns, or the allocation of the last one would wait for another to exit.
@@ -773,9 +773,13 @@ public:
                     kern<<<grid, block, 0, stream>>>(tp_args(which));
                 };
                 // resident CTAs per SM the kernel is compiled for (register budget 255 / 168 / 128)
-                if (LF >= 2 || tmem_min_blocks <= 2) launch(tp_reverse_tmem_kernel<LF, 2>, 2);
-                else if (tmem_min_blocks == 3) launch(tp_reverse_tmem_kernel<LF, 3>, 3);
-                else launch(tp_reverse_tmem_kernel<LF, 4>, 4);
+                if constexpr (LF >= 2) {
+                    launch(tp_reverse_tmem_kernel<LF, 2>, 2);
+                } else {
+                    if (tmem_min_blocks <= 2) launch(tp_reverse_tmem_kernel<LF, 2>, 2);
+                    else if (tmem_min_blocks == 3) launch(tp_reverse_tmem_kernel<LF, 3>, 3);
+                    else launch(tp_reverse_tmem_kernel<LF, 4>, 4);
+                }
                 check_launch("tp_reverse_tmem_kernel");
                 return;
             }
@@ -795,19 +799,23 @@ public:
         if (reverse) {
             // two slots of one spline-row chunk each; staged only if that costs no resident CTA
             const size_t slots = 2 * sizeof(T) * 4 * make_tp_table(LF).P * static_cast<size_t>(std::min(model.K, block));
-            bool staged = staged_reverse && !radial_mlp && slots <= static_cast<size_t>(max_dynamic_smem);
-            int plain_per_sm = 0, staged_per_sm = 0;
-            if (staged) {
-                SMX_CUDA(cudaFuncSetAttribute(tp_reverse_kernel<T, LF, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(slots)));
-                SMX_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&plain_per_sm, tp_reverse_kernel<T, LF, false>, block, 0));
-                SMX_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&staged_per_sm, tp_reverse_kernel<T, LF, true>, block, slots));
-                staged = staged_per_sm >= 1 && staged_per_sm >= plain_per_sm;
+            bool staged = false;
+            if constexpr (LF <= 2) {      // the row-staging variant is not built for L_max = 3
+                staged = staged_reverse && !radial_mlp && slots <= static_cast<size_t>(max_dynamic_smem);
+                int plain_per_sm = 0, staged_per_sm = 0;
+                if (staged) {
+                    SMX_CUDA(cudaFuncSetAttribute(tp_reverse_kernel<T, LF, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(slots)));
+                    SMX_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&plain_per_sm, tp_reverse_kernel<T, LF, false>, block, 0));
+                    SMX_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&staged_per_sm, tp_reverse_kernel<T, LF, true>, block, slots));
+                    staged = staged_per_sm >= 1 && staged_per_sm >= plain_per_sm;
+                }
+                if (staged) {
+                    const int grid = persistent_grid(tp_reverse_kernel<T, LF, true>, block, slots, N);
+                    waits_in_flight = true;
+                    tp_reverse_kernel<T, LF, true><<<grid, block, slots, stream>>>(tp_args(which));
+                }
             }
-            if (staged) {
-                const int grid = persistent_grid(tp_reverse_kernel<T, LF, true>, block, slots, N);
-                waits_in_flight = true;
-                tp_reverse_kernel<T, LF, true><<<grid, block, slots, stream>>>(tp_args(which));
-            } else {
+            if (!staged) {
                 const int grid = persistent_grid(tp_reverse_kernel<T, LF, false>, block, 0, N);
                 tp_reverse_kernel<T, LF, false><<<grid, block, 0, stream>>>(tp_args(which));
             }
@@ -835,7 +843,8 @@ public:
             case 0: launch_tp<0>(reverse, which); break;
             case 1: launch_tp<1>(reverse, which); break;
             case 2: launch_tp<2>(reverse, which); break;
-            default: throw UnsupportedError("L_max > 2");
+            case 3: launch_tp<3>(reverse, which); break;
+            default: throw UnsupportedError("L_max > 3");
         }
     }
 

@@ -587,8 +587,10 @@ __global__ void __launch_bounds__(kChannelBlock, tp_min_blocks<T>(LF, false)) tp
 #include "generated/tp_L0_forward.inc"
                     } else if constexpr (LF == 1) {
 #include "generated/tp_L1_forward.inc"
-                    } else {
+                    } else if constexpr (LF == 2) {
 #include "generated/tp_L2_forward.inc"
+                    } else {
+#include "generated/tp_L3_forward.inc"
                     }
                 }
             }
@@ -734,8 +736,10 @@ __global__ void __launch_bounds__(kChannelBlock, tp_min_blocks<T>(LF, true)) tp_
 #include "generated/tp_L0_reverse.inc"
                     } else if constexpr (LF == 1) {
 #include "generated/tp_L1_reverse.inc"
-                    } else {
+                    } else if constexpr (LF == 2) {
 #include "generated/tp_L2_reverse.inc"
+                    } else {
+#include "generated/tp_L3_reverse.inc"
                     }
                     if constexpr (sizeof(T) == 8) {
                         // float64: deterministic two-step scatter (per-edge message, then a fixed-order sum per sender)
@@ -932,8 +936,10 @@ __global__ void __launch_bounds__(kChannelBlock, MINB) tp_reverse_tmem_kernel(co
 #include "generated/tp_L0_reverse_bypath.inc"
                 } else if constexpr (LF == 1) {
 #include "generated/tp_L1_reverse_bypath.inc"
-                } else {
+                } else if constexpr (LF == 2) {
 #include "generated/tp_L2_reverse_bypath.inc"
+                } else {
+#include "generated/tp_L3_reverse_bypath.inc"
                 }
 #undef TP_PATH_D
                 if (active) {

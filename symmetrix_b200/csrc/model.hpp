@@ -262,7 +262,7 @@ inline HostModel load_model_file(const std::string& filename) {
     if (static_cast<int>(m.atomic_numbers.size()) != E || static_cast<int>(m.atomic_energies.size()) != E)
         throw ModelError("model file: atomic_numbers / atomic_energies do not match num_elements");
     if (m.l_max != kLmaxSH) throw UnsupportedError("only l_max == 3 is supported (as in the reference exporter)");
-    if (m.L_max < 0 || m.L_max > 2) throw UnsupportedError("hidden features up to L_max == 2 are supported");
+    if (m.L_max < 0 || m.L_max > 3) throw UnsupportedError("hidden features up to L_max == 3 are supported");
     if (K < 1 || K > 1024) throw UnsupportedError("num_channels must be in 1..1024");
     if (m.has_zbl) {
         m.zbl_a_exp = file.at("zbl_a_exp").as_double();
@@ -345,7 +345,8 @@ inline HostModel load_model_file(const std::string& filename) {
         switch (m.L_max) {
             case 0: canon = CanonCGTable<0>::e; n_canon = CanonCGTable<0>::n; break;
             case 1: canon = CanonCGTable<1>::e; n_canon = CanonCGTable<1>::n; break;
-            default: canon = CanonCGTable<2>::e; n_canon = CanonCGTable<2>::n; break;
+            case 2: canon = CanonCGTable<2>::e; n_canon = CanonCGTable<2>::n; break;
+            default: canon = CanonCGTable<3>::e; n_canon = CanonCGTable<3>::n; break;
         }
         std::vector<double> file_val(n_canon, 0.0);
         std::vector<int> hits(n_canon, 0);
@@ -536,11 +537,17 @@ inline HostModel load_model_file(const std::string& filename) {
         }
         num_mono = mono_off[m.num_LM];
         coef.assign(size_t(E) * num_mono * K, 0.0);
-        num_canon = kCanonPolyOffset[m.num_LM];
+        // the straight-line contraction kernels exist for outputs up to L = 2 (9 components); beyond that the table-driven
+        // kernels run the file's own monomial lists
+        constexpr int kCanonOutputs = static_cast<int>(sizeof(kCanonPolyCount) / sizeof(kCanonPolyCount[0]));
+        const bool have_canon = m.num_LM <= kCanonOutputs;
+        if (!have_canon) m.poly_canonical = false;
+        num_canon = have_canon ? kCanonPolyOffset[m.num_LM] : 0;
         coef_canon.assign(size_t(E) * num_canon * K, 0.0);
         std::vector<std::vector<int>> slots0;
         for (int lm = 0; lm < m.num_LM; ++lm) {
-            slots0.push_back(detail::canonical_slots(detail::int_lists(monos.at(std::to_string(lm))), lm));
+            auto lists = detail::int_lists(monos.at(std::to_string(lm)));
+            slots0.push_back(have_canon ? detail::canonical_slots(lists, lm) : std::vector<int>(lists.size(), -1));
             for (int sl : slots0.back()) if (sl < 0) m.poly_canonical = false;
         }
         for (int a = 0; a < E; ++a) {

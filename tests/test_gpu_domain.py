@@ -27,8 +27,8 @@ def _single(path, s, dtype="float64"):
 @pytest.mark.parametrize("dtype,world,mode", [("float64", 2, "message_passing"), ("float64", 3, "message_passing"),
                                               ("float32", 2, "message_passing"), ("float64", 2, "recompute"),
                                               ("float64", 3, "recompute"), ("float32", 3, "recompute")])
-def test_emulated_ranks_on_one_gpu_match_single_domain(model_file, dtype, world, mode):
-    path, model, spec = model_file("fcc128", num_channels=32, num_spline_points=32)
+def test_emulated_ranks_on_one_gpu_match_single_domain(model_file, dtype, world, mode, extra=None):
+    path, model, spec = model_file("fcc128", num_channels=32, num_spline_points=32, **(extra or {}))
     s = st.fcc_box((4 * world, 3, 3), 3.6, model["atomic_numbers"], seed=17, jitter=0.12)
     f_ref, v_ref, e_ref = _single(path, s)
     ranks = []
@@ -46,6 +46,12 @@ def test_emulated_ranks_on_one_gpu_match_single_domain(model_file, dtype, world,
         assert abs(energy - e_ref) <= rel * abs(e_ref)
         assert np.abs(forces - f_ref).max() <= fabs
         assert np.abs(virial - v_ref).max() <= 100 * rel * max(1.0, np.abs(v_ref).max())
+
+
+@pytest.mark.parametrize("mode", ["message_passing", "recompute"])
+def test_degree_three_features_decompose_on_gpu(model_file, mode):
+    """Halo rows of 16 feature components (L_max = 3)."""
+    test_emulated_ranks_on_one_gpu_match_single_domain(model_file, "float64", 2, mode, extra={"L_max": 3})
 
 
 @pytest.mark.parametrize("dtype,mode", [("float64", "message_passing"), ("float64", "recompute"), ("float32", "message_passing")])

@@ -109,6 +109,23 @@ def test_downsized_benchmark_models(model_file, dtype, name, channels, builder):
     check_against(dtype, e, f, e_ref, f_ref)
 
 
+@pytest.mark.parametrize("dtype", ["float64", "float32"])
+@pytest.mark.parametrize("channels", [8, 40])
+def test_hidden_features_up_to_degree_three(model_file, dtype, channels):
+    """L_max = 3 (hidden 0e + 1o + 2e + 3o: 23 tensor-product paths, 16 feature components), which the reference's MACE class
+    handles like any other L_max (mace.cpp:397-423, 607-642): generated coupling code for the tensor product, the file's own
+    monomial lists for the contraction (the straight-line contraction kernels stop at nine outputs)."""
+    path, model, spec = model_file("fcc128", num_channels=channels, num_spline_points=32, L_max=3)
+    assert model["L_max"] == 3 and len(model["Phi1_l"]) == 23
+    s = st.fcc_box(3, 3.6, model["atomic_numbers"], seed=8)
+    nl = st.neighbor_list(s, spec.r_cut)
+    inputs = st.evaluator_inputs(s, nl, model["atomic_numbers"])
+    e_ref, f_ref = _oracle_for(path, model)(inputs)
+    ev = MACE(path, dtype=dtype)
+    e, f = run(ev, inputs)
+    check_against(dtype, e, f, e_ref, f_ref)
+
+
 @pytest.mark.parametrize("dtype,env", [
     ("float32", {"SMX_GEMM": "mma"}),           # mma.sync 3xTF32 GEMM instead of the tcgen05 kernel
     ("float64", {"SMX_GEMM": "mma"}),           # register-staged DMMA GEMM instead of the cp.async one
