@@ -63,7 +63,7 @@ def test_create_reports_missing_and_malformed_files(tmp_path):
 
 def test_create_rejects_models_outside_the_supported_set(tmp_path):
     model = json.loads((GOLDEN / "tiny_model.json").read_text())
-    for key, val, expect in [("l_max", 2, "l_max"), ("L_max", 3, "L_max")]:
+    for key, val, expect in [("l_max", 2, "l_max"), ("L_max", 4, "L_max")]:
         m = dict(model); m[key] = val
         p = tmp_path / f"{key}.json"
         p.write_text(json.dumps(m))
