@@ -35,6 +35,9 @@ WORKLOADS = {
                 "l_max 3, correlation 3, r_cut 6 A, 10 radial functions, 89-element model exported for the 5 species present"),
     "fcc1372": ("fcc128", lambda st, z, seed: st.fcc_box(7, 3.6, z, seed=seed),
                 "profiling case: 1372-atom FCC box (7x7x7 cells) of the configs[1] construction and model"),
+    "fcc6912": ("fcc128", lambda st, z, seed: st.fcc_box(12, 3.6, z, seed=seed),
+                "profiling case for the float64 GEMMs: 6,912-atom FCC box (12x12x12 cells) of the configs[1] construction and model, "
+                "110,592 rows per operand of the tensor-product output GEMM, about 3 GB on the device"),
     "fcc32k": ("fcc128", lambda st, z, seed: st.fcc_box(20, 3.6, z, seed=seed),
                "profiling case for the channel-mixing GEMMs: 32,000-atom FCC box (20x20x20 cells) of the configs[1] construction and "
                "model, 1.28 M rows of 128 channels per GEMM operand"),
@@ -468,7 +471,7 @@ def run_decomposed(args, rank, world, local_rank, dist):
     path, numbers, spec = model_path(spec_name) if rank == 0 else (None, None, None)
     dist.barrier()
     path, numbers, spec = model_path(spec_name)
-    cells = {"fcc4000": (10, 10, 10), "fcc1372": (7, 7, 7), "fcc32k": (20, 20, 20), "fcc256k": (10, 80, 80)}.get(args.workload)
+    cells = {"fcc4000": (10, 10, 10), "fcc1372": (7, 7, 7), "fcc6912": (12, 12, 12), "fcc32k": (20, 20, 20), "fcc256k": (10, 80, 80)}.get(args.workload)
     if cells is not None:
         # weak scaling: the box grows along x with the number of GPUs
         s = st.fcc_box((cells[0] * world, cells[1], cells[2]), 3.6, numbers, seed=1)
@@ -627,7 +630,7 @@ def _cpu_sample_inputs(workload: str, seed: int):
     from symmetrix_b200 import structures as st
     spec_name, _, _ = WORKLOADS[workload]
     path, numbers, spec = model_path(spec_name)
-    if workload in ("fcc4000", "fcc1372", "fcc32k", "fcc256k"):
+    if workload in ("fcc4000", "fcc1372", "fcc6912", "fcc32k", "fcc256k"):
         s = st.fcc_box(CPU_SAMPLE_CELLS, 3.6, numbers, seed=seed)
         sample = f"{CPU_SAMPLE_CELLS}x{CPU_SAMPLE_CELLS}x{CPU_SAMPLE_CELLS}-cell FCC box ({s.num_atoms} atoms) of the same construction and model"
     else:
