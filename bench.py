@@ -315,6 +315,19 @@ def run_ours(args):
             "clocks": clocks, "roofline": roof, "stage_ms": stage_ms,
             "wall_ms_per_step": wall_s * 1e3 / args.steps,
         }
+        if "compute_A1" in stage_ms and fma:
+            # the channel-mixing GEMM of the tensor-product output (tensor cores: DMMA in float64, tcgen05 3xTF32 in float32):
+            # Phi1 [N, Q, K] in, A1 [N, 16, K] out; its flop rate beside the measured FMA peak of the same precision
+            K, Q = ev.num_channels, ev.num_lme
+            a1_ms = stage_ms["compute_A1"]
+            a1_bytes = n_atoms * (Q + 16) * K * dtype_bytes
+            a1_flops = 2.0 * n_atoms * Q * K * K
+            peak_gbs, how = measured_peaks()
+            out["gemm_A1"] = {"kernel": "gemm_rows_f64_async_kernel" if dtype_bytes == 8 else "gemm_rows_tcgen05_kernel",
+                              "launch_ms": a1_ms, "algorithmic_bytes": a1_bytes, "achieved_gbs": a1_bytes / (a1_ms * 1e-3) / 1e9,
+                              "hbm_frac": a1_bytes / (a1_ms * 1e-3) / 1e9 / peak_gbs, "peak_source": f"of {how}",
+                              "achieved_tflops": a1_flops / (a1_ms * 1e-3) / 1e12,
+                              "tflops_over_fma_peak": a1_flops / (a1_ms * 1e-3) / 1e12 / fma}
         sample = None
         if world == 1 and not args.no_cpu_baseline:
             out["cpu_baseline"], sample = cpu_baseline(args.workload)
