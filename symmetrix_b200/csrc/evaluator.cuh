@@ -942,9 +942,16 @@ public:
         ensure_sender_lists(std::max(rows, N));
         if (E > 0) {
             const int width = nLM * K;
-            const int block = std::min(256, ((width + 31) / 32) * 32);
             const int grid = std::min(rows, num_sms * 16);
-            sender_gather_kernel<T><<<grid, block, 0, stream>>>(rows, width, in_ptr.p, in_edge.p, Hmsg.p, adj.p);
+            const bool vec = sizeof(T) == 8 && width % 2 == 0 && (reinterpret_cast<uintptr_t>(Hmsg.p) & 15) == 0 &&
+                             (reinterpret_cast<uintptr_t>(adj.p) & 15) == 0;
+            if (vec) {
+                const int block = std::min(256, ((width / 2 + 31) / 32) * 32);
+                sender_gather_kernel<T, true><<<grid, block, 0, stream>>>(rows, width, in_ptr.p, in_edge.p, Hmsg.p, adj.p);
+            } else {
+                const int block = std::min(256, ((width + 31) / 32) * 32);
+                sender_gather_kernel<T, false><<<grid, block, 0, stream>>>(rows, width, in_ptr.p, in_edge.p, Hmsg.p, adj.p);
+            }
             check_launch("sender_gather_kernel");
         }
     }

@@ -1128,11 +1128,36 @@ __global__ void row_stream_probe_kernel(int N, int K, int P, const int* __restri
 // of the sender-sorted edge list (deterministic; takes the place of the atomic scatter the
 // reference's device code uses, mace_kokkos.cpp:1008-1010):
 //   H_adj[j, :, :] += sum_{e in in_edges(j)} Hmsg[e, :, :]
-template <typename T>
+// VEC: a thread sums two neighbouring values with 16-byte loads (float64 rows of even width; the rows start 16-byte aligned).
+template <typename T, bool VEC>
 __global__ void sender_gather_kernel(int rows, int width, const long long* __restrict__ in_ptr,
                                      const int* __restrict__ in_edge, const T* __restrict__ Hmsg, T* __restrict__ H_adj) {
     for (int j = blockIdx.x; j < rows; j += gridDim.x) {
         const long long b = in_ptr[j], e = in_ptr[j + 1];
+        if constexpr (VEC && sizeof(T) == 8) {
+            for (int c = 2 * threadIdx.x; c < width; c += 2 * blockDim.x) {
+                // eight rows in flight per thread; the additions stay in list order
+                double a0 = 0, a1 = 0;
+                long long n = b;
+                for (; n + 8 <= e; n += 8) {
+                    double2 v[8];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u)
+                        v[u] = __ldcs(reinterpret_cast<const double2*>(Hmsg + static_cast<size_t>(in_edge[n + u]) * width + c));
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) { a0 += v[u].x; a1 += v[u].y; }
+                }
+                for (; n < e; ++n) {
+                    const double2 v = __ldcs(reinterpret_cast<const double2*>(Hmsg + static_cast<size_t>(in_edge[n]) * width + c));
+                    a0 += v.x; a1 += v.y;
+                }
+                double2* out = reinterpret_cast<double2*>(H_adj + static_cast<size_t>(j) * width + c);
+                double2 o = *out;
+                o.x += a0; o.y += a1;
+                *out = o;
+            }
+            continue;
+        }
         for (int c = threadIdx.x; c < width; c += blockDim.x) {
             // eight rows in flight per thread; the additions stay in list order
             T acc = 0;
