@@ -82,6 +82,8 @@ public:
 
     // model tables on the device
     DevBuf<T> coef0, coef1, H0_w, A0_w, H1_w, A1_w, H2_w_H1, H2_w_M1, ro1, ro2_w1, ro2_w2, coefM0, coefM1;
+    DevBuf<T> coef0_folded;       // layer-0 table with H0 and the per-type channel mix folded in (see fold_layer0_kernel)
+    bool fold_a0 = false;
     DevBuf<T> coefm, Am_w, Hm_w, Hm_res, ro_m, coefMm;    // middle interaction block (models with three blocks)
     DevBuf<int> progm, progm_off, progm_cnt, monom_off;
     bool poly_fixed = false;      // coefM0 / coefM1 hold the canonical order and the straight-line kernels are used
@@ -226,6 +228,26 @@ public:
 
         H0_w.upload(cast_vec<T>(m.H0_w), stream);
         A0_w.upload(cast_vec<T>(m.A0_w), stream);
+        {
+            // Folded layer-0 table (SMX_A0_FOLD=0 keeps the two-step form): E^2 instead of E (E + 1) / 2 pair tables, so only
+            // for models with few element types
+            const char* f = std::getenv("SMX_A0_FOLD");
+            fold_a0 = !(f && std::string(f) == "0") && m.num_elements <= 16 && m.K <= 1024;
+            const size_t bins = static_cast<size_t>(m.num_bins);
+            const size_t pairs = static_cast<size_t>(m.num_elements) * (m.num_elements + 1) / 2;
+            if (fold_a0 && m.coef0.size() == pairs * bins * 16 * m.K && m.A0_w.size() == static_cast<size_t>(m.num_elements) * 4 * m.K * m.K) {
+                DevBuf<double> d_coef, d_h0, d_w;
+                d_coef.upload(m.coef0, stream); d_h0.upload(m.H0_w, stream); d_w.upload(m.A0_w, stream);
+                const size_t rows = static_cast<size_t>(m.num_elements) * m.num_elements * bins * 4;
+                coef0_folded.resize(rows * 4 * m.K, stream);
+                fold_layer0_kernel<T><<<static_cast<unsigned>(rows), std::min(256, ((m.K + 31) / 32) * 32), static_cast<size_t>(4) * m.K * sizeof(double), stream>>>(
+                    m.num_elements, static_cast<int>(bins), m.K, d_coef.p, d_h0.p, d_w.p, coef0_folded.p);
+                check_launch("fold_layer0_kernel");
+                SMX_CUDA(cudaStreamSynchronize(stream));      // the temporaries are freed on leaving this scope
+            } else {
+                fold_a0 = false;
+            }
+        }
         H1_w.upload(cast_vec<T>(m.H1_w), stream);
         A1_w.upload(cast_vec<T>(m.A1_w), stream);
         H2_w_H1.upload(cast_vec<T>(m.H2_w_H1), stream);
@@ -546,7 +568,9 @@ public:
         a.N = N; a.K = model.K;
         a.node_types = node_types; a.first_neigh = first_neigh.p; a.neigh_indices = neigh_indices; a.neigh_types = neigh_types;
         a.xyz = xyz; a.r = r; a.coef0 = coef0.p; a.sm = sm; a.H0_w = H0_w.p; a.order = type_order ? perm.p : nullptr;
-        a.Phi0 = Phi0.p; a.Phi0_adj = Phi0_adj.p; a.node_forces = node_forces.p;
+        a.coef0_folded = fold_a0 ? coef0_folded.p : nullptr;
+        // folded table: the edge sums are A0 / act on A0_adj themselves
+        a.Phi0 = fold_a0 ? A0.p : Phi0.p; a.Phi0_adj = fold_a0 ? A0_adj.p : Phi0_adj.p; a.node_forces = node_forces.p;
         a.sched = work_sched.p; a.items = work_items.p; a.n_items = work_n_items.p;
         return a;
     }
@@ -590,13 +614,14 @@ public:
 
     void compute_A0() {   // MACE::compute_A0, mace.cpp:150-201
         const int K = model.K;
-        Phi0.resize(static_cast<size_t>(N) * kNumLm * K, stream);
+        if (!fold_a0) Phi0.resize(static_cast<size_t>(N) * kNumLm * K, stream);
         A0.resize(static_cast<size_t>(N) * kNumLm * K, stream);
         if (N == 0) return;
         const int block = channel_block();
         const int grid = persistent_grid(layer0_forward_kernel<T>, block, 0, N);
         layer0_forward_kernel<T><<<grid, block, 0, stream>>>(layer0_args());
         check_launch("layer0_forward_kernel");
+        if (fold_a0) return;       // the table already holds H0 and the channel mix
         std::vector<GemmProblem<T>> list;
         for (int a = 0; a < model.num_elements; ++a)
             for (int l = 0; l <= kLmaxSH; ++l)
@@ -608,14 +633,16 @@ public:
     void reverse_A0() {   // MACE::reverse_A0, mace.cpp:203-271
         const int K = model.K;
         if (A0_adj.n != static_cast<size_t>(N) * kNumLm * K) throw ArgError("reverse_A0: A0_adj has not been computed");
-        Phi0_adj.resize(static_cast<size_t>(N) * kNumLm * K, stream);
         if (N == 0) return;
-        std::vector<GemmProblem<T>> list;
-        for (int a = 0; a < model.num_elements; ++a)
-            for (int l = 0; l <= kLmaxSH; ++l)
-                list.push_back(problem(A0_adj.p, Phi0_adj.p, A0_w.p + (static_cast<size_t>(a) * (kLmaxSH + 1) + l) * K * K, true, a,
-                                       2 * l + 1, 16LL * K, 1LL * l * l * K, K, 16LL * K, 1LL * l * l * K, K, K, K, K, true, false));
-        run_gemms(list, 7LL * N, K);
+        if (!fold_a0) {
+            Phi0_adj.resize(static_cast<size_t>(N) * kNumLm * K, stream);
+            std::vector<GemmProblem<T>> list;
+            for (int a = 0; a < model.num_elements; ++a)
+                for (int l = 0; l <= kLmaxSH; ++l)
+                    list.push_back(problem(A0_adj.p, Phi0_adj.p, A0_w.p + (static_cast<size_t>(a) * (kLmaxSH + 1) + l) * K * K, true, a,
+                                           2 * l + 1, 16LL * K, 1LL * l * l * K, K, 16LL * K, 1LL * l * l * K, K, K, K, K, true, false));
+            run_gemms(list, 7LL * N, K);
+        }
 #ifndef SMX_L0R_CPT
 #define SMX_L0R_CPT 2
 #endif

@@ -257,6 +257,7 @@ struct EdgeStage {
     T x;                      // r - h * bin
     T ux, uy, uz;             // unit vector
     long long coef_base;      // (pair * num_bins + bin) * F * 4
+    long long coef_base_dir;  // the same with the ordered pair (type_i * num_elements + type_j): folded layer-0 table
     int j;                    // sender row
     int tj;                   // sender type
 };
@@ -342,6 +343,46 @@ __device__ __forceinline__ void stage_edge(EdgeStage<T>& s, long long edge, int 
     const int lo = type_i <= tj ? type_i : tj, hi = type_i <= tj ? tj : type_i;
     const int pair = lo * (2 * sm.num_elements - lo - 1) / 2 + hi;   // mace.cpp:81-83
     s.coef_base = (static_cast<long long>(pair) * sm.num_bins + bin) * F * 4;
+    s.coef_base_dir = (static_cast<long long>(type_i * sm.num_elements + tj) * sm.num_bins + bin) * F * 4;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Folded layer-0 table. A0[i, lm, k'] = sum_k Phi0[i, lm, k] W[a][l][k, k'] with Phi0 a sum over edges of
+// R0_ab(r)[l, k] Y[lm] H0[b, k] (a, b = receiver, sender type). The spline is linear in its coefficients, so
+//   c'[(a, b), bin, l, k', q] = sum_k c[pair(a, b), bin, l, k, q] H0[b, k] W[a][l][k, k']        (q = 0..3)
+// is again a table of cubics, per ordered pair, whose edge sum is A0 itself (the reference's device code folds the same
+// two factors into its table, mace_kokkos.cpp). Built once per model in float64 from the file's numbers and stored in the
+// evaluator's precision and row layout. One CTA per (a, b, bin, l), thread = output channel k'.
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void fold_layer0_kernel(int E, int bins, int K, const double* __restrict__ coef /* [pairs][bins][4][K][4] */,
+                                   const double* __restrict__ H0 /* [E][K] */, const double* __restrict__ W /* [E][4][K][K] */,
+                                   T* __restrict__ out) {
+    extern __shared__ double fold_v[];     // [K][4]: coefficients of input channel k times H0[b, k]
+    const int l = blockIdx.x & 3;
+    const long long rest = blockIdx.x >> 2;
+    const int bin = static_cast<int>(rest % bins);
+    const int ab = static_cast<int>(rest / bins);
+    const int a = ab / E, b = ab % E;
+    const int lo = a <= b ? a : b, hi = a <= b ? b : a;
+    const int pair = lo * (2 * E - lo - 1) / 2 + hi;
+    const double* in = coef + ((static_cast<size_t>(pair) * bins + bin) * 4 + l) * 4 * K;
+    for (int t = threadIdx.x; t < 4 * K; t += blockDim.x) fold_v[t] = in[t] * H0[static_cast<size_t>(b) * K + (t >> 2)];
+    __syncthreads();
+    const double* w = W + (static_cast<size_t>(a) * 4 + l) * K * K;
+    T* row = out + ((static_cast<size_t>(ab) * bins + bin) * 4 + l) * 4 * K;
+    for (int kp = threadIdx.x; kp < K; kp += blockDim.x) {
+        double s0 = 0, s1 = 0, s2 = 0, s3 = 0;
+        for (int k = 0; k < K; ++k) {
+            const double wk = w[static_cast<size_t>(k) * K + kp];
+            s0 += fold_v[4 * k] * wk; s1 += fold_v[4 * k + 1] * wk; s2 += fold_v[4 * k + 2] * wk; s3 += fold_v[4 * k + 3] * wk;
+        }
+        if constexpr (sizeof(T) == 4) {        // rows [K][4]
+            row[4 * kp] = T(s0); row[4 * kp + 1] = T(s1); row[4 * kp + 2] = T(s2); row[4 * kp + 3] = T(s3);
+        } else {                               // rows [2][K][2]
+            row[2 * kp] = T(s0); row[2 * kp + 1] = T(s1); row[2 * K + 2 * kp] = T(s2); row[2 * K + 2 * kp + 1] = T(s3);
+        }
+    }
 }
 
 // =============================================================================================
@@ -355,6 +396,10 @@ struct Layer0Args {
     const double* xyz; const double* r;
     const T* coef0; SplineMeta sm;
     const T* H0_w;          // [E][K]
+    // Folded table (optional): per ORDERED element pair (receiver type a, sender type b) the radial coefficients already
+    // multiplied by H0[b] and by the per-type channel mix W[a][l] (fold_layer0_kernel), so that the edge sum gives A0
+    // directly: Phi0 / Phi0_adj then point at A0 / A0_adj and the two channel-mixing GEMMs of layer 0 are not run.
+    const T* coef0_folded;
     // Optional processing order of the receivers (node ids sorted by element type). All CTAs then work on receivers of
     // one type at a time, whose edges touch only the pair tables of that type: for configs[1] 5 of 15 tables (73 MB of
     // 220 MB), which stay resident in the 126 MB L2 instead of being re-fetched from HBM.
@@ -390,9 +435,9 @@ __global__ void __launch_bounds__(kChannelBlock) layer0_forward_kernel(const Lay
             if (active) {
                 for (int e = 0; e < nb; ++e) {
                     const EdgeStage<T>& s = st[e];
-                    const T h0 = a.H0_w[s.tj * a.K + k];
+                    const T h0 = a.coef0_folded ? T(1) : a.H0_w[s.tj * a.K + k];
                     const T x = s.x;
-                    const T* cb = a.coef0 + s.coef_base;
+                    const T* cb = a.coef0_folded ? a.coef0_folded + s.coef_base_dir : a.coef0 + s.coef_base;
 #pragma unroll
                     for (int l = 0; l <= kLmaxSH; ++l) {
                         const Vec4<T> c = load_coef<T>(cb + 4 * l * a.K, k, a.K);
@@ -457,11 +502,11 @@ __global__ void __launch_bounds__(kChannelBlock) layer0_reverse_kernel(const Lay
 #pragma unroll
                 for (int lm = 0; lm < kNumLm; ++lm) W[lm] = T(0);
                 const T x = s.x;
-                const T* cb = a.coef0 + s.coef_base;
+                const T* cb = a.coef0_folded ? a.coef0_folded + s.coef_base_dir : a.coef0 + s.coef_base;
 #pragma unroll
                 for (int c = 0; c < CPT; ++c) {
                     if (!active[c]) continue;
-                    const T h0 = a.H0_w[s.tj * a.K + kk[c]];
+                    const T h0 = a.coef0_folded ? T(1) : a.H0_w[s.tj * a.K + kk[c]];
 #pragma unroll
                     for (int l = 0; l <= kLmaxSH; ++l) {
                         const Vec4<T> cf = load_coef<T>(cb + 4 * l * a.K, kk[c], a.K);

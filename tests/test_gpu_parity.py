@@ -132,6 +132,8 @@ def test_hidden_features_up_to_degree_three(model_file, dtype, channels):
     ("float64", {"SMX_TP_TMEM": "0"}),          # receiver adjoint of the tensor-product reverse in registers instead of tensor memory
     ("float64", {"SMX_TP_STAGED": "1"}),        # spline rows of the tensor-product reverse through TMA bulk copies
     ("float32", {"SMX_TP_STAGED": "1"}),
+    ("float64", {"SMX_A0_FOLD": "0"}),          # layer 0 as edge sum + channel-mixing GEMMs instead of the folded table
+    ("float32", {"SMX_A0_FOLD": "0"}),
 ])
 @pytest.mark.parametrize("name,channels,builder", [
     ("fcc128", 128, lambda z: st.fcc_box(3, 3.6, z, seed=5)),
